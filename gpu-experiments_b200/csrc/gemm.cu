@@ -1,0 +1,438 @@
+// Block-scaled MXFP8 GEMM for sm_100a:  C[M][N] = dequant(A[M][K]) . dequant(B[N][K])^T.
+//
+// Persistent kernel, one CTA per SM, six warps:
+//   warp 0  producer   one thread streams A/B tiles (SWIZZLE_128B) and scale tiles with TMA into a
+//                      ring of shared-memory stages; each CTA fetches only its own tiles
+//   warp 1  MMA        one thread (of the leader CTA when CG == 2) copies the stage's scale tiles
+//                      into TMEM with tcgen05.cp and issues four K=32
+//                      tcgen05.mma.kind::mxf8f6f4.block_scale per 128-wide K step; tcgen05.commit
+//                      releases the stage and, after the last K step, publishes the accumulator
+//   warps 2-5 epilogue tcgen05.ld the fp32 accumulator (warp q owns TMEM lanes 32q..32q+31),
+//                      round to bf16 (or keep fp32), stage through swizzled shared memory and
+//                      write C with TMA stores
+// CG == 2: a cluster of two CTAs computes one 256x256 tile with cta_group::2 instructions; each
+// CTA holds 128 rows of A, 128 rows of B, its own A scales and both B scale tiles.
+// CG == 1: one CTA computes a 128x256 tile.
+//
+// TMEM budget (512 columns): two accumulators of 256 columns cannot sit beside the scale
+// columns, so they overlap: accumulator 0 = columns [0,256), accumulator 1 = [224,480), scales
+// in [480,512).  The epilogue drains the shared 32 columns first and signals the MMA warp, which
+// may then start the next tile while the remaining 224 columns are still being drained.
+//
+// M/N tails need no special case: out-of-range TMA loads are zero-filled, out-of-range TMA stores
+// are clipped.  Replaces blackwell/047-mxfp8-mma-2cta-MNK128-polished.cu:12-541 of the reference.
+#include "mx8_host.cuh"
+#include "mx8_ptx.cuh"
+
+namespace mx8 {
+namespace gemm {
+
+constexpr int BK = 128;                 // K elements (bytes) per stage
+constexpr int BN = 256;                 // tile columns
+constexpr int ACC1_COL = 224;           // first column of accumulator 1
+constexpr int SF_COL = 480;             // first scale column; slot s at SF_COL + 16 s: A +0, B +4 and +8
+constexpr int EPI_WARPS = 4;
+constexpr int THREADS = 32 * (2 + EPI_WARPS);
+
+template <int CG>
+struct Cfg {
+    static constexpr int STAGES = CG == 2 ? 6 : 4;
+    static constexpr int A_BYTES = 128 * BK;                 // this CTA's 128 rows of A
+    static constexpr int B_ROWS = BN / CG;                   // this CTA's rows of B
+    static constexpr int B_BYTES = B_ROWS * BK;
+    static constexpr int SFA_BYTES = 512;
+    static constexpr int SFB_BYTES = 1024;                   // both 128-column scale tiles
+    static constexpr int STAGE_TX = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;   // bytes one CTA loads per stage
+    static constexpr int EPI_BYTES = 32 * 128;               // per warp: 32 rows x 128 bytes (64 bf16 or 32 f32 columns)
+    // offsets from the 1024-aligned base
+    static constexpr int a_off = 0;
+    static constexpr int b_off = a_off + STAGES * A_BYTES;
+    static constexpr int sfa_off = b_off + STAGES * B_BYTES;
+    static constexpr int sfb_off = sfa_off + STAGES * SFA_BYTES;
+    static constexpr int epi_off = (sfb_off + STAGES * SFB_BYTES + 1023) & ~1023;
+    static constexpr int bar_off = epi_off + EPI_WARPS * EPI_BYTES;
+    // barriers: full[STAGES], empty[STAGES], acc_full[2], drained
+    static constexpr int n_bars = 2 * STAGES + 3;
+    static constexpr int tmem_ptr_off = bar_off + n_bars * 8;
+    static constexpr int flag_off = tmem_ptr_off + 8;
+    static constexpr int total = flag_off + 8;
+    static constexpr int dynamic = total + 1024;
+    static_assert(dynamic <= 232448, "shared memory budget exceeded");
+};
+
+struct Params {
+    int tiles_m, tiles_n, k_steps;      // tile grid (tile = 128*CG x 256) and K / 128
+    int group_m;                        // rasterisation: tiles_m rows per supergroup
+    int c_is_f32;
+    int* status;
+};
+
+// persistent tile order: supergroups of `group_m` tile rows, column-major inside a supergroup so
+// that CTAs running at the same time share A row panels and B column panels in L2
+__device__ __forceinline__ void tile_coords(int t, const Params& p, int& tm, int& tn) {
+    const int per_group = p.group_m * p.tiles_n;
+    const int grp = t / per_group;
+    const int in_grp = t - grp * per_group;
+    const int rows = min(p.group_m, p.tiles_m - grp * p.group_m);
+    tm = grp * p.group_m + in_grp % rows;
+    tn = in_grp / rows;
+}
+
+template <int CG>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+            const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb,
+            const __grid_constant__ CUtensorMap tm_c, const Params p) {
+    using C = Cfg<CG>;
+    constexpr int S = C::STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t full0 = base + C::bar_off;
+    const uint32_t empty0 = full0 + S * 8;
+    const uint32_t accfull0 = empty0 + S * 8;
+    const uint32_t drained = accfull0 + 2 * 8;
+    volatile uint32_t* tmem_ptr = reinterpret_cast<volatile uint32_t*>(base_ptr + C::tmem_ptr_off);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + C::flag_off);
+    const AbortCtl ab{abort_flag, p.status};
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = CG == 2 ? cluster_ctarank() : 0;
+    const int cluster = CG == 2 ? static_cast<int>(cluster_id_x()) : static_cast<int>(blockIdx.x);
+    const int num_clusters = CG == 2 ? static_cast<int>(num_clusters_x()) : static_cast<int>(gridDim.x);
+    const int num_tiles = p.tiles_m * p.tiles_n;
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        for (int s = 0; s < S; ++s) {
+            mbar_init(full0 + s * 8, 1);       // the leader producer's arrive.expect_tx
+            mbar_init(empty0 + s * 8, 1);      // one tcgen05.commit
+        }
+        mbar_init(accfull0, 1);
+        mbar_init(accfull0 + 8, 1);
+        mbar_init(drained, EPI_WARPS * CG);
+        fence_mbar_init();
+        prefetch_tmap(&tm_a);
+        prefetch_tmap(&tm_b);
+        prefetch_tmap(&tm_sfa);
+        prefetch_tmap(&tm_sfb);
+        prefetch_tmap(&tm_c);
+    }
+    if (warp == 1) {
+        tmem_alloc<CG>(smem_u32(const_cast<uint32_t*>(tmem_ptr)), 512);
+        tmem_relinquish<CG>();
+    }
+    __syncwarp();
+    tc_fence_before();
+    if constexpr (CG == 2) cluster_sync_all(); else __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_ptr;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ producer
+        if (lane == 0) {
+            uint32_t stage = 0, ph = 0;
+            const uint32_t full_leader0 = CG == 2 ? map_to_cta(full0, 0) : full0;
+            bool ok = true;
+            for (int t = cluster; t < num_tiles && ok; t += num_clusters) {
+                int tm, tn;
+                tile_coords(t, p, tm, tn);
+                const int a_row = (tm * CG + static_cast<int>(rank)) * 128;
+                const int b_row = tn * BN + static_cast<int>(rank) * C::B_ROWS;
+                for (int ks = 0; ks < p.k_steps; ++ks) {
+                    if (!mbar_wait(empty0 + stage * 8, ph ^ 1, ab, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
+                    const uint32_t a_dst = base + C::a_off + stage * C::A_BYTES;
+                    const uint32_t b_dst = base + C::b_off + stage * C::B_BYTES;
+                    const uint32_t sfa_dst = base + C::sfa_off + stage * C::SFA_BYTES;
+                    const uint32_t sfb_dst = base + C::sfb_off + stage * C::SFB_BYTES;
+                    if constexpr (CG == 2) {
+                        const uint32_t bar = full_leader0 + stage * 8;
+                        if (rank == 0) mbar_arrive_expect_tx(full0 + stage * 8, 2 * C::STAGE_TX);
+                        tma_load_2d_pair(a_dst, &tm_a, ks * BK, a_row, bar);
+                        tma_load_2d_pair(b_dst, &tm_b, ks * BK, b_row, bar);
+                        tma_load_3d_pair(sfa_dst, &tm_sfa, 0, ks, a_row / 128, bar);
+                        tma_load_3d_pair(sfb_dst, &tm_sfb, 0, ks, tn * 2, bar);
+                    } else {
+                        const uint32_t bar = full0 + stage * 8;
+                        mbar_arrive_expect_tx(bar, C::STAGE_TX);
+                        tma_load_2d(a_dst, &tm_a, ks * BK, a_row, bar);
+                        tma_load_2d(b_dst, &tm_b, ks * BK, b_row, bar);
+                        tma_load_3d(sfa_dst, &tm_sfa, 0, ks, a_row / 128, bar);
+                        tma_load_3d(sfb_dst, &tm_sfb, 0, ks, tn * 2, bar);
+                    }
+                    if (++stage == S) { stage = 0; ph ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+        if (lane == 0 && rank == 0) {
+            uint32_t stage = 0, ph = 0, sf_slot = 0;
+            int it = 0;
+            bool ok = true;
+            for (int t = cluster; t < num_tiles && ok; t += num_clusters, ++it) {
+                const uint32_t d_tmem = tmem_base + ((it & 1) ? ACC1_COL : 0);
+                if (it > 0) {
+                    // the epilogue has emptied the previous-but-one accumulator and the 32 columns
+                    // the previous accumulator shares with this one
+                    if (!mbar_wait(drained, (it - 1) & 1, ab, DEV_TIMEOUT_TMEM_FREE)) { ok = false; break; }
+                    tc_fence_after();
+                }
+                for (int ks = 0; ks < p.k_steps; ++ks) {
+                    if (!mbar_wait(full0 + stage * 8, ph, ab, DEV_TIMEOUT_FULL)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sf_t = tmem_base + SF_COL + sf_slot * 16;
+                    const uint32_t sfa_s = base + C::sfa_off + stage * C::SFA_BYTES;
+                    const uint32_t sfb_s = base + C::sfb_off + stage * C::SFB_BYTES;
+                    tc_cp_scales<CG>(sf_t, smem_desc_scales(sfa_s));
+                    tc_cp_scales<CG>(sf_t + 4, smem_desc_scales(sfb_s));
+                    tc_cp_scales<CG>(sf_t + 8, smem_desc_scales(sfb_s + 512));
+                    const uint64_t adesc = smem_desc_sw128(base + C::a_off + stage * C::A_BYTES);
+                    const uint64_t bdesc = smem_desc_sw128(base + C::b_off + stage * C::B_BYTES);
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) {
+                        // 32 bytes further along K inside the swizzle atom: +2 in the address field
+                        tc_mma_mxf8<CG>(d_tmem, adesc + 2 * kk, bdesc + 2 * kk, idesc_mxf8(128 * CG, BN, kk),
+                                        sf_t, sf_t + 4, (ks | kk) != 0);
+                    }
+                    tc_commit<CG>(empty0 + stage * 8);          // stage reusable once these MMAs retire
+                    sf_slot ^= 1;
+                    if (++stage == S) { stage = 0; ph ^= 1; }
+                }
+                if (ok) tc_commit<CG>(accfull0 + (it & 1) * 8);  // accumulator complete
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue
+        const int q = warp & 3;                                  // TMEM lane quadrant this warp may read
+        const uint32_t stg = base + C::epi_off + (warp - 2) * C::EPI_BYTES;
+        const uint32_t drained_leader = CG == 2 ? map_to_cta(drained, 0) : drained;
+        int it = 0;
+        bool ok = true;
+        for (int t = cluster; t < num_tiles && ok; t += num_clusters, ++it) {
+            int tm, tn;
+            tile_coords(t, p, tm, tn);
+            const int acc = it & 1;
+            if (!mbar_wait(accfull0 + acc * 8, (it >> 1) & 1, ab, DEV_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + (acc ? ACC1_COL : 0);
+            const int row0 = (tm * CG + static_cast<int>(rank)) * 128 + q * 32;
+            const int col0 = tn * BN;
+#pragma unroll 1
+            for (int s = 0; s < 8; ++s) {
+                const int u = acc ? s : 7 - s;                   // 32-column unit; the shared unit goes first
+                uint32_t r[32];
+                tc_ld_32x32(t_acc + u * 32, r);
+                tc_wait_ld(r);
+                if (s == 0) {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_remote(drained_leader);
+                }
+                const uint32_t rowa = stg + lane * 128;
+                if (p.c_is_f32) {
+                    if (lane == 0) bulk_wait_read<0>();
+                    __syncwarp();
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        st_shared_v4(rowa + ((j ^ (lane & 7)) << 4), r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_2d(&tm_c, col0 + u * 32, row0, stg);
+                        bulk_commit();
+                    }
+                } else {
+                    if ((s & 1) == 0) {
+                        if (lane == 0) bulk_wait_read<0>();
+                        __syncwarp();
+                    }
+                    const int hh = u & 1;                        // which half of the 64-column chunk
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint32_t w0 = pack_bf16x2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
+                        const uint32_t w1 = pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+                        const uint32_t w2 = pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+                        const uint32_t w3 = pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+                        st_shared_v4(rowa + (((hh * 4 + j) ^ (lane & 7)) << 4), w0, w1, w2, w3);
+                    }
+                    if (s & 1) {
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            tma_store_2d(&tm_c, col0 + (u & ~1) * 32, row0, stg);
+                            bulk_commit();
+                        }
+                    }
+                }
+            }
+        }
+        if (lane == 0) bulk_wait_all<0>();
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    if (*abort_flag) {
+        // a wait gave up: let copies that may still be in flight land before shared memory goes away
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 1000000ull) __nanosleep(1000);
+    }
+    __syncwarp();
+    tc_fence_before();
+    if constexpr (CG == 2) cluster_sync_all(); else __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc<CG>(tmem_base, 512);
+    }
+}
+
+struct Maps {
+    CUtensorMap a, b, sfa, sfb, c;
+};
+
+template <int CG>
+static int build_maps(Maps& m, const void* A, const void* A_sc, const void* B, const void* B_sc, void* Cp,
+                      int M, int N, int K, int c_dtype) {
+    int rc;
+    const uint64_t kb = static_cast<uint64_t>(K) / 128;
+    {
+        const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(K)};
+        const uint32_t box[2] = {BK, 128};
+        if ((rc = make_tmap(&m.a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, A, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) != MX8_OK) return rc;
+    }
+    {
+        const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(K)};
+        const uint32_t box[2] = {BK, static_cast<uint32_t>(Cfg<CG>::B_ROWS)};
+        if ((rc = make_tmap(&m.b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, B, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) != MX8_OK) return rc;
+    }
+    {
+        // scale tiles [rows/128][K/128][512 bytes] seen as 32-bit words so one box row is a whole tile
+        const uint64_t dims[3] = {128, kb, static_cast<uint64_t>(M) / 128};
+        const uint64_t strides[2] = {512, 512 * kb};
+        const uint32_t box[3] = {128, 1, 1};
+        if ((rc = make_tmap(&m.sfa, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, A_sc, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE)) != MX8_OK) return rc;
+    }
+    {
+        const uint64_t dims[3] = {128, kb, static_cast<uint64_t>(N) / 128};
+        const uint64_t strides[2] = {512, 512 * kb};
+        const uint32_t box[3] = {128, 1, 2};
+        if ((rc = make_tmap(&m.sfb, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, B_sc, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE)) != MX8_OK) return rc;
+    }
+    {
+        const bool f32 = c_dtype == MX8_C_F32;
+        const uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(M)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(N) * (f32 ? 4 : 2)};
+        const uint32_t box[2] = {f32 ? 32u : 64u, 32};
+        if ((rc = make_tmap(&m.c, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, Cp, dims, strides,
+                            box, CU_TENSOR_MAP_SWIZZLE_128B)) != MX8_OK) return rc;
+    }
+    return MX8_OK;
+}
+
+template <int CG>
+static int max_grid() {
+    // CTAs that can be resident at once (cluster placement included), cached per device
+    static int cached[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    dev &= 63;
+    if (cached[dev]) return cached[dev];
+    auto kern = gemm_kernel<CG>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<CG>::dynamic);
+    if (e != cudaSuccess) {
+        note_cuda_error("cudaFuncSetAttribute(gemm)", cudaGetErrorString(e));
+        return 0;
+    }
+    int n = sm_count();
+    if (CG == 2) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(static_cast<unsigned>(n & ~1));
+        cfg.blockDim = dim3(THREADS);
+        cfg.dynamicSmemBytes = Cfg<CG>::dynamic;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension;
+        at[0].val.clusterDim.x = 2;
+        at[0].val.clusterDim.y = 1;
+        at[0].val.clusterDim.z = 1;
+        cfg.attrs = at;
+        cfg.numAttrs = 1;
+        int clusters = 0;
+        e = cudaOccupancyMaxActiveClusters(&clusters, kern, &cfg);
+        if (e != cudaSuccess || clusters <= 0) {
+            note_cuda_error("cudaOccupancyMaxActiveClusters", cudaGetErrorString(e));
+            cudaGetLastError();
+            clusters = n / 2;
+        }
+        n = clusters * 2;
+    }
+    cached[dev] = n;
+    return n;
+}
+
+template <int CG>
+static int run(const void* A, const void* A_sc, const void* B, const void* B_sc, void* Cp, int M, int N, int K,
+               int c_dtype, int max_ctas, cudaStream_t stream) {
+    Maps m;
+    int rc = build_maps<CG>(m, A, A_sc, B, B_sc, Cp, M, N, K, c_dtype);
+    if (rc != MX8_OK) return rc;
+    Params p{};
+    p.tiles_m = (M + 128 * CG - 1) / (128 * CG);
+    p.tiles_n = (N + BN - 1) / BN;
+    p.k_steps = K / BK;
+    p.group_m = 8;
+    p.c_is_f32 = c_dtype == MX8_C_F32;
+    p.status = device_status_ptr();
+    if (!p.status) return MX8_ERR_CUDA;
+    int grid = max_grid<CG>();
+    if (grid <= 0) return MX8_ERR_CUDA;
+    if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
+    const int tiles = p.tiles_m * p.tiles_n;
+    if (grid > tiles * CG) grid = tiles * CG;
+    grid = (grid / CG) * CG;
+    if (grid <= 0) grid = CG;
+
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(grid));
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = Cfg<CG>::dynamic;
+    cfg.stream = stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = CG;
+    at[0].val.clusterDim.y = 1;
+    at[0].val.clusterDim.z = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_kernel<CG>, m.a, m.b, m.sfa, m.sfb, m.c, p);
+    if (e != cudaSuccess) {
+        note_cuda_error("gemm launch", cudaGetErrorString(e));
+        return MX8_ERR_CUDA;
+    }
+    return MX8_OK;
+}
+
+}  // namespace gemm
+}  // namespace mx8
+
+extern "C" int mx8_gemm_ex(const void* A, const void* A_sc, const void* B, const void* B_sc, void* C, int M, int N, int K,
+                           int c_dtype, int cta_group, int max_ctas, void* stream) {
+    using namespace mx8;
+    if (!A || !A_sc || !B || !B_sc || !C) return MX8_ERR_ARG;
+    if (c_dtype != MX8_C_BF16 && c_dtype != MX8_C_F32) return MX8_ERR_ARG;
+    if (cta_group < 0 || cta_group > 2 || max_ctas < 0) return MX8_ERR_ARG;
+    if (M <= 0 || N <= 0 || K <= 0 || M % 128 || N % 128 || K % 128) return MX8_ERR_SHAPE;
+    if (!aligned16(A) || !aligned16(A_sc) || !aligned16(B) || !aligned16(B_sc) || !aligned16(C)) return MX8_ERR_ALIGN;
+    int rc = check_device_sm100();
+    if (rc != MX8_OK) return rc;
+    if (cta_group == 0) cta_group = (M <= 128) ? 1 : 2;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (cta_group == 2) return gemm::run<2>(A, A_sc, B, B_sc, C, M, N, K, c_dtype, max_ctas, st);
+    return gemm::run<1>(A, A_sc, B, B_sc, C, M, N, K, c_dtype, max_ctas, st);
+}
+
+extern "C" int mx8_gemm(const void* A, const void* A_sc, const void* B, const void* B_sc, void* C, int M, int N, int K,
+                        int c_dtype, void* stream) {
+    return mx8_gemm_ex(A, A_sc, B, B_sc, C, M, N, K, c_dtype, 0, 0, stream);
+}

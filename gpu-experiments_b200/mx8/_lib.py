@@ -1,0 +1,58 @@
+"""ctypes binding of libmx8.so (declared in include/mx8.h).  Fails loudly when the library is
+missing or a call returns a non-zero status: there is no fallback path."""
+import ctypes
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libmx8.so")
+
+OK, ERR_ARG, ERR_SHAPE, ERR_ALIGN, ERR_CUDA, ERR_UNSUPPORTED, ERR_DEVICE_TIMEOUT = range(7)
+SCALE_RCEIL, SCALE_FLOOR = 0, 1
+C_BF16, C_F32 = 0, 1
+
+# every symbol include/mx8.h declares, with its ctypes signature
+_vp, _i = ctypes.c_void_p, ctypes.c_int
+SIGNATURES = {
+    "mx8_quantize": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp]),
+    "mx8_gemm": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "mx8_gemm_ex": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
+    "mx8_device_status": (_i, [ctypes.POINTER(_i), _vp]),
+    "mx8_strerror": (ctypes.c_char_p, [_i]),
+    "mx8_last_cuda_error": (ctypes.c_char_p, []),
+    "mx8_version": (ctypes.c_char_p, []),
+}
+
+_lib = None
+
+
+class Mx8Error(RuntimeError):
+    def __init__(self, code, where):
+        self.code = code
+        lib = load()
+        msg = lib.mx8_strerror(code).decode()
+        detail = lib.mx8_last_cuda_error().decode() if code == ERR_CUDA else ""
+        super().__init__(f"{where}: mx8 status {code}: {msg}" + (f" [{detail}]" if detail else ""))
+
+
+def load():
+    """Load libmx8.so once.  torch is imported first so that its CUDA runtime is the one in the
+    process."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(
+                f"{LIB_PATH} is missing: build it with `python gpu-experiments_b200/build.py` "
+                "(the mx8 operators have no fallback implementation)")
+        import torch  # noqa: F401  (loads libcudart)
+        lib = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = lib
+    return _lib
+
+
+def check(code, where):
+    if code != OK:
+        raise Mx8Error(code, where)

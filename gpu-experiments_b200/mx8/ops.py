@@ -1,0 +1,136 @@
+"""Host-side mirror of the reference's pybind11 module `_C` for the MXFP8 path.
+
+Function names, argument order and argument meaning follow the reference's harness-facing
+bindings; each docstring cites the binding it stands in for.  Tensors stay owned by the caller,
+launches go to torch's current CUDA stream and are asynchronous, exactly as in the reference.
+Unlike the reference (which prints and exits), errors raise `Mx8Error`.
+"""
+import torch
+
+from . import _lib
+from ._lib import SCALE_FLOOR, SCALE_RCEIL, Mx8Error  # noqa: F401
+
+_SCALE_MODES = {"rceil": SCALE_RCEIL, "floor": SCALE_FLOOR, SCALE_RCEIL: SCALE_RCEIL, SCALE_FLOOR: SCALE_FLOOR}
+_FP8 = (torch.float8_e4m3fn, torch.uint8)
+_SC = (torch.uint8, getattr(torch, "float8_e8m0fnu", torch.uint8))
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _chk(t, name, dtypes, shape=None):
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor")
+    if t.dtype not in dtypes:
+        raise ValueError(f"{name} has dtype {t.dtype}, expected one of {dtypes}")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+    if shape is not None and t.numel() != _numel(shape):
+        raise ValueError(f"{name} has {t.numel()} elements, expected shape {tuple(shape)}")
+    return t.data_ptr()
+
+
+def _numel(shape):
+    n = 1
+    for s in shape:
+        n *= s
+    return n
+
+
+def mxfp8_quantize(x_bf16, *args, scale_mode="rceil"):
+    """Two call forms, as in the reference:
+
+    mxfp8_quantize(x_bf16, x_fp8, x_sc, x_fp8_t, x_sc_t, return_normal, return_transposed) -> None
+        caller-allocated outputs (blackwell-ultra/019-mxfp8-quantize.cu:185-219); an output pair
+        that is not requested is ignored and may be any tensor.
+    mxfp8_quantize(x_bf16, return_normal, return_transposed) -> (x_fp8, x_sc, x_fp8_t, x_sc_t)
+        outputs allocated here; x_bf16 is [M, N] or [E, M, N]; outputs not requested are None
+        (blackwell-ultra/022-moe-dispatch-mlp-swiglu-combine-mxfp8-bw.cu:404-448).
+
+    x_sc is uint8 [rows/128, cols/128, 32, 16] in the tcgen05 scale tile layout.
+    `scale_mode` ("rceil" = the reference's rule, "floor" = OCP) is an addition.
+    """
+    lib = _lib.load()
+    if x_bf16.dim() not in (2, 3):
+        raise ValueError("x_bf16 must be [M, N] or [E, M, N]")
+    E = x_bf16.shape[0] if x_bf16.dim() == 3 else 1
+    M, N = x_bf16.shape[-2], x_bf16.shape[-1]
+    xp = _chk(x_bf16, "x_bf16", (torch.bfloat16,))
+    mode = _SCALE_MODES[scale_mode]
+    if len(args) == 2:
+        rn, rt = bool(args[0]), bool(args[1])
+        lead = (E,) if x_bf16.dim() == 3 else ()
+        dev = x_bf16.device
+        x_fp8 = torch.empty(lead + (M, N), dtype=torch.float8_e4m3fn, device=dev) if rn else None
+        x_sc = torch.empty(E * M // 128, N // 128, 32, 16, dtype=torch.uint8, device=dev) if rn else None
+        x_fp8_t = torch.empty(lead + (N, M), dtype=torch.float8_e4m3fn, device=dev) if rt else None
+        x_sc_t = torch.empty(E * N // 128, M // 128, 32, 16, dtype=torch.uint8, device=dev) if rt else None
+        ret = (x_fp8, x_sc, x_fp8_t, x_sc_t)
+    elif len(args) == 6:
+        x_fp8, x_sc, x_fp8_t, x_sc_t = args[:4]
+        rn, rt = bool(args[4]), bool(args[5])
+        ret = None
+    else:
+        raise TypeError("mxfp8_quantize takes (x, rn, rt) or (x, x_fp8, x_sc, x_fp8_t, x_sc_t, rn, rt)")
+    if not (rn or rt):
+        raise ValueError("at least one of return_normal / return_transposed must be set")
+    p = [None, None, None, None]
+    if rn:
+        p[0] = _chk(x_fp8, "x_fp8", _FP8, (E, M, N))
+        p[1] = _chk(x_sc, "x_sc", _SC, (E * M // 128, N // 128, 512))
+    if rt:
+        p[2] = _chk(x_fp8_t, "x_fp8_t", _FP8, (E, N, M))
+        p[3] = _chk(x_sc_t, "x_sc_t", _SC, (E * N // 128, M // 128, 512))
+    with torch.cuda.device(x_bf16.device):
+        _lib.check(lib.mx8_quantize(xp, E, M, N, p[0], p[1], p[2], p[3], mode, _stream()), "mxfp8_quantize")
+    return ret
+
+
+def kernel(A, A_sc, B, B_sc, C, *, cta_group=0, max_ctas=0):
+    """kernel(A_fp8, A_sc, B_fp8, B_sc, C) -> None:  C = dequant(A) . dequant(B)^T.
+
+    A [M, K], B [N, K] E4M3; A_sc [M/128, K/128, 512] (or [.., 32, 16]) and B_sc likewise, uint8 in
+    the scale tile layout; C [M, N] preallocated, bf16 (blackwell/047-mxfp8-mma-2cta-MNK128-
+    polished.cu:532-541, also 045/046) or float32 (blackwell/009-mxfp8-mm.cu:225-234, 010-017).
+    """
+    lib = _lib.load()
+    M, K = A.shape
+    N = B.shape[0]
+    if B.shape[1] != K or tuple(C.shape) != (M, N):
+        raise ValueError("shape mismatch: A [M,K], B [N,K], C [M,N]")
+    ap = _chk(A, "A", _FP8)
+    bp = _chk(B, "B", _FP8)
+    asp = _chk(A_sc, "A_sc", _SC, (M // 128, K // 128, 512))
+    bsp = _chk(B_sc, "B_sc", _SC, (N // 128, K // 128, 512))
+    cp = _chk(C, "C", (torch.bfloat16, torch.float32))
+    cd = _lib.C_F32 if C.dtype == torch.float32 else _lib.C_BF16
+    with torch.cuda.device(A.device):
+        _lib.check(lib.mx8_gemm_ex(ap, asp, bp, bsp, cp, M, N, K, cd, cta_group, max_ctas, _stream()), "kernel")
+
+
+def quantize_kernel(A, A_fp8, A_sc, A_t_fp8=None, A_t_sc=None):
+    """Legacy quantize entry points of the older harnesses, which call the binding `kernel`:
+    kernel(A, A_fp8, A_sc) (blackwell/018-mxfp8-quantize.cu:288-300, 036) and
+    kernel(A, A_fp8, A_sc, A_t_fp8, A_t_sc) (blackwell/038-mxfp8-quantize-combined.cu:397-399).
+    A_sc is [M/128, N/128, 512]."""
+    both = A_t_fp8 is not None
+    mxfp8_quantize(A, A_fp8, A_sc, A_t_fp8, A_t_sc, True, both)
+
+
+def kernel_transpose(A, A_fp8, A_sc):
+    """kernel_transpose(A, A_t_fp8, A_t_sc): transposed-only quantize
+    (blackwell/018-mxfp8-quantize.cu:294-300, blackwell/037-mxfp8-transpose-quantize.cu)."""
+    mxfp8_quantize(A, None, None, A_fp8, A_sc, False, True)
+
+
+def device_status():
+    """Synchronize the current stream and return the device status word (0 = healthy); raises
+    Mx8Error if a kernel's bounded wait expired."""
+    import ctypes
+    lib = _lib.load()
+    v = ctypes.c_int(0)
+    rc = lib.mx8_device_status(ctypes.byref(v), _stream())
+    if rc != _lib.OK:
+        raise Mx8Error(rc, f"device_status (device word = {v.value})")
+    return v.value

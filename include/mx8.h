@@ -1,0 +1,95 @@
+/* mx8 — C ABI of the B200 (sm_100a) MXFP8 hot path: bf16 -> E4M3 + E8M0 quantize and the
+ * block-scaled GEMM that consumes it.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer owned by the caller; the library allocates nothing and
+ *     keeps no reference after the call returns;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream); launches are
+ *     asynchronous, exactly like the reference's entry points;
+ *   - the return value is a status code (MX8_OK == 0); nothing calls exit() and nothing traps.
+ *     The reference prints and exits on errors (blackwell/gpu-experiments.cuh:29-47);
+ *   - M, N, K are multiples of 128, the granularity of the tcgen05 scale-factor layout, as in
+ *     the reference (blackwell-ultra/019-mxfp8-quantize.py:59);
+ *   - "scale tile layout": the E8M0 bytes of a 128-row x 128-column (4 blocks of 32) tile are
+ *     512 consecutive bytes, the byte of (row r, block kb) at (r % 32) * 16 + (r / 32) * 4 + kb;
+ *     tiles are ordered [rows / 128][cols / 128] (blackwell-ultra/019-mxfp8-quantize.cu:131).
+ *
+ * There is no CPU fallback: on a machine without an sm_100 device every compute entry point
+ * returns MX8_ERR_UNSUPPORTED or MX8_ERR_CUDA.
+ */
+#ifndef MX8_H_
+#define MX8_H_
+
+#if defined(__GNUC__)
+#define MX8_API __attribute__((visibility("default")))
+#else
+#define MX8_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+    MX8_OK = 0,
+    MX8_ERR_ARG = 1,            /* null pointer, bad enum value, nothing requested          */
+    MX8_ERR_SHAPE = 2,          /* a dimension is not a positive multiple of 128            */
+    MX8_ERR_ALIGN = 3,          /* a pointer is not 16-byte aligned                         */
+    MX8_ERR_CUDA = 4,           /* a CUDA runtime / driver call failed (mx8_last_cuda_error) */
+    MX8_ERR_UNSUPPORTED = 5,    /* device is not compute capability 10.x                    */
+    MX8_ERR_DEVICE_TIMEOUT = 6  /* a kernel's bounded wait expired (mx8_device_status)      */
+};
+
+/* scale rounding */
+enum {
+    MX8_SCALE_RCEIL = 0, /* E = ceil(log2(amax / 448)); the reference's rule                  */
+    MX8_SCALE_FLOOR = 1  /* E = floor(log2(amax)) - 8; OCP rule, E4M3 saturation live         */
+};
+
+/* GEMM output element type */
+enum {
+    MX8_C_BF16 = 0, /* blackwell/047-mxfp8-mma-2cta-MNK128-polished.cu:461 (C is bf16)       */
+    MX8_C_F32 = 1   /* blackwell/009-mxfp8-mm.cu:46, 010..017 (C is float)                   */
+};
+
+/* Quantize x[E][M][N] (bf16, row-major; E = 1 for a matrix) to MXFP8.
+ *   fp8   [E][M][N] bytes and sc   [E*M/128][N/128][512]: blocks of 32 along N ("normal");
+ *   fp8_t [E][N][M] bytes and sc_t [E*N/128][M/128][512]: the transpose, blocks of 32 along M.
+ * Pass fp8 == sc == NULL or fp8_t == sc_t == NULL to skip that orientation.
+ * Replaces mxfp8_quantize_entrypoint, blackwell-ultra/019-mxfp8-quantize.cu:185-219 (caller-
+ * allocated outputs) and the [E,M,N] form at
+ * blackwell-ultra/022-moe-dispatch-mlp-swiglu-combine-mxfp8-bw.cu:404-448; also the legacy
+ * kernel / kernel_transpose pair of blackwell/018-mxfp8-quantize.cu:288-300 and the combined
+ * blackwell/038-mxfp8-quantize-combined.cu:397-399. */
+MX8_API int mx8_quantize(const void* x_bf16, int E, int M, int N,
+                 void* fp8, void* sc, void* fp8_t, void* sc_t,
+                 int scale_mode, void* stream);
+
+/* C[M][N] = dequant(A[M][K]) . dequant(B[N][K])^T, fp32 accumulation on tcgen05 tensor cores.
+ *   A, B: E4M3 bytes, K contiguous; A_sc [M/128][K/128][512], B_sc [N/128][K/128][512] in the
+ *   scale tile layout; C row-major, bf16 or float per c_dtype.
+ * Replaces `kernel(A_fp8, A_sc, B_fp8, B_sc, C)`,
+ * blackwell/047-mxfp8-mma-2cta-MNK128-polished.cu:525-541 (and 009/010/016/017/045/046). */
+MX8_API int mx8_gemm(const void* A, const void* A_sc, const void* B, const void* B_sc, void* C,
+             int M, int N, int K, int c_dtype, void* stream);
+
+/* Same contract as mx8_gemm with the kernel variant chosen by the caller:
+ *   cta_group 2 = one 256x256 tile per CTA pair (cluster of 2), 1 = one 128x256 tile per CTA,
+ *   0 = library default; max_ctas caps the persistent grid (0 = all SMs). Used by the tests and
+ *   the benchmark's ablations. */
+MX8_API int mx8_gemm_ex(const void* A, const void* A_sc, const void* B, const void* B_sc, void* C,
+                int M, int N, int K, int c_dtype, int cta_group, int max_ctas, void* stream);
+
+/* Synchronizes `stream`, then reads and clears the current device's status word: 0 = healthy,
+ * otherwise the code of the first bounded wait that expired (see csrc/mx8_ptx.cuh).
+ * Returns MX8_OK, MX8_ERR_DEVICE_TIMEOUT (status != 0) or MX8_ERR_CUDA. */
+MX8_API int mx8_device_status(int* status_out, void* stream);
+
+MX8_API const char* mx8_strerror(int code);
+MX8_API const char* mx8_last_cuda_error(void); /* text of the last CUDA failure seen by this thread */
+MX8_API const char* mx8_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MX8_H_ */

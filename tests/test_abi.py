@@ -1,0 +1,73 @@
+"""CPU-side checks of the C-ABI library: it loads, exports every declared symbol, and validates
+arguments before touching a device."""
+import ctypes
+import os
+import re
+
+import pytest
+
+import mx8
+from mx8 import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    if not os.path.exists(_lib.LIB_PATH):
+        import importlib.util
+        spec = importlib.util.spec_from_file_location("mx8_build", os.path.join(ROOT, "gpu-experiments_b200", "build.py"))
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        mod.build()
+    return mx8.load()
+
+
+def test_header_and_binding_agree(lib):
+    hdr = open(os.path.join(ROOT, "include", "mx8.h")).read()
+    declared = set(re.findall(r"MX8_API\s+[\w\s\*]+?\b(mx8_\w+)\s*\(", hdr))
+    assert declared == set(_lib.SIGNATURES), (declared, set(_lib.SIGNATURES))
+    for name in declared:
+        assert hasattr(lib, name)
+
+
+def test_status_codes_have_text(lib):
+    hdr = open(os.path.join(ROOT, "include", "mx8.h")).read()
+    codes = dict((n, int(v)) for n, v in re.findall(r"(MX8_(?:OK|ERR_\w+))\s*=\s*(\d+)", hdr))
+    assert codes["MX8_OK"] == _lib.OK and codes["MX8_ERR_DEVICE_TIMEOUT"] == _lib.ERR_DEVICE_TIMEOUT
+    for v in codes.values():
+        assert b"unknown" not in lib.mx8_strerror(v)
+    assert b"unknown" in lib.mx8_strerror(99)
+    assert lib.mx8_version().startswith(b"mx8")
+
+
+def test_argument_validation_needs_no_device(lib):
+    p = ctypes.c_void_p(4096)      # never dereferenced: validation fails first
+    odd = ctypes.c_void_p(4100)
+    q = lib.mx8_quantize
+    assert q(None, 1, 128, 128, p, p, p, p, 0, None) == _lib.ERR_ARG
+    assert q(p, 1, 128, 128, None, None, None, None, 0, None) == _lib.ERR_ARG       # nothing requested
+    assert q(p, 1, 128, 128, p, None, None, None, 0, None) == _lib.ERR_ARG          # half a pair
+    assert q(p, 1, 128, 128, p, p, None, None, 7, None) == _lib.ERR_ARG             # bad scale mode
+    assert q(p, 1, 100, 128, p, p, None, None, 0, None) == _lib.ERR_SHAPE
+    assert q(p, 1, 128, 0, p, p, None, None, 0, None) == _lib.ERR_SHAPE
+    assert q(p, 0, 128, 128, p, p, None, None, 0, None) == _lib.ERR_SHAPE
+    assert q(odd, 1, 128, 128, p, p, None, None, 0, None) == _lib.ERR_ALIGN
+    g = lib.mx8_gemm
+    assert g(None, p, p, p, p, 128, 128, 128, 0, None) == _lib.ERR_ARG
+    assert g(p, p, p, p, p, 128, 128, 128, 5, None) == _lib.ERR_ARG
+    assert g(p, p, p, p, p, 128, 192, 128, 0, None) == _lib.ERR_SHAPE
+    assert g(p, p, p, p, p, 128, 128, 64, 0, None) == _lib.ERR_SHAPE
+    assert g(p, p, odd, p, p, 128, 128, 128, 0, None) == _lib.ERR_ALIGN
+    assert lib.mx8_gemm_ex(p, p, p, p, p, 128, 128, 128, 0, 3, 0, None) == _lib.ERR_ARG
+
+
+def test_no_device_means_error_not_fallback(lib):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a CUDA device is present")
+    p = ctypes.c_void_p(4096)
+    rc = lib.mx8_quantize(p, 1, 128, 128, p, p, None, None, 0, None)
+    assert rc in (_lib.ERR_CUDA, _lib.ERR_UNSUPPORTED)
+    with pytest.raises(ValueError):
+        mx8.mxfp8_quantize(torch.zeros(128, 128, dtype=torch.bfloat16), True, False)   # CPU tensor rejected
