@@ -1,0 +1,422 @@
+#!/usr/bin/env python
+"""Benchmark of the MXFP8 hot path on B200: quantize GB/s (headline line) and block-scaled GEMM
+TFLOP/s (the "gemm" object of the same line), with roofline fractions, clocks, an end-to-end
+number through host buffers and the CPU port of the reference's torch code timed beside it.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl mx8|reference] [--workload quantize|gemm]
+
+One JSON line on stdout (rank 0).  Under torchrun every rank works on its own shard; there is no
+data-path collective, only the barrier and the max-over-ranks reduction of the timing.
+
+Workloads (synthetic, seeded; stand-ins with the shapes and value distributions the benchmark
+configurations name):
+  quantize  bf16 16384 x 16384 ~ N(0,1), 0.1 % of entries x1000, one all-zero 1x32 block per 1024
+            rows; row-wise and transposed E4M3 + E8M0 (tcgen05 scale layout).  Each rank quantizes
+            its own matrix (weak scaling).
+  gemm      M = N = K = 8192, operands quantized from bf16 ~ N(0, 1/sqrt(K)), bf16 output.  With N
+            GPUs the rows of A and C are split M/N per rank, B replicated (strong scaling).
+"""
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "gpu-experiments_b200"))
+
+import torch  # noqa: E402
+
+QM = QN = 16384
+GM = GN = GK = 8192
+L2_BYTES = 126 * 1024 * 1024
+
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
+# summarised under profiles/; None until a capture exists for that kernel.
+NCU_TRAFFIC_BYTES = {"quantize_16384x16384_both": None, "gemm_8192": None}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Polls SM clock and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4),
+        }
+        get_reasons = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or nv.nvmlDeviceGetCurrentClocksThrottleReasons
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                r = get_reasons(self.h)
+                for k, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            time.sleep(0.002)
+
+    def start(self):
+        if self.nv:
+            self._stop.clear()
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        if self._thread:
+            self._stop.set()
+            self._thread.join()
+            self._thread = None
+
+    def summary(self):
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+def dist_setup(n_gpus):
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    else:
+        torch.cuda.set_device(0)
+    return world, rank, local
+
+
+def barrier(world):
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def max_over_ranks(ms, world):
+    if world > 1:
+        import torch.distributed as dist
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+    return ms
+
+
+def timed(fn, steps, world, sampler=None):
+    """K calls of fn(i) between two CUDA events on the current stream; barrier + synchronize on
+    both sides; returns the max over ranks of the elapsed milliseconds."""
+    barrier(world)
+    if sampler:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    if sampler:
+        sampler.stop()
+    ms = e0.elapsed_time(e1)
+    barrier(world)
+    return max_over_ranks(ms, world)
+
+
+# ------------------------------------------------------------------------------------------
+# CPU port of the reference's torch code (the oracle), timed on the host cores
+# ------------------------------------------------------------------------------------------
+def cpu_quantize_step(x):
+    """Row-wise + transposed quantize with the oracle's float restatement of the reference's
+    mxfp8_quantize_ref (the same torch ops in the same order)."""
+    from oracle import mx8_oracle as O
+    O.quantize_ref_float(x, "rceil")
+    O.quantize_ref_float(x.t().contiguous(), "rceil")
+
+
+def cpu_quantize_input(rows, cols):
+    from oracle import mx8_oracle as O
+    torch.set_num_threads(os.cpu_count() or 1)
+    return O.make_input(rows, cols, seed=1234, outliers=True, zero_blocks=True)
+
+
+def cpu_gemm_operands(n):
+    from oracle import mx8_oracle as O
+    torch.set_num_threads(os.cpu_count() or 1)
+    a = O.make_input(n, n, seed=1, std=n ** -0.5)
+    b = O.make_input(n, n, seed=2, std=n ** -0.5)
+    return O.quantize_tiled(a) + O.quantize_tiled(b)
+
+
+def cpu_gemm_step(ops):
+    """dequantize + fp32 matmul + bf16 round with the oracle."""
+    from oracle import mx8_oracle as O
+    O.gemm_ref(*ops)
+
+
+def time_cpu(fn, arg, steps, warmup):
+    for _ in range(warmup):
+        fn(arg)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        fn(arg)
+    return (time.perf_counter() - t0) / steps
+
+
+def cpu_baseline_quantize(target_s=12.0):
+    rows = 1024
+    x = cpu_quantize_input(rows, QN)
+    per = time_cpu(cpu_quantize_step, x, 1, 1)
+    reps = max(2, min(100, int(target_s / per)))
+    per = time_cpu(cpu_quantize_step, x, reps, 0)
+    return {"value": rows * QN * 4.0625 / per / 1e9, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{reps} passes over a {rows} x {QN} row slab of the workload, row-wise + transposed ({per * reps:.1f} s)"}
+
+
+def cpu_baseline_gemm(target_s=8.0):
+    n = 2048
+    ops = cpu_gemm_operands(n)
+    per = time_cpu(cpu_gemm_step, ops, 1, 1)
+    reps = max(2, min(100, int(target_s / per)))
+    per = time_cpu(cpu_gemm_step, ops, reps, 0)
+    return {"value": 2.0 * n ** 3 / per / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{reps} passes of a {n}^3 sub-problem: dequantize + fp32 matmul + bf16 round ({per * reps:.1f} s)"}
+
+
+def run_reference(args, rank):
+    """--impl reference: the reference's own CPU implementation of the path (its torch code,
+    restated in oracle/) on all host threads; each step is a bounded sample of the workload."""
+    if rank != 0:
+        return
+    total = max(1, args.steps + args.warmup)
+    if args.workload == "quantize":
+        rows = 1024
+        x = cpu_quantize_input(rows, QN)
+        est = time_cpu(cpu_quantize_step, x, 1, 1)
+        while rows > 128 and est * total > 150.0:      # keep the whole run within a few minutes
+            rows //= 2
+            est /= 2
+        x = x[:rows].contiguous()
+        per = time_cpu(cpu_quantize_step, x, args.steps, args.warmup)
+        value, unit, metric = rows * QN * 4.0625 / per / 1e9, "GB/s", "mxfp8_quantize_bandwidth"
+        sample = f"{rows} x {QN} row slab of the 16384 x 16384 input per step, row-wise + transposed"
+        cfg = {"workload": "quantize bf16 16384x16384 -> E4M3 + E8M0 scales, row-wise + transposed", "scale_mode": "rceil"}
+    else:
+        n = 2048
+        ops = cpu_gemm_operands(n)
+        est = time_cpu(cpu_gemm_step, ops, 1, 1)
+        if est * total > 150.0:
+            n = 1024
+            ops = cpu_gemm_operands(n)
+        per = time_cpu(cpu_gemm_step, ops, args.steps, args.warmup)
+        value, unit, metric = 2.0 * n ** 3 / per / 1e12, "TFLOP/s", "mxfp8_gemm_throughput"
+        sample = f"{n}^3 sub-problem of the 8192^3 GEMM per step (dequantize + fp32 matmul + bf16 round)"
+        cfg = {"workload": "MXFP8 GEMM M=N=K=8192, bf16 out"}
+    line = {"impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": per * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "u8", "data": "synthetic", "config": cfg,
+            "cpu_baseline": {"value": value, "unit": unit, "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
+            "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------
+def bench_quantize(args, world, rank, local, peaks, with_cpu):
+    import mx8
+    from oracle import mx8_oracle as O   # input generator only (make_input); nothing is computed with it
+    dev = torch.device("cuda", local)
+    M, N = QM, QN
+    x_h = O.make_input(M, N, seed=1234 + rank, outliers=True, zero_blocks=True).pin_memory()
+    x = x_h.to(dev, non_blocking=True)
+    outs = list(mx8.mxfp8_quantize(x, True, True))
+    algo_bytes = M * N * 2 + 2 * (M * N + M * N // 32)
+
+    def step(_):
+        mx8.mxfp8_quantize(x, outs[0], outs[1], outs[2], outs[3], True, True)
+
+    for i in range(args.warmup):
+        step(i)
+    sampler = ClockSampler(local) if rank == 0 else None
+    ms = timed(step, args.steps, world, sampler)
+    mx8.device_status()
+    per_ms = ms / args.steps
+    value = world * algo_bytes / (per_ms * 1e-3) / 1e9
+    achieved = algo_bytes / (per_ms * 1e-3) / 1e9
+
+    # end to end through host buffers: pinned input -> device, quantize, all four outputs -> pinned host
+    outs_h = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in outs]
+    h2d = x_h.numel() * 2
+    d2h = sum(o.numel() * o.element_size() for o in outs)
+
+    def e2e_step(_):
+        x.copy_(x_h, non_blocking=True)
+        mx8.mxfp8_quantize(x, outs[0], outs[1], outs[2], outs[3], True, True)
+        for o_h, o in zip(outs_h, outs):
+            o_h.copy_(o, non_blocking=True)
+
+    e2e_steps = max(3, min(args.steps, 10))
+    for i in range(2):
+        e2e_step(i)
+    e2e_ms = timed(e2e_step, e2e_steps, world) / e2e_steps
+    e2e_val = world * algo_bytes / (e2e_ms * 1e-3) / 1e9
+
+    line = {
+        "metric": "mxfp8_quantize_bandwidth", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": per_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "u8", "data": "synthetic",
+        "config": {"workload": "quantize bf16 16384x16384 (N(0,1), 0.1% outliers x1000, zero blocks) -> E4M3 + E8M0 scales "
+                               "in tcgen05 layout, row-wise + transposed, per GPU",
+                   "scale_mode": "rceil", "l2": "inputs (512 MiB) and outputs (528 MiB) larger than L2",
+                   "bytes_per_step_per_gpu": algo_bytes, "sharding": "one matrix per GPU, no collective"},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC_BYTES["quantize_16384x16384_both"],
+                     "peak_source": peaks["source"], "frac_of_nominal_8000": achieved / 8000.0,
+                     "kernel": "quantize_kernel<4,4,true,true>", "algorithmic_bytes_per_launch": algo_bytes},
+        "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": e2e_ms, "steps": e2e_steps},
+        "gpu_launches": args.steps,
+    }
+    if sampler:
+        line["clocks"] = sampler.summary()
+    if with_cpu and rank == 0:
+        line["cpu_baseline"] = cpu_baseline_quantize()
+    return line
+
+
+def bench_gemm(args, world, rank, local, peaks, with_cpu):
+    import mx8
+    from oracle import mx8_oracle as O   # input generator only
+    dev = torch.device("cuda", local)
+    M, N, K = GM // world, GN, GK         # rows of A and C split across ranks, B replicated
+    M = max(128, (M // 128) * 128)
+    sets = []
+    for s in range(3):                    # rotate operand sets so no iteration finds its inputs in L2
+        a = O.make_input(M, K, seed=100 + 10 * s + rank, std=K ** -0.5).to(dev)
+        b = O.make_input(N, K, seed=200 + 10 * s, std=K ** -0.5).to(dev)
+        aq, asc, _, _ = mx8.mxfp8_quantize(a, True, False)
+        bq, bsc, _, _ = mx8.mxfp8_quantize(b, True, False)
+        sets.append((aq, asc, bq, bsc, torch.empty(M, N, dtype=torch.bfloat16, device=dev)))
+        del a, b
+    flops = 2.0 * M * N * K
+
+    def step(i):
+        aq, asc, bq, bsc, c = sets[i % 3]
+        mx8.kernel(aq, asc, bq, bsc, c)
+
+    for i in range(args.warmup):
+        step(i)
+    sampler = ClockSampler(local) if rank == 0 else None
+    ms = timed(step, args.steps, world, sampler)
+    mx8.device_status()
+    per_ms = ms / args.steps
+    achieved = flops / (per_ms * 1e-3) / 1e12
+    value = world * achieved
+
+    aq, asc, bq, bsc, c = sets[0]
+    host_in = [t.cpu().pin_memory() for t in (aq, asc, bq, bsc)]
+    c_h = torch.empty(c.shape, dtype=c.dtype).pin_memory()
+    h2d = sum(t.numel() * t.element_size() for t in host_in)
+    d2h = c.numel() * 2
+
+    def e2e_step(_):
+        for d, h in zip((aq, asc, bq, bsc), host_in):
+            d.copy_(h, non_blocking=True)
+        mx8.kernel(aq, asc, bq, bsc, c)
+        c_h.copy_(c, non_blocking=True)
+
+    e2e_steps = max(3, min(args.steps, 10))
+    for i in range(2):
+        e2e_step(i)
+    e2e_ms = timed(e2e_step, e2e_steps, world) / e2e_steps
+    fp8_peak = 2.0 * peaks["bf16_tflops"]
+    line = {
+        "metric": "mxfp8_gemm_throughput", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": per_ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "fp8_e4m3 x ue8m0 -> f32 accumulate -> bf16", "data": "synthetic",
+        "config": {"workload": f"MXFP8 GEMM M=N=K=8192 (per GPU {M}x{N}x{K}), operands quantized from bf16 N(0,1/sqrt(K)), bf16 out",
+                   "l2": "three operand/output sets (256 MiB each at 1 GPU) used in rotation", "tile": "256x256x128, 2-CTA cluster, 6 stages",
+                   "sharding": "rows of A and C split across GPUs, B replicated, no collective"},
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": fp8_peak, "unit": "TFLOP/s", "frac": achieved / fp8_peak,
+                     "traffic": NCU_TRAFFIC_BYTES["gemm_8192"],
+                     "peak_source": "2 x cuBLAS bf16 burst (" + peaks["source"] + "); no fp8 peak was measured on this pool",
+                     "frac_of_nominal_4500": achieved / 4500.0, "kernel": "gemm_kernel<2>", "algorithmic_flops_per_launch": flops},
+        "e2e": {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": e2e_steps},
+        "gpu_launches": args.steps,
+    }
+    if sampler:
+        line["clocks"] = sampler.summary()
+    if with_cpu and rank == 0:
+        line["cpu_baseline"] = cpu_baseline_gemm()
+    return line
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="mx8", choices=["mx8", "reference"])
+    ap.add_argument("--workload", default="quantize", choices=["quantize", "gemm"])
+    ap.add_argument("--no-gemm", action="store_true", help="skip the GEMM object of the quantize line")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    args.steps = max(args.steps, 1)
+
+    if args.impl == "reference":
+        run_reference(args, int(os.environ.get("RANK", "0")))
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the mx8 path has no CPU fallback")
+    world, rank, local = dist_setup(args.gpus)
+    peaks = load_peaks()
+    with_cpu = world == 1 and not args.no_cpu
+    if args.workload == "quantize":
+        line = bench_quantize(args, world, rank, local, peaks, with_cpu)
+        if not args.no_gemm:
+            g = bench_gemm(args, world, rank, local, peaks, with_cpu)
+            line["gemm"] = {k: g[k] for k in ("metric", "value", "unit", "ms_per_step", "scaling", "config", "roofline", "e2e",
+                                              "gpu_launches", "clocks", "cpu_baseline") if k in g}
+            line["gpu_launches"] += g["gpu_launches"]
+    else:
+        line = bench_gemm(args, world, rank, local, peaks, with_cpu)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
