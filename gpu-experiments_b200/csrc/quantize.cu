@@ -1,16 +1,21 @@
 // MXFP8 quantizer for sm_100a: bf16 [E][M][N] -> E4M3 bytes + one E8M0 scale per 1x32 block,
 // row-wise ("normal") and/or transposed, scales written in the tcgen05 scale tile layout.
 //
-// One persistent CTA per SM.  Warp 0 is the producer: it streams 128x128 bf16 tiles (32 KiB)
-// into a ring of shared-memory slots with TMA.  G consumer groups of 128 threads take tiles
-// round-robin.  Per tile a group
-//   1. reads the tile by rows with 16-byte shared loads (two lanes per 32-element block, one
-//      warp shuffle for the block amax), converts, and writes the row-wise bytes straight to
-//      global memory as full 128-byte lines (16 bytes per lane);
-//   2. reads the tile again by columns (8-byte loads, four columns per lane, warp w owns rows
-//      32w..32w+31), releases the slot to the producer, converts in registers;
-//   3. stages the transposed bytes in shared memory under the 128-byte TMA swizzle and lets one
-//      thread issue four TMA tile stores plus two 512-byte bulk stores for the scale tiles.
+// One persistent CTA per SM: warp 0 is the producer, W consumer warps work independently (no
+// CTA-wide or group barrier anywhere).  The unit of work is a slab of 32 rows x 128 columns
+// (8 KiB of bf16); a 128x128 scale tile is four consecutive slabs.  Every consumer warp owns
+// one shared-memory slot and one staging buffer:
+//   producer  one thread streams slabs into the warps' slots with TMA (slab n -> warp n % W);
+//   consumer  1. copies its slab into registers with 32 conflict-free 8-byte shared loads
+//                (lane l holds columns 4l..4l+3 of all 32 rows) and hands the slot back at
+//                once, so the next load overlaps all of the arithmetic below;
+//             2. row-wise: block amax by a packed (two rows per register) butterfly over the
+//                eight lanes of a 32-column block, scale bytes with packed integer arithmetic,
+//                bf16x2 multiply by the exact power-of-two reciprocal, cvt to E4M3, and one
+//                4-byte store per lane and row: 128 contiguous bytes per warp instruction;
+//             3. transposed: column amax in registers (no shuffle), convert, stage 4 KiB in
+//                shared memory and let one lane issue four TMA tile stores (32 bytes along M
+//                for each of 32 columns per store).
 // HBM traffic is the algorithmic minimum: 2 bytes read and (1 + 1/32) bytes written per element
 // and orientation.  Replaces blackwell-ultra/019-mxfp8-quantize.cu:40-179 and the persistent
 // variant blackwell-ultra/020-mxfp8-quantize-persistent.cu:139-219 of the reference.
@@ -21,9 +26,10 @@ namespace mx8 {
 namespace quant {
 
 constexpr int TILE = 128;
-constexpr int SLOT_BYTES = TILE * TILE * 2;       // one bf16 tile
-constexpr int TSTAGE_BYTES = TILE * TILE;         // transposed fp8 staging per group
-constexpr int SCSTAGE_BYTES = 2 * 1024;           // [parity][row scales 512 | column scales 512]
+constexpr int SLAB_ROWS = 32;
+constexpr int SLOT_BYTES = SLAB_ROWS * TILE * 2;   // one bf16 slab
+constexpr int TSTAGE_BYTES = SLAB_ROWS * TILE;     // transposed fp8 staging per warp
+constexpr int SCSTAGE_BYTES = 128;                 // row-wise scale bytes of one slab: [row][kb]
 
 struct Params {
     uint8_t* out;        // row-wise fp8 [E*M][N]
@@ -33,20 +39,23 @@ struct Params {
     int tiles_c;         // N/128
     int tiles_rm;        // M/128 (row tiles per expert)
     int N;
-    int round_add;       // 0x1F: round the scale exponent up (rceil); 0: floor
-    int min_byte;        // 88 (rceil: amax/448 clamped to 1e-12) or 0 (floor)
+    int group_r;         // tile rows per rasterisation group
+    uint32_t round_add2; // packed per 16-bit half: 0x1F rounds the scale exponent up (rceil), 0 = floor
+    uint32_t min_byte8_2;// packed per half: smallest scale byte + 8 (rceil 88: amax/448 clamped to 1e-12; floor 0)
     int* status;
 };
 
-template <int G, int S>
+template <int W, int D>
 struct Smem {
+    static constexpr int S = W * D;                               // slots in the ring
     static constexpr int ring = 0;
     static constexpr int tstage = ring + S * SLOT_BYTES;
-    static constexpr int scstage = tstage + G * TSTAGE_BYTES;
-    static constexpr int bars = scstage + G * SCSTAGE_BYTES;      // full[S], empty[S]
+    static constexpr int scstage = tstage + W * TSTAGE_BYTES;
+    static constexpr int bars = scstage + W * SCSTAGE_BYTES;      // full[S], empty[S]
     static constexpr int flag = bars + 2 * S * 8;
     static constexpr int total = flag + 16;
     static constexpr int dynamic = total + 1024;                  // slack to align the base to 1024
+    static_assert(dynamic <= 232448, "shared memory budget exceeded");
 };
 
 __device__ __forceinline__ uint32_t maxabs_bf16x2(uint32_t a, uint32_t b) {
@@ -54,27 +63,51 @@ __device__ __forceinline__ uint32_t maxabs_bf16x2(uint32_t a, uint32_t b) {
     asm("max.xorsign.abs.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
     return d;
 }
+__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+__device__ __forceinline__ uint32_t max_u16x2(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("max.u16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
 __device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xFFFF0000u); }
-__device__ __forceinline__ void group_sync(int g) {
-    asm volatile("bar.sync %0, %1;" ::"r"(g + 1), "r"(128) : "memory");
+
+// Two non-negative bf16 amax bit patterns (one per 16-bit half) -> two E8M0 bytes (one per half):
+// byte = max(min_byte, ((amax + round_add) >> 7) - 8), the exact integer form of
+// ceil(log2(amax / 448)) + 127 (round_add 0x1F) or floor(log2(amax)) - 8 + 127 (round_add 0).
+__device__ __forceinline__ uint32_t scale_bytes2(uint32_t amax2, const Params& p) {
+    uint32_t t = ((amax2 + p.round_add2) >> 7) & 0x00FF00FFu;
+    return max_u16x2(t, p.min_byte8_2) - 0x00080008u;
 }
-// E8M0 byte from the bit pattern of a non-negative bf16 amax; exact integer form of
-// ceil(log2(amax/448)) + 127 (round_add = 0x1F) or floor(log2(amax)) - 8 + 127 (round_add = 0).
-__device__ __forceinline__ int scale_byte(uint32_t amax_bits, int round_add, int min_byte) {
-    return max(min_byte, static_cast<int>((amax_bits + round_add) >> 7) - 8);
-}
-// 2^(127 - byte) as a float: the exact reciprocal of the scale
-__device__ __forceinline__ float inv_scale(int byte) { return __uint_as_float(static_cast<uint32_t>(254 - byte) << 23); }
-// four bf16 (two packed words) -> four E4M3 bytes
-__device__ __forceinline__ uint32_t cvt4(uint32_t v0, uint32_t v1, float inv) {
-    return cvt_e4m3x2(bf16_lo(v0) * inv, bf16_hi(v0) * inv) | (cvt_e4m3x2(bf16_lo(v1) * inv, bf16_hi(v1) * inv) << 16);
+// two scale bytes -> two bf16 reciprocals 2^(127 - byte): exponent field 254 - byte, mantissa 0
+__device__ __forceinline__ uint32_t inv_scales2(uint32_t bytes2) { return (0x00FE00FEu - bytes2) << 7; }
+// four bf16 (two packed words, already scaled) -> four E4M3 bytes
+__device__ __forceinline__ uint32_t cvt4(uint32_t v0, uint32_t v1) {
+    return cvt_e4m3x2(bf16_lo(v0), bf16_hi(v0)) | (cvt_e4m3x2(bf16_lo(v1), bf16_hi(v1)) << 16);
 }
 
-template <int G, int S, bool ROW, bool COL>
-__global__ void __launch_bounds__(32 + G * 128, 1)
+// Tile order: groups of `group_r` tile rows, walked column by column inside a group.  The ~148
+// tiles in flight at any time then form a patch about group_r tiles tall, so each input row, each
+// row-wise output row AND each transposed output row receives a contiguous run of a kilobyte or
+// more within a short time window, which keeps DRAM pages open for all three streams.
+__device__ __forceinline__ void tile_coords(int t, const Params& p, int& tr, int& tc) {
+    const int per_group = p.group_r * p.tiles_c;
+    const int grp = t / per_group;
+    const int in_grp = t - grp * per_group;
+    const int rows = min(p.group_r, p.tiles_r - grp * p.group_r);
+    tc = in_grp / rows;
+    tr = grp * p.group_r + (in_grp - tc * rows);
+}
+
+template <int W, int D, bool ROW, bool COL>
+__global__ void __launch_bounds__(32 + W * 32, 1)
 quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ CUtensorMap tm_t, const Params p) {
-    using L = Smem<G, S>;
+    using L = Smem<W, D>;
+    constexpr int S = L::S;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
@@ -88,7 +121,7 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
         *abort_flag = 0;
         for (int s = 0; s < S; ++s) {
             mbar_init(full0 + s * 8, 1);
-            mbar_init(empty0 + s * 8, 4);      // one elected lane of each of the group's four warps
+            mbar_init(empty0 + s * 8, 1);
         }
         fence_mbar_init();
         prefetch_tmap(&tm_in);
@@ -96,88 +129,82 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
     }
     __syncthreads();
 
+    // this CTA's tiles: blockIdx.x, blockIdx.x + gridDim.x, ...; slab n = 4 * (tile ordinal) + quarter
     const int num_tiles = p.tiles_r * p.tiles_c;
-    const int first = blockIdx.x;
-    const int step = gridDim.x;
+    const int my_tiles = (num_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
+    const int my_slabs = my_tiles * 4;
 
     if (tid < 32) {
         // ---------------------------------------------------------------- producer
         if (tid == 0) {
-            int n = 0;
-            for (int t = first; t < num_tiles; t += step, ++n) {
+            for (int n = 0; n < my_slabs; ++n) {
                 const int slot = n % S;
                 const uint32_t ph = (n / S) & 1;
                 if (!mbar_wait(empty0 + slot * 8, ph ^ 1, ab, DEV_TIMEOUT_EMPTY)) break;
-                const int tr = t / p.tiles_c, tc = t - tr * p.tiles_c;
+                const int t = static_cast<int>(blockIdx.x) + (n >> 2) * static_cast<int>(gridDim.x);
+                int tr, tc;
+                tile_coords(t, p, tr, tc);
                 mbar_arrive_expect_tx(full0 + slot * 8, SLOT_BYTES);
-                tma_load_2d(base + L::ring + slot * SLOT_BYTES, &tm_in, tc * TILE, tr * TILE, full0 + slot * 8);
+                tma_load_2d(base + L::ring + slot * SLOT_BYTES, &tm_in, tc * TILE, tr * TILE + (n & 3) * SLAB_ROWS, full0 + slot * 8);
             }
         }
         return;
     }
 
-    // -------------------------------------------------------------------- consumers
-    const int ct = tid - 32;
-    const int g = ct >> 7;             // group
-    const int t128 = ct & 127;         // thread within group
-    const int w = t128 >> 5;           // warp within group
-    const int l = t128 & 31;
-    const uint32_t tstage = base + L::tstage + g * TSTAGE_BYTES;
-    const uint32_t scstage = base + L::scstage + g * SCSTAGE_BYTES;
-    uint8_t* scstage_ptr = base_ptr + L::scstage + g * SCSTAGE_BYTES;
+    // -------------------------------------------------------------------- consumer warp
+    const int w = (tid >> 5) - 1;
+    const int l = tid & 31;
+    const uint32_t tstage = base + L::tstage + w * TSTAGE_BYTES;
+    uint8_t* scstage_ptr = base_ptr + L::scstage + w * SCSTAGE_BYTES;
+    const int hswap = (l >> 2) & 1;     // staging stores: which 16-byte half goes first (bank spreading)
 
-    int n = g;
-    int local = 0;                     // tiles this group has processed (parity of the scale staging)
-    for (int t = first + g * step; t < num_tiles; t += G * step, n += G, ++local) {
+    for (int n = w; n < my_slabs; n += W) {
+        // slab n lives in slot n % S; S is a multiple of W, so a slot is only ever read by one warp
         const int slot = n % S;
         const uint32_t ph = (n / S) & 1;
-        const int tr = t / p.tiles_c, tc = t - tr * p.tiles_c;
         const uint32_t slot_addr = base + L::ring + slot * SLOT_BYTES;
-        const int par = local & 1;
+        const int wq = n & 3;
+        const int t = static_cast<int>(blockIdx.x) + (n >> 2) * static_cast<int>(gridDim.x);
+        int tr, tc;
+        tile_coords(t, p, tr, tc);
         if (!mbar_wait(full0 + slot * 8, ph, ab, DEV_TIMEOUT_FULL)) break;
 
-        if constexpr (ROW) {
-            // lane l: row 4j + l/8 of this warp's 32 rows, 16-element segment l%8; the lane pair
-            // (l, l^1) shares one 32-element block.  The two 16-byte loads are issued in an order
-            // that depends on bit 2 of the lane so a quarter-warp touches all 32 banks.
-            const int seg = l & 7;
-            const int h0 = (l >> 2) & 1;
-            const int kb = seg >> 1;
-            uint8_t* out_base = p.out + (static_cast<size_t>(tr) * TILE + w * 32 + (l >> 3)) * p.N + tc * TILE + seg * 16;
-#pragma unroll 4
-            for (int j = 0; j < 8; ++j) {
-                const int r32 = j * 4 + (l >> 3);
-                const uint32_t a = slot_addr + (w * 32 + r32) * 256 + seg * 32;
-                uint32_t v[8];
-                ld_shared_v4(a + h0 * 16, v[0], v[1], v[2], v[3]);
-                ld_shared_v4(a + (h0 ^ 1) * 16, v[4], v[5], v[6], v[7]);
-                uint32_t m = maxabs_bf16x2(v[0], v[1]);
+        uint32_t c[32][2];                 // c[i] = columns 4l..4l+3 of slab row i
 #pragma unroll
-                for (int q = 2; q < 8; ++q) m = maxabs_bf16x2(m, v[q]);
-                m &= 0x7FFF7FFFu;
-                uint32_t amax = max(m & 0xFFFFu, m >> 16);
-                amax = max(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
-                const int byte = scale_byte(amax, p.round_add, p.min_byte);
-                const float inv = inv_scale(byte);
-                const uint32_t o0 = cvt4(v[0], v[1], inv), o1 = cvt4(v[2], v[3], inv);
-                const uint32_t o2 = cvt4(v[4], v[5], inv), o3 = cvt4(v[6], v[7], inv);
-                uint4 o = h0 ? make_uint4(o2, o3, o0, o1) : make_uint4(o0, o1, o2, o3);
-                *reinterpret_cast<uint4*>(out_base + static_cast<size_t>(j) * 4 * p.N) = o;
-                if ((l & 1) == 0) scstage_ptr[par * 1024 + r32 * 16 + w * 4 + kb] = static_cast<uint8_t>(byte);
-            }
-        }
-
-        uint32_t c[32][2];
-        if constexpr (COL) {
-            // lane l: columns 4l..4l+3 of rows 32w..32w+31
-#pragma unroll
-            for (int i = 0; i < 32; ++i) ld_shared_v2(slot_addr + (w * 32 + i) * 256 + l * 8, c[i][0], c[i][1]);
-        }
+        for (int i = 0; i < 32; ++i) ld_shared_v2(slot_addr + i * 256 + l * 8, c[i][0], c[i][1]);
         __syncwarp();
-        if (l == 0) mbar_arrive(empty0 + slot * 8);     // slot may be refilled
+        if (l == 0) mbar_arrive(empty0 + slot * 8);       // the slot may be refilled now
 
-        int cb[4];
-        float cinv[4];
+        if constexpr (ROW) {
+            uint8_t* out_row = p.out + (static_cast<size_t>(tr) * TILE + wq * SLAB_ROWS) * p.N + tc * TILE + l * 4;
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+                // block amax of rows i and i+1 (one per 16-bit half) over the 8 lanes of a 32-column block
+                const uint32_t m0 = maxabs_bf16x2(c[i][0], c[i][1]);
+                const uint32_t m1 = maxabs_bf16x2(c[i + 1][0], c[i + 1][1]);
+                uint32_t a2 = maxabs_bf16x2(__byte_perm(m0, m1, 0x5410), __byte_perm(m0, m1, 0x7632));
+                a2 = maxabs_bf16x2(a2, __shfl_xor_sync(0xFFFFFFFFu, a2, 1));
+                a2 = maxabs_bf16x2(a2, __shfl_xor_sync(0xFFFFFFFFu, a2, 2));
+                a2 = maxabs_bf16x2(a2, __shfl_xor_sync(0xFFFFFFFFu, a2, 4));
+                const uint32_t b2 = scale_bytes2(a2 & 0x7FFF7FFFu, p);
+                const uint32_t inv2 = inv_scales2(b2);
+                const uint32_t inv_a = __byte_perm(inv2, inv2, 0x1010), inv_b = __byte_perm(inv2, inv2, 0x3232);
+                const uint32_t qa = cvt4(mul_bf16x2(c[i][0], inv_a), mul_bf16x2(c[i][1], inv_a));
+                const uint32_t qb = cvt4(mul_bf16x2(c[i + 1][0], inv_b), mul_bf16x2(c[i + 1][1], inv_b));
+                *reinterpret_cast<uint32_t*>(out_row + static_cast<size_t>(i) * p.N) = qa;
+                *reinterpret_cast<uint32_t*>(out_row + static_cast<size_t>(i + 1) * p.N) = qb;
+                if ((l & 7) == 0) {
+                    scstage_ptr[i * 4 + (l >> 3)] = static_cast<uint8_t>(b2);
+                    scstage_ptr[(i + 1) * 4 + (l >> 3)] = static_cast<uint8_t>(b2 >> 16);
+                }
+            }
+            __syncwarp();
+            // row r of the tile keeps its four scale bytes at (r % 32) * 16 + (r / 32) * 4
+            const uint32_t word = *reinterpret_cast<const uint32_t*>(scstage_ptr + l * 4);
+            *reinterpret_cast<uint32_t*>(p.sc + (static_cast<size_t>(tr) * p.tiles_c + tc) * 512 + l * 16 + wq * 4) = word;
+            __syncwarp();
+        }
+
         if constexpr (COL) {
             uint32_t m0 = maxabs_bf16x2(c[0][0], c[1][0]), m1 = maxabs_bf16x2(c[0][1], c[1][1]);
 #pragma unroll
@@ -185,19 +212,18 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
                 m0 = maxabs_bf16x2(m0, c[i][0]);
                 m1 = maxabs_bf16x2(m1, c[i][1]);
             }
-            cb[0] = scale_byte(m0 & 0x7FFFu, p.round_add, p.min_byte);
-            cb[1] = scale_byte((m0 >> 16) & 0x7FFFu, p.round_add, p.min_byte);
-            cb[2] = scale_byte(m1 & 0x7FFFu, p.round_add, p.min_byte);
-            cb[3] = scale_byte((m1 >> 16) & 0x7FFFu, p.round_add, p.min_byte);
+            const uint32_t b01 = scale_bytes2(m0 & 0x7FFF7FFFu, p), b23 = scale_bytes2(m1 & 0x7FFF7FFFu, p);
+            const uint32_t inv01 = inv_scales2(b01), inv23 = inv_scales2(b23);
 #pragma unroll
-            for (int k = 0; k < 4; ++k) cinv[k] = inv_scale(cb[k]);
-        }
-
-        // the stores of this group's previous tile must have finished reading the staging buffers
-        if (t128 == 0) bulk_wait_read<0>();
-        group_sync(g);
-
-        if constexpr (COL) {
+            for (int i = 0; i < 32; ++i) {
+                c[i][0] = mul_bf16x2(c[i][0], inv01);
+                c[i][1] = mul_bf16x2(c[i][1], inv23);
+            }
+            const int e = tr / p.tiles_rm, trm = tr - e * p.tiles_rm;
+            uint8_t* sct = p.sc_t + ((static_cast<size_t>(e) * p.tiles_c + tc) * p.tiles_rm + trm) * 512 + wq;
+            // the previous slab's tile stores must have finished reading the staging buffer
+            if (l == 0) bulk_wait_read<0>();
+            __syncwarp();
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
                 uint32_t wd[8];
@@ -205,42 +231,42 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
                 for (int q = 0; q < 8; ++q) {
                     float f[4];
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const uint32_t v = c[q * 4 + e][k >> 1];
-                        f[e] = ((k & 1) ? bf16_hi(v) : bf16_lo(v)) * cinv[k];
+                    for (int r = 0; r < 4; ++r) {
+                        const uint32_t v = c[q * 4 + r][k >> 1];
+                        f[r] = (k & 1) ? bf16_hi(v) : bf16_lo(v);
                     }
                     wd[q] = cvt_e4m3x2(f[0], f[1]) | (cvt_e4m3x2(f[2], f[3]) << 16);
                 }
-                // column 4l+k -> staging buffer k, row l; 16-byte chunk index XOR (row & 7)
-                const uint32_t rowa = tstage + k * 4096 + l * 128;
-                st_shared_v4(rowa + (((w * 2 + 0) ^ (l & 7)) << 4), wd[0], wd[1], wd[2], wd[3]);
-                st_shared_v4(rowa + (((w * 2 + 1) ^ (l & 7)) << 4), wd[4], wd[5], wd[6], wd[7]);
+                // column 4l+k -> staging buffer k, 32-byte row l (32 bytes = this slab's 32 rows)
+                const uint32_t rowa = tstage + k * 1024 + l * 32;
+                if (hswap) {
+                    st_shared_v4(rowa + 16, wd[4], wd[5], wd[6], wd[7]);
+                    st_shared_v4(rowa, wd[0], wd[1], wd[2], wd[3]);
+                } else {
+                    st_shared_v4(rowa, wd[0], wd[1], wd[2], wd[3]);
+                    st_shared_v4(rowa + 16, wd[4], wd[5], wd[6], wd[7]);
+                }
                 const int col = 4 * l + k;
-                scstage_ptr[par * 1024 + 512 + (col & 31) * 16 + (col >> 5) * 4 + w] = static_cast<uint8_t>(cb[k]);
+                const uint32_t bk = ((k >> 1) ? b23 : b01) >> ((k & 1) * 16);
+                sct[(col & 31) * 16 + (col >> 5) * 4] = static_cast<uint8_t>(bk);
             }
-        }
-        fence_proxy_async_smem();
-        group_sync(g);
-        if (t128 == 0) {
-            const int e = tr / p.tiles_rm, trm = tr - e * p.tiles_rm;
-            if constexpr (COL) {
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (l == 0) {
 #pragma unroll
-                for (int k = 0; k < 4; ++k) tma_store_4d(&tm_t, trm * TILE, k, tc * 32, e, tstage + k * 4096);
-                bulk_store_1d(p.sc_t + ((static_cast<size_t>(e) * p.tiles_c + tc) * p.tiles_rm + trm) * 512,
-                              scstage + par * 1024 + 512, 512);
+                for (int k = 0; k < 4; ++k)
+                    tma_store_4d(&tm_t, trm * TILE + wq * SLAB_ROWS, k, tc * 32, e, tstage + k * 1024);
+                bulk_commit();
             }
-            if constexpr (ROW)
-                bulk_store_1d(p.sc + (static_cast<size_t>(tr) * p.tiles_c + tc) * 512, scstage + par * 1024, 512);
-            bulk_commit();
         }
     }
-    if (t128 == 0) bulk_wait_all<0>();
+    if (COL && l == 0) bulk_wait_all<0>();
 }
 
-template <int G, int S, bool ROW, bool COL>
+template <int W, int D, bool ROW, bool COL>
 static int launch(const CUtensorMap& tm_in, const CUtensorMap& tm_t, const Params& p, int grid, cudaStream_t stream) {
-    auto kern = quantize_kernel<G, S, ROW, COL>;
-    constexpr int smem = Smem<G, S>::dynamic;
+    auto kern = quantize_kernel<W, D, ROW, COL>;
+    constexpr int smem = Smem<W, D>::dynamic;
     static bool configured[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -252,7 +278,7 @@ static int launch(const CUtensorMap& tm_in, const CUtensorMap& tm_t, const Param
         }
         configured[dev & 63] = true;
     }
-    kern<<<grid, 32 + G * 128, smem, stream>>>(tm_in, tm_t, p);
+    kern<<<grid, 32 + W * 32, smem, stream>>>(tm_in, tm_t, p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
         note_cuda_error("quantize launch", cudaGetErrorString(e));
@@ -287,8 +313,9 @@ extern "C" int mx8_quantize(const void* x_bf16, int E, int M, int N, void* fp8, 
     p.tiles_c = N / 128;
     p.tiles_rm = M / 128;
     p.N = N;
-    p.round_add = scale_mode == MX8_SCALE_RCEIL ? 0x1F : 0;
-    p.min_byte = scale_mode == MX8_SCALE_RCEIL ? 88 : 0;
+    p.group_r = 8;
+    p.round_add2 = scale_mode == MX8_SCALE_RCEIL ? 0x001F001Fu : 0u;
+    p.min_byte8_2 = scale_mode == MX8_SCALE_RCEIL ? 0x00600060u : 0x00080008u;   // (88 + 8), (0 + 8)
     p.status = device_status_ptr();
     if (!p.status) return MX8_ERR_CUDA;
 
@@ -296,17 +323,17 @@ extern "C" int mx8_quantize(const void* x_bf16, int E, int M, int N, void* fp8, 
     {
         const uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(E) * M};
         const uint64_t strides[1] = {static_cast<uint64_t>(N) * 2};
-        const uint32_t box[2] = {128, 128};
+        const uint32_t box[2] = {128, SLAB_ROWS};
         rc = make_tmap(&tm_in, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x_bf16, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
         if (rc != MX8_OK) return rc;
     }
     if (col) {
         // transposed bytes [E][N][M] seen as (M, 4, N/4, E): column c = 4q + k lives at (k, q), so
-        // one store covers the 32 columns a staging buffer holds (k fixed, q = 0..31)
+        // one store covers the 32 columns a staging buffer holds (k fixed, q = 0..31), 32 bytes each
         const uint64_t dims[4] = {static_cast<uint64_t>(M), 4, static_cast<uint64_t>(N) / 4, static_cast<uint64_t>(E)};
         const uint64_t strides[3] = {static_cast<uint64_t>(M), static_cast<uint64_t>(M) * 4, static_cast<uint64_t>(M) * N};
-        const uint32_t box[4] = {128, 1, 32, 1};
-        rc = make_tmap(&tm_t, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, fp8_t, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B,
+        const uint32_t box[4] = {SLAB_ROWS, 1, 32, 1};
+        rc = make_tmap(&tm_t, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, fp8_t, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE,
                        CU_TENSOR_MAP_L2_PROMOTION_NONE);
         if (rc != MX8_OK) return rc;
     } else {
@@ -318,7 +345,10 @@ extern "C" int mx8_quantize(const void* x_bf16, int E, int M, int N, void* fp8, 
     if (grid <= 0) return MX8_ERR_CUDA;
     if (grid > tiles) grid = tiles;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (row && col) return launch<4, 4, true, true>(tm_in, tm_t, p, grid, st);
-    if (row) return launch<4, 4, true, false>(tm_in, tm_t, p, grid, st);
-    return launch<4, 4, false, true>(tm_in, tm_t, p, grid, st);
+    // Both orientations: 8 consumer warps with one slot each measured best (deeper prefetch lowers
+    // throughput once reads and both write streams compete); a single orientation does less
+    // arithmetic per slab and prefers 6 warps with two slots each.
+    if (row && col) return launch<8, 1, true, true>(tm_in, tm_t, p, grid, st);
+    if (row) return launch<6, 2, true, false>(tm_in, tm_t, p, grid, st);
+    return launch<6, 2, false, true>(tm_in, tm_t, p, grid, st);
 }
