@@ -21,6 +21,8 @@
 //
 // M/N tails need no special case: out-of-range TMA loads are zero-filled, out-of-range TMA stores
 // are clipped.  Replaces blackwell/047-mxfp8-mma-2cta-MNK128-polished.cu:12-541 of the reference.
+#include <cstdlib>
+
 #include "mx8_host.cuh"
 #include "mx8_ptx.cuh"
 
@@ -64,6 +66,7 @@ struct Params {
     int tiles_m, tiles_n, k_steps;      // tile grid (tile = 128*CG x 256) and K / 128
     int group_m;                        // rasterisation: tiles_m rows per supergroup
     int c_is_f32;
+    int dbg;                            // tuning experiments: 1 no MMA, 2 no TMA loads, 4 no C stores, 8 no scale traffic
     int* status;
 };
 
@@ -148,11 +151,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     const uint32_t sfb_dst = base + C::sfb_off + stage * C::SFB_BYTES;
                     if constexpr (CG == 2) {
                         const uint32_t bar = full_leader0 + stage * 8;
+                        if (p.dbg & 2) {
+                            if (rank == 0) mbar_arrive(full0 + stage * 8);
+                        } else if (p.dbg & (8 | 32)) {
+                            if (rank == 0) mbar_arrive_expect_tx(full0 + stage * 8, 2 * (C::A_BYTES + C::B_BYTES));
+                            tma_load_2d_pair(a_dst, &tm_a, ks * BK, a_row, bar);
+                            tma_load_2d_pair(b_dst, &tm_b, ks * BK, b_row, bar);
+                        } else {
                         if (rank == 0) mbar_arrive_expect_tx(full0 + stage * 8, 2 * C::STAGE_TX);
                         tma_load_2d_pair(a_dst, &tm_a, ks * BK, a_row, bar);
                         tma_load_2d_pair(b_dst, &tm_b, ks * BK, b_row, bar);
                         tma_load_3d_pair(sfa_dst, &tm_sfa, 0, ks, a_row / 128, bar);
                         tma_load_3d_pair(sfb_dst, &tm_sfb, 0, ks, tn * 2, bar);
+                        }
                     } else {
                         const uint32_t bar = full0 + stage * 8;
                         mbar_arrive_expect_tx(bar, C::STAGE_TX);
@@ -168,10 +179,43 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer (leader CTA only)
         if (lane == 0 && rank == 0) {
-            uint32_t stage = 0, ph = 0, sf_slot = 0;
-            int it = 0;
+            // Everything this loop needs per K step is kept as a running 32-bit value so that the
+            // single issuing thread spends its time on tcgen05 instructions, not on address math.
+            // The scale copies run one K step ahead of the MMAs (two scale slots in TMEM), so an MMA
+            // never waits for the copy issued right before it.
+            const uint32_t a_lo0 = desc_sw128_lo(base + C::a_off), b_lo0 = desc_sw128_lo(base + C::b_off);
+            const uint32_t sfa_lo0 = desc_scales_lo(base + C::sfa_off), sfb_lo0 = desc_scales_lo(base + C::sfb_off);
+            uint32_t a_lo = a_lo0, b_lo = b_lo0;                 // stage the MMAs read
+            uint32_t sfa_lo = sfa_lo0, sfb_lo = sfb_lo0;         // stage the next scale copy reads
+            uint32_t empty_bar = empty0, stage = 0;              // MMA side
+            uint32_t full_bar = full0, cstage = 0, cph = 0;      // copy side (one step ahead)
+            uint32_t sf_mma = tmem_base + SF_COL, sf_cp = tmem_base + SF_COL;
+            constexpr uint32_t ID0 = idesc_mxf8(128 * CG, BN, 0), ID1 = idesc_mxf8(128 * CG, BN, 1);
+            constexpr uint32_t ID2 = idesc_mxf8(128 * CG, BN, 2), ID3 = idesc_mxf8(128 * CG, BN, 3);
+            const bool do_cp = !(p.dbg & (8 | 16)), do_mma = !(p.dbg & 1);
+            const int my_tiles = cluster < num_tiles ? (num_tiles - cluster + num_clusters - 1) / num_clusters : 0;
+            long long remaining = static_cast<long long>(my_tiles) * p.k_steps;   // K steps whose scales are not copied yet
             bool ok = true;
-            for (int t = cluster; t < num_tiles && ok; t += num_clusters, ++it) {
+            // wait for a stage and copy its scale tiles into the next TMEM scale slot
+            auto copy_scales = [&]() -> bool {
+                if (!mbar_wait(full_bar, cph, ab, DEV_TIMEOUT_FULL)) return false;
+                tc_fence_after();
+                if (do_cp) {
+                    tc_cp_scales_lo<CG>(sf_cp, sfa_lo);
+                    tc_cp_scales_lo<CG>(sf_cp + 4, sfb_lo);
+                    tc_cp_scales_lo<CG>(sf_cp + 8, sfb_lo + (512 >> 4));
+                }
+                sf_cp ^= 16;                                     // SF_COL is a multiple of 32: toggles the slot
+                --remaining;
+                if (++cstage == S) {
+                    cstage = 0; cph ^= 1; sfa_lo = sfa_lo0; sfb_lo = sfb_lo0; full_bar = full0;
+                } else {
+                    sfa_lo += C::SFA_BYTES >> 4; sfb_lo += C::SFB_BYTES >> 4; full_bar += 8;
+                }
+                return true;
+            };
+            if (remaining > 0) ok = copy_scales();
+            for (int it = 0; it < my_tiles && ok; ++it) {
                 const uint32_t d_tmem = tmem_base + ((it & 1) ? ACC1_COL : 0);
                 if (it > 0) {
                     // the epilogue has emptied the previous-but-one accumulator and the 32 columns
@@ -180,25 +224,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     tc_fence_after();
                 }
                 for (int ks = 0; ks < p.k_steps; ++ks) {
-                    if (!mbar_wait(full0 + stage * 8, ph, ab, DEV_TIMEOUT_FULL)) { ok = false; break; }
-                    tc_fence_after();
-                    const uint32_t sf_t = tmem_base + SF_COL + sf_slot * 16;
-                    const uint32_t sfa_s = base + C::sfa_off + stage * C::SFA_BYTES;
-                    const uint32_t sfb_s = base + C::sfb_off + stage * C::SFB_BYTES;
-                    tc_cp_scales<CG>(sf_t, smem_desc_scales(sfa_s));
-                    tc_cp_scales<CG>(sf_t + 4, smem_desc_scales(sfb_s));
-                    tc_cp_scales<CG>(sf_t + 8, smem_desc_scales(sfb_s + 512));
-                    const uint64_t adesc = smem_desc_sw128(base + C::a_off + stage * C::A_BYTES);
-                    const uint64_t bdesc = smem_desc_sw128(base + C::b_off + stage * C::B_BYTES);
-#pragma unroll
-                    for (int kk = 0; kk < 4; ++kk) {
-                        // 32 bytes further along K inside the swizzle atom: +2 in the address field
-                        tc_mma_mxf8<CG>(d_tmem, adesc + 2 * kk, bdesc + 2 * kk, idesc_mxf8(128 * CG, BN, kk),
-                                        sf_t, sf_t + 4, (ks | kk) != 0);
+                    if (remaining > 0 && !copy_scales()) { ok = false; break; }
+                    if (do_mma) {
+                        // each K=32 slice lies 32 bytes further inside the swizzle atom: +2 in the address field
+                        tc_mma_mxf8_lo<CG, 2>(d_tmem, a_lo, b_lo, ID0, sf_mma, sf_mma + 4, static_cast<uint32_t>(ks));
+                        tc_mma_mxf8_lo<CG, 1>(d_tmem, a_lo + 2, b_lo + 2, ID1, sf_mma, sf_mma + 4);
+                        tc_mma_mxf8_lo<CG, 1>(d_tmem, a_lo + 4, b_lo + 4, ID2, sf_mma, sf_mma + 4);
+                        tc_mma_mxf8_lo<CG, 1>(d_tmem, a_lo + 6, b_lo + 6, ID3, sf_mma, sf_mma + 4);
                     }
-                    tc_commit<CG>(empty0 + stage * 8);          // stage reusable once these MMAs retire
-                    sf_slot ^= 1;
-                    if (++stage == S) { stage = 0; ph ^= 1; }
+                    tc_commit<CG>(empty_bar);                    // stage reusable once these MMAs retire
+                    sf_mma ^= 16;
+                    if (++stage == S) {
+                        stage = 0; a_lo = a_lo0; b_lo = b_lo0; empty_bar = empty0;
+                    } else {
+                        a_lo += C::A_BYTES >> 4; b_lo += C::B_BYTES >> 4; empty_bar += 8;
+                    }
                 }
                 if (ok) tc_commit<CG>(accfull0 + (it & 1) * 8);  // accumulator complete
             }
@@ -239,7 +279,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                         st_shared_v4(rowa + ((j ^ (lane & 7)) << 4), r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
                     fence_proxy_async_smem();
                     __syncwarp();
-                    if (lane == 0) {
+                    if (lane == 0 && !(p.dbg & 4)) {
                         tma_store_2d(&tm_c, col0 + u * 32, row0, stg);
                         bulk_commit();
                     }
@@ -260,7 +300,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     if (s & 1) {
                         fence_proxy_async_smem();
                         __syncwarp();
-                        if (lane == 0) {
+                        if (lane == 0 && !(p.dbg & 4)) {
                             tma_store_2d(&tm_c, col0 + (u & ~1) * 32, row0, stg);
                             bulk_commit();
                         }
@@ -383,6 +423,8 @@ static int run(const void* A, const void* A_sc, const void* B, const void* B_sc,
     p.k_steps = K / BK;
     p.group_m = 8;
     p.c_is_f32 = c_dtype == MX8_C_F32;
+    { const char* e = getenv("MX8_GEMM_DEBUG"); p.dbg = e ? atoi(e) : 0; }
+    { const char* e = getenv("MX8_GEMM_GROUP"); if (e) p.group_m = atoi(e); }
     p.status = device_status_ptr();
     if (!p.status) return MX8_ERR_CUDA;
     int grid = max_grid<CG>();

@@ -231,7 +231,42 @@ __host__ __device__ constexpr uint32_t idesc_mxf8(int M, int N, int sf_id) {
          | (static_cast<uint32_t>(sf_id) << 29);    // A scale byte within the TMEM word
 }
 
+// The same descriptors split into 32-bit halves: the high word is a constant, the low word carries
+// the address field, so advancing to another stage or K offset is one 32-bit add.
+constexpr uint32_t DESC_SW128_HI = (1024u >> 4) | (1u << 14) | (2u << 29);
+constexpr uint32_t DESC_SCALES_HI = (128u >> 4) | (1u << 14);
+__device__ __forceinline__ uint32_t desc_sw128_lo(uint32_t addr) { return (addr >> 4) | (1u << 16); }
+__device__ __forceinline__ uint32_t desc_scales_lo(uint32_t addr) { return (addr >> 4) | ((128u >> 4) << 16); }
+
 // ------------------------------------------------------------------ tcgen05: copy, MMA, commit, load
+template <int CG>
+__device__ __forceinline__ void tc_cp_scales_lo(uint32_t taddr, uint32_t desc_lo) {
+    if constexpr (CG == 2)
+        asm volatile("{\n\t.reg .b64 d;\n\tmov.b64 d, {%1, %2};\n\ttcgen05.cp.cta_group::2.32x128b.warpx4 [%0], d;\n\t}"
+                     ::"r"(taddr), "r"(desc_lo), "n"(DESC_SCALES_HI) : "memory");
+    else
+        asm volatile("{\n\t.reg .b64 d;\n\tmov.b64 d, {%1, %2};\n\ttcgen05.cp.cta_group::1.32x128b.warpx4 [%0], d;\n\t}"
+                     ::"r"(taddr), "r"(desc_lo), "n"(DESC_SCALES_HI) : "memory");
+}
+// ACC: 0 = overwrite the accumulator, 1 = accumulate, 2 = decide at run time from `acc`
+template <int CG, int ACC>
+__device__ __forceinline__ void tc_mma_mxf8_lo(uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
+                                               uint32_t sfa, uint32_t sfb, uint32_t acc = 1) {
+    if constexpr (CG == 2)
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+            "mov.b64 da, {%1, %7};\n\tmov.b64 db, {%2, %7};\n\tsetp.ne.u32 p, %6, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], da, db, %3, [%4], [%5], p;\n\t}"
+            ::"r"(d), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(sfa), "r"(sfb), "r"(ACC == 2 ? acc : static_cast<uint32_t>(ACC)), "n"(DESC_SW128_HI)
+            : "memory");
+    else
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+            "mov.b64 da, {%1, %7};\n\tmov.b64 db, {%2, %7};\n\tsetp.ne.u32 p, %6, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], da, db, %3, [%4], [%5], p;\n\t}"
+            ::"r"(d), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(sfa), "r"(sfb), "r"(ACC == 2 ? acc : static_cast<uint32_t>(ACC)), "n"(DESC_SW128_HI)
+            : "memory");
+}
 template <int CG>
 __device__ __forceinline__ void tc_cp_scales(uint32_t taddr, uint64_t sdesc) {
     if constexpr (CG == 2) asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
