@@ -54,5 +54,34 @@ def build(force=False, verbose=False):
     return LIB
 
 
+def torch_binding_path():
+    import sysconfig
+    return os.path.join(OUT_DIR, "_C" + sysconfig.get_config_var("EXT_SUFFIX"))
+
+
+def build_torch_binding(force=False, verbose=False):
+    """Compile csrc/torch_binding.cpp into the pybind11/torch module mx8/_C (links libmx8.so)."""
+    import sysconfig
+
+    from torch.utils import cpp_extension as ce
+    build(force=False, verbose=verbose)
+    src = os.path.join(CSRC, "torch_binding.cpp")
+    out = torch_binding_path()
+    if not (force or _stale(out, [src, os.path.join(HERE, "..", "include", "mx8.h"), LIB])):
+        return out
+    inc = ce.include_paths() + [sysconfig.get_paths()["include"], "/usr/local/cuda/include"]
+    libdirs = ce.library_paths()
+    cmd = (["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-DTORCH_EXTENSION_NAME=_C", "-DTORCH_API_INCLUDE_EXTENSION_H",
+            src, "-o", out] + ["-I" + i for i in inc] + ["-L" + d for d in libdirs]
+           + ["-L" + OUT_DIR, "-lmx8", "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch", "-ltorch_python", "-Wl,-rpath,$ORIGIN"]
+           + ["-Wl,-rpath," + d for d in libdirs])
+    if verbose:
+        print(" ".join(cmd))
+    subprocess.check_call(cmd)
+    return out
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    if "--torch" in sys.argv:
+        print(build_torch_binding(force="--force" in sys.argv, verbose="-v" in sys.argv))

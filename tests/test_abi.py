@@ -71,3 +71,21 @@ def test_no_device_means_error_not_fallback(lib):
     assert rc in (_lib.ERR_CUDA, _lib.ERR_UNSUPPORTED)
     with pytest.raises(ValueError):
         mx8.mxfp8_quantize(torch.zeros(128, 128, dtype=torch.bfloat16), True, False)   # CPU tensor rejected
+
+
+def test_torch_module_mirrors_reference_bindings(lib):
+    """mx8._C is the pybind11/torch module with the reference's function names."""
+    import importlib.util
+    import torch
+    spec = importlib.util.spec_from_file_location("mx8_build", os.path.join(ROOT, "gpu-experiments_b200", "build.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    if not os.path.exists(mod.torch_binding_path()):
+        mod.build_torch_binding()
+    from mx8 import _C
+    for name in ("mxfp8_quantize", "kernel", "kernel_transpose", "device_status", "version"):
+        assert hasattr(_C, name)
+    assert _C.version().startswith("mx8")
+    x = torch.zeros(128, 128, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError):
+        _C.mxfp8_quantize(x, True, False)          # CPU tensor: rejected, never computed on the host

@@ -1,0 +1,77 @@
+"""The pybind11/torch module mx8._C, called the way the reference's harnesses call their `_C`."""
+import pytest
+import torch
+
+from oracle import mx8_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def C():
+    from mx8 import _C
+    return _C
+
+
+def test_quantize_harness_flow(C):
+    # follows the reference harness: preallocated outputs, three modes, exact byte equality
+    M, N = 512, 384
+    x_cpu = O.make_input(M, N, seed=1234, outliers=True, zero_blocks=True)
+    x = x_cpu.to(DEV)
+    x_fp8 = torch.zeros(M, N, dtype=torch.float8_e4m3fn, device=DEV)
+    x_sc = torch.zeros(M // 128, N // 128, 32, 16, dtype=torch.uint8, device=DEV)
+    x_fp8_t = torch.zeros(N, M, dtype=torch.float8_e4m3fn, device=DEV)
+    x_sc_t = torch.zeros(N // 128, M // 128, 32, 16, dtype=torch.uint8, device=DEV)
+    want = O.quantize_both(x_cpu)
+    for rn, rt in ((True, False), (False, True), (True, True)):
+        for t in (x_fp8, x_sc, x_fp8_t, x_sc_t):
+            t.view(torch.uint8).zero_()
+        C.mxfp8_quantize(x, x_fp8, x_sc, x_fp8_t, x_sc_t, rn, rt)
+        assert C.device_status() == 0
+        errors = 0
+        if rn:
+            errors += int((x_fp8.view(torch.uint8).cpu() != want[0]).sum()) + int((x_sc.cpu() != want[1]).sum())
+        if rt:
+            errors += int((x_fp8_t.view(torch.uint8).cpu() != want[2]).sum()) + int((x_sc_t.cpu() != want[3]).sum())
+        assert errors == 0
+
+
+def test_allocating_form_and_3d(C):
+    x_cpu = torch.stack([O.make_input(256, 384, seed=s) for s in range(2)])
+    q, sc, qt, sct = C.mxfp8_quantize(x_cpu.to(DEV), True, True)
+    want = O.quantize_both(x_cpu)
+    for got, w in zip((q, sc, qt, sct), want):
+        assert torch.equal(got.view(torch.uint8).cpu(), w)
+    q, sc, qt, sct = C.mxfp8_quantize(x_cpu[0].to(DEV), True, False)
+    assert qt is None and sct is None and q.shape == (256, 384)
+
+
+def test_gemm_and_legacy_names(C):
+    M, N, K = 256, 384, 512
+    a = O.make_input(M, K, seed=1, std=K ** -0.25)
+    b = O.make_input(N, K, seed=2, std=K ** -0.25)
+    # legacy quantize bindings: kernel(A, A_fp8, A_sc) with A_sc [M/128, K/128, 512], kernel_transpose
+    a_fp8 = torch.empty(M, K, dtype=torch.float8_e4m3fn, device=DEV)
+    a_sc = torch.empty(M // 128, K // 128, 512, dtype=torch.uint8, device=DEV)
+    C.kernel(a.to(DEV), a_fp8, a_sc)
+    b_fp8, b_sc, _, _ = C.mxfp8_quantize(b.to(DEV), True, False)
+    at_fp8 = torch.empty(K, M, dtype=torch.float8_e4m3fn, device=DEV)
+    at_sc = torch.empty(K // 128, M // 128, 512, dtype=torch.uint8, device=DEV)
+    C.kernel_transpose(a.to(DEV), at_fp8, at_sc)
+    want = O.quantize_both(a)
+    assert torch.equal(a_fp8.view(torch.uint8).cpu(), want[0]) and torch.equal(a_sc.cpu().view(-1), want[1].view(-1))
+    assert torch.equal(at_fp8.view(torch.uint8).cpu(), want[2]) and torch.equal(at_sc.cpu().view(-1), want[3].view(-1))
+    ref = O.gemm_ref(want[0], want[1], *O.quantize_tiled(b))
+    for dtype in (torch.bfloat16, torch.float32):
+        c = torch.zeros(M, N, dtype=dtype, device=DEV)
+        C.kernel(a_fp8, a_sc, b_fp8, b_sc, c)
+        assert C.device_status() == 0
+        assert O.rel_frobenius(c.cpu(), ref) < 1e-2      # benchmark tolerance; observed ~1e-5
+        assert O.rel_frobenius(c.cpu(), ref) < 2e-3
+
+
+def test_errors_raise_runtime_error(C):
+    x = torch.zeros(100, 128, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(RuntimeError):
+        C.mxfp8_quantize(x, True, False)
