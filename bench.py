@@ -312,12 +312,18 @@ def bench_quantize(args, world, rank, local, peaks, with_cpu):
     return line
 
 
+def gemm_shard_rows(world):
+    """(total M, rows per rank): rows of A and C are split evenly across ranks, B is replicated."""
+    rows = max(128, (GM // world // 128) * 128)
+    return rows * world, rows
+
+
 def bench_gemm(args, world, rank, local, peaks, with_cpu):
     import mx8
     from oracle import mx8_oracle as O   # input generator only
     dev = torch.device("cuda", local)
-    M, N, K = GM // world, GN, GK         # rows of A and C split across ranks, B replicated
-    M = max(128, (M // 128) * 128)
+    _, M = gemm_shard_rows(world)
+    N, K = GN, GK
     sets = []
     for s in range(3):                    # rotate operand sets so no iteration finds its inputs in L2
         a = O.make_input(M, K, seed=100 + 10 * s + rank, std=K ** -0.5).to(dev)
