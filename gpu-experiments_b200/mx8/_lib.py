@@ -16,6 +16,7 @@ SIGNATURES = {
     "mx8_quantize": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp]),
     "mx8_gemm": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "mx8_gemm_ex": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
+    "mx8_moe_schedule": (_i, [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "mx8_device_status": (_i, [ctypes.POINTER(_i), _vp]),
     "mx8_strerror": (ctypes.c_char_p, [_i]),
     "mx8_last_cuda_error": (ctypes.c_char_p, []),

@@ -134,3 +134,28 @@ def device_status():
     if rc != _lib.OK:
         raise Mx8Error(rc, f"device_status (device word = {v.value})")
     return v.value
+
+
+def schedule(topk_all, num_local_experts, schedule_capacity, rank):
+    """schedule(topk_all, num_local_experts, schedule_capacity, rank)
+        -> (schedule_peer_rank, schedule_peer_token_idx, num_tokens, tokens_per_expert)
+
+    topk_all int32 [world, tokens, topk] on the device.  Outputs are int32 CUDA tensors, allocated
+    here like the reference does (blackwell-ultra/022-moe-dispatch-mlp-swiglu-combine-mxfp8-bw.cu:149-183,
+    bound at :2996-2997)."""
+    lib = _lib.load()
+    tp = _chk(topk_all, "topk_all", (torch.int32,))
+    if topk_all.dim() != 3:
+        raise ValueError("topk_all must be [world, tokens, topk]")
+    W, T, k = topk_all.shape
+    dev = topk_all.device
+    peer_rank = torch.empty(schedule_capacity, dtype=torch.int32, device=dev)
+    peer_tok = torch.empty(schedule_capacity, dtype=torch.int32, device=dev)
+    num_tokens = torch.empty(1, dtype=torch.int32, device=dev)
+    tpe = torch.empty(num_local_experts, dtype=torch.int32, device=dev)
+    scratch = torch.empty(num_local_experts * (W + 1), dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(lib.mx8_moe_schedule(tp, W, T, k, num_local_experts, schedule_capacity, rank, peer_rank.data_ptr(),
+                                        peer_tok.data_ptr(), num_tokens.data_ptr(), tpe.data_ptr(), scratch.data_ptr(),
+                                        _stream()), "schedule")
+    return peer_rank, peer_tok, num_tokens, tpe

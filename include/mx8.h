@@ -80,6 +80,19 @@ MX8_API int mx8_gemm(const void* A, const void* A_sc, const void* B, const void*
 MX8_API int mx8_gemm_ex(const void* A, const void* A_sc, const void* B, const void* B_sc, void* C,
                 int M, int N, int K, int c_dtype, int cta_group, int max_ctas, void* stream);
 
+/* Expert-parallel MoE routing schedule for the calling rank (int32 everywhere).
+ *   topk_all [world][tokens][topk]: global expert ids chosen by every rank's tokens;
+ *   this rank owns experts [rank*num_local_experts, (rank+1)*num_local_experts).
+ * Outputs: peer_rank[capacity] (source rank per row, -1 = padding/unused), peer_token_idx[capacity]
+ * (token*topk + k on the source rank), num_tokens[1] (rows used, every expert padded to 256),
+ * tokens_per_expert[num_local_experts] (padded).  `scratch` is num_local_experts*(world+1) ints of
+ * device memory, overwritten.  capacity is a multiple of 256; a schedule that does not fit sets the
+ * device status word (mx8_device_status) instead of trapping.
+ * Replaces scheduler::schedule, blackwell-ultra/022-moe-dispatch-mlp-swiglu-combine-mxfp8-bw.cu:149-183. */
+MX8_API int mx8_moe_schedule(const void* topk_all, int world, int tokens, int topk, int num_local_experts,
+                             int capacity, int rank, void* peer_rank, void* peer_token_idx, void* num_tokens,
+                             void* tokens_per_expert, void* scratch, void* stream);
+
 /* Synchronizes `stream`, then reads and clears the current device's status word: 0 = healthy,
  * otherwise the code of the first bounded wait that expired (see csrc/mx8_ptx.cuh).
  * Returns MX8_OK, MX8_ERR_DEVICE_TIMEOUT (status != 0) or MX8_ERR_CUDA. */

@@ -1,0 +1,136 @@
+"""CPU oracle for the expert-parallel MoE layer built on the MXFP8 path.  TEST INFRASTRUCTURE ONLY
+(same rules as mx8_oracle.py: imported by tests, the smoke check and the benchmark's CPU leg only).
+
+Parity status: the quantize and GEMM pieces are pinned through mx8_oracle.py; the routing schedule
+and the layer composition are restatements of reference code that only runs on a multi-GPU box
+("parity unpinned" for those two: no reference output could be generated here).  They follow
+
+* schedule ............ blackwell-ultra/022-moe-dispatch-mlp-swiglu-combine-mxfp8-bw.cu:34-147
+* routed forward ...... blackwell-ultra/022-moe-dispatch-mlp-swiglu-combine-mxfp8-bw.py:91-126
+* dispatch / combine .. blackwell-ultra/022-moe-dispatch-mlp-swiglu-combine-mxfp8-bw.py:386-411
+* forward epilogue .... blackwell-ultra/022-moe-dispatch-mlp-swiglu-combine-mxfp8-bw.cu:2789-2840
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from . import mx8_oracle as O
+
+PAD = 256
+
+
+def schedule_ref(topk_all: torch.Tensor, num_local_experts: int, capacity: int, rank: int):
+    """topk_all int32 [W, T, k] -> (peer_rank[capacity], peer_token_idx[capacity], num_tokens[1],
+    tokens_per_expert[E]).  Rows of an expert: round j takes the j-th routed pair (token*k + kk order)
+    of every source rank that still has one, ranks ascending; segments padded to 256 rows."""
+    W, T, k = topk_all.shape
+    flat = topk_all.reshape(W, T * k).numpy()
+    peer_rank = np.full(capacity, -1, np.int32)
+    peer_tok = np.zeros(capacity, np.int32)
+    tpe = np.zeros(num_local_experts, np.int32)
+    base = 0
+    written = np.zeros(capacity, bool)
+    for e in range(num_local_experts):
+        g = rank * num_local_experts + e
+        lists = [np.nonzero(flat[r] == g)[0] for r in range(W)]
+        n = sum(len(x) for x in lists)
+        row = base
+        for j in range(max((len(x) for x in lists), default=0)):
+            for r in range(W):
+                if j < len(lists[r]):
+                    if row < capacity:
+                        peer_rank[row] = r
+                        peer_tok[row] = lists[r][j]
+                        written[row] = True
+                    row += 1
+        tpe[e] = (n + PAD - 1) // PAD * PAD
+        base += int(tpe[e])
+    return (torch.from_numpy(peer_rank), torch.from_numpy(peer_tok), torch.tensor([base], dtype=torch.int32),
+            torch.from_numpy(tpe), torch.from_numpy(written))
+
+
+def route(logits: torch.Tensor, k: int):
+    """The reference's router: top-k of the logits, softmax over the selected k values
+    (blackwell-ultra/022-…-mxfp8-bw.py:270-272)."""
+    vals, ids = torch.topk(logits, k, dim=1)
+    return ids.to(torch.int32), torch.softmax(vals.float(), dim=-1)
+
+
+def dispatch_ref(x_all: torch.Tensor, peer_rank, peer_tok, num_tokens: int, k: int) -> torch.Tensor:
+    """x_all bf16 [W, T, H] -> x_routed bf16 [num_tokens, H]; padding rows are zero."""
+    H = x_all.shape[-1]
+    out = torch.zeros(num_tokens, H, dtype=torch.bfloat16)
+    pr = peer_rank[:num_tokens].long()
+    valid = pr >= 0
+    out[valid] = x_all[pr[valid], (peer_tok[:num_tokens].long()[valid]) // k]
+    return out
+
+
+def swiglu_ref(gate_q, gate_sc_tiles, up_q, up_sc_tiles) -> torch.Tensor:
+    """hidden = bf16( silu(dequant(gate)) * dequant(up) ), fp32 arithmetic; the dequantized values
+    pass through bf16 first, as in the reference's `dequant` (…-mxfp8-bw.py:68-72, 120-122)."""
+    g = O.dequantize(gate_q, O.scale_unswizzle(gate_sc_tiles)).to(torch.bfloat16).float()
+    u = O.dequantize(up_q, O.scale_unswizzle(up_sc_tiles)).to(torch.bfloat16).float()
+    return ((g / (1.0 + torch.exp(-g))) * u).to(torch.bfloat16)
+
+
+def expert_mlp_ref(x_routed, tokens_per_expert, wg, wu, wd):
+    """Routed-expert forward on already dispatched rows.  wg/wu: (fp8 [E, I, H], scale tiles
+    [E*I/128, H/128, 512]); wd: (fp8 [E, H, I], scale tiles [E*H/128, I/128, 512]).
+    Returns a dict of every intermediate the CUDA path emits."""
+    (wg_q, wg_sc), (wu_q, wu_sc), (wd_q, wd_sc) = wg, wu, wd
+    E, I, H = wg_q.shape
+    R = x_routed.shape[0]
+    xq, xsc, xqt, xsct = O.quantize_both(x_routed)
+    gate_q = torch.zeros(R, I, dtype=torch.uint8)
+    up_q = torch.zeros(R, I, dtype=torch.uint8)
+    gate_sc = torch.zeros(R // 128, I // 128, 32, 16, dtype=torch.uint8)
+    up_sc = torch.zeros_like(gate_sc)
+    hidden = torch.zeros(R, I, dtype=torch.bfloat16)
+    y = torch.zeros(R, H, dtype=torch.bfloat16)
+    off = 0
+    for e, n in enumerate(tokens_per_expert.tolist()):
+        if n == 0:
+            continue
+        rows = slice(off, off + n)
+        tiles = slice(off // 128, (off + n) // 128)
+        g = O.gemm_ref(xq[rows], xsc[tiles], wg_q[e], wg_sc[e * I // 128:(e + 1) * I // 128])
+        u = O.gemm_ref(xq[rows], xsc[tiles], wu_q[e], wu_sc[e * I // 128:(e + 1) * I // 128])
+        gate_q[rows], gate_sc[tiles] = O.quantize_tiled(g)
+        up_q[rows], up_sc[tiles] = O.quantize_tiled(u)
+        hidden[rows] = swiglu_ref(gate_q[rows], gate_sc[tiles], up_q[rows], up_sc[tiles])
+        off += n
+    hq, hsc, hqt, hsct = O.quantize_both(hidden)
+    off = 0
+    for e, n in enumerate(tokens_per_expert.tolist()):
+        if n == 0:
+            continue
+        rows = slice(off, off + n)
+        tiles = slice(off // 128, (off + n) // 128)
+        y[rows] = O.gemm_ref(hq[rows], hsc[tiles], wd_q[e], wd_sc[e * H // 128:(e + 1) * H // 128])
+        off += n
+    return dict(x_fp8=xq, x_sc=xsc, x_fp8_t=xqt, x_sc_t=xsct, gate_fp8=gate_q, gate_sc=gate_sc, up_fp8=up_q, up_sc=up_sc,
+                hidden=hidden, hidden_fp8=hq, hidden_sc=hsc, hidden_fp8_t=hqt, hidden_sc_t=hsct, y=y)
+
+
+def combine_ref(y_routed_by_rank, peer_rank_by_rank, peer_tok_by_rank, owner: int, T: int, k: int) -> torch.Tensor:
+    """combine_buffer [T*k, H] of rank `owner`: row peer_token_idx receives the expert output row."""
+    H = y_routed_by_rank[0].shape[-1]
+    buf = torch.zeros(T * k, H, dtype=torch.bfloat16)
+    for dst in range(len(y_routed_by_rank)):
+        n = y_routed_by_rank[dst].shape[0]
+        sel = peer_rank_by_rank[dst][:n] == owner
+        buf[peer_tok_by_rank[dst][:n][sel].long()] = y_routed_by_rank[dst][sel]
+    return buf
+
+
+def fwd_epilogue_ref(y_shared, combine_buffer, topk_weights) -> torch.Tensor:
+    """out[t] = bf16( y_shared[t] + sum_j w[t, j] * combine[t*k + j] ), fp32, products and sums
+    rounded separately, j ascending."""
+    T, k = topk_weights.shape
+    acc = y_shared.float().clone()
+    cb = combine_buffer.float().view(T, k, -1)
+    for j in range(k):
+        acc = acc + cb[:, j] * topk_weights[:, j:j + 1].float()
+    return acc.to(torch.bfloat16)
