@@ -167,3 +167,57 @@ extern "C" int mx8_moe_schedule(const void* topk_all, int world, int tokens, int
     if (!p.status) return MX8_ERR_CUDA;
     return moe::run_schedule(p, static_cast<cudaStream_t>(stream));
 }
+
+// ---------------------------------------------------------------------------------------------
+// Variant of the schedule that needs no scratch buffer from the caller.
+//
+// Some hosts of this library cannot hand over scratch memory: a serving loop whose memory plan is
+// frozen after start-up, or a plugin that runs inside someone else's allocator and may not call
+// cudaMalloc (which synchronizes the device) on the request path.  For them the counting scratch
+// lives in this fixed array, which every device that loads the library keeps until the process
+// exits (64 KiB).  The kernels clear the part they use at the start of every call; the contents
+// left behind by the previous call are never read.  All calls on a device share the array, so two
+// calls that overlap on the GPU (different streams, no ordering between them) race.
+namespace mx8 {
+namespace moe {
+
+constexpr int STATIC_SCRATCH_INTS = 16384;     // limit: num_local_experts * (world + 1) <= 16384
+static __device__ __align__(256) int g_schedule_scratch[STATIC_SCRATCH_INTS];
+
+// Device address of the array on the current device.  In host code the array's name is only a
+// handle for the runtime, not an address a kernel can use, so it is resolved once per device.
+static int* static_scratch_ptr() {
+    static int* cached[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (!cached[dev]) {
+        int* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_schedule_scratch);
+        if (e != cudaSuccess) {
+            note_cuda_error("cudaGetSymbolAddress(schedule scratch)", cudaGetErrorString(e));
+            return nullptr;
+        }
+        cached[dev] = p;
+    }
+    return cached[dev];
+}
+
+}  // namespace moe
+}  // namespace mx8
+
+extern "C" int mx8_moe_schedule_static(const void* topk_all, int world, int tokens, int topk, int num_local_experts,
+                                       int capacity, int rank, void* peer_rank, void* peer_token_idx, void* num_tokens,
+                                       void* tokens_per_expert, void* stream) {
+    using namespace mx8;
+    if (world <= 0 || num_local_experts <= 0) return MX8_ERR_ARG;
+    if (static_cast<long long>(num_local_experts) * (static_cast<long long>(world) + 1) > moe::STATIC_SCRATCH_INTS) {
+        note_cuda_error("mx8_moe_schedule_static", "num_local_experts * (world + 1) exceeds the built-in scratch of 16384 ints");
+        return MX8_ERR_LIMIT;
+    }
+    int rc = check_device_sm100();
+    if (rc != MX8_OK) return rc;
+    int* scratch = moe::static_scratch_ptr();     // first call on a device resolves the address
+    if (!scratch) return MX8_ERR_CUDA;
+    return mx8_moe_schedule(topk_all, world, tokens, topk, num_local_experts, capacity, rank, peer_rank, peer_token_idx,
+                            num_tokens, tokens_per_expert, scratch, stream);
+}

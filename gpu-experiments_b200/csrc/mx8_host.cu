@@ -138,6 +138,7 @@ const char* mx8_strerror(int code) {
         case MX8_ERR_CUDA: return "CUDA call failed (see mx8_last_cuda_error)";
         case MX8_ERR_UNSUPPORTED: return "current device is not compute capability 10.x (sm_100a required)";
         case MX8_ERR_DEVICE_TIMEOUT: return "a bounded wait inside a kernel expired (see mx8_device_status)";
+        case MX8_ERR_LIMIT: return "problem exceeds a built-in size limit (see mx8_last_cuda_error)";
         default: return "unknown mx8 status code";
     }
 }

@@ -6,7 +6,7 @@ import os
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libmx8.so")
 
-OK, ERR_ARG, ERR_SHAPE, ERR_ALIGN, ERR_CUDA, ERR_UNSUPPORTED, ERR_DEVICE_TIMEOUT = range(7)
+OK, ERR_ARG, ERR_SHAPE, ERR_ALIGN, ERR_CUDA, ERR_UNSUPPORTED, ERR_DEVICE_TIMEOUT, ERR_LIMIT = range(8)
 SCALE_RCEIL, SCALE_FLOOR = 0, 1
 C_BF16, C_F32 = 0, 1
 
@@ -17,6 +17,7 @@ SIGNATURES = {
     "mx8_gemm": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "mx8_gemm_ex": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "mx8_moe_schedule": (_i, [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "mx8_moe_schedule_static": (_i, [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "mx8_device_status": (_i, [ctypes.POINTER(_i), _vp]),
     "mx8_strerror": (ctypes.c_char_p, [_i]),
     "mx8_last_cuda_error": (ctypes.c_char_p, []),
@@ -31,7 +32,7 @@ class Mx8Error(RuntimeError):
         self.code = code
         lib = load()
         msg = lib.mx8_strerror(code).decode()
-        detail = lib.mx8_last_cuda_error().decode() if code == ERR_CUDA else ""
+        detail = lib.mx8_last_cuda_error().decode() if code in (ERR_CUDA, ERR_LIMIT) else ""
         super().__init__(f"{where}: mx8 status {code}: {msg}" + (f" [{detail}]" if detail else ""))
 
 

@@ -37,7 +37,8 @@ enum {
     MX8_ERR_ALIGN = 3,          /* a pointer is not 16-byte aligned                         */
     MX8_ERR_CUDA = 4,           /* a CUDA runtime / driver call failed (mx8_last_cuda_error) */
     MX8_ERR_UNSUPPORTED = 5,    /* device is not compute capability 10.x                    */
-    MX8_ERR_DEVICE_TIMEOUT = 6  /* a kernel's bounded wait expired (mx8_device_status)      */
+    MX8_ERR_DEVICE_TIMEOUT = 6, /* a kernel's bounded wait expired (mx8_device_status)      */
+    MX8_ERR_LIMIT = 7           /* problem exceeds a built-in size limit (mx8_last_cuda_error has the text) */
 };
 
 /* scale rounding */
@@ -92,6 +93,18 @@ MX8_API int mx8_gemm_ex(const void* A, const void* A_sc, const void* B, const vo
 MX8_API int mx8_moe_schedule(const void* topk_all, int world, int tokens, int topk, int num_local_experts,
                              int capacity, int rank, void* peer_rank, void* peer_token_idx, void* num_tokens,
                              void* tokens_per_expert, void* scratch, void* stream);
+
+/* Same schedule, same outputs, for callers that cannot provide scratch memory.  It has no counterpart
+ * in the reference.  Hosts whose memory plan is fixed after start-up, or that run under a foreign
+ * allocator and must not call cudaMalloc on the request path, use this form: the counting scratch is
+ * a fixed 64 KiB array inside the library (one copy per device, held until the process exits), and
+ * the call allocates nothing.  Limit: num_local_experts * (world + 1) <= 16384, otherwise
+ * MX8_ERR_LIMIT.  The first call on a device looks the array's address up; make that call before
+ * starting any stream capture.  Every call on a device uses the same array (cleared at the start of
+ * each call), so calls that can overlap on the GPU must be ordered by the caller. */
+MX8_API int mx8_moe_schedule_static(const void* topk_all, int world, int tokens, int topk, int num_local_experts,
+                                    int capacity, int rank, void* peer_rank, void* peer_token_idx, void* num_tokens,
+                                    void* tokens_per_expert, void* stream);
 
 /* Synchronizes `stream`, then reads and clears the current device's status word: 0 = healthy,
  * otherwise the code of the first bounded wait that expired (see csrc/mx8_ptx.cuh).
