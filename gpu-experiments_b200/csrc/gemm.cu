@@ -25,6 +25,7 @@
 
 #include "mx8_host.cuh"
 #include "mx8_ptx.cuh"
+#include "mx8_qmath.cuh"
 
 namespace mx8 {
 namespace gemm {
@@ -34,6 +35,7 @@ constexpr int BN = 256;                 // tile columns
 constexpr int ACC1_COL = 224;           // first column of accumulator 1
 constexpr int SF_COL = 480;             // first scale column; slot s at SF_COL + 16 s: A +0, B +4 and +8
 constexpr int EPI_WARPS = 4;
+constexpr int MAX_GROUPS = 256;          // experts per launch of the grouped form
 constexpr int THREADS = 32 * (2 + EPI_WARPS);
 
 template <int CG>
@@ -57,7 +59,8 @@ struct Cfg {
     static constexpr int n_bars = 2 * STAGES + 3;
     static constexpr int tmem_ptr_off = bar_off + n_bars * 8;
     static constexpr int flag_off = tmem_ptr_off + 8;
-    static constexpr int total = flag_off + 8;
+    static constexpr int seg_off = flag_off + 8;               // end row of every group's segment (grouped GEMM)
+    static constexpr int total = seg_off + MAX_GROUPS * 4;
     static constexpr int dynamic = total + 1024;
     static_assert(dynamic <= 232448, "shared memory budget exceeded");
 };
@@ -65,18 +68,25 @@ struct Cfg {
 struct Params {
     int tiles_m, tiles_n, k_steps;      // tile grid (tile = 128*CG x 256) and K / 128
     int group_m;                        // rasterisation: tiles_m rows per supergroup
-    int c_is_f32;
+    int c_mode;                         // 0 bf16, 1 f32, 2 MXFP8 (E4M3 bytes + scale tiles, blocks along N)
+    uint8_t* c_sc;                      // scale tiles of C for c_mode 2
+    int n_cols;                         // N
+    int rows_cap;                       // M (rows the C tensors have)
+    const int* rows_dev;                // device: rows actually present (nullptr: all tiles_m tiles)
+    const int* group_rows;              // device: rows of every group (multiples of the tile height), nullptr = dense
+    int num_groups;
+    int group_b_rows;                   // rows of B per group (N)
     int dbg;                            // tuning experiments: 1 no MMA, 2 no TMA loads, 4 no C stores, 8 no scale traffic
     int* status;
 };
 
 // persistent tile order: supergroups of `group_m` tile rows, column-major inside a supergroup so
 // that CTAs running at the same time share A row panels and B column panels in L2
-__device__ __forceinline__ void tile_coords(int t, const Params& p, int& tm, int& tn) {
+__device__ __forceinline__ void tile_coords(int t, const Params& p, int tiles_m, int& tm, int& tn) {
     const int per_group = p.group_m * p.tiles_n;
     const int grp = t / per_group;
     const int in_grp = t - grp * per_group;
-    const int rows = min(p.group_m, p.tiles_m - grp * p.group_m);
+    const int rows = min(p.group_m, tiles_m - grp * p.group_m);
     tm = grp * p.group_m + in_grp % rows;
     tn = in_grp / rows;
 }
@@ -104,7 +114,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     const uint32_t rank = CG == 2 ? cluster_ctarank() : 0;
     const int cluster = CG == 2 ? static_cast<int>(cluster_id_x()) : static_cast<int>(blockIdx.x);
     const int num_clusters = CG == 2 ? static_cast<int>(num_clusters_x()) : static_cast<int>(gridDim.x);
-    const int num_tiles = p.tiles_m * p.tiles_n;
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
@@ -131,6 +140,24 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     if constexpr (CG == 2) cluster_sync_all(); else __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_ptr;
+    // grouped form: row tiles come from a device-side count and every tile's B rows from its group
+    int* seg_end = reinterpret_cast<int*>(base_ptr + C::seg_off);
+    int tiles_m = p.tiles_m;
+    if (p.rows_dev) {
+        const int rows = *p.rows_dev;
+        tiles_m = min(tiles_m, (rows + 128 * CG - 1) / (128 * CG));
+    }
+    if (p.num_groups > 0) {
+        if (threadIdx.x == 0) {
+            int acc = 0;
+            for (int e = 0; e < p.num_groups; ++e) {
+                acc += p.group_rows[e];
+                seg_end[e] = acc;
+            }
+        }
+        __syncthreads();
+    }
+    const int num_tiles = tiles_m * p.tiles_n;
 
     if (warp == 0) {
         // ------------------------------------------------------------------ producer
@@ -140,9 +167,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             bool ok = true;
             for (int t = cluster; t < num_tiles && ok; t += num_clusters) {
                 int tm, tn;
-                tile_coords(t, p, tm, tn);
+                tile_coords(t, p, tiles_m, tm, tn);
                 const int a_row = (tm * CG + static_cast<int>(rank)) * 128;
-                const int b_row = tn * BN + static_cast<int>(rank) * C::B_ROWS;
+                int b_base = tn * BN;                       // first B row of this tile
+                if (p.num_groups > 0) {
+                    const int row0 = tm * 128 * CG;
+                    int lo = 0, hi = p.num_groups - 1;        // first group whose segment ends beyond row0
+                    while (lo < hi) {
+                        const int mid = (lo + hi) >> 1;
+                        if (seg_end[mid] > row0) hi = mid; else lo = mid + 1;
+                    }
+                    b_base += lo * p.group_b_rows;
+                }
+                const int b_row = b_base + static_cast<int>(rank) * C::B_ROWS;
                 for (int ks = 0; ks < p.k_steps; ++ks) {
                     if (!mbar_wait(empty0 + stage * 8, ph ^ 1, ab, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
                     const uint32_t a_dst = base + C::a_off + stage * C::A_BYTES;
@@ -162,7 +199,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                         tma_load_2d_pair(a_dst, &tm_a, ks * BK, a_row, bar);
                         tma_load_2d_pair(b_dst, &tm_b, ks * BK, b_row, bar);
                         tma_load_3d_pair(sfa_dst, &tm_sfa, 0, ks, a_row / 128, bar);
-                        tma_load_3d_pair(sfb_dst, &tm_sfb, 0, ks, tn * 2, bar);
+                        tma_load_3d_pair(sfb_dst, &tm_sfb, 0, ks, b_base / 128, bar);
                         }
                     } else {
                         const uint32_t bar = full0 + stage * 8;
@@ -170,7 +207,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                         tma_load_2d(a_dst, &tm_a, ks * BK, a_row, bar);
                         tma_load_2d(b_dst, &tm_b, ks * BK, b_row, bar);
                         tma_load_3d(sfa_dst, &tm_sfa, 0, ks, a_row / 128, bar);
-                        tma_load_3d(sfb_dst, &tm_sfb, 0, ks, tn * 2, bar);
+                        tma_load_3d(sfb_dst, &tm_sfb, 0, ks, b_base / 128, bar);
                     }
                     if (++stage == S) { stage = 0; ph ^= 1; }
                 }
@@ -252,13 +289,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         bool ok = true;
         for (int t = cluster; t < num_tiles && ok; t += num_clusters, ++it) {
             int tm, tn;
-            tile_coords(t, p, tm, tn);
+            tile_coords(t, p, tiles_m, tm, tn);
             const int acc = it & 1;
             if (!mbar_wait(accfull0 + acc * 8, (it >> 1) & 1, ab, DEV_TIMEOUT_TMEM_FULL)) { ok = false; break; }
             tc_fence_after();
             const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + (acc ? ACC1_COL : 0);
             const int row0 = (tm * CG + static_cast<int>(rank)) * 128 + q * 32;
             const int col0 = tn * BN;
+            uint32_t scword = 0;                                 // four scale bytes of one row (c_mode 2)
 #pragma unroll 1
             for (int s = 0; s < 8; ++s) {
                 const int u = acc ? s : 7 - s;                   // 32-column unit; the shared unit goes first
@@ -271,7 +309,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     if (lane == 0) mbar_arrive_remote(drained_leader);
                 }
                 const uint32_t rowa = stg + lane * 128;
-                if (p.c_is_f32) {
+                if (p.c_mode == 1) {
                     if (lane == 0) bulk_wait_read<0>();
                     __syncwarp();
 #pragma unroll
@@ -282,6 +320,45 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     if (lane == 0 && !(p.dbg & 4)) {
                         tma_store_2d(&tm_c, col0 + u * 32, row0, stg);
                         bulk_commit();
+                    }
+                } else if (p.c_mode == 2) {
+                    // MXFP8 output: round the accumulator to bf16, then quantize this thread's 32
+                    // consecutive columns as one block (amax in registers, no shuffle)
+                    using namespace qmath;
+                    uint32_t h[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) h[j] = pack_bf16x2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+                    uint32_t m = maxabs_bf16x2(h[0], h[1]);
+#pragma unroll
+                    for (int j = 2; j < 16; ++j) m = maxabs_bf16x2(m, h[j]);
+                    m &= 0x7FFF7FFFu;
+                    const uint32_t amax = max(m & 0xFFFFu, m >> 16);
+                    const uint32_t byte = scale_bytes2(amax, RCEIL_ROUND_ADD2, RCEIL_MIN_BYTE8_2) & 0xFFu;
+                    const uint32_t inv = inv_scales2(byte | (byte << 16));
+                    if ((u & 3) == (acc ? 0 : 3)) {      // first unit of a 128-column group
+                        if (lane == 0) bulk_wait_read<0>();
+                        __syncwarp();
+                        scword = 0;
+                    }
+                    const uint32_t w0 = cvt4(mul_bf16x2(h[0], inv), mul_bf16x2(h[1], inv)), w1 = cvt4(mul_bf16x2(h[2], inv), mul_bf16x2(h[3], inv));
+                    const uint32_t w2 = cvt4(mul_bf16x2(h[4], inv), mul_bf16x2(h[5], inv)), w3 = cvt4(mul_bf16x2(h[6], inv), mul_bf16x2(h[7], inv));
+                    const uint32_t w4 = cvt4(mul_bf16x2(h[8], inv), mul_bf16x2(h[9], inv)), w5 = cvt4(mul_bf16x2(h[10], inv), mul_bf16x2(h[11], inv));
+                    const uint32_t w6 = cvt4(mul_bf16x2(h[12], inv), mul_bf16x2(h[13], inv)), w7 = cvt4(mul_bf16x2(h[14], inv), mul_bf16x2(h[15], inv));
+                    const int cpos = (u & 3) * 2;                        // 16-byte chunk inside the 128-byte row
+                    st_shared_v4(rowa + (((cpos + 0) ^ (lane & 7)) << 4), w0, w1, w2, w3);
+                    st_shared_v4(rowa + (((cpos + 1) ^ (lane & 7)) << 4), w4, w5, w6, w7);
+                    scword |= byte << ((u & 3) * 8);
+                    if ((u & 3) == (acc ? 3 : 0)) {      // last unit of the group
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        const int ctile = (col0 + (u & ~3) * 32) / 128;  // scale tile column
+                        if (lane == 0 && !(p.dbg & 4)) {
+                            tma_store_2d(&tm_c, col0 + (u & ~3) * 32, row0, stg);
+                            bulk_commit();
+                        }
+                        if (row0 + lane < p.rows_cap && ctile * 128 < p.n_cols)
+                            *reinterpret_cast<uint32_t*>(p.c_sc + (static_cast<size_t>(row0 / 128) * (p.n_cols / 128) + ctile) * 512 +
+                                                         lane * 16 + q * 4) = scword;
                     }
                 } else {
                     if ((s & 1) == 0) {
@@ -332,7 +409,7 @@ struct Maps {
 
 template <int CG>
 static int build_maps(Maps& m, const void* A, const void* A_sc, const void* B, const void* B_sc, void* Cp,
-                      int M, int N, int K, int c_dtype) {
+                      int M, int N, int K, int c_dtype, int b_rows) {
     int rc;
     const uint64_t kb = static_cast<uint64_t>(K) / 128;
     {
@@ -342,7 +419,7 @@ static int build_maps(Maps& m, const void* A, const void* A_sc, const void* B, c
         if ((rc = make_tmap(&m.a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, A, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) != MX8_OK) return rc;
     }
     {
-        const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N)};
+        const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(b_rows)};
         const uint64_t strides[1] = {static_cast<uint64_t>(K)};
         const uint32_t box[2] = {BK, static_cast<uint32_t>(Cfg<CG>::B_ROWS)};
         if ((rc = make_tmap(&m.b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, B, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) != MX8_OK) return rc;
@@ -355,18 +432,20 @@ static int build_maps(Maps& m, const void* A, const void* A_sc, const void* B, c
         if ((rc = make_tmap(&m.sfa, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, A_sc, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE)) != MX8_OK) return rc;
     }
     {
-        const uint64_t dims[3] = {128, kb, static_cast<uint64_t>(N) / 128};
+        const uint64_t dims[3] = {128, kb, static_cast<uint64_t>(b_rows) / 128};
         const uint64_t strides[2] = {512, 512 * kb};
         const uint32_t box[3] = {128, 1, 2};
         if ((rc = make_tmap(&m.sfb, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, B_sc, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE)) != MX8_OK) return rc;
     }
     {
-        const bool f32 = c_dtype == MX8_C_F32;
+        // C rows are 128 bytes wide in the staging buffer: 64 bf16, 32 float or 128 E4M3 columns
+        const int esz = c_dtype == MX8_C_F32 ? 4 : (c_dtype == MX8_C_MXFP8 ? 1 : 2);
+        const CUtensorMapDataType dt = c_dtype == MX8_C_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                     : (c_dtype == MX8_C_MXFP8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16);
         const uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(M)};
-        const uint64_t strides[1] = {static_cast<uint64_t>(N) * (f32 ? 4 : 2)};
-        const uint32_t box[2] = {f32 ? 32u : 64u, 32};
-        if ((rc = make_tmap(&m.c, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, Cp, dims, strides,
-                            box, CU_TENSOR_MAP_SWIZZLE_128B)) != MX8_OK) return rc;
+        const uint64_t strides[1] = {static_cast<uint64_t>(N) * esz};
+        const uint32_t box[2] = {static_cast<uint32_t>(128 / esz), 32};
+        if ((rc = make_tmap(&m.c, dt, 2, Cp, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) != MX8_OK) return rc;
     }
     return MX8_OK;
 }
@@ -411,18 +490,32 @@ static int max_grid() {
     return n;
 }
 
+struct Grouping {
+    void* c_sc = nullptr;            // scale tiles of C (MX8_C_MXFP8)
+    const int* rows_dev = nullptr;   // device count of rows present
+    const int* group_rows = nullptr; // device rows per group
+    int num_groups = 0;
+};
+
 template <int CG>
 static int run(const void* A, const void* A_sc, const void* B, const void* B_sc, void* Cp, int M, int N, int K,
-               int c_dtype, int max_ctas, cudaStream_t stream) {
+               int c_dtype, int max_ctas, const Grouping& gr, cudaStream_t stream) {
     Maps m;
-    int rc = build_maps<CG>(m, A, A_sc, B, B_sc, Cp, M, N, K, c_dtype);
+    int rc = build_maps<CG>(m, A, A_sc, B, B_sc, Cp, M, N, K, c_dtype, gr.num_groups > 0 ? gr.num_groups * N : N);
     if (rc != MX8_OK) return rc;
     Params p{};
+    p.c_sc = static_cast<uint8_t*>(gr.c_sc);
+    p.n_cols = N;
+    p.rows_cap = M;
+    p.rows_dev = gr.rows_dev;
+    p.group_rows = gr.group_rows;
+    p.num_groups = gr.num_groups;
+    p.group_b_rows = N;
     p.tiles_m = (M + 128 * CG - 1) / (128 * CG);
     p.tiles_n = (N + BN - 1) / BN;
     p.k_steps = K / BK;
     p.group_m = 8;
-    p.c_is_f32 = c_dtype == MX8_C_F32;
+    p.c_mode = c_dtype;
     { const char* e = getenv("MX8_GEMM_DEBUG"); p.dbg = e ? atoi(e) : 0; }
     { const char* e = getenv("MX8_GEMM_GROUP"); if (e) p.group_m = atoi(e); }
     p.status = device_status_ptr();
@@ -470,8 +563,34 @@ extern "C" int mx8_gemm_ex(const void* A, const void* A_sc, const void* B, const
     if (rc != MX8_OK) return rc;
     if (cta_group == 0) cta_group = (M <= 128) ? 1 : 2;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (cta_group == 2) return gemm::run<2>(A, A_sc, B, B_sc, C, M, N, K, c_dtype, max_ctas, st);
-    return gemm::run<1>(A, A_sc, B, B_sc, C, M, N, K, c_dtype, max_ctas, st);
+    const gemm::Grouping none;
+    if (cta_group == 2) return gemm::run<2>(A, A_sc, B, B_sc, C, M, N, K, c_dtype, max_ctas, none, st);
+    return gemm::run<1>(A, A_sc, B, B_sc, C, M, N, K, c_dtype, max_ctas, none, st);
+}
+
+extern "C" int mx8_gemm_grouped(const void* A, const void* A_sc, const void* B, const void* B_sc, void* C, void* C_sc,
+                                int M, int N, int K, int c_dtype, const void* num_rows, const void* group_rows,
+                                int num_groups, void* stream) {
+    using namespace mx8;
+    if (!A || !A_sc || !B || !B_sc || !C) return MX8_ERR_ARG;
+    if (c_dtype != MX8_C_BF16 && c_dtype != MX8_C_F32 && c_dtype != MX8_C_MXFP8) return MX8_ERR_ARG;
+    if ((c_dtype == MX8_C_MXFP8) != (C_sc != nullptr)) return MX8_ERR_ARG;
+    if (num_groups < 0 || (num_groups > 0 && !group_rows)) return MX8_ERR_ARG;
+    if (num_groups > gemm::MAX_GROUPS) {
+        note_cuda_error("mx8_gemm_grouped", "more than 256 groups in one call");
+        return MX8_ERR_LIMIT;
+    }
+    if (M <= 0 || N <= 0 || K <= 0 || M % 128 || N % 128 || K % 128) return MX8_ERR_SHAPE;
+    if (num_groups > 0 && (M % 256 || N % 256)) return MX8_ERR_SHAPE;     // groups are whole 256-row / 256-column tiles
+    if (!aligned16(A) || !aligned16(A_sc) || !aligned16(B) || !aligned16(B_sc) || !aligned16(C) || !aligned16(C_sc)) return MX8_ERR_ALIGN;
+    int rc = check_device_sm100();
+    if (rc != MX8_OK) return rc;
+    gemm::Grouping gr;
+    gr.c_sc = C_sc;
+    gr.rows_dev = static_cast<const int*>(num_rows);
+    gr.group_rows = static_cast<const int*>(group_rows);
+    gr.num_groups = num_groups;
+    return gemm::run<2>(A, A_sc, B, B_sc, C, M, N, K, c_dtype, 0, gr, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int mx8_gemm(const void* A, const void* A_sc, const void* B, const void* B_sc, void* C, int M, int N, int K,

@@ -21,6 +21,7 @@
 // variant blackwell-ultra/020-mxfp8-quantize-persistent.cu:139-219 of the reference.
 #include "mx8_host.cuh"
 #include "mx8_ptx.cuh"
+#include "mx8_qmath.cuh"
 
 namespace mx8 {
 namespace quant {
@@ -58,37 +59,7 @@ struct Smem {
     static_assert(dynamic <= 232448, "shared memory budget exceeded");
 };
 
-__device__ __forceinline__ uint32_t maxabs_bf16x2(uint32_t a, uint32_t b) {
-    uint32_t d;
-    asm("max.xorsign.abs.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-    return d;
-}
-__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
-    uint32_t d;
-    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-    return d;
-}
-__device__ __forceinline__ uint32_t max_u16x2(uint32_t a, uint32_t b) {
-    uint32_t d;
-    asm("max.u16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-    return d;
-}
-__device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
-__device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xFFFF0000u); }
-
-// Two non-negative bf16 amax bit patterns (one per 16-bit half) -> two E8M0 bytes (one per half):
-// byte = max(min_byte, ((amax + round_add) >> 7) - 8), the exact integer form of
-// ceil(log2(amax / 448)) + 127 (round_add 0x1F) or floor(log2(amax)) - 8 + 127 (round_add 0).
-__device__ __forceinline__ uint32_t scale_bytes2(uint32_t amax2, const Params& p) {
-    uint32_t t = ((amax2 + p.round_add2) >> 7) & 0x00FF00FFu;
-    return max_u16x2(t, p.min_byte8_2) - 0x00080008u;
-}
-// two scale bytes -> two bf16 reciprocals 2^(127 - byte): exponent field 254 - byte, mantissa 0
-__device__ __forceinline__ uint32_t inv_scales2(uint32_t bytes2) { return (0x00FE00FEu - bytes2) << 7; }
-// four bf16 (two packed words, already scaled) -> four E4M3 bytes
-__device__ __forceinline__ uint32_t cvt4(uint32_t v0, uint32_t v1) {
-    return cvt_e4m3x2(bf16_lo(v0), bf16_hi(v0)) | (cvt_e4m3x2(bf16_lo(v1), bf16_hi(v1)) << 16);
-}
+using namespace qmath;
 
 // Tile order: groups of `group_r` tile rows, walked column by column inside a group.  The ~148
 // tiles in flight at any time then form a patch about group_r tiles tall, so each input row, each
@@ -186,7 +157,7 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
                 a2 = maxabs_bf16x2(a2, __shfl_xor_sync(0xFFFFFFFFu, a2, 1));
                 a2 = maxabs_bf16x2(a2, __shfl_xor_sync(0xFFFFFFFFu, a2, 2));
                 a2 = maxabs_bf16x2(a2, __shfl_xor_sync(0xFFFFFFFFu, a2, 4));
-                const uint32_t b2 = scale_bytes2(a2 & 0x7FFF7FFFu, p);
+                const uint32_t b2 = scale_bytes2(a2 & 0x7FFF7FFFu, p.round_add2, p.min_byte8_2);
                 const uint32_t inv2 = inv_scales2(b2);
                 const uint32_t inv_a = __byte_perm(inv2, inv2, 0x1010), inv_b = __byte_perm(inv2, inv2, 0x3232);
                 const uint32_t qa = cvt4(mul_bf16x2(c[i][0], inv_a), mul_bf16x2(c[i][1], inv_a));
@@ -212,7 +183,7 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
                 m0 = maxabs_bf16x2(m0, c[i][0]);
                 m1 = maxabs_bf16x2(m1, c[i][1]);
             }
-            const uint32_t b01 = scale_bytes2(m0 & 0x7FFF7FFFu, p), b23 = scale_bytes2(m1 & 0x7FFF7FFFu, p);
+            const uint32_t b01 = scale_bytes2(m0 & 0x7FFF7FFFu, p.round_add2, p.min_byte8_2), b23 = scale_bytes2(m1 & 0x7FFF7FFFu, p.round_add2, p.min_byte8_2);
             const uint32_t inv01 = inv_scales2(b01), inv23 = inv_scales2(b23);
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
@@ -314,8 +285,8 @@ extern "C" int mx8_quantize(const void* x_bf16, int E, int M, int N, void* fp8, 
     p.tiles_rm = M / 128;
     p.N = N;
     p.group_r = 8;
-    p.round_add2 = scale_mode == MX8_SCALE_RCEIL ? 0x001F001Fu : 0u;
-    p.min_byte8_2 = scale_mode == MX8_SCALE_RCEIL ? 0x00600060u : 0x00080008u;   // (88 + 8), (0 + 8)
+    p.round_add2 = scale_mode == MX8_SCALE_RCEIL ? RCEIL_ROUND_ADD2 : FLOOR_ROUND_ADD2;
+    p.min_byte8_2 = scale_mode == MX8_SCALE_RCEIL ? RCEIL_MIN_BYTE8_2 : FLOOR_MIN_BYTE8_2;
     p.status = device_status_ptr();
     if (!p.status) return MX8_ERR_CUDA;
 

@@ -1,4 +1,4 @@
 """mx8: B200-native MXFP8 quantize + block-scaled GEMM behind the C ABI in include/mx8.h."""
 from ._lib import LIB_PATH, Mx8Error, load  # noqa: F401
-from .ops import (device_status, kernel, kernel_transpose, mxfp8_quantize, schedule,  # noqa: F401
+from .ops import (device_status, gemm_grouped, kernel, kernel_transpose, mxfp8_quantize, schedule,  # noqa: F401
                   quantize_kernel)

@@ -8,7 +8,7 @@ LIB_PATH = os.path.join(HERE, "libmx8.so")
 
 OK, ERR_ARG, ERR_SHAPE, ERR_ALIGN, ERR_CUDA, ERR_UNSUPPORTED, ERR_DEVICE_TIMEOUT, ERR_LIMIT = range(8)
 SCALE_RCEIL, SCALE_FLOOR = 0, 1
-C_BF16, C_F32 = 0, 1
+C_BF16, C_F32, C_MXFP8 = 0, 1, 2
 
 # every symbol include/mx8.h declares, with its ctypes signature
 _vp, _i = ctypes.c_void_p, ctypes.c_int
@@ -16,6 +16,7 @@ SIGNATURES = {
     "mx8_quantize": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp]),
     "mx8_gemm": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "mx8_gemm_ex": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
+    "mx8_gemm_grouped": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _i, _vp]),
     "mx8_moe_schedule": (_i, [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "mx8_moe_schedule_static": (_i, [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "mx8_device_status": (_i, [ctypes.POINTER(_i), _vp]),

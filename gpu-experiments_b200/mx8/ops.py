@@ -159,3 +159,40 @@ def schedule(topk_all, num_local_experts, schedule_capacity, rank):
                                         peer_tok.data_ptr(), num_tokens.data_ptr(), tpe.data_ptr(), scratch.data_ptr(),
                                         _stream()), "schedule")
     return peer_rank, peer_tok, num_tokens, tpe
+
+
+def gemm_grouped(A, A_sc, B, B_sc, C, C_sc=None, num_rows=None, group_rows=None):
+    """Grouped / quantizing GEMM (mx8_gemm_grouped).
+
+    A [M, K] E4M3 rows of all groups back to back, A_sc its scale tiles; B [G, N, K] (or [N, K] when
+    group_rows is None) with B_sc [G*N/128, K/128, 512]; C [M, N] bf16/float32, or E4M3/uint8 together
+    with C_sc [M/128, N/128, 32, 16] for the quantizing epilogue.  num_rows: int32 device tensor with
+    the rows present; group_rows: int32 device tensor [G], multiples of 256.
+    Stands in for expert_grouped_gemm<false> inside the reference's MoE kernel
+    (blackwell-ultra/022-moe-dispatch-mlp-swiglu-combine-mxfp8-bw.cu:1399-1736)."""
+    lib = _lib.load()
+    M, K = A.shape
+    G = 0
+    if group_rows is not None:
+        G, N = B.shape[0], B.shape[1]
+        if B.dim() != 3 or B.shape[2] != K:
+            raise ValueError("grouped B must be [G, N, K]")
+    else:
+        N = B.shape[0]
+    if tuple(C.shape) != (M, N):
+        raise ValueError("C must be [M, N]")
+    ap, bp = _chk(A, "A", _FP8), _chk(B, "B", _FP8)
+    asp = _chk(A_sc, "A_sc", _SC, (M // 128, K // 128, 512))
+    bsp = _chk(B_sc, "B_sc", _SC, (max(G, 1) * N // 128, K // 128, 512))
+    if C_sc is not None:
+        cp = _chk(C, "C", _FP8)
+        csp = _chk(C_sc, "C_sc", _SC, (M // 128, N // 128, 512))
+        cd = _lib.C_MXFP8
+    else:
+        cp = _chk(C, "C", (torch.bfloat16, torch.float32))
+        csp = None
+        cd = _lib.C_F32 if C.dtype == torch.float32 else _lib.C_BF16
+    nr = _chk(num_rows, "num_rows", (torch.int32,)) if num_rows is not None else None
+    grp = _chk(group_rows, "group_rows", (torch.int32,)) if group_rows is not None else None
+    with torch.cuda.device(A.device):
+        _lib.check(lib.mx8_gemm_grouped(ap, asp, bp, bsp, cp, csp, M, N, K, cd, nr, grp, G, _stream()), "gemm_grouped")

@@ -50,7 +50,9 @@ enum {
 /* GEMM output element type */
 enum {
     MX8_C_BF16 = 0, /* blackwell/047-mxfp8-mma-2cta-MNK128-polished.cu:461 (C is bf16)       */
-    MX8_C_F32 = 1   /* blackwell/009-mxfp8-mm.cu:46, 010..017 (C is float)                   */
+    MX8_C_F32 = 1,  /* blackwell/009-mxfp8-mm.cu:46, 010..017 (C is float)                   */
+    MX8_C_MXFP8 = 2 /* E4M3 bytes + scale tiles (mx8_gemm_grouped only): the quantizing epilogue of
+                       blackwell-ultra/022-moe-dispatch-mlp-swiglu-combine-mxfp8-bw.cu:1644-1700 */
 };
 
 /* Quantize x[E][M][N] (bf16, row-major; E = 1 for a matrix) to MXFP8.
@@ -80,6 +82,20 @@ MX8_API int mx8_gemm(const void* A, const void* A_sc, const void* B, const void*
  *   the benchmark's ablations. */
 MX8_API int mx8_gemm_ex(const void* A, const void* A_sc, const void* B, const void* B_sc, void* C,
                 int M, int N, int K, int c_dtype, int cta_group, int max_ctas, void* stream);
+
+/* Grouped / quantizing form of the GEMM.
+ *   A [M][K] holds the rows of all groups back to back; group g owns group_rows[g] rows (device
+ *   int32, multiples of 256) and multiplies them with its own B_g [N][K]: B is [num_groups][N][K],
+ *   B_sc [num_groups*N/128][K/128][512].  num_groups == 0: one B for all rows (plain GEMM).
+ *   num_rows (device int32, may be NULL): rows actually present; row tiles beyond it are skipped,
+ *   so M can be a capacity.  c_dtype MX8_C_MXFP8: the accumulator is rounded to bf16 and quantized
+ *   with blocks of 32 along N into C (bytes [M][N]) and C_sc ([M/128][N/128][512]); otherwise C_sc
+ *   must be NULL.
+ * Replaces expert_grouped_gemm<false> and its two epilogues,
+ * blackwell-ultra/022-moe-dispatch-mlp-swiglu-combine-mxfp8-bw.cu:1399-1736. */
+MX8_API int mx8_gemm_grouped(const void* A, const void* A_sc, const void* B, const void* B_sc, void* C, void* C_sc,
+                             int M, int N, int K, int c_dtype, const void* num_rows, const void* group_rows,
+                             int num_groups, void* stream);
 
 /* Expert-parallel MoE routing schedule for the calling rank (int32 everywhere).
  *   topk_all [world][tokens][topk]: global expert ids chosen by every rank's tokens;

@@ -54,3 +54,65 @@ def test_schedule_overflow_is_reported_not_trapped():
         mx8.device_status()
     assert int(nt) > 256
     assert mx8.device_status() == 0          # the word is cleared by the read
+
+
+def _quant(x):
+    return O.quantize_tiled(x)
+
+
+def test_gemm_quantizing_epilogue_dense():
+    # C emitted as MXFP8 must equal the oracle's quantization of the kernel's own bf16 C, bit for bit
+    M, N, K = 512, 768, 512
+    aq, asc = _quant(O.make_input(M, K, seed=1, std=K ** -0.25))
+    bq, bsc = _quant(O.make_input(N, K, seed=2, std=K ** -0.25))
+    d = [t.to(DEV) for t in (aq, asc, bq, bsc)]
+    c_bf16 = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    mx8.gemm_grouped(*d, c_bf16)
+    c_q = torch.full((M, N), 0xFF, dtype=torch.uint8, device=DEV)
+    c_sc = torch.full((M // 128, N // 128, 32, 16), 0xFF, dtype=torch.uint8, device=DEV)
+    mx8.gemm_grouped(*d, c_q, c_sc)
+    assert mx8.device_status() == 0
+    ref = O.gemm_ref(aq, asc, bq, bsc)
+    assert O.rel_frobenius(c_bf16.cpu(), ref) < 2e-3
+    want_q, want_sc = O.quantize_tiled(c_bf16.cpu())
+    assert torch.equal(c_q.cpu(), want_q)
+    assert torch.equal(c_sc.cpu(), want_sc)
+
+
+@pytest.mark.parametrize("mode", ["bf16", "mxfp8"])
+def test_gemm_grouped_by_expert(mode):
+    E, N, K = 5, 512, 384
+    group_rows = torch.tensor([512, 0, 256, 768, 256], dtype=torch.int32)
+    used = int(group_rows.sum())
+    cap = used + 512                                     # capacity beyond the rows present
+    a = O.make_input(cap, K, seed=3, std=K ** -0.25)
+    w = torch.stack([O.make_input(N, K, seed=10 + e, std=K ** -0.25) for e in range(E)])
+    aq, asc = _quant(a)
+    wq, wsc, _, _ = O.quantize_both(w)
+    num_rows = torch.tensor([used], dtype=torch.int32)
+    d = [t.to(DEV) for t in (aq, asc, wq, wsc)]
+    if mode == "bf16":
+        c = torch.full((cap, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+        mx8.gemm_grouped(*d, c, None, num_rows.to(DEV), group_rows.to(DEV))
+    else:
+        c = torch.full((cap, N), 0xFF, dtype=torch.uint8, device=DEV)
+        csc = torch.full((cap // 128, N // 128, 32, 16), 0xFF, dtype=torch.uint8, device=DEV)
+        mx8.gemm_grouped(*d, c, csc, num_rows.to(DEV), group_rows.to(DEV))
+    assert mx8.device_status() == 0
+    off = 0
+    for e, n in enumerate(group_rows.tolist()):
+        if n == 0:
+            continue
+        ref = O.gemm_ref(aq[off:off + n], asc[off // 128:(off + n) // 128], wq[e], wsc[e * N // 128:(e + 1) * N // 128])
+        if mode == "bf16":
+            got = c[off:off + n].cpu()
+            assert not torch.isnan(got.float()).any()
+            assert O.rel_frobenius(got, ref) < 2e-3, f"expert {e}"
+        else:
+            deq = O.dequantize(c[off:off + n].cpu(), O.scale_unswizzle(csc[off // 128:(off + n) // 128].cpu()))
+            # E4M3 payload: half an ulp of 3 mantissa bits relative to the block amax
+            assert O.rel_frobenius(deq, ref) < 5e-2, f"expert {e}"
+        off += n
+    # rows beyond num_rows are untouched
+    tail = c[used:].cpu()
+    assert bool(torch.isnan(tail.float()).all()) if mode == "bf16" else bool((tail == 0xFF).all())
