@@ -1,0 +1,154 @@
+// MoE combine (expert output rows back to the ranks that own the tokens) and the weighted sum that
+// finishes the layer.
+//
+// combine: row r of y_routed (bf16, `hidden` wide) goes to row peer_token_idx[r] of the combine
+// buffer of rank peer_rank[r]; rows with peer_rank < 0 (padding) are skipped.  The destination is
+// that rank's memory, written directly with 16-byte stores over NVLink (one warp per row, 512 bytes
+// per warp instruction).  The copy is exact.  Replaces combine_kernel,
+// blackwell-ultra/022-moe-dispatch-mlp-swiglu-combine-mxfp8-bw.cu:830-922.
+//
+// epilogue: out[t] = bf16( y_shared[t] + sum_j w[t][j] * combine[t*topk + j] ), fp32, products and
+// sums rounded separately, j ascending, so the result does not depend on the launch shape.
+// Replaces fwd_epilogue_kernel, blackwell-ultra/022-…-mxfp8-bw.cu:2789-2856.
+#include "mx8_host.cuh"
+#include "mx8_ptx.cuh"
+
+namespace mx8 {
+namespace moe {
+
+struct CombineParams {
+    const uint8_t* y;            // [rows][hidden] bf16
+    const int* peer_rank;
+    const int* peer_token_idx;
+    const int* num_tokens;       // device
+    int hidden;
+    uint8_t* dst[16];            // every rank's combine buffer [tokens*topk][hidden] bf16
+};
+
+__global__ void __launch_bounds__(256) combine_kernel(CombineParams p) {
+    const int rows = *p.num_tokens;
+    const int lane = threadIdx.x & 31;
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int warps = (gridDim.x * blockDim.x) >> 5;
+    const size_t row_bytes = static_cast<size_t>(p.hidden) * 2;
+    for (int r = warp; r < rows; r += warps) {
+        const int pr = p.peer_rank[r];
+        if (pr < 0) continue;
+        const uint4* src = reinterpret_cast<const uint4*>(p.y + r * row_bytes);
+        uint4* dst = reinterpret_cast<uint4*>(p.dst[pr] + static_cast<size_t>(p.peer_token_idx[r]) * row_bytes);
+        const int n16 = p.hidden / 8;
+        for (int i = lane; i < n16; i += 128) {
+            // four independent 16-byte copies in flight per lane
+            uint4 v0 = src[i], v1, v2, v3;
+            const bool b1 = i + 32 < n16, b2 = i + 64 < n16, b3 = i + 96 < n16;
+            if (b1) v1 = src[i + 32];
+            if (b2) v2 = src[i + 64];
+            if (b3) v3 = src[i + 96];
+            dst[i] = v0;
+            if (b1) dst[i + 32] = v1;
+            if (b2) dst[i + 64] = v2;
+            if (b3) dst[i + 96] = v3;
+        }
+    }
+}
+
+struct EpilogueParams {
+    const uint8_t* y_shared;     // [tokens][hidden] bf16 or nullptr (no shared expert)
+    const uint8_t* combine;      // [tokens*topk][hidden] bf16
+    const float* weights;        // [tokens][topk]
+    uint8_t* out;                // [tokens][hidden] bf16
+    int tokens, hidden, topk;
+};
+
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        f[2 * i] = __uint_as_float(w[i] << 16);
+        f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+    }
+}
+
+__global__ void __launch_bounds__(256) epilogue_kernel(EpilogueParams p) {
+    const int n16 = p.hidden / 8;
+    const long long total = static_cast<long long>(p.tokens) * n16;
+    for (long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
+         idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int t = static_cast<int>(idx / n16), c = static_cast<int>(idx - static_cast<long long>(t) * n16);
+        float acc[8];
+        if (p.y_shared) {
+            unpack8(reinterpret_cast<const uint4*>(p.y_shared)[idx], acc);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+        }
+        for (int j = 0; j < p.topk; ++j) {
+            const float w = p.weights[static_cast<size_t>(t) * p.topk + j];
+            float v[8];
+            unpack8(reinterpret_cast<const uint4*>(p.combine)[(static_cast<size_t>(t) * p.topk + j) * n16 + c], v);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] = __fadd_rn(acc[i], __fmul_rn(v[i], w));   // no fused multiply-add
+        }
+        uint4 o;
+        o.x = pack_bf16x2(acc[0], acc[1]);
+        o.y = pack_bf16x2(acc[2], acc[3]);
+        o.z = pack_bf16x2(acc[4], acc[5]);
+        o.w = pack_bf16x2(acc[6], acc[7]);
+        reinterpret_cast<uint4*>(p.out)[idx] = o;
+    }
+}
+
+}  // namespace moe
+}  // namespace mx8
+
+extern "C" int mx8_moe_combine(const void* y_routed, const void* peer_rank, const void* peer_token_idx, const void* num_tokens,
+                               int hidden, void* const* combine_ptrs, int world, void* stream) {
+    using namespace mx8;
+    if (!y_routed || !peer_rank || !peer_token_idx || !num_tokens || !combine_ptrs) return MX8_ERR_ARG;
+    if (world <= 0 || world > 16) return MX8_ERR_ARG;
+    if (hidden <= 0 || hidden % 8) return MX8_ERR_SHAPE;
+    if (!aligned16(y_routed)) return MX8_ERR_ALIGN;
+    moe::CombineParams p{};
+    for (int r = 0; r < world; ++r) {
+        if (!combine_ptrs[r] || !aligned16(combine_ptrs[r])) return MX8_ERR_ALIGN;
+        p.dst[r] = static_cast<uint8_t*>(combine_ptrs[r]);
+    }
+    int rc = check_device_sm100();
+    if (rc != MX8_OK) return rc;
+    p.y = static_cast<const uint8_t*>(y_routed);
+    p.peer_rank = static_cast<const int*>(peer_rank);
+    p.peer_token_idx = static_cast<const int*>(peer_token_idx);
+    p.num_tokens = static_cast<const int*>(num_tokens);
+    p.hidden = hidden;
+    const int sms = sm_count();
+    if (sms <= 0) return MX8_ERR_CUDA;
+    moe::combine_kernel<<<sms * 4, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        note_cuda_error("moe combine launch", cudaGetErrorString(e));
+        return MX8_ERR_CUDA;
+    }
+    return MX8_OK;
+}
+
+extern "C" int mx8_moe_fwd_epilogue(const void* y_shared, const void* combine_buffer, const void* topk_weights, void* out,
+                                    int tokens, int hidden, int topk, void* stream) {
+    using namespace mx8;
+    if (!combine_buffer || !topk_weights || !out) return MX8_ERR_ARG;
+    if (tokens <= 0 || topk <= 0) return MX8_ERR_ARG;
+    if (hidden <= 0 || hidden % 8) return MX8_ERR_SHAPE;
+    if (!aligned16(y_shared) || !aligned16(combine_buffer) || !aligned16(out)) return MX8_ERR_ALIGN;
+    int rc = check_device_sm100();
+    if (rc != MX8_OK) return rc;
+    moe::EpilogueParams p{static_cast<const uint8_t*>(y_shared), static_cast<const uint8_t*>(combine_buffer),
+                          static_cast<const float*>(topk_weights), static_cast<uint8_t*>(out), tokens, hidden, topk};
+    const int sms = sm_count();
+    if (sms <= 0) return MX8_ERR_CUDA;
+    moe::epilogue_kernel<<<sms * 8, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        note_cuda_error("moe epilogue launch", cudaGetErrorString(e));
+        return MX8_ERR_CUDA;
+    }
+    return MX8_OK;
+}

@@ -43,8 +43,19 @@ struct Params {
     int group_r;         // tile rows per rasterisation group
     uint32_t round_add2; // packed per 16-bit half: 0x1F rounds the scale exponent up (rceil), 0 = floor
     uint32_t min_byte8_2;// packed per half: smallest scale byte + 8 (rceil 88: amax/448 clamped to 1e-12; floor 0)
+    // source modes other than a dense bf16 matrix
+    const int* rows_dev;          // device: rows present (gather / SwiGLU); tiles beyond it are skipped
+    const int* peer_rank;         // gather: source rank per row, -1 = zero row
+    const int* peer_token_idx;    // gather: token * topk + k on the source rank
+    int topk;
+    const uint8_t* src[16];       // gather: every rank's token matrix [tokens][N] bf16 (peer-mapped pointers)
+    const uint8_t* gate_sc;       // SwiGLU: scale tiles of the two E4M3 inputs
+    const uint8_t* up_sc;
+    uint8_t* hidden_bf16;         // SwiGLU: optional bf16 copy of the activation (tests), else nullptr
     int* status;
 };
+
+constexpr int SRC_DENSE = 0, SRC_GATHER = 1, SRC_SWIGLU = 2;
 
 template <int W, int D>
 struct Smem {
@@ -65,18 +76,19 @@ using namespace qmath;
 // tiles in flight at any time then form a patch about group_r tiles tall, so each input row, each
 // row-wise output row AND each transposed output row receives a contiguous run of a kilobyte or
 // more within a short time window, which keeps DRAM pages open for all three streams.
-__device__ __forceinline__ void tile_coords(int t, const Params& p, int& tr, int& tc) {
+__device__ __forceinline__ void tile_coords(int t, const Params& p, int tiles_r, int& tr, int& tc) {
     const int per_group = p.group_r * p.tiles_c;
     const int grp = t / per_group;
     const int in_grp = t - grp * per_group;
-    const int rows = min(p.group_r, p.tiles_r - grp * p.group_r);
+    const int rows = min(p.group_r, tiles_r - grp * p.group_r);
     tc = in_grp / rows;
     tr = grp * p.group_r + (in_grp - tc * rows);
 }
 
-template <int W, int D, bool ROW, bool COL>
+template <int W, int D, int SRC, bool ROW, bool COL>
 __global__ void __launch_bounds__(32 + W * 32, 1)
-quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ CUtensorMap tm_t, const Params p) {
+quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ CUtensorMap tm_in2,
+                const __grid_constant__ CUtensorMap tm_t, const Params p) {
     using L = Smem<W, D>;
     constexpr int S = L::S;
     extern __shared__ uint8_t smem_raw[];
@@ -91,7 +103,7 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
     if (tid == 0) {
         *abort_flag = 0;
         for (int s = 0; s < S; ++s) {
-            mbar_init(full0 + s * 8, 1);
+            mbar_init(full0 + s * 8, SRC == SRC_GATHER ? 32 : 1);   // gather: one arrival per row
             mbar_init(empty0 + s * 8, 1);
         }
         fence_mbar_init();
@@ -101,22 +113,56 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
     __syncthreads();
 
     // this CTA's tiles: blockIdx.x, blockIdx.x + gridDim.x, ...; slab n = 4 * (tile ordinal) + quarter
-    const int num_tiles = p.tiles_r * p.tiles_c;
+    const int tiles_r = p.rows_dev ? min(p.tiles_r, (*p.rows_dev + TILE - 1) / TILE) : p.tiles_r;
+    const int num_tiles = tiles_r * p.tiles_c;
     const int my_tiles = (num_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
     const int my_slabs = my_tiles * 4;
 
     if (tid < 32) {
         // ---------------------------------------------------------------- producer
-        if (tid == 0) {
+        if constexpr (SRC == SRC_GATHER) {
+            // every lane fetches one row of the slab (256 bytes) from the rank that owns the token,
+            // straight from that rank's memory; rows without a source are filled with zeros
+            for (int n = 0; n < my_slabs; ++n) {
+                const int slot = n % S;
+                const uint32_t ph = (n / S) & 1;
+                int ok = 1;
+                if (tid == 0) ok = mbar_wait(empty0 + slot * 8, ph ^ 1, ab, DEV_TIMEOUT_EMPTY) ? 1 : 0;
+                ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+                if (!ok) break;
+                const int t = static_cast<int>(blockIdx.x) + (n >> 2) * static_cast<int>(gridDim.x);
+                int tr, tc;
+                tile_coords(t, p, tiles_r, tr, tc);
+                const int row = tr * TILE + (n & 3) * SLAB_ROWS + tid;
+                const int pr = p.peer_rank[row];
+                const uint32_t dst = base + L::ring + slot * SLOT_BYTES + tid * 256;
+                if (pr >= 0) {
+                    const uint8_t* s = p.src[pr] + (static_cast<size_t>(p.peer_token_idx[row] / p.topk) * p.N + tc * TILE) * 2;
+                    mbar_arrive_expect_tx(full0 + slot * 8, 256);
+                    bulk_load_1d(dst, s, 256, full0 + slot * 8);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) st_shared_v4(dst + j * 16, 0, 0, 0, 0);
+                    mbar_arrive(full0 + slot * 8);
+                }
+            }
+        } else if (tid == 0) {
             for (int n = 0; n < my_slabs; ++n) {
                 const int slot = n % S;
                 const uint32_t ph = (n / S) & 1;
                 if (!mbar_wait(empty0 + slot * 8, ph ^ 1, ab, DEV_TIMEOUT_EMPTY)) break;
                 const int t = static_cast<int>(blockIdx.x) + (n >> 2) * static_cast<int>(gridDim.x);
                 int tr, tc;
-                tile_coords(t, p, tr, tc);
+                tile_coords(t, p, tiles_r, tr, tc);
+                const uint32_t dst = base + L::ring + slot * SLOT_BYTES;
                 mbar_arrive_expect_tx(full0 + slot * 8, SLOT_BYTES);
-                tma_load_2d(base + L::ring + slot * SLOT_BYTES, &tm_in, tc * TILE, tr * TILE + (n & 3) * SLAB_ROWS, full0 + slot * 8);
+                if constexpr (SRC == SRC_SWIGLU) {
+                    // two E4M3 slabs of 32 x 128 bytes: gate, then up
+                    tma_load_2d(dst, &tm_in, tc * TILE, tr * TILE + (n & 3) * SLAB_ROWS, full0 + slot * 8);
+                    tma_load_2d(dst + SLOT_BYTES / 2, &tm_in2, tc * TILE, tr * TILE + (n & 3) * SLAB_ROWS, full0 + slot * 8);
+                } else {
+                    tma_load_2d(dst, &tm_in, tc * TILE, tr * TILE + (n & 3) * SLAB_ROWS, full0 + slot * 8);
+                }
             }
         }
         return;
@@ -137,12 +183,42 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
         const int wq = n & 3;
         const int t = static_cast<int>(blockIdx.x) + (n >> 2) * static_cast<int>(gridDim.x);
         int tr, tc;
-        tile_coords(t, p, tr, tc);
+        tile_coords(t, p, tiles_r, tr, tc);
         if (!mbar_wait(full0 + slot * 8, ph, ab, DEV_TIMEOUT_FULL)) break;
 
-        uint32_t c[32][2];                 // c[i] = columns 4l..4l+3 of slab row i
+        uint32_t c[32][2];                 // c[i] = columns 4l..4l+3 of slab row i (bf16 pairs)
+        if constexpr (SRC == SRC_SWIGLU) {
+            // hidden = bf16( silu(dequant(gate)) * dequant(up) ), computed in fp32
+            const size_t sc_tile = (static_cast<size_t>(tr) * p.tiles_c + tc) * 512 + l * 16 + wq * 4;
+            const uint32_t gw = *reinterpret_cast<const uint32_t*>(p.gate_sc + sc_tile);   // lane i: scale bytes of row i
+            const uint32_t uw = *reinterpret_cast<const uint32_t*>(p.up_sc + sc_tile);
+            const int sh = (l >> 3) * 8;                                                 // this lane's 32-column block
 #pragma unroll
-        for (int i = 0; i < 32; ++i) ld_shared_v2(slot_addr + i * 256 + l * 8, c[i][0], c[i][1]);
+            for (int i = 0; i < 32; ++i) {
+                uint32_t g4, u4;
+                asm volatile("ld.shared.b32 %0, [%1];" : "=r"(g4) : "r"(slot_addr + i * 128 + l * 4));
+                asm volatile("ld.shared.b32 %0, [%1];" : "=r"(u4) : "r"(slot_addr + SLOT_BYTES / 2 + i * 128 + l * 4));
+                const float gs = __uint_as_float(((__shfl_sync(0xFFFFFFFFu, gw, i) >> sh) & 0xFFu) << 23);
+                const float us = __uint_as_float(((__shfl_sync(0xFFFFFFFFu, uw, i) >> sh) & 0xFFu) << 23);
+                float h[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float g = e4m3_to_float((g4 >> (8 * e)) & 0xFFu) * gs;
+                    const float u = e4m3_to_float((u4 >> (8 * e)) & 0xFFu) * us;
+                    h[e] = (g / (1.0f + expf(-g))) * u;
+                }
+                c[i][0] = pack_bf16x2(h[0], h[1]);
+                c[i][1] = pack_bf16x2(h[2], h[3]);
+            }
+            if (p.hidden_bf16) {
+                uint8_t* hb = p.hidden_bf16 + ((static_cast<size_t>(tr) * TILE + wq * SLAB_ROWS) * p.N + tc * TILE + l * 4) * 2;
+#pragma unroll
+                for (int i = 0; i < 32; ++i) *reinterpret_cast<uint2*>(hb + static_cast<size_t>(i) * p.N * 2) = make_uint2(c[i][0], c[i][1]);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) ld_shared_v2(slot_addr + i * 256 + l * 8, c[i][0], c[i][1]);
+        }
         __syncwarp();
         if (l == 0) mbar_arrive(empty0 + slot * 8);       // the slot may be refilled now
 
@@ -234,9 +310,10 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
     if (COL && l == 0) bulk_wait_all<0>();
 }
 
-template <int W, int D, bool ROW, bool COL>
-static int launch(const CUtensorMap& tm_in, const CUtensorMap& tm_t, const Params& p, int grid, cudaStream_t stream) {
-    auto kern = quantize_kernel<W, D, ROW, COL>;
+template <int W, int D, int SRC, bool ROW, bool COL>
+static int launch(const CUtensorMap& tm_in, const CUtensorMap& tm_in2, const CUtensorMap& tm_t, const Params& p, int grid,
+                  cudaStream_t stream) {
+    auto kern = quantize_kernel<W, D, SRC, ROW, COL>;
     constexpr int smem = Smem<W, D>::dynamic;
     static bool configured[64] = {};
     int dev = 0;
@@ -249,7 +326,7 @@ static int launch(const CUtensorMap& tm_in, const CUtensorMap& tm_t, const Param
         }
         configured[dev & 63] = true;
     }
-    kern<<<grid, 32 + W * 32, smem, stream>>>(tm_in, tm_t, p);
+    kern<<<grid, 32 + W * 32, smem, stream>>>(tm_in, tm_in2, tm_t, p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
         note_cuda_error("quantize launch", cudaGetErrorString(e));
@@ -319,7 +396,101 @@ extern "C" int mx8_quantize(const void* x_bf16, int E, int M, int N, void* fp8, 
     // Both orientations: 8 consumer warps with one slot each measured best (deeper prefetch lowers
     // throughput once reads and both write streams compete); a single orientation does less
     // arithmetic per slab and prefers 6 warps with two slots each.
-    if (row && col) return launch<8, 1, true, true>(tm_in, tm_t, p, grid, st);
-    if (row) return launch<6, 2, true, false>(tm_in, tm_t, p, grid, st);
-    return launch<6, 2, false, true>(tm_in, tm_t, p, grid, st);
+    if (row && col) return launch<8, 1, SRC_DENSE, true, true>(tm_in, tm_in, tm_t, p, grid, st);
+    if (row) return launch<6, 2, SRC_DENSE, true, false>(tm_in, tm_in, tm_t, p, grid, st);
+    return launch<6, 2, SRC_DENSE, false, true>(tm_in, tm_in, tm_t, p, grid, st);
+}
+
+namespace mx8 {
+namespace quant {
+
+// transposed bytes [E][N][M] seen as (M, 4, N/4, E): column c = 4q + k lives at (k, q), so one store
+// covers the 32 columns a staging buffer holds (k fixed, q = 0..31), 32 bytes each
+static int make_transposed_map(CUtensorMap* tm, void* fp8_t, int E, int M, int N) {
+    const uint64_t dims[4] = {static_cast<uint64_t>(M), 4, static_cast<uint64_t>(N) / 4, static_cast<uint64_t>(E)};
+    const uint64_t strides[3] = {static_cast<uint64_t>(M), static_cast<uint64_t>(M) * 4, static_cast<uint64_t>(M) * N};
+    const uint32_t box[4] = {SLAB_ROWS, 1, 32, 1};
+    return make_tmap(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, fp8_t, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE,
+                     CU_TENSOR_MAP_L2_PROMOTION_NONE);
+}
+
+static void fill_common(Params& p, void* fp8, void* sc, void* sc_t, int rows, int N) {
+    p.out = static_cast<uint8_t*>(fp8);
+    p.sc = static_cast<uint8_t*>(sc);
+    p.sc_t = static_cast<uint8_t*>(sc_t);
+    p.tiles_r = rows / 128;
+    p.tiles_c = N / 128;
+    p.tiles_rm = rows / 128;
+    p.N = N;
+    p.group_r = 8;
+    p.round_add2 = RCEIL_ROUND_ADD2;
+    p.min_byte8_2 = RCEIL_MIN_BYTE8_2;
+}
+
+}  // namespace quant
+}  // namespace mx8
+
+extern "C" int mx8_moe_dispatch_quantize(const void* const* x_ptrs, int world, int hidden, int topk, const void* peer_rank,
+                                         const void* peer_token_idx, const void* num_tokens, int capacity, void* fp8,
+                                         void* sc, void* fp8_t, void* sc_t, void* stream) {
+    using namespace mx8;
+    using namespace mx8::quant;
+    if (!x_ptrs || !peer_rank || !peer_token_idx || !num_tokens || !fp8 || !sc || !fp8_t || !sc_t) return MX8_ERR_ARG;
+    if (world <= 0 || world > 16 || topk <= 0) return MX8_ERR_ARG;
+    if (capacity <= 0 || hidden <= 0 || capacity % 128 || hidden % 128) return MX8_ERR_SHAPE;
+    if (!aligned16(fp8) || !aligned16(sc) || !aligned16(fp8_t) || !aligned16(sc_t)) return MX8_ERR_ALIGN;
+    for (int r = 0; r < world; ++r)
+        if (!x_ptrs[r] || !aligned16(x_ptrs[r])) return MX8_ERR_ALIGN;
+    int rc = check_device_sm100();
+    if (rc != MX8_OK) return rc;
+    Params p{};
+    fill_common(p, fp8, sc, sc_t, capacity, hidden);
+    p.rows_dev = static_cast<const int*>(num_tokens);
+    p.peer_rank = static_cast<const int*>(peer_rank);
+    p.peer_token_idx = static_cast<const int*>(peer_token_idx);
+    p.topk = topk;
+    for (int r = 0; r < world; ++r) p.src[r] = static_cast<const uint8_t*>(x_ptrs[r]);
+    p.status = device_status_ptr();
+    if (!p.status) return MX8_ERR_CUDA;
+    CUtensorMap tm_t;
+    if ((rc = make_transposed_map(&tm_t, fp8_t, 1, capacity, hidden)) != MX8_OK) return rc;
+    int grid = sm_count();
+    if (grid <= 0) return MX8_ERR_CUDA;
+    const int tiles = p.tiles_r * p.tiles_c;
+    if (grid > tiles) grid = tiles;
+    return launch<8, 1, SRC_GATHER, true, true>(tm_t, tm_t, tm_t, p, grid, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int mx8_swiglu_quantize(const void* gate_fp8, const void* gate_sc, const void* up_fp8, const void* up_sc,
+                                   int rows, int cols, const void* num_rows, void* hidden_fp8, void* hidden_sc,
+                                   void* hidden_fp8_t, void* hidden_sc_t, void* hidden_bf16, void* stream) {
+    using namespace mx8;
+    using namespace mx8::quant;
+    if (!gate_fp8 || !gate_sc || !up_fp8 || !up_sc || !hidden_fp8 || !hidden_sc || !hidden_fp8_t || !hidden_sc_t) return MX8_ERR_ARG;
+    if (rows <= 0 || cols <= 0 || rows % 128 || cols % 128) return MX8_ERR_SHAPE;
+    if (!aligned16(gate_fp8) || !aligned16(gate_sc) || !aligned16(up_fp8) || !aligned16(up_sc) || !aligned16(hidden_fp8) ||
+        !aligned16(hidden_sc) || !aligned16(hidden_fp8_t) || !aligned16(hidden_sc_t) || !aligned16(hidden_bf16))
+        return MX8_ERR_ALIGN;
+    int rc = check_device_sm100();
+    if (rc != MX8_OK) return rc;
+    Params p{};
+    fill_common(p, hidden_fp8, hidden_sc, hidden_sc_t, rows, cols);
+    p.rows_dev = static_cast<const int*>(num_rows);
+    p.gate_sc = static_cast<const uint8_t*>(gate_sc);
+    p.up_sc = static_cast<const uint8_t*>(up_sc);
+    p.hidden_bf16 = static_cast<uint8_t*>(hidden_bf16);
+    p.status = device_status_ptr();
+    if (!p.status) return MX8_ERR_CUDA;
+    CUtensorMap tm_g, tm_u, tm_t;
+    const uint64_t dims[2] = {static_cast<uint64_t>(cols), static_cast<uint64_t>(rows)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(cols)};
+    const uint32_t box[2] = {128, SLAB_ROWS};
+    if ((rc = make_tmap(&tm_g, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, gate_fp8, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE)) != MX8_OK) return rc;
+    if ((rc = make_tmap(&tm_u, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, up_fp8, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE)) != MX8_OK) return rc;
+    if ((rc = make_transposed_map(&tm_t, hidden_fp8_t, 1, rows, cols)) != MX8_OK) return rc;
+    int grid = sm_count();
+    if (grid <= 0) return MX8_ERR_CUDA;
+    const int tiles = p.tiles_r * p.tiles_c;
+    if (grid > tiles) grid = tiles;
+    return launch<8, 1, SRC_SWIGLU, true, true>(tm_g, tm_u, tm_t, p, grid, static_cast<cudaStream_t>(stream));
 }

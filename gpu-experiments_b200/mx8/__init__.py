@@ -2,3 +2,5 @@
 from ._lib import LIB_PATH, Mx8Error, load  # noqa: F401
 from .ops import (device_status, gemm_grouped, kernel, kernel_transpose, mxfp8_quantize, schedule,  # noqa: F401
                   quantize_kernel)
+from .moe import (combine, dispatch_mlp_swiglu_combine_fwd, dispatch_quantize, fwd_epilogue,  # noqa: F401
+                  swiglu_quantize)

@@ -1,0 +1,129 @@
+"""Host-side mirror of the reference's MoE bindings (forward, routed experts) on top of the C ABI.
+
+The reference runs the whole forward as one persistent kernel; here it is a sequence of launches on
+the current stream — dispatch+quantize, grouped GEMM (gate, up) with quantizing epilogue,
+SwiGLU+quantize, grouped GEMM (down), combine — with the same inputs, outputs and tensor layouts.
+Cross-rank ordering (tokens ready before dispatch, combine finished before the epilogue) is the
+caller's barrier, exactly where the reference's harness has it
+(blackwell-ultra/022-moe-dispatch-mlp-swiglu-combine-mxfp8-bw.py:277-301).
+"""
+import ctypes
+
+import torch
+
+from . import _lib
+from .ops import _FP8, _SC, _chk, _stream, gemm_grouped
+
+
+def _ptr_array(ptrs):
+    arr = (ctypes.c_void_p * len(ptrs))()
+    for i, p in enumerate(ptrs):
+        arr[i] = int(p)
+    return arr
+
+
+def dispatch_quantize(x_ptrs, hidden, topk, schedule_peer_rank, schedule_peer_token_idx, num_tokens, capacity=None):
+    """Pull the routed token rows from every rank's token matrix (x_ptrs: list of device pointers,
+    peer-mapped for other GPUs) and quantize them both ways.
+    Returns (x_fp8 [cap, H], x_sc, x_fp8_t [H, cap], x_sc_t); rows beyond num_tokens are not written.
+    Stands in for dispatch_quantize_kernel (blackwell-ultra/022-…-mxfp8-bw.cu:717-828)."""
+    lib = _lib.load()
+    cap = int(capacity if capacity is not None else schedule_peer_rank.numel())
+    dev = schedule_peer_rank.device
+    x_fp8 = torch.empty(cap, hidden, dtype=torch.float8_e4m3fn, device=dev)
+    x_sc = torch.empty(cap // 128, hidden // 128, 32, 16, dtype=torch.uint8, device=dev)
+    x_fp8_t = torch.empty(hidden, cap, dtype=torch.float8_e4m3fn, device=dev)
+    x_sc_t = torch.empty(hidden // 128, cap // 128, 32, 16, dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(lib.mx8_moe_dispatch_quantize(
+            _ptr_array(x_ptrs), len(x_ptrs), hidden, topk, _chk(schedule_peer_rank, "schedule_peer_rank", (torch.int32,)),
+            _chk(schedule_peer_token_idx, "schedule_peer_token_idx", (torch.int32,)), _chk(num_tokens, "num_tokens", (torch.int32,)),
+            cap, x_fp8.data_ptr(), x_sc.data_ptr(), x_fp8_t.data_ptr(), x_sc_t.data_ptr(), _stream()), "dispatch_quantize")
+    return x_fp8, x_sc, x_fp8_t, x_sc_t
+
+
+def swiglu_quantize(gate_fp8, gate_sc, up_fp8, up_sc, num_rows=None, return_bf16=False):
+    """hidden = bf16(silu(dequant(gate)) * dequant(up)), re-quantized both ways.
+    Returns (hidden_fp8, hidden_sc, hidden_fp8_t, hidden_sc_t[, hidden_bf16]).
+    Stands in for swiglu_fwd<false> (blackwell-ultra/022-…-mxfp8-bw.cu:924-1129)."""
+    lib = _lib.load()
+    R, I = gate_fp8.shape
+    dev = gate_fp8.device
+    h_fp8 = torch.empty(R, I, dtype=torch.float8_e4m3fn, device=dev)
+    h_sc = torch.empty(R // 128, I // 128, 32, 16, dtype=torch.uint8, device=dev)
+    h_fp8_t = torch.empty(I, R, dtype=torch.float8_e4m3fn, device=dev)
+    h_sc_t = torch.empty(I // 128, R // 128, 32, 16, dtype=torch.uint8, device=dev)
+    h_bf16 = torch.empty(R, I, dtype=torch.bfloat16, device=dev) if return_bf16 else None
+    with torch.cuda.device(dev):
+        _lib.check(lib.mx8_swiglu_quantize(
+            _chk(gate_fp8, "gate_fp8", _FP8), _chk(gate_sc, "gate_sc", _SC, (R // 128, I // 128, 512)),
+            _chk(up_fp8, "up_fp8", _FP8, (R, I)), _chk(up_sc, "up_sc", _SC, (R // 128, I // 128, 512)), R, I,
+            _chk(num_rows, "num_rows", (torch.int32,)) if num_rows is not None else None,
+            h_fp8.data_ptr(), h_sc.data_ptr(), h_fp8_t.data_ptr(), h_sc_t.data_ptr(),
+            h_bf16.data_ptr() if return_bf16 else None, _stream()), "swiglu_quantize")
+    return (h_fp8, h_sc, h_fp8_t, h_sc_t) + ((h_bf16,) if return_bf16 else ())
+
+
+def combine(y_routed, schedule_peer_rank, schedule_peer_token_idx, num_tokens, combine_buffer_ptrs):
+    """Write every routed output row into the combine buffer of the rank that owns the token.
+    Stands in for combine_kernel (blackwell-ultra/022-…-mxfp8-bw.cu:830-922)."""
+    lib = _lib.load()
+    with torch.cuda.device(y_routed.device):
+        _lib.check(lib.mx8_moe_combine(
+            _chk(y_routed, "y_routed", (torch.bfloat16,)), _chk(schedule_peer_rank, "schedule_peer_rank", (torch.int32,)),
+            _chk(schedule_peer_token_idx, "schedule_peer_token_idx", (torch.int32,)), _chk(num_tokens, "num_tokens", (torch.int32,)),
+            y_routed.shape[1], _ptr_array(combine_buffer_ptrs), len(combine_buffer_ptrs), _stream()), "combine")
+
+
+def fwd_epilogue(y_shared, combine_buffer, topk_weights):
+    """fwd_epilogue(y_shared, combine_buffer, topk_weights) -> output
+    (blackwell-ultra/022-…-mxfp8-bw.cu:2842-2856, bound at :3029-3030).  y_shared may be None."""
+    lib = _lib.load()
+    T, k = topk_weights.shape
+    H = combine_buffer.shape[1]
+    out = torch.empty(T, H, dtype=torch.bfloat16, device=combine_buffer.device)
+    with torch.cuda.device(combine_buffer.device):
+        _lib.check(lib.mx8_moe_fwd_epilogue(
+            _chk(y_shared, "y_shared", (torch.bfloat16,), (T, H)) if y_shared is not None else None,
+            _chk(combine_buffer, "combine_buffer", (torch.bfloat16,), (T * k, H)),
+            _chk(topk_weights, "topk_weights", (torch.float32,)), out.data_ptr(), T, H, k, _stream()), "fwd_epilogue")
+    return out
+
+
+def dispatch_mlp_swiglu_combine_fwd(x, x_ptrs, combine_buffer, combine_buffer_ptrs,
+                                    w_shared_gate, w_routed_gate, w_routed_gate_sc,
+                                    w_shared_up, w_routed_up, w_routed_up_sc,
+                                    w_shared_down, w_routed_down, w_routed_down_sc,
+                                    schedule_peer_rank, schedule_peer_token_idx, num_tokens, tokens_per_expert,
+                                    topk, num_comm_sms=0, macrobatch_size=0, minibatch_size=0):
+    """Same arguments and the same 13 return values as the reference's binding
+    (blackwell-ultra/022-…-mxfp8-bw.cu:2016-2136, bound at :3001-3010):
+      (x_fp8_t_routed, x_sc_t_routed, gate_shared, gate_fp8_routed, gate_sc_routed, up_shared,
+       up_fp8_routed, up_sc_routed, hidden_shared, hidden_fp8_t_routed, hidden_sc_t_routed,
+       y_shared, y_routed)
+    Routed buffers have schedule_capacity rows.  num_comm_sms / macrobatch_size / minibatch_size tune
+    the reference's single-kernel schedule and have no effect here.  The shared expert (bf16, outside
+    the MXFP8 path) runs on torch's library GEMM when its weights are given, else those outputs are None."""
+    E, I, H = w_routed_gate.shape
+    cap = schedule_peer_rank.numel()
+    x_fp8, x_sc, x_fp8_t, x_sc_t = dispatch_quantize(x_ptrs, H, topk, schedule_peer_rank, schedule_peer_token_idx, num_tokens, cap)
+    dev = x.device
+    gate_fp8 = torch.empty(cap, I, dtype=torch.float8_e4m3fn, device=dev)
+    gate_sc = torch.empty(cap // 128, I // 128, 32, 16, dtype=torch.uint8, device=dev)
+    up_fp8 = torch.empty_like(gate_fp8)
+    up_sc = torch.empty_like(gate_sc)
+    gemm_grouped(x_fp8, x_sc, w_routed_gate, w_routed_gate_sc, gate_fp8, gate_sc, num_tokens, tokens_per_expert)
+    gemm_grouped(x_fp8, x_sc, w_routed_up, w_routed_up_sc, up_fp8, up_sc, num_tokens, tokens_per_expert)
+    h_fp8, h_sc, h_fp8_t, h_sc_t = swiglu_quantize(gate_fp8, gate_sc, up_fp8, up_sc, num_tokens)
+    y_routed = torch.empty(cap, H, dtype=torch.bfloat16, device=dev)
+    gemm_grouped(h_fp8, h_sc, w_routed_down, w_routed_down_sc, y_routed, None, num_tokens, tokens_per_expert)
+    combine(y_routed, schedule_peer_rank, schedule_peer_token_idx, num_tokens, combine_buffer_ptrs)
+    gate_shared = up_shared = hidden_shared = y_shared = None
+    if w_shared_gate is not None:
+        gate_shared = x @ w_shared_gate.t()
+        up_shared = x @ w_shared_up.t()
+        g = gate_shared.float()
+        hidden_shared = ((g / (torch.exp(-g) + 1.0)) * up_shared.float()).to(torch.bfloat16)
+        y_shared = hidden_shared @ w_shared_down.t()
+    return (x_fp8_t, x_sc_t, gate_shared, gate_fp8, gate_sc, up_shared, up_fp8, up_sc,
+            hidden_shared, h_fp8_t, h_sc_t, y_shared, y_routed)

@@ -97,6 +97,39 @@ MX8_API int mx8_gemm_grouped(const void* A, const void* A_sc, const void* B, con
                              int M, int N, int K, int c_dtype, const void* num_rows, const void* group_rows,
                              int num_groups, void* stream);
 
+/* MoE dispatch fused with quantize: row r of the routed activation matrix is token
+ * peer_token_idx[r] / topk of rank peer_rank[r] (all-zero when peer_rank[r] < 0); the rows are pulled
+ * from x_ptrs[rank] (HOST array of `world` device pointers to every rank's [tokens][hidden] bf16
+ * matrix; peer-mapped memory for other GPUs) and quantized both ways in one pass:
+ *   fp8 [capacity][hidden], sc; fp8_t [hidden][capacity], sc_t.  Only the first *num_tokens rows
+ * (device int32, a multiple of 256) are produced.  world <= 16.
+ * Replaces dispatch_quantize_kernel, blackwell-ultra/022-…-mxfp8-bw.cu:717-828. */
+MX8_API int mx8_moe_dispatch_quantize(const void* const* x_ptrs, int world, int hidden, int topk, const void* peer_rank,
+                                      const void* peer_token_idx, const void* num_tokens, int capacity, void* fp8,
+                                      void* sc, void* fp8_t, void* sc_t, void* stream);
+
+/* hidden = bf16( silu(dequant(gate)) * dequant(up) ) from two MXFP8 matrices [rows][cols], re-quantized
+ * both ways (hidden_fp8/sc blocks along cols, hidden_fp8_t/sc_t the transpose).  num_rows (device
+ * int32 or NULL) bounds the rows processed.  hidden_bf16 (may be NULL) receives the bf16 activation.
+ * Replaces swiglu_fwd<false>, blackwell-ultra/022-…-mxfp8-bw.cu:924-1129. */
+MX8_API int mx8_swiglu_quantize(const void* gate_fp8, const void* gate_sc, const void* up_fp8, const void* up_sc,
+                                int rows, int cols, const void* num_rows, void* hidden_fp8, void* hidden_sc,
+                                void* hidden_fp8_t, void* hidden_sc_t, void* hidden_bf16, void* stream);
+
+/* MoE combine: row r (< *num_tokens, peer_rank[r] >= 0) of y_routed [rows][hidden] bf16 is written to
+ * row peer_token_idx[r] of combine_ptrs[peer_rank[r]] (HOST array of `world` device pointers to every
+ * rank's [tokens*topk][hidden] bf16 buffer, peer-mapped for other GPUs).  The caller orders this call
+ * against the readers of those buffers (a cross-rank barrier), as the reference's harness does.
+ * Replaces combine_kernel, blackwell-ultra/022-…-mxfp8-bw.cu:830-922. */
+MX8_API int mx8_moe_combine(const void* y_routed, const void* peer_rank, const void* peer_token_idx, const void* num_tokens,
+                            int hidden, void* const* combine_ptrs, int world, void* stream);
+
+/* out[t] = bf16( y_shared[t] + sum_j topk_weights[t][j] * combine_buffer[t*topk + j] ); y_shared may be
+ * NULL (no shared expert).  topk_weights float32 [tokens][topk]; the other tensors bf16.
+ * Replaces fwd_epilogue, blackwell-ultra/022-…-mxfp8-bw.cu:2789-2856. */
+MX8_API int mx8_moe_fwd_epilogue(const void* y_shared, const void* combine_buffer, const void* topk_weights, void* out,
+                                 int tokens, int hidden, int topk, void* stream);
+
 /* Expert-parallel MoE routing schedule for the calling rank (int32 everywhere).
  *   topk_all [world][tokens][topk]: global expert ids chosen by every rank's tokens;
  *   this rank owns experts [rank*num_local_experts, (rank+1)*num_local_experts).

@@ -1,0 +1,50 @@
+"""CPU checks of the MoE oracle: the schedule's placement rule, padding, and the layer composition."""
+import torch
+
+from oracle import moe_oracle as MO
+from oracle import mx8_oracle as O
+
+
+def _topk(W, T, E, k, seed):
+    g = torch.Generator().manual_seed(seed)
+    return MO.route(torch.randn(W * T, E, generator=g), k)[0].view(W, T, k)
+
+
+def test_schedule_interleaves_source_ranks_round_by_round():
+    # 2 ranks, one local expert (id 0): rank 0 routes pairs 1 and 5 to it, rank 1 routes pairs 0, 2, 7
+    topk_all = torch.full((2, 4, 2), 9, dtype=torch.int32)
+    topk_all.view(2, 8)[0, [1, 5]] = 0
+    topk_all.view(2, 8)[1, [0, 2, 7]] = 0
+    pr, pt, nt, tpe, written = MO.schedule_ref(topk_all, 1, 512, 0)
+    assert pr[:5].tolist() == [0, 1, 0, 1, 1] and pt[:5].tolist() == [1, 0, 5, 2, 7]
+    assert int(nt) == 256 and tpe.tolist() == [256] and bool((pr[5:] == -1).all())
+
+
+def test_schedule_segments_are_padded_and_complete():
+    W, T, E_local, k = 4, 128, 4, 4
+    topk_all = _topk(W, T, W * E_local, k, 3)
+    for rank in range(W):
+        pr, pt, nt, tpe, written = MO.schedule_ref(topk_all, E_local, W * T * k, rank)
+        assert bool((tpe % 256 == 0).all()) and int(tpe.sum()) == int(nt)
+        n_local = int(((topk_all >= rank * E_local) & (topk_all < (rank + 1) * E_local)).sum())
+        assert int((pr >= 0).sum()) == n_local == int(written.sum())
+
+
+def test_layer_composition_shapes_and_padding_rows():
+    W, T, H, I, k, E_local, rank = 2, 128, 256, 128, 2, 2, 0
+    topk_all = _topk(W, T, W * E_local, k, 5)
+    x_all = torch.stack([O.make_input(T, H, seed=r) for r in range(W)])
+    pr, pt, nt, tpe, _ = MO.schedule_ref(topk_all, E_local, 1024, rank)
+    n = int(nt)
+    xr = MO.dispatch_ref(x_all, pr, pt, n, k)
+    assert not xr[pr[:n] < 0].any()
+    q = lambda w: O.quantize_both(w)[:2]
+    wg = q(torch.stack([O.make_input(I, H, seed=10 + e, std=H ** -0.5) for e in range(E_local)]))
+    wu = q(torch.stack([O.make_input(I, H, seed=20 + e, std=H ** -0.5) for e in range(E_local)]))
+    wd = q(torch.stack([O.make_input(H, I, seed=30 + e, std=I ** -0.5) for e in range(E_local)]))
+    ref = MO.expert_mlp_ref(xr, tpe, wg, wu, wd)
+    assert ref["y"].shape == (n, H) and ref["hidden_fp8_t"].shape == (I, n)
+    assert not ref["y"][pr[:n] < 0].any()            # zero rows stay zero through the whole MLP
+    w = torch.softmax(torch.randn(T, k), -1)
+    out = MO.fwd_epilogue_ref(torch.zeros(T, H, dtype=torch.bfloat16), torch.ones(T * k, H, dtype=torch.bfloat16), w)
+    assert torch.allclose(out.float(), torch.ones(T, H), atol=1e-2)
