@@ -386,13 +386,129 @@ def bench_gemm(args, world, rank, local, peaks, with_cpu):
     return line
 
 
+def bench_ffn(args, world, rank, local, peaks):
+    """Configuration 4: Llama-70B-shaped FFN, tokens sharded across ranks, weights replicated and
+    pre-quantized; X is quantized per step and the intermediate H never exists in bf16: the first
+    GEMM's epilogue emits MXFP8 directly."""
+    import mx8
+    dev = torch.device("cuda", local)
+    T, H, F = 16384 // world, 8192, 28672
+    g = torch.Generator(device=dev).manual_seed(4000 + rank)
+    x = torch.randn(T, H, device=dev, generator=g).to(torch.bfloat16)
+    gw = torch.Generator(device=dev).manual_seed(4100)
+    w1 = (torch.randn(F, H, device=dev, generator=gw) * 0.02).to(torch.bfloat16)
+    w1q, w1s, _, _ = mx8.mxfp8_quantize(w1, True, False)
+    del w1
+    w2 = (torch.randn(H, F, device=dev, generator=gw) * 0.02).to(torch.bfloat16)
+    w2q, w2s, _, _ = mx8.mxfp8_quantize(w2, True, False)
+    del w2
+    xq = torch.empty(T, H, dtype=torch.float8_e4m3fn, device=dev)
+    xs = torch.empty(T // 128, H // 128, 32, 16, dtype=torch.uint8, device=dev)
+    hq = torch.empty(T, F, dtype=torch.float8_e4m3fn, device=dev)
+    hs = torch.empty(T // 128, F // 128, 32, 16, dtype=torch.uint8, device=dev)
+    y = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+
+    def step(_):
+        mx8.mxfp8_quantize(x, xq, xs, None, None, True, False)
+        mx8.gemm_grouped(xq, xs, w1q, w1s, hq, hs)       # H = X W1^T, emitted as MXFP8
+        mx8.kernel(hq, hs, w2q, w2s, y)                  # Y = H W2^T
+
+    steps = max(3, args.steps // 20)
+    for i in range(3):
+        step(i)
+    ms = timed(step, steps, world) / steps
+    mx8.device_status()
+    flops = 2.0 * 2.0 * T * H * F
+    achieved = flops / (ms * 1e-3) / 1e12
+    return {"metric": "mxfp8_ffn_throughput", "value": world * achieved, "unit": "TFLOP/s", "ms_per_step": ms, "steps": steps,
+            "scaling": "strong",
+            "config": {"workload": f"FFN X[{T}x{H}] bf16 -> quantize -> [{F}x{H}] GEMM with MXFP8-quantizing epilogue -> [{H}x{F}] GEMM -> bf16, per GPU",
+                       "sharding": "tokens split across GPUs, weights replicated, no collective"},
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": 2.0 * peaks["bf16_tflops"], "unit": "TFLOP/s",
+                         "frac": achieved / (2.0 * peaks["bf16_tflops"]), "frac_of_nominal_4500": achieved / 4500.0, "traffic": None},
+            "gpu_launches": 3 * steps}
+
+
+def bench_moe(args, world, rank, local, peaks):
+    """Configuration 5: DeepSeek-V3-like expert-parallel layer, 256 experts and 32768 tokens split over
+    the ranks, top-8 routing, routed experts only.  A step is the reference harness's run_fwd_once."""
+    import mx8
+    dev = torch.device("cuda", local)
+    E_total, H, I, k = 256, 7168, 2048, 8
+    T, E = 32768 // world, E_total // world
+    cap = ((T * k * max(2, world // 4)) // 256) * 256
+    g = torch.Generator(device=dev).manual_seed(1234 + rank)
+    logits = torch.randn(T, E_total, device=dev, generator=g)
+    if world > 1:
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+        x = symm_mem.empty(T, H, dtype=torch.bfloat16, device=dev)
+        x.normal_(generator=g)
+        x_ptrs = list(symm_mem.rendezvous(x, dist.group.WORLD.group_name).buffer_ptrs)
+        cb = symm_mem.empty(T * k, H, dtype=torch.bfloat16, device=dev)
+        cb_ptrs = list(symm_mem.rendezvous(cb, dist.group.WORLD.group_name).buffer_ptrs)
+    else:
+        x = torch.randn(T, H, device=dev, generator=g).to(torch.bfloat16)
+        cb = torch.empty(T * k, H, dtype=torch.bfloat16, device=dev)
+        x_ptrs, cb_ptrs = [x.data_ptr()], [cb.data_ptr()]
+
+    def make_w(rows, cols):
+        q = torch.empty(E, rows, cols, dtype=torch.float8_e4m3fn, device=dev)
+        sc = torch.empty(E * rows // 128, cols // 128, 32, 16, dtype=torch.uint8, device=dev)
+        for e0 in range(0, E, 16):                       # quantize in slices to bound the bf16 temporary
+            n = min(16, E - e0)
+            w = (torch.randn(n, rows, cols, device=dev, generator=g) * 0.02).to(torch.bfloat16)
+            mx8.mxfp8_quantize(w, q[e0:e0 + n], sc[e0 * rows // 128:(e0 + n) * rows // 128], None, None, True, False)
+        return q, sc
+
+    wg, wgs = make_w(I, H)
+    wu, wus = make_w(I, H)
+    wd, wds = make_w(H, I)
+    vals, ids = torch.topk(logits, k, dim=1)            # the reference's router: top-k, softmax over the k values
+    weights = torch.softmax(vals.float(), dim=-1)
+    ids = ids.to(torch.int32)
+    ids_all = torch.empty(world, T, k, dtype=torch.int32, device=dev)
+
+    def step(_):
+        if world > 1:
+            import torch.distributed as dist
+            dist.all_gather_into_tensor(ids_all, ids)
+        else:
+            ids_all.copy_(ids.view(1, T, k))
+        pr, pt, nt, tpe = mx8.schedule(ids_all, E, cap, rank)
+        mx8.dispatch_mlp_swiglu_combine_fwd(x, x_ptrs, cb, cb_ptrs, None, wg, wgs, None, wu, wus, None, wd, wds,
+                                            pr, pt, nt, tpe, k)
+        if world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        return mx8.fwd_epilogue(None, cb, weights)
+
+    steps = max(3, args.steps // 40)
+    for i in range(3):
+        step(i)
+    ms = timed(step, steps, world) / steps
+    mx8.device_status()
+    flops_total = 6.0 * (32768 * k) * H * I
+    value = flops_total / (ms * 1e-3) / 1e12
+    per_gpu = value / world
+    return {"metric": "mxfp8_moe_forward_throughput", "value": value, "unit": "TFLOP/s", "ms_per_step": ms, "steps": steps,
+            "scaling": "strong",
+            "config": {"workload": f"MoE forward, {E_total} experts / {world} GPUs, hidden {H}, intermediate {I}, 32768 tokens, top-{k}, routed experts only",
+                       "flops": "6 * routed rows * hidden * intermediate (padding rows not counted)",
+                       "sharding": "experts and tokens split across GPUs; dispatch pulls and combine pushes over peer-mapped memory"},
+            "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": 2.0 * peaks["bf16_tflops"], "unit": "TFLOP/s",
+                         "frac": per_gpu / (2.0 * peaks["bf16_tflops"]), "frac_of_nominal_4500": per_gpu / 4500.0, "traffic": None},
+            "gpu_launches": 10 * steps}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="mx8", choices=["mx8", "reference"])
-    ap.add_argument("--workload", default="quantize", choices=["quantize", "gemm"])
+    ap.add_argument("--workload", default="quantize", choices=["quantize", "gemm", "ffn", "moe"])
+    ap.add_argument("--no-layers", action="store_true", help="skip the FFN and MoE objects of the quantize line")
     ap.add_argument("--no-gemm", action="store_true", help="skip the GEMM object of the quantize line")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
@@ -414,8 +530,20 @@ def main():
             line["gemm"] = {k: g[k] for k in ("metric", "value", "unit", "ms_per_step", "scaling", "config", "roofline", "e2e",
                                               "gpu_launches", "clocks", "cpu_baseline") if k in g}
             line["gpu_launches"] += g["gpu_launches"]
-    else:
+        if not args.no_layers:
+            for name, fn in (("ffn", bench_ffn), ("moe", bench_moe)):
+                try:
+                    torch.cuda.empty_cache()
+                    line[name] = fn(args, world, rank, local, peaks)
+                    line["gpu_launches"] += line[name]["gpu_launches"]
+                except Exception as ex:      # a layer benchmark must not take the headline line down
+                    line[name] = {"error": f"{type(ex).__name__}: {ex}"[:300]}
+    elif args.workload == "gemm":
         line = bench_gemm(args, world, rank, local, peaks, with_cpu)
+    else:
+        line = (bench_ffn if args.workload == "ffn" else bench_moe)(args, world, rank, local, peaks)
+        line.update({"n_gpus": world, "warmup": args.warmup, "higher_is_better": True, "vs_baseline": None, "dtype": "fp8_e4m3 x ue8m0",
+                     "data": "synthetic"})
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -348,11 +348,14 @@ __device__ __forceinline__ uint32_t cvt_e4m3x2(float lo, float hi) {
     asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(d) : "f"(hi), "f"(lo));
     return d;
 }
-// one E4M3 byte -> float (exact)
-__device__ __forceinline__ float e4m3_to_float(uint32_t b) {
-    uint32_t h2;
-    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(static_cast<uint16_t>(b)));
-    return __half2float(__ushort_as_half(static_cast<unsigned short>(h2 & 0xFFFFu)));
+// four packed E4M3 bytes -> four floats (exact)
+__device__ __forceinline__ void e4m3x4_to_float(uint32_t b4, float (&f)[4]) {
+    uint32_t lo, hi;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(lo) : "h"(static_cast<uint16_t>(b4 & 0xFFFFu)));
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(hi) : "h"(static_cast<uint16_t>(b4 >> 16)));
+    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&lo));
+    const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&hi));
+    f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
 }
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");

@@ -56,6 +56,9 @@ struct Params {
 };
 
 constexpr int SRC_DENSE = 0, SRC_GATHER = 1, SRC_SWIGLU = 2;
+// producer warps: the gather source looks two indices up per row before it can issue a copy, so
+// several warps work on different slabs to keep enough copies in flight
+__host__ __device__ constexpr int producer_warps(int src) { return src == SRC_GATHER ? 4 : 1; }
 
 template <int W, int D>
 struct Smem {
@@ -86,7 +89,7 @@ __device__ __forceinline__ void tile_coords(int t, const Params& p, int tiles_r,
 }
 
 template <int W, int D, int SRC, bool ROW, bool COL>
-__global__ void __launch_bounds__(32 + W * 32, 1)
+__global__ void __launch_bounds__((producer_warps(SRC) + W) * 32, 1)
 quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ CUtensorMap tm_in2,
                 const __grid_constant__ CUtensorMap tm_t, const Params p) {
     using L = Smem<W, D>;
@@ -118,26 +121,29 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
     const int my_tiles = (num_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
     const int my_slabs = my_tiles * 4;
 
-    if (tid < 32) {
+    constexpr int P = producer_warps(SRC);
+    if (tid < 32 * P) {
         // ---------------------------------------------------------------- producer
         if constexpr (SRC == SRC_GATHER) {
             // every lane fetches one row of the slab (256 bytes) from the rank that owns the token,
             // straight from that rank's memory; rows without a source are filled with zeros
-            for (int n = 0; n < my_slabs; ++n) {
+            const int pw = tid >> 5, pl = tid & 31;              // producer warp pw takes slabs pw, pw + P, ...
+            for (int n = pw; n < my_slabs; n += P) {
                 const int slot = n % S;
                 const uint32_t ph = (n / S) & 1;
-                int ok = 1;
-                if (tid == 0) ok = mbar_wait(empty0 + slot * 8, ph ^ 1, ab, DEV_TIMEOUT_EMPTY) ? 1 : 0;
-                ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
-                if (!ok) break;
                 const int t = static_cast<int>(blockIdx.x) + (n >> 2) * static_cast<int>(gridDim.x);
                 int tr, tc;
                 tile_coords(t, p, tiles_r, tr, tc);
-                const int row = tr * TILE + (n & 3) * SLAB_ROWS + tid;
-                const int pr = p.peer_rank[row];
-                const uint32_t dst = base + L::ring + slot * SLOT_BYTES + tid * 256;
+                const int row = tr * TILE + (n & 3) * SLAB_ROWS + pl;
+                const int pr = p.peer_rank[row];                 // issued before the wait: the look-up overlaps it
+                const int tok = p.peer_token_idx[row];
+                int ok = 1;
+                if (pl == 0) ok = mbar_wait(empty0 + slot * 8, ph ^ 1, ab, DEV_TIMEOUT_EMPTY) ? 1 : 0;
+                ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+                if (!ok) break;
+                const uint32_t dst = base + L::ring + slot * SLOT_BYTES + pl * 256;
                 if (pr >= 0) {
-                    const uint8_t* s = p.src[pr] + (static_cast<size_t>(p.peer_token_idx[row] / p.topk) * p.N + tc * TILE) * 2;
+                    const uint8_t* s = p.src[pr] + (static_cast<size_t>(tok / p.topk) * p.N + tc * TILE) * 2;
                     mbar_arrive_expect_tx(full0 + slot * 8, 256);
                     bulk_load_1d(dst, s, 256, full0 + slot * 8);
                 } else {
@@ -169,7 +175,7 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
     }
 
     // -------------------------------------------------------------------- consumer warp
-    const int w = (tid >> 5) - 1;
+    const int w = (tid >> 5) - P;
     const int l = tid & 31;
     const uint32_t tstage = base + L::tstage + w * TSTAGE_BYTES;
     uint8_t* scstage_ptr = base_ptr + L::scstage + w * SCSTAGE_BYTES;
@@ -200,12 +206,13 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
                 asm volatile("ld.shared.b32 %0, [%1];" : "=r"(u4) : "r"(slot_addr + SLOT_BYTES / 2 + i * 128 + l * 4));
                 const float gs = __uint_as_float(((__shfl_sync(0xFFFFFFFFu, gw, i) >> sh) & 0xFFu) << 23);
                 const float us = __uint_as_float(((__shfl_sync(0xFFFFFFFFu, uw, i) >> sh) & 0xFFu) << 23);
-                float h[4];
+                float gf[4], uf[4], h[4];
+                e4m3x4_to_float(g4, gf);
+                e4m3x4_to_float(u4, uf);
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    const float g = e4m3_to_float((g4 >> (8 * e)) & 0xFFu) * gs;
-                    const float u = e4m3_to_float((u4 >> (8 * e)) & 0xFFu) * us;
-                    h[e] = (g / (1.0f + expf(-g))) * u;
+                    const float g = gf[e] * gs;
+                    h[e] = __fdividef(g, 1.0f + __expf(-g)) * (uf[e] * us);
                 }
                 c[i][0] = pack_bf16x2(h[0], h[1]);
                 c[i][1] = pack_bf16x2(h[2], h[3]);
@@ -326,7 +333,7 @@ static int launch(const CUtensorMap& tm_in, const CUtensorMap& tm_in2, const CUt
         }
         configured[dev & 63] = true;
     }
-    kern<<<grid, 32 + W * 32, smem, stream>>>(tm_in, tm_in2, tm_t, p);
+    kern<<<grid, (producer_warps(SRC) + W) * 32, smem, stream>>>(tm_in, tm_in2, tm_t, p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
         note_cuda_error("quantize launch", cudaGetErrorString(e));

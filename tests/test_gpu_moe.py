@@ -151,10 +151,11 @@ def test_swiglu_quantize():
     n = 384
     want = MO.swiglu_ref(gq[:n], gsc[:n // 128], uq[:n], usc[:n // 128])
     got = h_bf16[:n].cpu()
-    # expf and the division differ from the host library in the last fp32 bit at most: after rounding
-    # to bf16 a few elements may land on the neighbouring value
+    # the kernel uses the fast exponential and reciprocal (as the reference, which builds with
+    # fast math): relative error ~1e-6 in fp32, so after rounding to bf16 a small share of elements
+    # lands on the neighbouring value
     diff_ulp = (got.view(torch.int16).int() - want.view(torch.int16).int()).abs()
-    assert int(diff_ulp.max()) <= 1 and float((diff_ulp > 0).float().mean()) < 1e-3
+    assert int(diff_ulp.max()) <= 1 and float((diff_ulp > 0).float().mean()) < 5e-3
     # the quantized outputs are exactly the oracle's quantization of the kernel's own bf16 activation
     q, sc, qt, sct = O.quantize_both(got)
     assert torch.equal(h_fp8[:n].view(torch.uint8).cpu(), q) and torch.equal(h_sc[:n // 128].cpu(), sc)
