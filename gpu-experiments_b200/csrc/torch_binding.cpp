@@ -10,6 +10,8 @@
 //   kernel(A, A_fp8, A_sc[, A_t_fp8, A_t_sc]) -> None     blackwell/018-mxfp8-quantize.cu:288-293,
 //                                                         blackwell/038-mxfp8-quantize-combined.cu:397-399
 //   kernel_transpose(A, A_t_fp8, A_t_sc) -> None          blackwell/018-mxfp8-quantize.cu:294-300
+//   schedule(...), dispatch_mlp_swiglu_combine_fwd(...), fwd_epilogue(...)
+//                                                         blackwell-ultra/022-…-mxfp8-bw.cu:2996-3030 (forward, routed experts)
 // Errors raise RuntimeError (the reference prints and exits).
 #include <c10/cuda/CUDAGuard.h>
 #include <c10/cuda/CUDAStream.h>
@@ -18,6 +20,7 @@
 #include <optional>
 #include <string>
 #include <tuple>
+#include <vector>
 
 #include "../../include/mx8.h"
 
@@ -119,6 +122,110 @@ void kernel_transpose(const at::Tensor& A, const at::Tensor& A_t_fp8, const at::
     quantize_into(A, at::Tensor(), at::Tensor(), A_t_fp8, A_t_sc, false, true, MX8_SCALE_RCEIL);
 }
 
+// ---------------------------------------------------------------------------------------------
+// MoE forward (routed experts) with the reference's binding signatures
+// (blackwell-ultra/022-moe-dispatch-mlp-swiglu-combine-mxfp8-bw.cu:2996-3030)
+
+const void* iptr(const at::Tensor& t, const char* name) {
+    TORCH_CHECK(t.defined() && t.is_cuda() && t.scalar_type() == at::kInt && t.is_contiguous(), name, " must be a contiguous int32 CUDA tensor");
+    return t.data_ptr();
+}
+
+std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> schedule(const at::Tensor& topk_all, int num_local_experts,
+                                                                    int schedule_capacity, int rank) {
+    TORCH_CHECK(topk_all.dim() == 3, "topk_all must be [world, tokens, topk]");
+    c10::cuda::CUDAGuard guard(topk_all.device());
+    const int world = static_cast<int>(topk_all.size(0));
+    auto opt = topk_all.options().dtype(at::kInt);
+    at::Tensor peer_rank = at::empty({schedule_capacity}, opt), peer_tok = at::empty({schedule_capacity}, opt);
+    at::Tensor num_tokens = at::empty({1}, opt), tpe = at::empty({num_local_experts}, opt);
+    at::Tensor scratch = at::empty({static_cast<int64_t>(num_local_experts) * (world + 1)}, opt);
+    check(mx8_moe_schedule(iptr(topk_all, "topk_all"), world, static_cast<int>(topk_all.size(1)), static_cast<int>(topk_all.size(2)),
+                           num_local_experts, schedule_capacity, rank, peer_rank.data_ptr(), peer_tok.data_ptr(),
+                           num_tokens.data_ptr(), tpe.data_ptr(), scratch.data_ptr(), stream()),
+          "schedule");
+    return {peer_rank, peer_tok, num_tokens, tpe};
+}
+
+void grouped(const at::Tensor& A, const at::Tensor& A_sc, const at::Tensor& B, const at::Tensor& B_sc, const at::Tensor& C,
+             const at::Tensor& C_sc, const at::Tensor& num_tokens, const at::Tensor& tokens_per_expert) {
+    const bool q = C_sc.defined();
+    check(mx8_gemm_grouped(A.data_ptr(), A_sc.data_ptr(), B.data_ptr(), B_sc.data_ptr(), C.data_ptr(), q ? C_sc.data_ptr() : nullptr,
+                           static_cast<int>(A.size(0)), static_cast<int>(B.size(1)), static_cast<int>(A.size(1)),
+                           q ? MX8_C_MXFP8 : MX8_C_BF16, num_tokens.data_ptr(), tokens_per_expert.data_ptr(),
+                           static_cast<int>(B.size(0)), stream()),
+          "expert grouped gemm");
+}
+
+std::vector<at::Tensor> dispatch_mlp_swiglu_combine_fwd(
+    const at::Tensor& x, const std::vector<int64_t>& x_ptrs, const at::Tensor& combine_buffer,
+    const std::vector<int64_t>& combine_buffer_ptrs, const std::optional<at::Tensor>& w_shared_gate, const at::Tensor& w_routed_gate,
+    const at::Tensor& w_routed_gate_sc, const std::optional<at::Tensor>& w_shared_up, const at::Tensor& w_routed_up,
+    const at::Tensor& w_routed_up_sc, const std::optional<at::Tensor>& w_shared_down, const at::Tensor& w_routed_down,
+    const at::Tensor& w_routed_down_sc, const at::Tensor& schedule_peer_rank, const at::Tensor& schedule_peer_token_idx,
+    const at::Tensor& num_tokens, const at::Tensor& tokens_per_expert, int topk, int /*num_comm_sms*/, int /*macrobatch_size*/,
+    int /*minibatch_size*/) {
+    TORCH_CHECK(w_routed_gate.dim() == 3 && w_routed_down.dim() == 3, "routed weights must be [E, rows, cols]");
+    TORCH_CHECK(x_ptrs.size() == combine_buffer_ptrs.size() && !x_ptrs.empty() && x_ptrs.size() <= 16, "1..16 ranks");
+    c10::cuda::CUDAGuard guard(x.device());
+    const int64_t I = w_routed_gate.size(1), H = w_routed_gate.size(2), cap = schedule_peer_rank.size(0);
+    auto fp8 = x.options().dtype(at::kFloat8_e4m3fn);
+    auto u8 = x.options().dtype(at::kByte);
+    at::Tensor x_fp8 = at::empty({cap, H}, fp8), x_sc = at::empty({cap / 128, H / 128, 32, 16}, u8);
+    at::Tensor x_fp8_t = at::empty({H, cap}, fp8), x_sc_t = at::empty({H / 128, cap / 128, 32, 16}, u8);
+    at::Tensor gate_fp8 = at::empty({cap, I}, fp8), gate_sc = at::empty({cap / 128, I / 128, 32, 16}, u8);
+    at::Tensor up_fp8 = at::empty({cap, I}, fp8), up_sc = at::empty({cap / 128, I / 128, 32, 16}, u8);
+    at::Tensor h_fp8 = at::empty({cap, I}, fp8), h_sc = at::empty({cap / 128, I / 128, 32, 16}, u8);
+    at::Tensor h_fp8_t = at::empty({I, cap}, fp8), h_sc_t = at::empty({I / 128, cap / 128, 32, 16}, u8);
+    at::Tensor y_routed = at::empty({cap, H}, x.options());
+    std::vector<const void*> xp(x_ptrs.size());
+    std::vector<void*> cp(x_ptrs.size());
+    for (size_t i = 0; i < x_ptrs.size(); ++i) {
+        xp[i] = reinterpret_cast<const void*>(x_ptrs[i]);
+        cp[i] = reinterpret_cast<void*>(combine_buffer_ptrs[i]);
+    }
+    const int world = static_cast<int>(x_ptrs.size());
+    check(mx8_moe_dispatch_quantize(xp.data(), world, static_cast<int>(H), topk, iptr(schedule_peer_rank, "schedule_peer_rank"),
+                                    iptr(schedule_peer_token_idx, "schedule_peer_token_idx"), iptr(num_tokens, "num_tokens"),
+                                    static_cast<int>(cap), x_fp8.data_ptr(), x_sc.data_ptr(), x_fp8_t.data_ptr(), x_sc_t.data_ptr(), stream()),
+          "dispatch + quantize");
+    grouped(x_fp8, x_sc, w_routed_gate, w_routed_gate_sc, gate_fp8, gate_sc, num_tokens, tokens_per_expert);
+    grouped(x_fp8, x_sc, w_routed_up, w_routed_up_sc, up_fp8, up_sc, num_tokens, tokens_per_expert);
+    check(mx8_swiglu_quantize(gate_fp8.data_ptr(), gate_sc.data_ptr(), up_fp8.data_ptr(), up_sc.data_ptr(), static_cast<int>(cap),
+                              static_cast<int>(I), num_tokens.data_ptr(), h_fp8.data_ptr(), h_sc.data_ptr(), h_fp8_t.data_ptr(),
+                              h_sc_t.data_ptr(), nullptr, stream()),
+          "swiglu + quantize");
+    grouped(h_fp8, h_sc, w_routed_down, w_routed_down_sc, y_routed, at::Tensor(), num_tokens, tokens_per_expert);
+    check(mx8_moe_combine(y_routed.data_ptr(), schedule_peer_rank.data_ptr(), schedule_peer_token_idx.data_ptr(), num_tokens.data_ptr(),
+                          static_cast<int>(H), cp.data(), world, stream()),
+          "combine");
+    // shared expert: bf16, outside the MXFP8 path; torch's library GEMM when weights are given
+    at::Tensor gate_shared, up_shared, hidden_shared, y_shared;
+    if (w_shared_gate.has_value() && w_shared_up.has_value() && w_shared_down.has_value()) {
+        gate_shared = at::matmul(x, w_shared_gate->t());
+        up_shared = at::matmul(x, w_shared_up->t());
+        at::Tensor g = gate_shared.to(at::kFloat);
+        hidden_shared = (g / (at::exp(-g) + 1.0) * up_shared.to(at::kFloat)).to(at::kBFloat16);
+        y_shared = at::matmul(hidden_shared, w_shared_down->t());
+    }
+    return {x_fp8_t, x_sc_t, gate_shared, gate_fp8, gate_sc, up_shared, up_fp8, up_sc, hidden_shared, h_fp8_t, h_sc_t, y_shared, y_routed};
+}
+
+at::Tensor fwd_epilogue(const std::optional<at::Tensor>& y_shared, const at::Tensor& combine_buffer, const at::Tensor& topk_weights) {
+    TORCH_CHECK(topk_weights.dim() == 2 && topk_weights.scalar_type() == at::kFloat && topk_weights.is_contiguous(), "topk_weights float32 [tokens, topk]");
+    TORCH_CHECK(combine_buffer.scalar_type() == at::kBFloat16 && combine_buffer.is_contiguous(), "combine_buffer must be contiguous bf16");
+    c10::cuda::CUDAGuard guard(combine_buffer.device());
+    const int64_t T = topk_weights.size(0), k = topk_weights.size(1), H = combine_buffer.size(1);
+    TORCH_CHECK(combine_buffer.size(0) == T * k, "combine_buffer must be [tokens * topk, hidden]");
+    at::Tensor out = at::empty({T, H}, combine_buffer.options());
+    const void* ys = nullptr;
+    if (y_shared.has_value() && y_shared->defined()) ys = dptr(*y_shared, "y_shared", T * H);
+    check(mx8_moe_fwd_epilogue(ys, combine_buffer.data_ptr(), topk_weights.data_ptr(), out.data_ptr(), static_cast<int>(T),
+                               static_cast<int>(H), static_cast<int>(k), stream()),
+          "fwd_epilogue");
+    return out;
+}
+
 int device_status() {
     int v = 0;
     int rc = mx8_device_status(&v, stream());
@@ -138,6 +245,16 @@ PYBIND11_MODULE(_C, m) {
     m.def("kernel", &kernel, "", pybind11::arg("a0"), pybind11::arg("a1"), pybind11::arg("a2"),
           pybind11::arg("a3") = std::nullopt, pybind11::arg("a4") = std::nullopt);
     m.def("kernel_transpose", &kernel_transpose);
+    m.def("schedule", &schedule, "", pybind11::arg("topk_all"), pybind11::arg("num_local_experts"), pybind11::arg("schedule_capacity"),
+          pybind11::arg("rank"));
+    m.def("dispatch_mlp_swiglu_combine_fwd", &dispatch_mlp_swiglu_combine_fwd, "", pybind11::arg("x"), pybind11::arg("x_ptrs"),
+          pybind11::arg("combine_buffer"), pybind11::arg("combine_buffer_ptrs"), pybind11::arg("w_shared_gate"),
+          pybind11::arg("w_routed_gate"), pybind11::arg("w_routed_gate_sc"), pybind11::arg("w_shared_up"), pybind11::arg("w_routed_up"),
+          pybind11::arg("w_routed_up_sc"), pybind11::arg("w_shared_down"), pybind11::arg("w_routed_down"),
+          pybind11::arg("w_routed_down_sc"), pybind11::arg("schedule_peer_rank"), pybind11::arg("schedule_peer_token_idx"),
+          pybind11::arg("num_tokens"), pybind11::arg("tokens_per_expert"), pybind11::arg("topk"), pybind11::arg("num_comm_sms") = 0,
+          pybind11::arg("macrobatch_size") = 0, pybind11::arg("minibatch_size") = 0);
+    m.def("fwd_epilogue", &fwd_epilogue, "", pybind11::arg("y_shared"), pybind11::arg("combine_buffer"), pybind11::arg("topk_weights"));
     m.def("device_status", &device_status);
     m.def("version", []() { return std::string(mx8_version()); });
 }

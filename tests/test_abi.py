@@ -83,7 +83,8 @@ def test_torch_module_mirrors_reference_bindings(lib):
     if not os.path.exists(mod.torch_binding_path()):
         mod.build_torch_binding()
     from mx8 import _C
-    for name in ("mxfp8_quantize", "kernel", "kernel_transpose", "device_status", "version"):
+    for name in ("mxfp8_quantize", "kernel", "kernel_transpose", "schedule", "dispatch_mlp_swiglu_combine_fwd", "fwd_epilogue",
+                 "device_status", "version"):
         assert hasattr(_C, name)
     assert _C.version().startswith("mx8")
     x = torch.zeros(128, 128, dtype=torch.bfloat16)

@@ -75,3 +75,34 @@ def test_errors_raise_runtime_error(C):
     x = torch.zeros(100, 128, dtype=torch.bfloat16, device=DEV)
     with pytest.raises(RuntimeError):
         C.mxfp8_quantize(x, True, False)
+
+
+def test_moe_forward_through_the_cpp_module(C):
+    # the reference harness's run_fwd_once with one rank: schedule -> fused forward -> epilogue
+    from oracle import moe_oracle as MO
+    T, H, I, k, E = 256, 512, 256, 4, 4
+    g = torch.Generator().manual_seed(3)
+    ids, w = MO.route(torch.randn(T, E, generator=g), k)
+    x_cpu = O.make_input(T, H, seed=5)
+    x = x_cpu.to(DEV)
+    cb = torch.zeros(T * k, H, dtype=torch.bfloat16, device=DEV)
+    ws = []
+    for seed, (r, c) in ((10, (I, H)), (20, (I, H)), (30, (H, I))):
+        wt = torch.stack([O.make_input(r, c, seed=seed + e, std=c ** -0.5) for e in range(E)])
+        ws.append(C.mxfp8_quantize(wt.to(DEV), True, False)[:2])
+    cap = ((T * k) // 256 + E) * 256
+    pr, pt, nt, tpe = C.schedule(ids.view(1, T, k).to(DEV), E, cap, 0)
+    outs = C.dispatch_mlp_swiglu_combine_fwd(x, [x.data_ptr()], cb, [cb.data_ptr()], None, ws[0][0], ws[0][1], None, ws[1][0], ws[1][1],
+                                             None, ws[2][0], ws[2][1], pr, pt, nt, tpe, k, 40, 8 * 16384, 16384)
+    out = C.fwd_epilogue(None, cb, w.to(DEV))
+    assert C.device_status() == 0 and len(outs) == 13 and outs[2] is None
+    n = int(nt)
+    rpr, rpt, rnt, rtpe, _ = MO.schedule_ref(ids.view(1, T, k), E, cap, 0)
+    assert torch.equal(pr.cpu(), rpr) and n == int(rnt)
+    ref = MO.expert_mlp_ref(MO.dispatch_ref(x_cpu.view(1, T, H), rpr, rpt, n, k), rtpe,
+                            *[(q.view(torch.uint8).cpu(), s.cpu()) for q, s in ws])
+    assert torch.equal(outs[0][:, :n].view(torch.uint8).cpu(), ref["x_fp8_t"])
+    assert O.rel_frobenius(outs[12][:n].cpu(), ref["y"]) < 1e-2
+    cb_ref = MO.combine_ref([ref["y"]], [rpr], [rpt], 0, T, k)
+    ref_out = MO.fwd_epilogue_ref(torch.zeros(T, H, dtype=torch.bfloat16), cb_ref, w)
+    assert O.rel_frobenius(out.cpu(), ref_out) < 1e-2
