@@ -309,6 +309,14 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
     else
         asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
+// Same, arriving only on the issuing CTA's barrier.
+template <int CG>
+__device__ __forceinline__ void tc_commit_local(uint32_t bar) {
+    if constexpr (CG == 2)
+        asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+    else
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
 // 32 lanes x 32 consecutive 32-bit columns: thread `lane` of the warp receives row (lane base + lane).
 __device__ __forceinline__ void tc_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile(
