@@ -70,7 +70,11 @@ struct Cfg {
 struct Params {
     int tiles_m, tiles_n, k_steps;      // tile grid (tile = 128*CG x 256) and K / 128
     int group_m;                        // rasterisation: tiles_m rows per supergroup
-    int c_mode;                         // 0 bf16, 1 f32, 2 MXFP8 (E4M3 bytes + scale tiles, blocks along N)
+    int c_mode;                         // 0 bf16, 1 f32, 2 MXFP8 (E4M3 bytes + scale tiles, blocks along N),
+                                        // 3 bf16 rows scattered to the ranks that own the tokens (MoE combine)
+    const int* sc_peer_rank;            // c_mode 3: destination rank per row (-1: skip) and row in its buffer
+    const int* sc_peer_token_idx;
+    uint8_t* sc_dst[16];
     uint8_t* c_sc;                      // scale tiles of C for c_mode 2
     int n_cols;                         // N
     int rows_cap;                       // M (rows the C tensors have)
@@ -330,6 +334,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             const int row0 = (tm * CG + static_cast<int>(rank)) * 128 + q * 32;
             const int col0 = tn * BN;
             uint32_t scword = 0;                                 // four scale bytes of one row (c_mode 2)
+            uint8_t* sc_row = nullptr;                           // c_mode 3: where this lane's row goes
 #pragma unroll 1
             for (int s = 0; s < 8; ++s) {
                 const int u = acc ? s : 7 - s;                   // 32-column unit; the shared unit goes first
@@ -395,7 +400,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     }
                 } else {
                     if ((s & 1) == 0) {
-                        if (lane == 0) bulk_wait_read<0>();
+                        if (p.c_mode == 3) {
+                            // combine fused into the epilogue: look up where this lane's row goes
+                            if (s == 0) {
+                                const int row = row0 + lane;
+                                const int pr = p.sc_peer_rank[row];
+                                sc_row = pr >= 0 ? p.sc_dst[pr] + static_cast<size_t>(p.sc_peer_token_idx[row]) * p.n_cols * 2 : nullptr;
+                            }
+                        } else if (lane == 0) {
+                            bulk_wait_read<0>();
+                        }
                         __syncwarp();
                     }
                     const int hh = u & 1;                        // which half of the 64-column chunk
@@ -407,7 +421,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                         const uint32_t w3 = pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
                         st_shared_v4(rowa + (((hh * 4 + j) ^ (lane & 7)) << 4), w0, w1, w2, w3);
                     }
-                    if (s & 1) {
+                    if ((s & 1) && p.c_mode == 3) {
+                        // staged 32 rows x 128 bytes -> the owners' buffers, four whole 128-byte row
+                        // pieces per warp instruction (8 lanes per row)
+                        __syncwarp();
+                        const int cbyte = (col0 + (u & ~1) * 32) * 2 + (lane & 7) * 16;
+                        const bool col_ok = col0 + (u & ~1) * 32 < p.n_cols;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const int rr = 4 * i + (lane >> 3);
+                            uint32_t v0, v1, v2, v3;
+                            ld_shared_v4(stg + rr * 128 + (((lane & 7) ^ (rr & 7)) << 4), v0, v1, v2, v3);
+                            const unsigned long long dp = __shfl_sync(0xFFFFFFFFu, reinterpret_cast<unsigned long long>(sc_row), rr);
+                            if (dp && col_ok) *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(dp) + cbyte) = make_uint4(v0, v1, v2, v3);
+                        }
+                        __syncwarp();
+                    } else if (s & 1) {
                         fence_proxy_async_smem();
                         __syncwarp();
                         if (lane == 0 && !(p.dbg & 4)) {
@@ -528,6 +557,10 @@ struct Grouping {
     const int* rows_dev = nullptr;   // device count of rows present
     const int* group_rows = nullptr; // device rows per group
     int num_groups = 0;
+    const int* peer_rank = nullptr;  // scatter epilogue
+    const int* peer_token_idx = nullptr;
+    void* const* dst = nullptr;
+    int world = 0;
 };
 
 template <int CG>
@@ -544,11 +577,14 @@ static int run(const void* A, const void* A_sc, const void* B, const void* B_sc,
     p.group_rows = gr.group_rows;
     p.num_groups = gr.num_groups;
     p.group_b_rows = N;
+    p.sc_peer_rank = gr.peer_rank;
+    p.sc_peer_token_idx = gr.peer_token_idx;
+    for (int i = 0; i < gr.world && i < 16; ++i) p.sc_dst[i] = static_cast<uint8_t*>(gr.dst[i]);
     p.tiles_m = (M + 128 * CG - 1) / (128 * CG);
     p.tiles_n = (N + BN - 1) / BN;
     p.k_steps = K / BK;
     p.group_m = 16;
-    p.c_mode = c_dtype;
+    p.c_mode = gr.dst ? 3 : c_dtype;
     { const char* e = getenv("MX8_GEMM_DEBUG"); p.dbg = e ? atoi(e) : 0; }
     { const char* e = getenv("MX8_GEMM_GROUP"); if (e) p.group_m = atoi(e); }
     p.status = device_status_ptr();
@@ -629,4 +665,32 @@ extern "C" int mx8_gemm_grouped(const void* A, const void* A_sc, const void* B, 
 extern "C" int mx8_gemm(const void* A, const void* A_sc, const void* B, const void* B_sc, void* C, int M, int N, int K,
                         int c_dtype, void* stream) {
     return mx8_gemm_ex(A, A_sc, B, B_sc, C, M, N, K, c_dtype, 0, 0, stream);
+}
+
+extern "C" int mx8_gemm_grouped_scatter(const void* A, const void* A_sc, const void* B, const void* B_sc, int M, int N, int K,
+                                        const void* num_rows, const void* group_rows, int num_groups, const void* peer_rank,
+                                        const void* peer_token_idx, void* const* dst_ptrs, int world, void* stream) {
+    using namespace mx8;
+    if (!A || !A_sc || !B || !B_sc || !num_rows || !peer_rank || !peer_token_idx || !dst_ptrs) return MX8_ERR_ARG;
+    if (world <= 0 || world > 16 || num_groups < 0 || (num_groups > 0 && !group_rows)) return MX8_ERR_ARG;
+    if (num_groups > gemm::MAX_GROUPS) {
+        note_cuda_error("mx8_gemm_grouped_scatter", "more than 256 groups in one call");
+        return MX8_ERR_LIMIT;
+    }
+    if (M <= 0 || N <= 0 || K <= 0 || M % 256 || N % 128 || K % 128 || (num_groups > 0 && N % 256)) return MX8_ERR_SHAPE;
+    if (!aligned16(A) || !aligned16(A_sc) || !aligned16(B) || !aligned16(B_sc)) return MX8_ERR_ALIGN;
+    for (int r = 0; r < world; ++r)
+        if (!dst_ptrs[r] || !aligned16(dst_ptrs[r])) return MX8_ERR_ALIGN;
+    int rc = check_device_sm100();
+    if (rc != MX8_OK) return rc;
+    gemm::Grouping gr;
+    gr.rows_dev = static_cast<const int*>(num_rows);
+    gr.group_rows = static_cast<const int*>(group_rows);
+    gr.num_groups = num_groups;
+    gr.peer_rank = static_cast<const int*>(peer_rank);
+    gr.peer_token_idx = static_cast<const int*>(peer_token_idx);
+    gr.dst = dst_ptrs;
+    gr.world = world;
+    // the C tensor map is unused by this epilogue; A stands in so that the map encodes
+    return gemm::run<2>(A, A_sc, B, B_sc, const_cast<void*>(A), M, N, K, MX8_C_MXFP8, 0, gr, static_cast<cudaStream_t>(stream));
 }

@@ -21,6 +21,7 @@ SIGNATURES = {
     "mx8_swiglu_quantize": (_i, [_vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "mx8_moe_combine": (_i, [_vp, _vp, _vp, _vp, _i, ctypes.POINTER(_vp), _i, _vp]),
     "mx8_moe_fwd_epilogue": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "mx8_gemm_grouped_scatter": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _i, _vp, _vp, ctypes.POINTER(_vp), _i, _vp]),
     "mx8_moe_schedule": (_i, [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "mx8_moe_schedule_static": (_i, [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "mx8_device_status": (_i, [ctypes.POINTER(_i), _vp]),

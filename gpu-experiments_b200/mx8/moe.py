@@ -95,7 +95,7 @@ def dispatch_mlp_swiglu_combine_fwd(x, x_ptrs, combine_buffer, combine_buffer_pt
                                     w_shared_up, w_routed_up, w_routed_up_sc,
                                     w_shared_down, w_routed_down, w_routed_down_sc,
                                     schedule_peer_rank, schedule_peer_token_idx, num_tokens, tokens_per_expert,
-                                    topk, num_comm_sms=0, macrobatch_size=0, minibatch_size=0):
+                                    topk, num_comm_sms=0, macrobatch_size=0, minibatch_size=0, fuse_combine=False):
     """Same arguments and the same 13 return values as the reference's binding
     (blackwell-ultra/022-…-mxfp8-bw.cu:2016-2136, bound at :3001-3010):
       (x_fp8_t_routed, x_sc_t_routed, gate_shared, gate_fp8_routed, gate_sc_routed, up_shared,
@@ -103,7 +103,8 @@ def dispatch_mlp_swiglu_combine_fwd(x, x_ptrs, combine_buffer, combine_buffer_pt
        y_shared, y_routed)
     Routed buffers have schedule_capacity rows.  num_comm_sms / macrobatch_size / minibatch_size tune
     the reference's single-kernel schedule and have no effect here.  The shared expert (bf16, outside
-    the MXFP8 path) runs on torch's library GEMM when its weights are given, else those outputs are None."""
+    the MXFP8 path) runs on torch's library GEMM when its weights are given, else those outputs are None.
+    fuse_combine=True (an addition) lets the down projection's epilogue do the combine; y_routed is then None."""
     E, I, H = w_routed_gate.shape
     cap = schedule_peer_rank.numel()
     x_fp8, x_sc, x_fp8_t, x_sc_t = dispatch_quantize(x_ptrs, H, topk, schedule_peer_rank, schedule_peer_token_idx, num_tokens, cap)
@@ -115,9 +116,20 @@ def dispatch_mlp_swiglu_combine_fwd(x, x_ptrs, combine_buffer, combine_buffer_pt
     gemm_grouped(x_fp8, x_sc, w_routed_gate, w_routed_gate_sc, gate_fp8, gate_sc, num_tokens, tokens_per_expert)
     gemm_grouped(x_fp8, x_sc, w_routed_up, w_routed_up_sc, up_fp8, up_sc, num_tokens, tokens_per_expert)
     h_fp8, h_sc, h_fp8_t, h_sc_t = swiglu_quantize(gate_fp8, gate_sc, up_fp8, up_sc, num_tokens)
-    y_routed = torch.empty(cap, H, dtype=torch.bfloat16, device=dev)
-    gemm_grouped(h_fp8, h_sc, w_routed_down, w_routed_down_sc, y_routed, None, num_tokens, tokens_per_expert)
-    combine(y_routed, schedule_peer_rank, schedule_peer_token_idx, num_tokens, combine_buffer_ptrs)
+    if fuse_combine:
+        # the down projection's epilogue writes every row into its owner's combine buffer; y_routed is None
+        y_routed = None
+        lib = _lib.load()
+        with torch.cuda.device(dev):
+            _lib.check(lib.mx8_gemm_grouped_scatter(
+                h_fp8.data_ptr(), h_sc.data_ptr(), _chk(w_routed_down, "w_routed_down", _FP8), _chk(w_routed_down_sc, "w_routed_down_sc", _SC),
+                cap, H, I, num_tokens.data_ptr(), tokens_per_expert.data_ptr(), E, schedule_peer_rank.data_ptr(),
+                schedule_peer_token_idx.data_ptr(), _ptr_array(combine_buffer_ptrs), len(combine_buffer_ptrs), _stream()),
+                "grouped gemm + combine")
+    else:
+        y_routed = torch.empty(cap, H, dtype=torch.bfloat16, device=dev)
+        gemm_grouped(h_fp8, h_sc, w_routed_down, w_routed_down_sc, y_routed, None, num_tokens, tokens_per_expert)
+        combine(y_routed, schedule_peer_rank, schedule_peer_token_idx, num_tokens, combine_buffer_ptrs)
     gate_shared = up_shared = hidden_shared = y_shared = None
     if w_shared_gate is not None:
         gate_shared = x @ w_shared_gate.t()

@@ -130,6 +130,16 @@ MX8_API int mx8_moe_combine(const void* y_routed, const void* peer_rank, const v
 MX8_API int mx8_moe_fwd_epilogue(const void* y_shared, const void* combine_buffer, const void* topk_weights, void* out,
                                  int tokens, int hidden, int topk, void* stream);
 
+/* Grouped GEMM whose epilogue performs the MoE combine: row r (< *num_rows, peer_rank[r] >= 0) of
+ * dequant(A).dequant(B_g)^T is written as bf16 to row peer_token_idx[r] of dst_ptrs[peer_rank[r]]
+ * (HOST array of `world` device pointers to [.][N] bf16 buffers, peer-mapped for other GPUs); no
+ * [M][N] result is materialised.  Same result as mx8_gemm_grouped followed by mx8_moe_combine.
+ * Fuses expert_grouped_gemm<false> (bf16 epilogue) with combine_kernel,
+ * blackwell-ultra/022-…-mxfp8-bw.cu:1701-1720 and :830-922. */
+MX8_API int mx8_gemm_grouped_scatter(const void* A, const void* A_sc, const void* B, const void* B_sc, int M, int N, int K,
+                                     const void* num_rows, const void* group_rows, int num_groups, const void* peer_rank,
+                                     const void* peer_token_idx, void* const* dst_ptrs, int world, void* stream);
+
 /* Expert-parallel MoE routing schedule for the calling rank (int32 everywhere).
  *   topk_all [world][tokens][topk]: global expert ids chosen by every rank's tokens;
  *   this rank owns experts [rank*num_local_experts, (rank+1)*num_local_experts).

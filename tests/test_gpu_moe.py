@@ -230,3 +230,29 @@ def test_moe_forward_layer_two_emulated_ranks():
         cb_own = MO.combine_ref(ys, prs, pts, owner, T, k)
         own = MO.fwd_epilogue_ref(torch.zeros(T, H, dtype=torch.bfloat16), cb_own, weights[owner])
         assert torch.equal(out.cpu().view(torch.int16), own.view(torch.int16))
+
+
+def test_fused_combine_equals_gemm_then_combine():
+    # the down projection with the combine in its epilogue must leave exactly the bytes that
+    # the separate GEMM + combine kernels leave
+    W, T, H, I, k, E_local, rank = 2, 256, 512, 256, 4, 3, 1
+    topk_all, _ = make_topk(W, T, W * E_local, k, seed=91)
+    cap = ((W * T * k) // 256 + E_local) * 256
+    pr, pt, nt, tpe = mx8.schedule(topk_all.to(DEV), E_local, cap, rank)
+    xs = [O.make_input(T, H, seed=95 + r).to(DEV) for r in range(W)]
+    ws = []
+    for seed, (r, c) in ((10, (I, H)), (20, (I, H)), (30, (H, I))):
+        wt = torch.stack([O.make_input(r, c, seed=seed + e, std=c ** -0.5) for e in range(E_local)])
+        ws.append(mx8.mxfp8_quantize(wt.to(DEV), True, False)[:2])
+    results = []
+    for fuse in (False, True):
+        bufs = [torch.full((T * k, H), -1.0, dtype=torch.bfloat16, device=DEV) for _ in range(W)]
+        outs = mx8.dispatch_mlp_swiglu_combine_fwd(xs[rank], [t.data_ptr() for t in xs], bufs[rank], [b.data_ptr() for b in bufs],
+                                                   None, ws[0][0], ws[0][1], None, ws[1][0], ws[1][1], None, ws[2][0], ws[2][1],
+                                                   pr, pt, nt, tpe, k, fuse_combine=fuse)
+        assert mx8.device_status() == 0
+        assert (outs[12] is None) == fuse
+        results.append([b.cpu() for b in bufs])
+    for a, b in zip(*results):
+        assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+    assert bool((results[0][0] != -1.0).any())
