@@ -82,7 +82,9 @@ struct Params {
     const int* group_rows;              // device: rows of every group (multiples of the tile height), nullptr = dense
     int num_groups;
     int group_b_rows;                   // rows of B per group (N)
-    int dbg;                            // tuning experiments: 1 no MMA, 2 no TMA loads, 4 no C stores, 8 no scale traffic
+    int dbg;                            // ablation switches (MX8_GEMM_DEBUG, timing only, results are wrong):
+                                        // 1 no MMA, 2 no TMA loads, 4 no C stores, 8 no scale traffic, 16 no scale copies,
+                                        // 32 no scale loads, 64 scale copies by the MMA thread, 128 no wait for the epilogue
     int* status;
 };
 
@@ -268,7 +270,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 if (it > 0) {
                     // the epilogue has emptied the previous-but-one accumulator and the 32 columns
                     // the previous accumulator shares with this one
-                    if (!(p.dbg & 128) && !mbar_wait(drained, (it - 1) & 1, ab, DEV_TIMEOUT_TMEM_FREE)) { ok = false; break; }
+                    if (!(p.dbg & 128) && !mbar_wait<true>(drained, (it - 1) & 1, ab, DEV_TIMEOUT_TMEM_FREE)) { ok = false; break; }
                     tc_fence_after();
                 }
                 for (int ks = 0; ks < p.k_steps; ++ks) {

@@ -78,7 +78,21 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
+// Acquire at CTA scope: enough for barriers completed by TMA byte counts, by tcgen05.commit or by
+// threads of this CTA.
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Acquire at cluster scope: for barriers that threads of the peer CTA arrive on with release.cluster.
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
@@ -97,12 +111,14 @@ struct AbortCtl {
 };
 
 // Bounded wait.  Returns false after MX8_WAIT_LIMIT_NS (recording `code`) or as soon as
-// another role of this CTA has given up.
+// another role of this CTA has given up.  CLUSTER selects the acquire scope (see above).
+template <bool CLUSTER = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const AbortCtl& ab, int code) {
-    if (mbar_try_wait(bar, parity)) return true;
+    auto probe = [&]() { return CLUSTER ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity); };
+    if (probe()) return true;
     uint64_t t0 = 0;
     for (uint32_t spins = 1;; ++spins) {
-        if (mbar_try_wait(bar, parity)) return true;
+        if (probe()) return true;
         if ((spins & 0x3FF) == 0) {
             if (*ab.smem_flag) return false;
             const uint64_t now = globaltimer_ns();
