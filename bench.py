@@ -209,6 +209,52 @@ def cpu_baseline_gemm(target_s=8.0):
             "sample": f"{reps} passes of a {n}^3 sub-problem: dequantize + fp32 matmul + bf16 round ({per * reps:.1f} s)"}
 
 
+def cpu_ffn_operands(T=512, H=8192, F=4096):
+    from oracle import mx8_oracle as O
+    torch.set_num_threads(os.cpu_count() or 1)
+    x = O.make_input(T, H, seed=3)
+    w1 = O.quantize_tiled(O.make_input(F, H, seed=4, std=0.02))
+    w2 = O.quantize_tiled(O.make_input(H, F, seed=5, std=0.02))
+    return x, w1, w2
+
+
+def cpu_ffn_step(ops):
+    """quantize X, H = X W1^T rounded to bf16 and re-quantized, Y = H W2^T, all with the oracle."""
+    from oracle import mx8_oracle as O
+    x, w1, w2 = ops
+    xq, xs = O.quantize_ref_float(x, "rceil")
+    h = O.gemm_ref(xq, O.scale_swizzle(xs), *w1)
+    hq, hs = O.quantize_ref_float(h, "rceil")
+    O.gemm_ref(hq, O.scale_swizzle(hs), *w2)
+
+
+def cpu_moe_operands(rows=1024, H=7168, I=2048):
+    from oracle import mx8_oracle as O
+    torch.set_num_threads(os.cpu_count() or 1)
+    x = O.make_input(rows, H, seed=6)
+    q = lambda r, c, sd: O.quantize_both(O.make_input(r, c, seed=sd, std=0.02).unsqueeze(0))[:2]
+    return x, torch.tensor([rows], dtype=torch.int32), q(I, H, 7), q(I, H, 8), q(H, I, 9)
+
+
+def cpu_moe_step(ops):
+    """One expert's routed forward (quantize, gate/up GEMMs, SwiGLU, down GEMM) with the oracle."""
+    from oracle import moe_oracle as MO
+    x, tpe, wg, wu, wd = ops
+    MO.expert_mlp_ref(x, tpe, wg, wu, wd)
+
+
+def cpu_baseline_layer(kind, target_s=6.0):
+    if kind == "ffn":
+        ops, fn, flops, what = cpu_ffn_operands(), cpu_ffn_step, 2.0 * 2.0 * 512 * 8192 * 4096, "512 tokens x 8192 -> 4096 -> 8192 slice of the FFN"
+    else:
+        ops, fn, flops, what = cpu_moe_operands(), cpu_moe_step, 6.0 * 1024 * 7168 * 2048, "one expert x 1024 routed rows of the MoE layer"
+    per = time_cpu(fn, ops, 1, 0)
+    reps = max(1, min(20, int(target_s / per)))
+    per = time_cpu(fn, ops, reps, 0)
+    return {"value": flops / per / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{reps} passes over {what} ({per * reps:.1f} s)"}
+
+
 def run_reference(args, rank):
     """--impl reference: the reference's own CPU implementation of the path (its torch code,
     restated in oracle/) on all host threads; each step is a bounded sample of the workload."""
@@ -227,6 +273,22 @@ def run_reference(args, rank):
         value, unit, metric = rows * QN * 4.0625 / per / 1e9, "GB/s", "mxfp8_quantize_bandwidth"
         sample = f"{rows} x {QN} row slab of the 16384 x 16384 input per step, row-wise + transposed"
         cfg = {"workload": "quantize bf16 16384x16384 -> E4M3 + E8M0 scales, row-wise + transposed", "scale_mode": "rceil"}
+    elif args.workload in ("ffn", "moe"):
+        if args.workload == "ffn":
+            ops, fn, flops = cpu_ffn_operands(), cpu_ffn_step, 2.0 * 2.0 * 512 * 8192 * 4096
+            sample, metric = "512-token, 4096-wide slice of the FFN per step", "mxfp8_ffn_throughput"
+            cfg = {"workload": "FFN X[16384x8192] -> [28672x8192] -> [8192x28672], MXFP8"}
+        else:
+            ops, fn, flops = cpu_moe_operands(), cpu_moe_step, 6.0 * 1024 * 7168 * 2048
+            sample, metric = "one expert x 1024 routed rows per step", "mxfp8_moe_forward_throughput"
+            cfg = {"workload": "MoE forward, 256 experts, hidden 7168, intermediate 2048, 32768 tokens, top-8"}
+        steps = args.steps
+        est = time_cpu(fn, ops, 1, 0)
+        while steps > 1 and est * (steps + args.warmup) > 150.0:
+            steps = max(1, steps // 2)
+        per = time_cpu(fn, ops, steps, min(args.warmup, 1))
+        value, unit = flops / per / 1e12, "TFLOP/s"
+        sample += f" ({steps} timed steps)"
     else:
         n = 2048
         ops = cpu_gemm_operands(n)
@@ -386,7 +448,7 @@ def bench_gemm(args, world, rank, local, peaks, with_cpu):
     return line
 
 
-def bench_ffn(args, world, rank, local, peaks):
+def bench_ffn(args, world, rank, local, peaks, with_cpu=False):
     """Configuration 4: Llama-70B-shaped FFN, tokens sharded across ranks, weights replicated and
     pre-quantized; X is quantized per step and the intermediate H never exists in bf16: the first
     GEMM's epilogue emits MXFP8 directly."""
@@ -426,10 +488,10 @@ def bench_ffn(args, world, rank, local, peaks):
                        "sharding": "tokens split across GPUs, weights replicated, no collective"},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": 2.0 * peaks["bf16_tflops"], "unit": "TFLOP/s",
                          "frac": achieved / (2.0 * peaks["bf16_tflops"]), "frac_of_nominal_4500": achieved / 4500.0, "traffic": None},
-            "gpu_launches": 3 * steps}
+            "gpu_launches": 3 * steps, **({"cpu_baseline": cpu_baseline_layer("ffn")} if with_cpu and rank == 0 else {})}
 
 
-def bench_moe(args, world, rank, local, peaks):
+def bench_moe(args, world, rank, local, peaks, with_cpu=False):
     """Configuration 5: DeepSeek-V3-like expert-parallel layer, 256 experts and 32768 tokens split over
     the ranks, top-8 routing, routed experts only.  A step is the reference harness's run_fwd_once."""
     import mx8
@@ -498,7 +560,7 @@ def bench_moe(args, world, rank, local, peaks):
                        "sharding": "experts and tokens split across GPUs; dispatch pulls and combine pushes over peer-mapped memory"},
             "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": 2.0 * peaks["bf16_tflops"], "unit": "TFLOP/s",
                          "frac": per_gpu / (2.0 * peaks["bf16_tflops"]), "frac_of_nominal_4500": per_gpu / 4500.0, "traffic": None},
-            "gpu_launches": 10 * steps}
+            "gpu_launches": 10 * steps, **({"cpu_baseline": cpu_baseline_layer("moe")} if with_cpu and rank == 0 else {})}
 
 
 def main():
@@ -534,14 +596,14 @@ def main():
             for name, fn in (("ffn", bench_ffn), ("moe", bench_moe)):
                 try:
                     torch.cuda.empty_cache()
-                    line[name] = fn(args, world, rank, local, peaks)
+                    line[name] = fn(args, world, rank, local, peaks, with_cpu)
                     line["gpu_launches"] += line[name]["gpu_launches"]
                 except Exception as ex:      # a layer benchmark must not take the headline line down
                     line[name] = {"error": f"{type(ex).__name__}: {ex}"[:300]}
     elif args.workload == "gemm":
         line = bench_gemm(args, world, rank, local, peaks, with_cpu)
     else:
-        line = (bench_ffn if args.workload == "ffn" else bench_moe)(args, world, rank, local, peaks)
+        line = (bench_ffn if args.workload == "ffn" else bench_moe)(args, world, rank, local, peaks, with_cpu)
         line.update({"n_gpus": world, "warmup": args.warmup, "higher_is_better": True, "vs_baseline": None, "dtype": "fp8_e4m3 x ue8m0",
                      "data": "synthetic"})
     if rank == 0:
