@@ -35,7 +35,7 @@ L2_BYTES = 126 * 1024 * 1024
 
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
 # summarised under profiles/; None until a capture exists for that kernel.
-NCU_TRAFFIC_BYTES = {"quantize_16384x16384_both": 1045880000, "gemm_8192": 494460000}
+NCU_TRAFFIC_BYTES = {"quantize_16384x16384_both": 1045880000, "gemm_8192": 373310000}
 
 
 def load_peaks():
