@@ -245,8 +245,9 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
                 const uint32_t inv_a = __byte_perm(inv2, inv2, 0x1010), inv_b = __byte_perm(inv2, inv2, 0x3232);
                 const uint32_t qa = cvt4(mul_bf16x2(c[i][0], inv_a), mul_bf16x2(c[i][1], inv_a));
                 const uint32_t qb = cvt4(mul_bf16x2(c[i + 1][0], inv_b), mul_bf16x2(c[i + 1][1], inv_b));
-                *reinterpret_cast<uint32_t*>(out_row + static_cast<size_t>(i) * p.N) = qa;
-                *reinterpret_cast<uint32_t*>(out_row + static_cast<size_t>(i + 1) * p.N) = qb;
+                // streaming stores: the bytes are not read again by this kernel
+                __stcs(reinterpret_cast<uint32_t*>(out_row + static_cast<size_t>(i) * p.N), qa);
+                __stcs(reinterpret_cast<uint32_t*>(out_row + static_cast<size_t>(i + 1) * p.N), qb);
                 if ((l & 7) == 0) {
                     scstage_ptr[i * 4 + (l >> 3)] = static_cast<uint8_t>(b2);
                     scstage_ptr[(i + 1) * 4 + (l >> 3)] = static_cast<uint8_t>(b2 >> 16);
