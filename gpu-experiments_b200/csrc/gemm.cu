@@ -23,8 +23,6 @@
 //
 // M/N tails need no special case: out-of-range TMA loads are zero-filled, out-of-range TMA stores
 // are clipped.  Replaces blackwell/047-mxfp8-mma-2cta-MNK128-polished.cu:12-541 of the reference.
-#include <cstdlib>
-
 #include "mx8_host.cuh"
 #include "mx8_ptx.cuh"
 #include "mx8_qmath.cuh"
@@ -467,6 +465,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     }
 }
 
+// process-wide ablation switches for timing studies (mx8_debug_set_gemm_ablation); 0 in normal use
+static int g_ablation_flags = 0;
+
 struct Maps {
     CUtensorMap a, b, sfa, sfb, c;
 };
@@ -587,8 +588,7 @@ static int run(const void* A, const void* A_sc, const void* B, const void* B_sc,
     p.k_steps = K / BK;
     p.group_m = 16;
     p.c_mode = gr.dst ? 3 : c_dtype;
-    { const char* e = getenv("MX8_GEMM_DEBUG"); p.dbg = e ? atoi(e) : 0; }
-    { const char* e = getenv("MX8_GEMM_GROUP"); if (e) p.group_m = atoi(e); }
+    p.dbg = g_ablation_flags;
     p.status = device_status_ptr();
     if (!p.status) return MX8_ERR_CUDA;
     int grid = max_grid<CG>();
@@ -695,4 +695,10 @@ extern "C" int mx8_gemm_grouped_scatter(const void* A, const void* A_sc, const v
     gr.world = world;
     // the C tensor map is unused by this epilogue; A stands in so that the map encodes
     return gemm::run<2>(A, A_sc, B, B_sc, const_cast<void*>(A), M, N, K, MX8_C_MXFP8, 0, gr, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int mx8_debug_set_gemm_ablation(int flags) {
+    const int old = mx8::gemm::g_ablation_flags;
+    mx8::gemm::g_ablation_flags = flags;
+    return old;
 }

@@ -24,6 +24,7 @@ SIGNATURES = {
     "mx8_gemm_grouped_scatter": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _i, _vp, _vp, ctypes.POINTER(_vp), _i, _vp]),
     "mx8_moe_schedule": (_i, [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "mx8_moe_schedule_static": (_i, [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
+    "mx8_debug_set_gemm_ablation": (_i, [_i]),
     "mx8_device_status": (_i, [ctypes.POINTER(_i), _vp]),
     "mx8_strerror": (ctypes.c_char_p, [_i]),
     "mx8_last_cuda_error": (ctypes.c_char_p, []),

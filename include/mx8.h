@@ -170,6 +170,11 @@ MX8_API int mx8_moe_schedule_static(const void* topk_all, int world, int tokens,
  * Returns MX8_OK, MX8_ERR_DEVICE_TIMEOUT (status != 0) or MX8_ERR_CUDA. */
 MX8_API int mx8_device_status(int* status_out, void* stream);
 
+/* Timing studies only: switches parts of the GEMM kernel off (bit mask, see csrc/gemm.cu `dbg`);
+ * results are WRONG while a non-zero mask is set.  Returns the previous mask.  No counterpart in the
+ * reference.  Normal use never calls this. */
+MX8_API int mx8_debug_set_gemm_ablation(int flags);
+
 MX8_API const char* mx8_strerror(int code);
 MX8_API const char* mx8_last_cuda_error(void); /* text of the last CUDA failure seen by this thread */
 MX8_API const char* mx8_version(void);
