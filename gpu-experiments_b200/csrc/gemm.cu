@@ -80,6 +80,9 @@ struct Params {
     const int* group_rows;              // device: rows of every group (multiples of the tile height), nullptr = dense
     int num_groups;
     int group_b_rows;                   // rows of B per group (N)
+    int k_steps2;                       // second operand pair accumulated into the same tile (0 = none)
+    int wgrad;                          // 1: one output matrix per group, K runs over the group's rows of A^T / B^T
+    int group_c_rows;                   // wgrad: rows of C per group (M)
     int dbg;                            // ablation switches (MX8_GEMM_DEBUG, timing only, results are wrong):
                                         // 1 no MMA, 2 no TMA loads, 4 no C stores, 8 no scale traffic, 16 no scale copies,
                                         // 32 no scale loads, 64 scale copies by the MMA thread, 128 no wait for the epilogue
@@ -97,10 +100,55 @@ __device__ __forceinline__ void tile_coords(int t, const Params& p, int tiles_m,
     tn = in_grp / rows;
 }
 
+// Everything a role needs to know about tile t.  Three shapes of problem share the kernel:
+//   dense    tile (tm, tn) of C = A B^T;
+//   grouped  the same, but the B rows of a tile come from the group that owns its A rows;
+//   wgrad    C_g = A^T_g B^T_g^T for every group g: A^T is [M][rows], B^T is [N][rows] and the K loop of
+//            a tile covers only the rows (columns of A^T) of its group.
+struct TileInfo {
+    int tm, tn;        // tile coordinates inside one C matrix
+    int b_base;        // first row of B for this tile (before the CTA's own offset)
+    int c_row;         // first row of C for this tile (before the CTA's own offset)
+    int k0, kcount;    // first K step and number of K steps
+};
+
+template <int CG>
+__device__ __forceinline__ TileInfo tile_info(int t, const Params& p, int tiles_m, const int* seg_end) {
+    TileInfo ti;
+    if (p.wgrad) {
+        const int per_group = tiles_m * p.tiles_n;
+        const int e = t / per_group;
+        tile_coords(t - e * per_group, p, tiles_m, ti.tm, ti.tn);
+        const int begin = e ? seg_end[e - 1] : 0;
+        ti.k0 = begin / BK;
+        ti.kcount = (seg_end[e] - begin) / BK;
+        ti.b_base = ti.tn * BN;
+        ti.c_row = e * p.group_c_rows + ti.tm * 128 * CG;
+        return ti;
+    }
+    tile_coords(t, p, tiles_m, ti.tm, ti.tn);
+    ti.b_base = ti.tn * BN;
+    if (p.num_groups > 0) {
+        const int row0 = ti.tm * 128 * CG;
+        int lo = 0, hi = p.num_groups - 1;            // first group whose segment ends beyond row0
+        while (lo < hi) {
+            const int mid = (lo + hi) >> 1;
+            if (seg_end[mid] > row0) hi = mid; else lo = mid + 1;
+        }
+        ti.b_base += lo * p.group_b_rows;
+    }
+    ti.c_row = ti.tm * 128 * CG;
+    ti.k0 = 0;
+    ti.kcount = p.k_steps + p.k_steps2;
+    return ti;
+}
+
 template <int CG>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
             const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb,
+            const __grid_constant__ CUtensorMap tm_a2, const __grid_constant__ CUtensorMap tm_b2,
+            const __grid_constant__ CUtensorMap tm_sfa2, const __grid_constant__ CUtensorMap tm_sfb2,
             const __grid_constant__ CUtensorMap tm_c, const Params p) {
     using C = Cfg<CG>;
     constexpr int S = C::STAGES;
@@ -166,7 +214,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         }
         __syncthreads();
     }
-    const int num_tiles = tiles_m * p.tiles_n;
+    const int num_tiles = tiles_m * p.tiles_n * (p.wgrad ? p.num_groups : 1);
 
     if (warp == 0) {
         // ------------------------------------------------------------------ producer
@@ -175,48 +223,45 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             const uint32_t full_leader0 = CG == 2 ? map_to_cta(full0, 0) : full0;
             bool ok = true;
             for (int t = cluster; t < num_tiles && ok; t += num_clusters) {
-                int tm, tn;
-                tile_coords(t, p, tiles_m, tm, tn);
-                const int a_row = (tm * CG + static_cast<int>(rank)) * 128;
-                int b_base = tn * BN;                       // first B row of this tile
-                if (p.num_groups > 0) {
-                    const int row0 = tm * 128 * CG;
-                    int lo = 0, hi = p.num_groups - 1;        // first group whose segment ends beyond row0
-                    while (lo < hi) {
-                        const int mid = (lo + hi) >> 1;
-                        if (seg_end[mid] > row0) hi = mid; else lo = mid + 1;
-                    }
-                    b_base += lo * p.group_b_rows;
-                }
+                const TileInfo ti = tile_info<CG>(t, p, tiles_m, seg_end);
+                const int a_row = (ti.tm * CG + static_cast<int>(rank)) * 128;
+                const int b_base = ti.b_base;
                 const int b_row = b_base + static_cast<int>(rank) * C::B_ROWS;
-                for (int ks = 0; ks < p.k_steps; ++ks) {
+                for (int ks = 0; ks < ti.kcount; ++ks) {
                     if (!mbar_wait(empty0 + stage * 8, ph ^ 1, ab, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
                     const uint32_t a_dst = base + C::a_off + stage * C::A_BYTES;
                     const uint32_t b_dst = base + C::b_off + stage * C::B_BYTES;
                     const uint32_t sfa_dst = base + C::sfa_off + stage * C::SFA_BYTES;
                     const uint32_t sfb_dst = base + C::sfb_off + stage * C::SFB_BYTES;
+                    // K step within the operand pair it belongs to
+                    const bool second = ks >= p.k_steps && p.k_steps2 > 0;
+                    const int kk = ti.k0 + (second ? ks - p.k_steps : ks);
+                    const CUtensorMap* ma = second ? &tm_a2 : &tm_a;
+                    const CUtensorMap* mb = second ? &tm_b2 : &tm_b;
+                    const CUtensorMap* msa = second ? &tm_sfa2 : &tm_sfa;
+                    const CUtensorMap* msb = second ? &tm_sfb2 : &tm_sfb;
                     if constexpr (CG == 2) {
                         const uint32_t bar = full_leader0 + stage * 8;
                         if (p.dbg & 2) {
                             if (rank == 0) mbar_arrive(full0 + stage * 8);
                         } else if (p.dbg & (8 | 32)) {
                             if (rank == 0) mbar_arrive_expect_tx(full0 + stage * 8, 2 * (C::A_BYTES + C::B_BYTES));
-                            tma_load_2d_pair(a_dst, &tm_a, ks * BK, a_row, bar);
-                            tma_load_2d_pair(b_dst, &tm_b, ks * BK, b_row, bar);
+                            tma_load_2d_pair(a_dst, ma, kk * BK, a_row, bar);
+                            tma_load_2d_pair(b_dst, mb, kk * BK, b_row, bar);
                         } else {
-                        if (rank == 0) mbar_arrive_expect_tx(full0 + stage * 8, 2 * C::STAGE_TX);
-                        tma_load_2d_pair(a_dst, &tm_a, ks * BK, a_row, bar);
-                        tma_load_2d_pair(b_dst, &tm_b, ks * BK, b_row, bar);
-                        tma_load_3d_pair(sfa_dst, &tm_sfa, 0, ks, a_row / 128, bar);
-                        tma_load_3d_pair(sfb_dst, &tm_sfb, 0, ks, b_base / 128, bar);
+                            if (rank == 0) mbar_arrive_expect_tx(full0 + stage * 8, 2 * C::STAGE_TX);
+                            tma_load_2d_pair(a_dst, ma, kk * BK, a_row, bar);
+                            tma_load_2d_pair(b_dst, mb, kk * BK, b_row, bar);
+                            tma_load_3d_pair(sfa_dst, msa, 0, kk, a_row / 128, bar);
+                            tma_load_3d_pair(sfb_dst, msb, 0, kk, b_base / 128, bar);
                         }
                     } else {
                         const uint32_t bar = full0 + stage * 8;
                         mbar_arrive_expect_tx(bar, C::STAGE_TX);
-                        tma_load_2d(a_dst, &tm_a, ks * BK, a_row, bar);
-                        tma_load_2d(b_dst, &tm_b, ks * BK, b_row, bar);
-                        tma_load_3d(sfa_dst, &tm_sfa, 0, ks, a_row / 128, bar);
-                        tma_load_3d(sfb_dst, &tm_sfb, 0, ks, b_base / 128, bar);
+                        tma_load_2d(a_dst, ma, kk * BK, a_row, bar);
+                        tma_load_2d(b_dst, mb, kk * BK, b_row, bar);
+                        tma_load_3d(sfa_dst, msa, 0, kk, a_row / 128, bar);
+                        tma_load_3d(sfb_dst, msb, 0, kk, b_base / 128, bar);
                     }
                     if (++stage == S) { stage = 0; ph ^= 1; }
                 }
@@ -240,7 +285,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             constexpr uint32_t ID2 = idesc_mxf8(128 * CG, BN, 2), ID3 = idesc_mxf8(128 * CG, BN, 3);
             const bool do_cp = !(p.dbg & (8 | 16)), do_mma = !(p.dbg & 1);
             const int my_tiles = cluster < num_tiles ? (num_tiles - cluster + num_clusters - 1) / num_clusters : 0;
-            long long remaining = static_cast<long long>(my_tiles) * p.k_steps;   // K steps whose scales are not copied yet
+            long long remaining = 0;                             // K steps whose scales are not copied yet
+            for (int t = cluster; t < num_tiles; t += num_clusters) remaining += tile_info<CG>(t, p, tiles_m, seg_end).kcount;
             bool ok = true;
             // wait for a stage and copy its scale tiles into the next TMEM scale slot
             auto copy_scales = [&]() -> bool {
@@ -271,7 +317,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     if (!(p.dbg & 128) && !mbar_wait<true>(drained, (it - 1) & 1, ab, DEV_TIMEOUT_TMEM_FREE)) { ok = false; break; }
                     tc_fence_after();
                 }
-                for (int ks = 0; ks < p.k_steps; ++ks) {
+                const int kcount = tile_info<CG>(cluster + it * num_clusters, p, tiles_m, seg_end).kcount;
+                for (int ks = 0; ks < kcount; ++ks) {
                     if (ext_copier) {
                         if (!mbar_wait(sffull0 + (kk & 1) * 8, (kk >> 1) & 1, ab, DEV_TIMEOUT_FULL)) { ok = false; break; }
                         tc_fence_after();
@@ -299,7 +346,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         // ------------------------------------------------------------------ scale copier (experiment, leader CTA only)
         if (lane == 0 && rank == 0 && !(p.dbg & 64) && !(p.dbg & (8 | 16))) {
             const int my_tiles = cluster < num_tiles ? (num_tiles - cluster + num_clusters - 1) / num_clusters : 0;
-            const long long total = static_cast<long long>(my_tiles) * p.k_steps;
+            long long total = 0;
+            for (int t = cluster; t < num_tiles; t += num_clusters) total += tile_info<CG>(t, p, tiles_m, seg_end).kcount;
+            (void)my_tiles;
             const uint32_t sfa_lo0 = desc_scales_lo(base + C::sfa_off), sfb_lo0 = desc_scales_lo(base + C::sfb_off);
             for (long long kk = 0; kk < total; ++kk) {
                 const uint32_t stage = static_cast<uint32_t>(kk % S), ph = static_cast<uint32_t>((kk / S) & 1);
@@ -325,13 +374,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         int it = 0;
         bool ok = true;
         for (int t = cluster; t < num_tiles && ok; t += num_clusters, ++it) {
-            int tm, tn;
-            tile_coords(t, p, tiles_m, tm, tn);
+            const TileInfo ti = tile_info<CG>(t, p, tiles_m, seg_end);
+            const int tn = ti.tn;
+            const bool zero_tile = ti.kcount == 0;                // wgrad of a group without rows: nothing was accumulated
             const int acc = it & 1;
             if (!mbar_wait(accfull0 + acc * 8, (it >> 1) & 1, ab, DEV_TIMEOUT_TMEM_FULL)) { ok = false; break; }
             tc_fence_after();
             const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + (acc ? ACC1_COL : 0);
-            const int row0 = (tm * CG + static_cast<int>(rank)) * 128 + q * 32;
+            const int row0 = ti.c_row + static_cast<int>(rank) * 128 + q * 32;
             const int col0 = tn * BN;
             uint32_t scword = 0;                                 // four scale bytes of one row (c_mode 2)
             uint8_t* sc_row = nullptr;                           // c_mode 3: where this lane's row goes
@@ -341,6 +391,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 uint32_t r[32];
                 tc_ld_32x32(t_acc + u * 32, r);
                 tc_wait_ld(r);
+                if (zero_tile) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) r[j] = 0;
+                }
                 if (s == 0) {
                     tc_fence_before();
                     __syncwarp();
@@ -469,50 +523,52 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
 static int g_ablation_flags = 0;
 
 struct Maps {
-    CUtensorMap a, b, sfa, sfb, c;
+    CUtensorMap a, b, sfa, sfb, a2, b2, sfa2, sfb2, c;
 };
 
+// tensor maps of one operand pair: A [a_rows][K], B [b_rows][K] and their scale tiles
 template <int CG>
-static int build_maps(Maps& m, const void* A, const void* A_sc, const void* B, const void* B_sc, void* Cp,
-                      int M, int N, int K, int c_dtype, int b_rows) {
+static int build_operand_maps(CUtensorMap* ma, CUtensorMap* mb, CUtensorMap* msa, CUtensorMap* msb, const void* A,
+                              const void* A_sc, const void* B, const void* B_sc, int a_rows, int b_rows, int K) {
     int rc;
     const uint64_t kb = static_cast<uint64_t>(K) / 128;
     {
-        const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
+        const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(a_rows)};
         const uint64_t strides[1] = {static_cast<uint64_t>(K)};
         const uint32_t box[2] = {BK, 128};
-        if ((rc = make_tmap(&m.a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, A, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) != MX8_OK) return rc;
+        if ((rc = make_tmap(ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, A, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) != MX8_OK) return rc;
     }
     {
         const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(b_rows)};
         const uint64_t strides[1] = {static_cast<uint64_t>(K)};
         const uint32_t box[2] = {BK, static_cast<uint32_t>(Cfg<CG>::B_ROWS)};
-        if ((rc = make_tmap(&m.b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, B, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) != MX8_OK) return rc;
+        if ((rc = make_tmap(mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, B, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) != MX8_OK) return rc;
     }
     {
         // scale tiles [rows/128][K/128][512 bytes] seen as 32-bit words so one box row is a whole tile
-        const uint64_t dims[3] = {128, kb, static_cast<uint64_t>(M) / 128};
+        const uint64_t dims[3] = {128, kb, static_cast<uint64_t>(a_rows) / 128};
         const uint64_t strides[2] = {512, 512 * kb};
         const uint32_t box[3] = {128, 1, 1};
-        if ((rc = make_tmap(&m.sfa, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, A_sc, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE)) != MX8_OK) return rc;
+        if ((rc = make_tmap(msa, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, A_sc, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE)) != MX8_OK) return rc;
     }
     {
         const uint64_t dims[3] = {128, kb, static_cast<uint64_t>(b_rows) / 128};
         const uint64_t strides[2] = {512, 512 * kb};
         const uint32_t box[3] = {128, 1, 2};
-        if ((rc = make_tmap(&m.sfb, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, B_sc, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE)) != MX8_OK) return rc;
-    }
-    {
-        // C rows are 128 bytes wide in the staging buffer: 64 bf16, 32 float or 128 E4M3 columns
-        const int esz = c_dtype == MX8_C_F32 ? 4 : (c_dtype == MX8_C_MXFP8 ? 1 : 2);
-        const CUtensorMapDataType dt = c_dtype == MX8_C_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
-                                     : (c_dtype == MX8_C_MXFP8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16);
-        const uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(M)};
-        const uint64_t strides[1] = {static_cast<uint64_t>(N) * esz};
-        const uint32_t box[2] = {static_cast<uint32_t>(128 / esz), 32};
-        if ((rc = make_tmap(&m.c, dt, 2, Cp, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) != MX8_OK) return rc;
+        if ((rc = make_tmap(msb, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, B_sc, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE)) != MX8_OK) return rc;
     }
     return MX8_OK;
+}
+
+static int build_c_map(CUtensorMap* mc, void* Cp, int c_rows, int N, int c_dtype) {
+    // C rows are 128 bytes wide in the staging buffer: 64 bf16, 32 float or 128 E4M3 columns
+    const int esz = c_dtype == MX8_C_F32 ? 4 : (c_dtype == MX8_C_MXFP8 ? 1 : 2);
+    const CUtensorMapDataType dt = c_dtype == MX8_C_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                 : (c_dtype == MX8_C_MXFP8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16);
+    const uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(c_rows)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(N) * esz};
+    const uint32_t box[2] = {static_cast<uint32_t>(128 / esz), 32};
+    return make_tmap(mc, dt, 2, Cp, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
 template <int CG>
@@ -564,18 +620,33 @@ struct Grouping {
     const int* peer_token_idx = nullptr;
     void* const* dst = nullptr;
     int world = 0;
+    // second operand pair accumulated into the same output: C = A B^T + A2 B2^T
+    const void *A2 = nullptr, *A2_sc = nullptr, *B2 = nullptr, *B2_sc = nullptr;
+    int K2 = 0;
+    // weight-gradient form: A is A^T [M][K], B is B^T [N][K] with K = all rows; one C [M][N] per group
+    bool wgrad = false;
 };
 
 template <int CG>
 static int run(const void* A, const void* A_sc, const void* B, const void* B_sc, void* Cp, int M, int N, int K,
                int c_dtype, int max_ctas, const Grouping& gr, cudaStream_t stream) {
     Maps m;
-    int rc = build_maps<CG>(m, A, A_sc, B, B_sc, Cp, M, N, K, c_dtype, gr.num_groups > 0 ? gr.num_groups * N : N);
+    const int groups = gr.num_groups > 0 ? gr.num_groups : 1;
+    const int b_rows = gr.wgrad ? N : groups * N;              // wgrad: B^T is one [N][K] matrix
+    const int c_rows = gr.wgrad ? groups * M : M;
+    int rc = build_operand_maps<CG>(&m.a, &m.b, &m.sfa, &m.sfb, A, A_sc, B, B_sc, M, b_rows, K);
     if (rc != MX8_OK) return rc;
+    if (gr.K2 > 0) rc = build_operand_maps<CG>(&m.a2, &m.b2, &m.sfa2, &m.sfb2, gr.A2, gr.A2_sc, gr.B2, gr.B2_sc, M, b_rows, gr.K2);
+    else { m.a2 = m.a; m.b2 = m.b; m.sfa2 = m.sfa; m.sfb2 = m.sfb; }
+    if (rc != MX8_OK) return rc;
+    if ((rc = build_c_map(&m.c, Cp, c_rows, N, c_dtype)) != MX8_OK) return rc;
     Params p{};
     p.c_sc = static_cast<uint8_t*>(gr.c_sc);
     p.n_cols = N;
-    p.rows_cap = M;
+    p.rows_cap = c_rows;
+    p.k_steps2 = gr.K2 / BK;
+    p.wgrad = gr.wgrad ? 1 : 0;
+    p.group_c_rows = M;
     p.rows_dev = gr.rows_dev;
     p.group_rows = gr.group_rows;
     p.num_groups = gr.num_groups;
@@ -585,7 +656,7 @@ static int run(const void* A, const void* A_sc, const void* B, const void* B_sc,
     for (int i = 0; i < gr.world && i < 16; ++i) p.sc_dst[i] = static_cast<uint8_t*>(gr.dst[i]);
     p.tiles_m = (M + 128 * CG - 1) / (128 * CG);
     p.tiles_n = (N + BN - 1) / BN;
-    p.k_steps = K / BK;
+    p.k_steps = gr.wgrad ? 0 : K / BK;
     p.group_m = 16;
     p.c_mode = gr.dst ? 3 : c_dtype;
     p.dbg = g_ablation_flags;
@@ -594,7 +665,7 @@ static int run(const void* A, const void* A_sc, const void* B, const void* B_sc,
     int grid = max_grid<CG>();
     if (grid <= 0) return MX8_ERR_CUDA;
     if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
-    const int tiles = p.tiles_m * p.tiles_n;
+    const int tiles = p.tiles_m * p.tiles_n * (gr.wgrad ? groups : 1);
     if (grid > tiles * CG) grid = tiles * CG;
     grid = (grid / CG) * CG;
     if (grid <= 0) grid = CG;
@@ -611,7 +682,7 @@ static int run(const void* A, const void* A_sc, const void* B, const void* B_sc,
     at[0].val.clusterDim.z = 1;
     cfg.attrs = at;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_kernel<CG>, m.a, m.b, m.sfa, m.sfb, m.c, p);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_kernel<CG>, m.a, m.b, m.sfa, m.sfb, m.a2, m.b2, m.sfa2, m.sfb2, m.c, p);
     if (e != cudaSuccess) {
         note_cuda_error("gemm launch", cudaGetErrorString(e));
         return MX8_ERR_CUDA;
@@ -701,4 +772,48 @@ extern "C" int mx8_debug_set_gemm_ablation(int flags) {
     const int old = mx8::gemm::g_ablation_flags;
     mx8::gemm::g_ablation_flags = flags;
     return old;
+}
+
+extern "C" int mx8_gemm_grouped_dual(const void* A1, const void* A1_sc, const void* B1, const void* B1_sc, const void* A2,
+                                     const void* A2_sc, const void* B2, const void* B2_sc, void* C, int M, int N, int K1, int K2,
+                                     const void* num_rows, const void* group_rows, int num_groups, void* stream) {
+    using namespace mx8;
+    if (!A1 || !A1_sc || !B1 || !B1_sc || !A2 || !A2_sc || !B2 || !B2_sc || !C) return MX8_ERR_ARG;
+    if (num_groups < 0 || (num_groups > 0 && !group_rows)) return MX8_ERR_ARG;
+    if (num_groups > gemm::MAX_GROUPS) {
+        note_cuda_error("mx8_gemm_grouped_dual", "more than 256 groups in one call");
+        return MX8_ERR_LIMIT;
+    }
+    if (M <= 0 || N <= 0 || K1 <= 0 || K2 <= 0 || M % 128 || N % 128 || K1 % 128 || K2 % 128) return MX8_ERR_SHAPE;
+    if (num_groups > 0 && (M % 256 || N % 256)) return MX8_ERR_SHAPE;
+    if (!aligned16(A1) || !aligned16(A1_sc) || !aligned16(B1) || !aligned16(B1_sc) || !aligned16(A2) || !aligned16(A2_sc) ||
+        !aligned16(B2) || !aligned16(B2_sc) || !aligned16(C)) return MX8_ERR_ALIGN;
+    int rc = check_device_sm100();
+    if (rc != MX8_OK) return rc;
+    gemm::Grouping gr;
+    gr.rows_dev = static_cast<const int*>(num_rows);
+    gr.group_rows = static_cast<const int*>(group_rows);
+    gr.num_groups = num_groups;
+    gr.A2 = A2; gr.A2_sc = A2_sc; gr.B2 = B2; gr.B2_sc = B2_sc; gr.K2 = K2;
+    return gemm::run<2>(A1, A1_sc, B1, B1_sc, C, M, N, K1, MX8_C_BF16, 0, gr, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int mx8_gemm_wgrad(const void* A_t, const void* A_t_sc, const void* B_t, const void* B_t_sc, void* C, int M, int N,
+                              int rows, const void* group_rows, int num_groups, void* stream) {
+    using namespace mx8;
+    if (!A_t || !A_t_sc || !B_t || !B_t_sc || !C || !group_rows) return MX8_ERR_ARG;
+    if (num_groups <= 0) return MX8_ERR_ARG;
+    if (num_groups > gemm::MAX_GROUPS) {
+        note_cuda_error("mx8_gemm_wgrad", "more than 256 groups in one call");
+        return MX8_ERR_LIMIT;
+    }
+    if (M <= 0 || N <= 0 || rows <= 0 || M % 256 || N % 128 || rows % 128) return MX8_ERR_SHAPE;
+    if (!aligned16(A_t) || !aligned16(A_t_sc) || !aligned16(B_t) || !aligned16(B_t_sc) || !aligned16(C)) return MX8_ERR_ALIGN;
+    int rc = check_device_sm100();
+    if (rc != MX8_OK) return rc;
+    gemm::Grouping gr;
+    gr.group_rows = static_cast<const int*>(group_rows);
+    gr.num_groups = num_groups;
+    gr.wgrad = true;
+    return gemm::run<2>(A_t, A_t_sc, B_t, B_t_sc, C, M, N, rows, MX8_C_BF16, 0, gr, static_cast<cudaStream_t>(stream));
 }

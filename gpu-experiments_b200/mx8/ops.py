@@ -196,3 +196,36 @@ def gemm_grouped(A, A_sc, B, B_sc, C, C_sc=None, num_rows=None, group_rows=None)
     grp = _chk(group_rows, "group_rows", (torch.int32,)) if group_rows is not None else None
     with torch.cuda.device(A.device):
         _lib.check(lib.mx8_gemm_grouped(ap, asp, bp, bsp, cp, csp, M, N, K, cd, nr, grp, G, _stream()), "gemm_grouped")
+
+
+def gemm_grouped_dual(A1, A1_sc, B1, B1_sc, A2, A2_sc, B2, B2_sc, C, num_rows=None, group_rows=None):
+    """C = dequant(A1) . dequant(B1_g)^T + dequant(A2) . dequant(B2_g)^T (bf16), grouped like gemm_grouped.
+    The data-gradient GEMM of the MoE backward (two operand pairs instead of concatenated tensors;
+    blackwell-ultra/022-moe-dispatch-mlp-swiglu-combine-mxfp8-bw.cu:1399-1736, second GEMM of expert_grouped_gemm)."""
+    lib = _lib.load()
+    M, K1 = A1.shape
+    K2 = A2.shape[1]
+    G = B1.shape[0] if group_rows is not None else 0
+    N = B1.shape[1] if group_rows is not None else B1.shape[0]
+    ptrs = [_chk(A1, "A1", _FP8), _chk(A1_sc, "A1_sc", _SC), _chk(B1, "B1", _FP8), _chk(B1_sc, "B1_sc", _SC),
+            _chk(A2, "A2", _FP8), _chk(A2_sc, "A2_sc", _SC), _chk(B2, "B2", _FP8), _chk(B2_sc, "B2_sc", _SC),
+            _chk(C, "C", (torch.bfloat16,), (M, N))]
+    nr = _chk(num_rows, "num_rows", (torch.int32,)) if num_rows is not None else None
+    grp = _chk(group_rows, "group_rows", (torch.int32,)) if group_rows is not None else None
+    with torch.cuda.device(A1.device):
+        _lib.check(lib.mx8_gemm_grouped_dual(*ptrs, M, N, K1, K2, nr, grp, G, _stream()), "gemm_grouped_dual")
+
+
+def gemm_wgrad(A_t, A_t_sc, B_t, B_t_sc, C, group_rows):
+    """C[g] = dequant(A_t[:, rows_g]) . dequant(B_t[:, rows_g])^T for every group g (bf16 [G, M, N]);
+    A_t [M, R] and B_t [N, R] are transposed quantizer outputs (blocks along R).  The weight-gradient
+    form of the reference's expert_grouped_gemm (IS_WGRAD)."""
+    lib = _lib.load()
+    M, R = A_t.shape
+    N = B_t.shape[0]
+    G = group_rows.numel()
+    with torch.cuda.device(A_t.device):
+        _lib.check(lib.mx8_gemm_wgrad(_chk(A_t, "A_t", _FP8), _chk(A_t_sc, "A_t_sc", _SC, (M // 128, R // 128, 512)),
+                                      _chk(B_t, "B_t", _FP8, (N, R)), _chk(B_t_sc, "B_t_sc", _SC, (N // 128, R // 128, 512)),
+                                      _chk(C, "C", (torch.bfloat16,), (G, M, N)), M, N, R,
+                                      _chk(group_rows, "group_rows", (torch.int32,)), G, _stream()), "gemm_wgrad")

@@ -140,6 +140,24 @@ MX8_API int mx8_gemm_grouped_scatter(const void* A, const void* A_sc, const void
                                      const void* num_rows, const void* group_rows, int num_groups, const void* peer_rank,
                                      const void* peer_token_idx, void* const* dst_ptrs, int world, void* stream);
 
+/* Grouped GEMM with two operand pairs accumulated into one bf16 result:
+ *   C = dequant(A1).dequant(B1_g)^T + dequant(A2).dequant(B2_g)^T,  A1 [M][K1], A2 [M][K2],
+ *   B1 [num_groups][N][K1], B2 [num_groups][N][K2]; grouping and num_rows as in mx8_gemm_grouped.
+ * This is the data-gradient GEMM of the MoE backward, d_x = [d_gate | d_up] . [Wg^T | Wu^T]^T without the
+ * concatenations; the optional second GEMM of expert_grouped_gemm,
+ * blackwell-ultra/022-…-mxfp8-bw.cu:1399-1736. */
+MX8_API int mx8_gemm_grouped_dual(const void* A1, const void* A1_sc, const void* B1, const void* B1_sc, const void* A2,
+                                  const void* A2_sc, const void* B2, const void* B2_sc, void* C, int M, int N, int K1, int K2,
+                                  const void* num_rows, const void* group_rows, int num_groups, void* stream);
+
+/* Weight-gradient GEMM: for every group g, C_g [M][N] (bf16) = dequant(A^T[:, rows_g]) . dequant(B^T[:, rows_g])^T
+ * where A^T is [M][rows] and B^T is [N][rows] (the transposed outputs of the quantizer, scale blocks
+ * along the row index), rows_g the consecutive group_rows[g] columns of group g (device int32,
+ * multiples of 128).  A group without rows yields zeros.  C is [num_groups][M][N].
+ * Replaces expert_grouped_gemm<false, true> (IS_WGRAD), blackwell-ultra/022-…-mxfp8-bw.cu:1399-1736. */
+MX8_API int mx8_gemm_wgrad(const void* A_t, const void* A_t_sc, const void* B_t, const void* B_t_sc, void* C, int M, int N,
+                           int rows, const void* group_rows, int num_groups, void* stream);
+
 /* Expert-parallel MoE routing schedule for the calling rank (int32 everywhere).
  *   topk_all [world][tokens][topk]: global expert ids chosen by every rank's tokens;
  *   this rank owns experts [rank*num_local_experts, (rank+1)*num_local_experts).

@@ -256,3 +256,51 @@ def test_fused_combine_equals_gemm_then_combine():
     for a, b in zip(*results):
         assert torch.equal(a.view(torch.int16), b.view(torch.int16))
     assert bool((results[0][0] != -1.0).any())
+
+
+def test_gemm_dual_operand_pairs():
+    # C = A1 B1_g^T + A2 B2_g^T equals the GEMM over the concatenated K dimension
+    E, N, K1, K2 = 3, 512, 256, 384
+    group_rows = torch.tensor([256, 512, 256], dtype=torch.int32)
+    R = int(group_rows.sum())
+    a1 = _quant(O.make_input(R, K1, seed=1, std=K1 ** -0.25))
+    a2 = _quant(O.make_input(R, K2, seed=2, std=K2 ** -0.25))
+    b1 = O.quantize_both(torch.stack([O.make_input(N, K1, seed=10 + e, std=K1 ** -0.25) for e in range(E)]))[:2]
+    b2 = O.quantize_both(torch.stack([O.make_input(N, K2, seed=20 + e, std=K2 ** -0.25) for e in range(E)]))[:2]
+    c = torch.full((R, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    mx8.gemm_grouped_dual(a1[0].to(DEV), a1[1].to(DEV), b1[0].to(DEV), b1[1].to(DEV), a2[0].to(DEV), a2[1].to(DEV),
+                          b2[0].to(DEV), b2[1].to(DEV), c, torch.tensor([R], dtype=torch.int32, device=DEV), group_rows.to(DEV))
+    assert mx8.device_status() == 0
+    off = 0
+    for e, n in enumerate(group_rows.tolist()):
+        rows, tiles = slice(off, off + n), slice(off // 128, (off + n) // 128)
+        d1 = O.dequantize(a1[0][rows], O.scale_unswizzle(a1[1][tiles])) @ O.dequantize(b1[0][e], O.scale_unswizzle(b1[1][e * N // 128:(e + 1) * N // 128])).t()
+        d2 = O.dequantize(a2[0][rows], O.scale_unswizzle(a2[1][tiles])) @ O.dequantize(b2[0][e], O.scale_unswizzle(b2[1][e * N // 128:(e + 1) * N // 128])).t()
+        ref = (d1 + d2).to(torch.bfloat16)
+        assert O.rel_frobenius(c[rows].cpu(), ref) < 2e-3, f"expert {e}"
+        off += n
+
+
+def test_gemm_wgrad_per_expert():
+    # dW_g = A^T[:, rows_g] B^T[:, rows_g]^T from transposed-quantized activations; an empty group gives zeros
+    M, N = 256, 384
+    group_rows = torch.tensor([256, 0, 512, 256], dtype=torch.int32)
+    R = int(group_rows.sum()) + 256                       # capacity beyond the rows in use
+    a = O.make_input(R, M, seed=5)                        # e.g. d_gate [rows, I]
+    b = O.make_input(R, N, seed=6)                        # e.g. x [rows, H]
+    _, _, at, ats = O.quantize_both(a)
+    _, _, bt, bts = O.quantize_both(b)
+    c = torch.full((4, M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    mx8.gemm_wgrad(at.to(DEV), ats.to(DEV), bt.to(DEV), bts.to(DEV), c, group_rows.to(DEV))
+    assert mx8.device_status() == 0
+    ad = O.dequantize(at, O.scale_unswizzle(ats))         # [M, R]
+    bd = O.dequantize(bt, O.scale_unswizzle(bts))         # [N, R]
+    off = 0
+    for e, n in enumerate(group_rows.tolist()):
+        got = c[e].cpu()
+        if n == 0:
+            assert not got.float().abs().any()
+        else:
+            ref = (ad[:, off:off + n] @ bd[:, off:off + n].t()).to(torch.bfloat16)
+            assert O.rel_frobenius(got, ref) < 2e-3, f"expert {e}"
+        off += n
