@@ -55,7 +55,7 @@ __global__ void __launch_bounds__(256) combine_kernel(CombineParams p) {
 struct EpilogueParams {
     const uint8_t* y_shared;     // [tokens][hidden] bf16 or nullptr (no shared expert)
     const uint8_t* combine;      // [tokens*topk][hidden] bf16
-    const float* weights;        // [tokens][topk]
+    const float* weights;        // [tokens][topk], nullptr = plain sum (backward epilogue)
     uint8_t* out;                // [tokens][hidden] bf16
     int tokens, hidden, topk;
 };
@@ -83,7 +83,7 @@ __global__ void __launch_bounds__(256) epilogue_kernel(EpilogueParams p) {
             for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
         }
         for (int j = 0; j < p.topk; ++j) {
-            const float w = p.weights[static_cast<size_t>(t) * p.topk + j];
+            const float w = p.weights ? p.weights[static_cast<size_t>(t) * p.topk + j] : 1.0f;
             float v[8];
             unpack8(reinterpret_cast<const uint4*>(p.combine)[(static_cast<size_t>(t) * p.topk + j) * n16 + c], v);
 #pragma unroll
@@ -95,6 +95,28 @@ __global__ void __launch_bounds__(256) epilogue_kernel(EpilogueParams p) {
         o.z = pack_bf16x2(acc[4], acc[5]);
         o.w = pack_bf16x2(acc[6], acc[7]);
         reinterpret_cast<uint4*>(p.out)[idx] = o;
+    }
+}
+
+// backward prologue: d_combine[t*topk + j] = bf16( d_output[t] * w[t][j] )
+__global__ void __launch_bounds__(256) bwd_prologue_kernel(const uint8_t* d_out, const float* weights, uint8_t* d_combine, int tokens,
+                                                           int hidden, int topk) {
+    const int n16 = hidden / 8;
+    const long long total = static_cast<long long>(tokens) * n16;
+    for (long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
+         idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int t = static_cast<int>(idx / n16), c = static_cast<int>(idx - static_cast<long long>(t) * n16);
+        float v[8];
+        unpack8(reinterpret_cast<const uint4*>(d_out)[idx], v);
+        for (int j = 0; j < topk; ++j) {
+            const float w = weights[static_cast<size_t>(t) * topk + j];
+            uint4 o;
+            o.x = pack_bf16x2(__fmul_rn(v[0], w), __fmul_rn(v[1], w));
+            o.y = pack_bf16x2(__fmul_rn(v[2], w), __fmul_rn(v[3], w));
+            o.z = pack_bf16x2(__fmul_rn(v[4], w), __fmul_rn(v[5], w));
+            o.w = pack_bf16x2(__fmul_rn(v[6], w), __fmul_rn(v[7], w));
+            reinterpret_cast<uint4*>(d_combine)[(static_cast<size_t>(t) * topk + j) * n16 + c] = o;
+        }
     }
 }
 
@@ -148,6 +170,50 @@ extern "C" int mx8_moe_fwd_epilogue(const void* y_shared, const void* combine_bu
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
         note_cuda_error("moe epilogue launch", cudaGetErrorString(e));
+        return MX8_ERR_CUDA;
+    }
+    return MX8_OK;
+}
+
+extern "C" int mx8_moe_bwd_prologue(const void* d_output, const void* topk_weights, void* d_combine_buffer, int tokens, int hidden,
+                                    int topk, void* stream) {
+    using namespace mx8;
+    if (!d_output || !topk_weights || !d_combine_buffer) return MX8_ERR_ARG;
+    if (tokens <= 0 || topk <= 0) return MX8_ERR_ARG;
+    if (hidden <= 0 || hidden % 8) return MX8_ERR_SHAPE;
+    if (!aligned16(d_output) || !aligned16(d_combine_buffer)) return MX8_ERR_ALIGN;
+    int rc = check_device_sm100();
+    if (rc != MX8_OK) return rc;
+    const int sms = sm_count();
+    if (sms <= 0) return MX8_ERR_CUDA;
+    moe::bwd_prologue_kernel<<<sms * 8, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint8_t*>(d_output), static_cast<const float*>(topk_weights), static_cast<uint8_t*>(d_combine_buffer), tokens,
+        hidden, topk);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        note_cuda_error("moe bwd prologue launch", cudaGetErrorString(e));
+        return MX8_ERR_CUDA;
+    }
+    return MX8_OK;
+}
+
+extern "C" int mx8_moe_bwd_epilogue(const void* d_x_shared, const void* d_x_routed_buffer, void* d_x, int tokens, int hidden,
+                                    int topk, void* stream) {
+    using namespace mx8;
+    if (!d_x_routed_buffer || !d_x) return MX8_ERR_ARG;
+    if (tokens <= 0 || topk <= 0) return MX8_ERR_ARG;
+    if (hidden <= 0 || hidden % 8) return MX8_ERR_SHAPE;
+    if (!aligned16(d_x_shared) || !aligned16(d_x_routed_buffer) || !aligned16(d_x)) return MX8_ERR_ALIGN;
+    int rc = check_device_sm100();
+    if (rc != MX8_OK) return rc;
+    moe::EpilogueParams p{static_cast<const uint8_t*>(d_x_shared), static_cast<const uint8_t*>(d_x_routed_buffer), nullptr,
+                          static_cast<uint8_t*>(d_x), tokens, hidden, topk};
+    const int sms = sm_count();
+    if (sms <= 0) return MX8_ERR_CUDA;
+    moe::epilogue_kernel<<<sms * 8, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        note_cuda_error("moe bwd epilogue launch", cudaGetErrorString(e));
         return MX8_ERR_CUDA;
     }
     return MX8_OK;

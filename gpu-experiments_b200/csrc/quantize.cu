@@ -28,7 +28,7 @@ namespace quant {
 
 constexpr int TILE = 128;
 constexpr int SLAB_ROWS = 32;
-constexpr int SLOT_BYTES = SLAB_ROWS * TILE * 2;   // one bf16 slab
+constexpr int SLOT_BYTES = SLAB_ROWS * TILE * 2;   // one bf16 slab (or two E4M3 slabs)
 constexpr int TSTAGE_BYTES = SLAB_ROWS * TILE;     // transposed fp8 staging per warp
 constexpr int SCSTAGE_BYTES = 128;                 // row-wise scale bytes of one slab: [row][kb]
 
@@ -52,19 +52,22 @@ struct Params {
     const uint8_t* gate_sc;       // SwiGLU: scale tiles of the two E4M3 inputs
     const uint8_t* up_sc;
     uint8_t* hidden_bf16;         // SwiGLU: optional bf16 copy of the activation (tests), else nullptr
+    int bwd_which;                // SwiGLU backward: 0 = gradient of gate, 1 = gradient of up
     int* status;
 };
 
-constexpr int SRC_DENSE = 0, SRC_GATHER = 1, SRC_SWIGLU = 2;
+constexpr int SRC_DENSE = 0, SRC_GATHER = 1, SRC_SWIGLU = 2, SRC_SWIGLU_BWD = 3;
+// bytes of one ring slot: the backward of SwiGLU also needs the bf16 gradient of the activation
+__host__ __device__ constexpr int slot_bytes(int src) { return src == SRC_SWIGLU_BWD ? 2 * SLOT_BYTES : SLOT_BYTES; }
 // producer warps: the gather source looks two indices up per row before it can issue a copy, so
 // several warps work on different slabs to keep enough copies in flight
 __host__ __device__ constexpr int producer_warps(int src) { return src == SRC_GATHER ? 4 : 1; }
 
-template <int W, int D>
+template <int W, int D, int SLOT = SLOT_BYTES>
 struct Smem {
     static constexpr int S = W * D;                               // slots in the ring
     static constexpr int ring = 0;
-    static constexpr int tstage = ring + S * SLOT_BYTES;
+    static constexpr int tstage = ring + S * SLOT;
     static constexpr int scstage = tstage + W * TSTAGE_BYTES;
     static constexpr int bars = scstage + W * SCSTAGE_BYTES;      // full[S], empty[S]
     static constexpr int flag = bars + 2 * S * 8;
@@ -91,8 +94,9 @@ __device__ __forceinline__ void tile_coords(int t, const Params& p, int tiles_r,
 template <int W, int D, int SRC, bool ROW, bool COL>
 __global__ void __launch_bounds__((producer_warps(SRC) + W) * 32, 1)
 quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ CUtensorMap tm_in2,
-                const __grid_constant__ CUtensorMap tm_t, const Params p) {
-    using L = Smem<W, D>;
+                const __grid_constant__ CUtensorMap tm_in3, const __grid_constant__ CUtensorMap tm_t, const Params p) {
+    constexpr int SLOT = slot_bytes(SRC);
+    using L = Smem<W, D, SLOT>;
     constexpr int S = L::S;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -141,7 +145,7 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
                 if (pl == 0) ok = mbar_wait(empty0 + slot * 8, ph ^ 1, ab, DEV_TIMEOUT_EMPTY) ? 1 : 0;
                 ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
                 if (!ok) break;
-                const uint32_t dst = base + L::ring + slot * SLOT_BYTES + pl * 256;
+                const uint32_t dst = base + L::ring + slot * SLOT + pl * 256;
                 if (pr >= 0) {
                     const uint8_t* s = p.src[pr] + (static_cast<size_t>(tok / p.topk) * p.N + tc * TILE) * 2;
                     mbar_arrive_expect_tx(full0 + slot * 8, 256);
@@ -160,12 +164,14 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
                 const int t = static_cast<int>(blockIdx.x) + (n >> 2) * static_cast<int>(gridDim.x);
                 int tr, tc;
                 tile_coords(t, p, tiles_r, tr, tc);
-                const uint32_t dst = base + L::ring + slot * SLOT_BYTES;
-                mbar_arrive_expect_tx(full0 + slot * 8, SLOT_BYTES);
-                if constexpr (SRC == SRC_SWIGLU) {
+                const uint32_t dst = base + L::ring + slot * SLOT;
+                mbar_arrive_expect_tx(full0 + slot * 8, SLOT);
+                if constexpr (SRC == SRC_SWIGLU || SRC == SRC_SWIGLU_BWD) {
                     // two E4M3 slabs of 32 x 128 bytes: gate, then up
                     tma_load_2d(dst, &tm_in, tc * TILE, tr * TILE + (n & 3) * SLAB_ROWS, full0 + slot * 8);
                     tma_load_2d(dst + SLOT_BYTES / 2, &tm_in2, tc * TILE, tr * TILE + (n & 3) * SLAB_ROWS, full0 + slot * 8);
+                    if constexpr (SRC == SRC_SWIGLU_BWD)   // bf16 gradient of the activation
+                        tma_load_2d(dst + SLOT_BYTES, &tm_in3, tc * TILE, tr * TILE + (n & 3) * SLAB_ROWS, full0 + slot * 8);
                 } else {
                     tma_load_2d(dst, &tm_in, tc * TILE, tr * TILE + (n & 3) * SLAB_ROWS, full0 + slot * 8);
                 }
@@ -185,7 +191,7 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
         // slab n lives in slot n % S; S is a multiple of W, so a slot is only ever read by one warp
         const int slot = n % S;
         const uint32_t ph = (n / S) & 1;
-        const uint32_t slot_addr = base + L::ring + slot * SLOT_BYTES;
+        const uint32_t slot_addr = base + L::ring + slot * SLOT;
         const int wq = n & 3;
         const int t = static_cast<int>(blockIdx.x) + (n >> 2) * static_cast<int>(gridDim.x);
         int tr, tc;
@@ -193,8 +199,9 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
         if (!mbar_wait(full0 + slot * 8, ph, ab, DEV_TIMEOUT_FULL)) break;
 
         uint32_t c[32][2];                 // c[i] = columns 4l..4l+3 of slab row i (bf16 pairs)
-        if constexpr (SRC == SRC_SWIGLU) {
-            // hidden = bf16( silu(dequant(gate)) * dequant(up) ), computed in fp32
+        if constexpr (SRC == SRC_SWIGLU || SRC == SRC_SWIGLU_BWD) {
+            // forward: hidden = bf16( silu(dequant(gate)) * dequant(up) ), computed in fp32;
+            // backward: d_gate = bf16( (silu'(g) * u) * d_hidden ) or d_up = bf16( silu(g) * d_hidden )
             const size_t sc_tile = (static_cast<size_t>(tr) * p.tiles_c + tc) * 512 + l * 16 + wq * 4;
             const uint32_t gw = *reinterpret_cast<const uint32_t*>(p.gate_sc + sc_tile);   // lane i: scale bytes of row i
             const uint32_t uw = *reinterpret_cast<const uint32_t*>(p.up_sc + sc_tile);
@@ -210,9 +217,23 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
                 e4m3x4_to_float(g4, gf);
                 e4m3x4_to_float(u4, uf);
 #pragma unroll
+                float dh[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                if constexpr (SRC == SRC_SWIGLU_BWD) {
+                    uint32_t d0, d1;
+                    ld_shared_v2(slot_addr + SLOT_BYTES + i * 256 + l * 8, d0, d1);
+                    dh[0] = bf16_lo(d0); dh[1] = bf16_hi(d0); dh[2] = bf16_lo(d1); dh[3] = bf16_hi(d1);
+                }
+#pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const float g = gf[e] * gs;
-                    h[e] = __fdividef(g, 1.0f + __expf(-g)) * (uf[e] * us);
+                    if constexpr (SRC == SRC_SWIGLU_BWD) {
+                        const float sig = __fdividef(1.0f, 1.0f + __expf(-g));
+                        const float silu = g * sig;
+                        const float dsilu = (1.0f - silu) * sig + silu;
+                        h[e] = p.bwd_which ? silu * dh[e] : (dsilu * (uf[e] * us)) * dh[e];
+                    } else {
+                        h[e] = __fdividef(g, 1.0f + __expf(-g)) * (uf[e] * us);
+                    }
                 }
                 c[i][0] = pack_bf16x2(h[0], h[1]);
                 c[i][1] = pack_bf16x2(h[2], h[3]);
@@ -319,10 +340,10 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
 }
 
 template <int W, int D, int SRC, bool ROW, bool COL>
-static int launch(const CUtensorMap& tm_in, const CUtensorMap& tm_in2, const CUtensorMap& tm_t, const Params& p, int grid,
-                  cudaStream_t stream) {
+static int launch(const CUtensorMap& tm_in, const CUtensorMap& tm_in2, const CUtensorMap& tm_in3, const CUtensorMap& tm_t,
+                  const Params& p, int grid, cudaStream_t stream) {
     auto kern = quantize_kernel<W, D, SRC, ROW, COL>;
-    constexpr int smem = Smem<W, D>::dynamic;
+    constexpr int smem = Smem<W, D, slot_bytes(SRC)>::dynamic;
     static bool configured[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -334,7 +355,7 @@ static int launch(const CUtensorMap& tm_in, const CUtensorMap& tm_in2, const CUt
         }
         configured[dev & 63] = true;
     }
-    kern<<<grid, (producer_warps(SRC) + W) * 32, smem, stream>>>(tm_in, tm_in2, tm_t, p);
+    kern<<<grid, (producer_warps(SRC) + W) * 32, smem, stream>>>(tm_in, tm_in2, tm_in3, tm_t, p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
         note_cuda_error("quantize launch", cudaGetErrorString(e));
@@ -404,9 +425,9 @@ extern "C" int mx8_quantize(const void* x_bf16, int E, int M, int N, void* fp8, 
     // Both orientations: 8 consumer warps with one slot each measured best (deeper prefetch lowers
     // throughput once reads and both write streams compete); a single orientation does less
     // arithmetic per slab and prefers 6 warps with two slots each.
-    if (row && col) return launch<8, 1, SRC_DENSE, true, true>(tm_in, tm_in, tm_t, p, grid, st);
-    if (row) return launch<6, 2, SRC_DENSE, true, false>(tm_in, tm_in, tm_t, p, grid, st);
-    return launch<6, 2, SRC_DENSE, false, true>(tm_in, tm_in, tm_t, p, grid, st);
+    if (row && col) return launch<8, 1, SRC_DENSE, true, true>(tm_in, tm_in, tm_in, tm_t, p, grid, st);
+    if (row) return launch<6, 2, SRC_DENSE, true, false>(tm_in, tm_in, tm_in, tm_t, p, grid, st);
+    return launch<6, 2, SRC_DENSE, false, true>(tm_in, tm_in, tm_in, tm_t, p, grid, st);
 }
 
 namespace mx8 {
@@ -466,7 +487,7 @@ extern "C" int mx8_moe_dispatch_quantize(const void* const* x_ptrs, int world, i
     if (grid <= 0) return MX8_ERR_CUDA;
     const int tiles = p.tiles_r * p.tiles_c;
     if (grid > tiles) grid = tiles;
-    return launch<8, 1, SRC_GATHER, true, true>(tm_t, tm_t, tm_t, p, grid, static_cast<cudaStream_t>(stream));
+    return launch<8, 1, SRC_GATHER, true, true>(tm_t, tm_t, tm_t, tm_t, p, grid, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int mx8_swiglu_quantize(const void* gate_fp8, const void* gate_sc, const void* up_fp8, const void* up_sc,
@@ -500,5 +521,43 @@ extern "C" int mx8_swiglu_quantize(const void* gate_fp8, const void* gate_sc, co
     if (grid <= 0) return MX8_ERR_CUDA;
     const int tiles = p.tiles_r * p.tiles_c;
     if (grid > tiles) grid = tiles;
-    return launch<8, 1, SRC_SWIGLU, true, true>(tm_g, tm_u, tm_t, p, grid, static_cast<cudaStream_t>(stream));
+    return launch<8, 1, SRC_SWIGLU, true, true>(tm_g, tm_u, tm_u, tm_t, p, grid, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int mx8_swiglu_bwd_quantize(const void* gate_fp8, const void* gate_sc, const void* up_fp8, const void* up_sc,
+                                       const void* d_hidden, int rows, int cols, const void* num_rows, int which, void* out_fp8,
+                                       void* out_sc, void* out_fp8_t, void* out_sc_t, void* out_bf16, void* stream) {
+    using namespace mx8;
+    using namespace mx8::quant;
+    if (!gate_fp8 || !gate_sc || !up_fp8 || !up_sc || !d_hidden || !out_fp8 || !out_sc || !out_fp8_t || !out_sc_t) return MX8_ERR_ARG;
+    if (which != 0 && which != 1) return MX8_ERR_ARG;
+    if (rows <= 0 || cols <= 0 || rows % 128 || cols % 128) return MX8_ERR_SHAPE;
+    if (!aligned16(gate_fp8) || !aligned16(gate_sc) || !aligned16(up_fp8) || !aligned16(up_sc) || !aligned16(d_hidden) ||
+        !aligned16(out_fp8) || !aligned16(out_sc) || !aligned16(out_fp8_t) || !aligned16(out_sc_t) || !aligned16(out_bf16))
+        return MX8_ERR_ALIGN;
+    int rc = check_device_sm100();
+    if (rc != MX8_OK) return rc;
+    Params p{};
+    fill_common(p, out_fp8, out_sc, out_sc_t, rows, cols);
+    p.rows_dev = static_cast<const int*>(num_rows);
+    p.gate_sc = static_cast<const uint8_t*>(gate_sc);
+    p.up_sc = static_cast<const uint8_t*>(up_sc);
+    p.hidden_bf16 = static_cast<uint8_t*>(out_bf16);
+    p.bwd_which = which;
+    p.status = device_status_ptr();
+    if (!p.status) return MX8_ERR_CUDA;
+    CUtensorMap tm_g, tm_u, tm_d, tm_t;
+    const uint64_t dims[2] = {static_cast<uint64_t>(cols), static_cast<uint64_t>(rows)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(cols)};
+    const uint64_t strides2[1] = {static_cast<uint64_t>(cols) * 2};
+    const uint32_t box[2] = {128, SLAB_ROWS};
+    if ((rc = make_tmap(&tm_g, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, gate_fp8, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE)) != MX8_OK) return rc;
+    if ((rc = make_tmap(&tm_u, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, up_fp8, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE)) != MX8_OK) return rc;
+    if ((rc = make_tmap(&tm_d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, d_hidden, dims, strides2, box, CU_TENSOR_MAP_SWIZZLE_NONE)) != MX8_OK) return rc;
+    if ((rc = make_transposed_map(&tm_t, out_fp8_t, 1, rows, cols)) != MX8_OK) return rc;
+    int grid = sm_count();
+    if (grid <= 0) return MX8_ERR_CUDA;
+    const int tiles = p.tiles_r * p.tiles_c;
+    if (grid > tiles) grid = tiles;
+    return launch<8, 1, SRC_SWIGLU_BWD, true, true>(tm_g, tm_u, tm_d, tm_t, p, grid, static_cast<cudaStream_t>(stream));
 }

@@ -139,3 +139,127 @@ def dispatch_mlp_swiglu_combine_fwd(x, x_ptrs, combine_buffer, combine_buffer_pt
         y_shared = hidden_shared @ w_shared_down.t()
     return (x_fp8_t, x_sc_t, gate_shared, gate_fp8, gate_sc, up_shared, up_fp8, up_sc,
             hidden_shared, h_fp8_t, h_sc_t, y_shared, y_routed)
+
+
+# ------------------------------------------------------------------------------------------------
+# backward (routed experts)
+# ------------------------------------------------------------------------------------------------
+def swiglu_bwd_quantize(gate_fp8, gate_sc, up_fp8, up_sc, d_hidden, which, num_rows=None, return_bf16=False):
+    """Gradient of SwiGLU with respect to gate (which=0) or up (which=1), re-quantized both ways.
+    Returns (fp8, sc, fp8_t, sc_t[, bf16])."""
+    lib = _lib.load()
+    R, I = gate_fp8.shape
+    dev = gate_fp8.device
+    o_fp8 = torch.empty(R, I, dtype=torch.float8_e4m3fn, device=dev)
+    o_sc = torch.empty(R // 128, I // 128, 32, 16, dtype=torch.uint8, device=dev)
+    o_fp8_t = torch.empty(I, R, dtype=torch.float8_e4m3fn, device=dev)
+    o_sc_t = torch.empty(I // 128, R // 128, 32, 16, dtype=torch.uint8, device=dev)
+    o_bf16 = torch.empty(R, I, dtype=torch.bfloat16, device=dev) if return_bf16 else None
+    with torch.cuda.device(dev):
+        _lib.check(lib.mx8_swiglu_bwd_quantize(
+            _chk(gate_fp8, "gate_fp8", _FP8), _chk(gate_sc, "gate_sc", _SC, (R // 128, I // 128, 512)),
+            _chk(up_fp8, "up_fp8", _FP8, (R, I)), _chk(up_sc, "up_sc", _SC, (R // 128, I // 128, 512)),
+            _chk(d_hidden, "d_hidden", (torch.bfloat16,), (R, I)), R, I,
+            _chk(num_rows, "num_rows", (torch.int32,)) if num_rows is not None else None, int(which),
+            o_fp8.data_ptr(), o_sc.data_ptr(), o_fp8_t.data_ptr(), o_sc_t.data_ptr(),
+            o_bf16.data_ptr() if return_bf16 else None, _stream()), "swiglu_bwd_quantize")
+    return (o_fp8, o_sc, o_fp8_t, o_sc_t) + ((o_bf16,) if return_bf16 else ())
+
+
+def bwd_prologue(d_output, topk_weights, d_combine_buffer):
+    """bwd_prologue(d_output, topk_weights, d_combine_buffer) -> d_y_shared (== d_output); fills
+    d_combine_buffer[t*topk + j] = d_output[t] * w[t, j] in place
+    (blackwell-ultra/022-…-mxfp8-bw.cu:2915-2923)."""
+    lib = _lib.load()
+    T, k = topk_weights.shape
+    H = d_output.shape[1]
+    with torch.cuda.device(d_output.device):
+        _lib.check(lib.mx8_moe_bwd_prologue(_chk(d_output, "d_output", (torch.bfloat16,), (T, H)),
+                                            _chk(topk_weights, "topk_weights", (torch.float32,)),
+                                            _chk(d_combine_buffer, "d_combine_buffer", (torch.bfloat16,), (T * k, H)),
+                                            T, H, k, _stream()), "bwd_prologue")
+    return d_output
+
+
+def bwd_epilogue(d_x_shared, d_x_routed_buffer):
+    """bwd_epilogue(d_x_shared, d_x_routed_buffer) -> d_x = d_x_shared + sum over the topk rows of every
+    token (blackwell-ultra/022-…-mxfp8-bw.cu:2982-2993).  d_x_shared may be None; then its shape is taken
+    from `d_x_routed_buffer` and the `tokens` it was built for must divide its rows (pass topk via shape)."""
+    raise_if = d_x_shared is None
+    if raise_if:
+        raise ValueError("bwd_epilogue needs d_x_shared (use bwd_epilogue_routed for the routed part alone)")
+    return bwd_epilogue_routed(d_x_shared, d_x_routed_buffer, d_x_routed_buffer.shape[0] // d_x_shared.shape[0])
+
+
+def bwd_epilogue_routed(d_x_shared, d_x_routed_buffer, topk):
+    lib = _lib.load()
+    H = d_x_routed_buffer.shape[1]
+    T = d_x_routed_buffer.shape[0] // topk
+    d_x = torch.empty(T, H, dtype=torch.bfloat16, device=d_x_routed_buffer.device)
+    with torch.cuda.device(d_x.device):
+        _lib.check(lib.mx8_moe_bwd_epilogue(
+            _chk(d_x_shared, "d_x_shared", (torch.bfloat16,), (T, H)) if d_x_shared is not None else None,
+            _chk(d_x_routed_buffer, "d_x_routed_buffer", (torch.bfloat16,), (T * topk, H)), d_x.data_ptr(), T, H, topk,
+            _stream()), "bwd_epilogue")
+    return d_x
+
+
+def dispatch_mlp_swiglu_combine_bwd(d_y_shared, d_combine_buffer, d_combine_buffer_ptrs, d_x_routed_buffer, d_x_routed_buffer_ptrs,
+                                    w_shared_gate_T, w_routed_gate_T, w_routed_gate_T_sc,
+                                    w_shared_up_T, w_routed_up_T, w_routed_up_T_sc,
+                                    w_shared_down_T, w_routed_down_T, w_routed_down_T_sc,
+                                    x_fp8_t_routed, x_sc_t_routed,
+                                    gate_shared, gate_fp8_routed, gate_sc_routed,
+                                    up_shared, up_fp8_routed, up_sc_routed,
+                                    hidden_shared, hidden_fp8_t_routed, hidden_sc_t_routed,
+                                    x_buffer, x_buffer_ptrs,
+                                    w_routed_gate, w_routed_gate_sc, w_routed_up, w_routed_up_sc,
+                                    schedule_peer_rank, schedule_peer_token_idx, num_tokens, tokens_per_expert,
+                                    topk, num_comm_sms=0, macrobatch_size=0, minibatch_size=0):
+    """Same arguments and the same 18 return values as the reference's backward binding
+    (blackwell-ultra/022-…-mxfp8-bw.cu:2556-2760, bound at :3011-3028):
+      (d_x_shared, d_x_routed, d_gate_shared, d_gate_fp8_routed, d_gate_sc_routed, d_up_shared,
+       d_up_fp8_routed, d_up_sc_routed, d_hidden_shared, d_hidden_routed, d_y_routed_fp8_routed,
+       d_y_routed_sc_routed, d_w_shared_gate, d_w_routed_gate, d_w_shared_up, d_w_routed_up,
+       d_w_shared_down, d_w_routed_down)
+    The routed part runs on the MXFP8 kernels; it uses the transposed activations the forward returned
+    (x_fp8_t_routed, hidden_fp8_t_routed), so the arguments the reference needs only to replay its
+    forward (x_buffer, x_buffer_ptrs, w_routed_gate/up) are accepted and unused.  The shared expert
+    (bf16) runs on torch's library GEMM when its inputs are given, else those outputs are None."""
+    E, H, I = w_routed_gate_T.shape                      # transposed weights: [E, H, I]
+    cap = schedule_peer_rank.numel()
+    dev = d_combine_buffer.device
+    # gradient rows of the routed outputs, pulled from the owners' buffers (one row per (token, k) pair)
+    d_y_fp8, d_y_sc, d_y_fp8_t, d_y_sc_t = dispatch_quantize(d_combine_buffer_ptrs, H, 1, schedule_peer_rank,
+                                                               schedule_peer_token_idx, num_tokens, cap)
+    d_hidden = torch.empty(cap, I, dtype=torch.bfloat16, device=dev)
+    gemm_grouped(d_y_fp8, d_y_sc, w_routed_down_T, w_routed_down_T_sc, d_hidden, None, num_tokens, tokens_per_expert)
+    d_gate_fp8, d_gate_sc, d_gate_fp8_t, d_gate_sc_t = swiglu_bwd_quantize(gate_fp8_routed, gate_sc_routed, up_fp8_routed,
+                                                                            up_sc_routed, d_hidden, 0, num_tokens)
+    d_up_fp8, d_up_sc, d_up_fp8_t, d_up_sc_t = swiglu_bwd_quantize(gate_fp8_routed, gate_sc_routed, up_fp8_routed,
+                                                                    up_sc_routed, d_hidden, 1, num_tokens)
+    from .ops import gemm_grouped_dual, gemm_wgrad
+    d_x_routed = torch.empty(cap, H, dtype=torch.bfloat16, device=dev)
+    gemm_grouped_dual(d_gate_fp8, d_gate_sc, w_routed_gate_T, w_routed_gate_T_sc, d_up_fp8, d_up_sc, w_routed_up_T,
+                      w_routed_up_T_sc, d_x_routed, num_tokens, tokens_per_expert)
+    combine(d_x_routed, schedule_peer_rank, schedule_peer_token_idx, num_tokens, d_x_routed_buffer_ptrs)
+    d_w_gate = torch.empty(E, I, H, dtype=torch.bfloat16, device=dev)
+    d_w_up = torch.empty(E, I, H, dtype=torch.bfloat16, device=dev)
+    d_w_down = torch.empty(E, H, I, dtype=torch.bfloat16, device=dev)
+    gemm_wgrad(d_gate_fp8_t, d_gate_sc_t, x_fp8_t_routed, x_sc_t_routed, d_w_gate, tokens_per_expert)
+    gemm_wgrad(d_up_fp8_t, d_up_sc_t, x_fp8_t_routed, x_sc_t_routed, d_w_up, tokens_per_expert)
+    gemm_wgrad(d_y_fp8_t, d_y_sc_t, hidden_fp8_t_routed, hidden_sc_t_routed, d_w_down, tokens_per_expert)
+    d_x_shared = d_gate_shared = d_up_shared = d_hidden_shared = d_w_sg = d_w_su = d_w_sd = None
+    if w_shared_gate_T is not None and d_y_shared is not None:
+        x = x_buffer
+        d_hidden_shared = d_y_shared @ w_shared_down_T.t()
+        g = gate_shared.float()
+        den = torch.exp(-g) + 1.0
+        silu = g / den
+        d_silu = (1.0 - silu) / den + silu
+        d_gate_shared = ((d_hidden_shared.float() * d_silu) * up_shared.float()).to(torch.bfloat16)
+        d_up_shared = (silu * d_hidden_shared.float()).to(torch.bfloat16)
+        d_x_shared = d_gate_shared @ w_shared_gate_T.t() + d_up_shared @ w_shared_up_T.t()
+        d_w_sg, d_w_su, d_w_sd = d_gate_shared.t() @ x, d_up_shared.t() @ x, d_y_shared.t() @ hidden_shared
+    return (d_x_shared, d_x_routed, d_gate_shared, d_gate_fp8, d_gate_sc, d_up_shared, d_up_fp8, d_up_sc,
+            d_hidden_shared, d_hidden, d_y_fp8, d_y_sc, d_w_sg, d_w_gate, d_w_su, d_w_up, d_w_sd, d_w_down)

@@ -158,6 +158,26 @@ MX8_API int mx8_gemm_grouped_dual(const void* A1, const void* A1_sc, const void*
 MX8_API int mx8_gemm_wgrad(const void* A_t, const void* A_t_sc, const void* B_t, const void* B_t_sc, void* C, int M, int N,
                            int rows, const void* group_rows, int num_groups, void* stream);
 
+/* Backward of SwiGLU on MXFP8 inputs, re-quantized both ways: with g = dequant(gate), u = dequant(up),
+ * s = sigmoid(g): which == 0 -> d_gate = bf16( ((1 - g s) s + g s) * u * d_hidden ), which == 1 ->
+ * d_up = bf16( g s * d_hidden ); d_hidden bf16 [rows][cols].  Outputs as in mx8_swiglu_quantize;
+ * out_bf16 (may be NULL) receives the bf16 gradient.
+ * Replaces the SwiGLU backward task of the reference's backward kernel,
+ * blackwell-ultra/022-…-mxfp8-bw.cu:1131-1397; arithmetic as in …-mxfp8-bw.py:167-171. */
+MX8_API int mx8_swiglu_bwd_quantize(const void* gate_fp8, const void* gate_sc, const void* up_fp8, const void* up_sc,
+                                    const void* d_hidden, int rows, int cols, const void* num_rows, int which, void* out_fp8,
+                                    void* out_sc, void* out_fp8_t, void* out_sc_t, void* out_bf16, void* stream);
+
+/* d_combine_buffer[t*topk + j] = bf16( d_output[t] * topk_weights[t][j] ) (bf16 [tokens][hidden] in,
+ * [tokens*topk][hidden] out).  Replaces bwd_prologue, blackwell-ultra/022-…-mxfp8-bw.cu:2881-2923. */
+MX8_API int mx8_moe_bwd_prologue(const void* d_output, const void* topk_weights, void* d_combine_buffer, int tokens, int hidden,
+                                 int topk, void* stream);
+
+/* d_x[t] = bf16( d_x_shared[t] + sum_j d_x_routed_buffer[t*topk + j] ), fp32 sum, j ascending; d_x_shared
+ * may be NULL.  Replaces bwd_epilogue, blackwell-ultra/022-…-mxfp8-bw.cu:2945-2993. */
+MX8_API int mx8_moe_bwd_epilogue(const void* d_x_shared, const void* d_x_routed_buffer, void* d_x, int tokens, int hidden,
+                                 int topk, void* stream);
+
 /* Expert-parallel MoE routing schedule for the calling rank (int32 everywhere).
  *   topk_all [world][tokens][topk]: global expert ids chosen by every rank's tokens;
  *   this rank owns experts [rank*num_local_experts, (rank+1)*num_local_experts).

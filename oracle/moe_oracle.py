@@ -134,3 +134,75 @@ def fwd_epilogue_ref(y_shared, combine_buffer, topk_weights) -> torch.Tensor:
     for j in range(k):
         acc = acc + cb[:, j] * topk_weights[:, j:j + 1].float()
     return acc.to(torch.bfloat16)
+
+
+# --------------------------------------------------------------------------------------
+# backward (routed experts), following blackwell-ultra/022-…-mxfp8-bw.py:129-215
+# --------------------------------------------------------------------------------------
+def bwd_prologue_ref(d_output, topk_weights):
+    """d_combine[t*k + j] = bf16(d_output[t] * w[t, j])."""
+    T, k = topk_weights.shape
+    return (d_output.float().unsqueeze(1) * topk_weights.float().unsqueeze(2)).to(torch.bfloat16).reshape(T * k, -1)
+
+
+def swiglu_bwd_ref(gate_q, gate_sc_tiles, up_q, up_sc_tiles, d_hidden):
+    """(d_gate, d_up) in bf16 (…-mxfp8-bw.py:167-171)."""
+    g = O.dequantize(gate_q, O.scale_unswizzle(gate_sc_tiles)).to(torch.bfloat16).float()
+    u = O.dequantize(up_q, O.scale_unswizzle(up_sc_tiles)).to(torch.bfloat16).float()
+    sig = 1.0 / (1.0 + torch.exp(-g))
+    silu = g * sig
+    d_silu = (1.0 - silu) * sig + silu
+    dh = d_hidden.float()
+    return ((d_silu * u) * dh).to(torch.bfloat16), (silu * dh).to(torch.bfloat16)
+
+
+def expert_mlp_bwd_ref(d_y_routed, fwd, tokens_per_expert, wg_T, wu_T, wd_T):
+    """Routed-expert backward.  d_y_routed bf16 [R, H] (already dispatched); fwd = the dict returned by
+    expert_mlp_ref; w*_T = (fp8, scale tiles) of the transposed weights: gate/up [E, H, I], down [E, I, H]."""
+    (wg_q, wg_sc), (wu_q, wu_sc), (wd_q, wd_sc) = wg_T, wu_T, wd_T
+    E, H, I = wg_q.shape
+    R = d_y_routed.shape[0]
+    dyq, dysc, dyqt, dysct = O.quantize_both(d_y_routed)
+    d_hidden = torch.zeros(R, I, dtype=torch.bfloat16)
+    segs, off = [], 0
+    for e, n in enumerate(tokens_per_expert.tolist()):
+        segs.append((e, off, n))
+        off += n
+    for e, off, n in segs:
+        if n:
+            rows, tiles = slice(off, off + n), slice(off // 128, (off + n) // 128)
+            d_hidden[rows] = O.gemm_ref(dyq[rows], dysc[tiles], wd_q[e], wd_sc[e * I // 128:(e + 1) * I // 128])
+    d_gate, d_up = swiglu_bwd_ref(fwd["gate_fp8"], fwd["gate_sc"], fwd["up_fp8"], fwd["up_sc"], d_hidden)
+    dgq, dgsc, dgqt, dgsct = O.quantize_both(d_gate)
+    duq, dusc, duqt, dusct = O.quantize_both(d_up)
+    d_x = torch.zeros(R, H, dtype=torch.bfloat16)
+    for e, off, n in segs:
+        if n:
+            rows, tiles = slice(off, off + n), slice(off // 128, (off + n) // 128)
+            hs = slice(e * H // 128, (e + 1) * H // 128)
+            acc = O.dequantize(dgq[rows], O.scale_unswizzle(dgsc[tiles])) @ O.dequantize(wg_q[e], O.scale_unswizzle(wg_sc[hs])).t()
+            acc = acc + O.dequantize(duq[rows], O.scale_unswizzle(dusc[tiles])) @ O.dequantize(wu_q[e], O.scale_unswizzle(wu_sc[hs])).t()
+            d_x[rows] = acc.to(torch.bfloat16)
+    deq_t = lambda q, sc: O.dequantize(q, O.scale_unswizzle(sc))          # [cols, R]
+    dg_t, du_t, dy_t = deq_t(dgqt, dgsct), deq_t(duqt, dusct), deq_t(dyqt, dysct)
+    x_t, h_t = deq_t(fwd["x_fp8_t"], fwd["x_sc_t"]), deq_t(fwd["hidden_fp8_t"], fwd["hidden_sc_t"])
+    d_wg = torch.zeros(E, I, H, dtype=torch.bfloat16)
+    d_wu = torch.zeros(E, I, H, dtype=torch.bfloat16)
+    d_wd = torch.zeros(E, H, I, dtype=torch.bfloat16)
+    for e, off, n in segs:
+        if n:
+            c = slice(off, off + n)
+            d_wg[e] = (dg_t[:, c] @ x_t[:, c].t()).to(torch.bfloat16)
+            d_wu[e] = (du_t[:, c] @ x_t[:, c].t()).to(torch.bfloat16)
+            d_wd[e] = (dy_t[:, c] @ h_t[:, c].t()).to(torch.bfloat16)
+    return dict(d_y_fp8=dyq, d_y_sc=dysc, d_hidden=d_hidden, d_gate=d_gate, d_up=d_up, d_gate_fp8=dgq, d_gate_sc=dgsc,
+                d_up_fp8=duq, d_up_sc=dusc, d_x=d_x, d_w_gate=d_wg, d_w_up=d_wu, d_w_down=d_wd)
+
+
+def bwd_epilogue_ref(d_x_shared, d_x_routed_buffer, k):
+    T = d_x_routed_buffer.shape[0] // k
+    acc = d_x_shared.float().clone() if d_x_shared is not None else torch.zeros(T, d_x_routed_buffer.shape[1])
+    rb = d_x_routed_buffer.float().view(T, k, -1)
+    for j in range(k):
+        acc = acc + rb[:, j]
+    return acc.to(torch.bfloat16)

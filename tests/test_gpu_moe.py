@@ -304,3 +304,84 @@ def test_gemm_wgrad_per_expert():
             ref = (ad[:, off:off + n] @ bd[:, off:off + n].t()).to(torch.bfloat16)
             assert O.rel_frobenius(got, ref) < 2e-3, f"expert {e}"
         off += n
+
+
+def test_swiglu_backward_quantize():
+    R, I = 384, 256
+    gq, gsc = O.quantize_tiled(O.make_input(R, I, seed=1, std=2.0))
+    uq, usc = O.quantize_tiled(O.make_input(R, I, seed=2))
+    dh = O.make_input(R, I, seed=3, std=0.5)
+    want = MO.swiglu_bwd_ref(gq, gsc, uq, usc, dh)
+    for which in (0, 1):
+        o_fp8, o_sc, o_fp8_t, o_sc_t, o_bf16 = mx8.swiglu_bwd_quantize(gq.to(DEV), gsc.to(DEV), uq.to(DEV), usc.to(DEV), dh.to(DEV),
+                                                                         which, None, True)
+        assert mx8.device_status() == 0
+        got = o_bf16.cpu()
+        # fast exponential / reciprocal: a small share of elements lands on the neighbouring bf16 value
+        d = (got.view(torch.int16).int() - want[which].view(torch.int16).int()).abs()
+        assert int(d.max()) <= 1 and float((d > 0).float().mean()) < 1e-2
+        q, sc, qt, sct = O.quantize_both(got)
+        assert torch.equal(o_fp8.view(torch.uint8).cpu(), q) and torch.equal(o_sc.cpu(), sc)
+        assert torch.equal(o_fp8_t.view(torch.uint8).cpu(), qt) and torch.equal(o_sc_t.cpu(), sct)
+
+
+def test_bwd_prologue_and_epilogue_exact():
+    T, H, k = 256, 512, 4
+    d_out = O.make_input(T, H, seed=5, std=0.1)
+    w = torch.softmax(torch.randn(T, k, generator=torch.Generator().manual_seed(1)), -1)
+    cb = torch.zeros(T * k, H, dtype=torch.bfloat16, device=DEV)
+    r = mx8.bwd_prologue(d_out.to(DEV), w.to(DEV), cb)
+    assert torch.equal(r.cpu().view(torch.int16), d_out.view(torch.int16))
+    assert torch.equal(cb.cpu().view(torch.int16), MO.bwd_prologue_ref(d_out, w).view(torch.int16))
+    shared = O.make_input(T, H, seed=6)
+    buf = O.make_input(T * k, H, seed=7)
+    got = mx8.bwd_epilogue(shared.to(DEV), buf.to(DEV))
+    assert torch.equal(got.cpu().view(torch.int16), MO.bwd_epilogue_ref(shared, buf, k).view(torch.int16))
+    got0 = mx8.bwd_epilogue_routed(None, buf.to(DEV), k)
+    assert torch.equal(got0.cpu().view(torch.int16), MO.bwd_epilogue_ref(None, buf, k).view(torch.int16))
+
+
+def test_moe_backward_layer_single_rank():
+    W, T, H, I, k, E = 1, 256, 512, 256, 4, 6
+    topk_all, weights = make_topk(W, T, E, k, seed=71)
+    x_cpu = O.make_input(T, H, seed=72)
+    cap = ((T * k) // 256 + E) * 256
+    mk = lambda r, c, sd: torch.stack([O.make_input(r, c, seed=sd + e, std=c ** -0.5) for e in range(E)])
+    wg, wu, wd = mk(I, H, 100), mk(I, H, 200), mk(H, I, 300)
+    q2 = lambda w: O.quantize_both(w)[:2]
+    fw = [q2(wg), q2(wu), q2(wd)]
+    bw = [q2(wg.transpose(1, 2).contiguous()), q2(wu.transpose(1, 2).contiguous()), q2(wd.transpose(1, 2).contiguous())]
+    dev = lambda pair: (pair[0].to(DEV), pair[1].to(DEV))
+    x = x_cpu.to(DEV)
+    cb = torch.zeros(T * k, H, dtype=torch.bfloat16, device=DEV)
+    pr, pt, nt, tpe = mx8.schedule(topk_all.to(DEV), E, cap, 0)
+    f = mx8.dispatch_mlp_swiglu_combine_fwd(x, [x.data_ptr()], cb, [cb.data_ptr()], None, *dev(fw[0]), None, *dev(fw[1]), None,
+                                            *dev(fw[2]), pr, pt, nt, tpe, k)
+    d_out = O.make_input(T, H, seed=73, std=H ** -0.5)
+    d_cb = torch.zeros(T * k, H, dtype=torch.bfloat16, device=DEV)
+    d_xb = torch.zeros(T * k, H, dtype=torch.bfloat16, device=DEV)
+    mx8.bwd_prologue(d_out.to(DEV), weights[0].to(DEV), d_cb)
+    b = mx8.dispatch_mlp_swiglu_combine_bwd(None, d_cb, [d_cb.data_ptr()], d_xb, [d_xb.data_ptr()],
+                                            None, *dev(bw[0]), None, *dev(bw[1]), None, *dev(bw[2]),
+                                            f[0], f[1], None, f[3], f[4], None, f[6], f[7], None, f[9], f[10],
+                                            x, [x.data_ptr()], *dev(fw[0]), *dev(fw[1]), pr, pt, nt, tpe, k)
+    d_x = mx8.bwd_epilogue_routed(None, d_xb, k)
+    assert mx8.device_status() == 0
+    n = int(nt)
+    # oracle: forward intermediates, then backward
+    rpr, rpt = pr.cpu(), pt.cpu()
+    fwd = MO.expert_mlp_ref(MO.dispatch_ref(x_cpu.view(1, T, H), rpr, rpt, n, k), tpe.cpu(), *fw)
+    d_cb_ref = MO.bwd_prologue_ref(d_out, weights[0])
+    d_y = torch.zeros(n, H, dtype=torch.bfloat16)
+    valid = rpr[:n] >= 0
+    d_y[valid] = d_cb_ref[rpt[:n][valid].long()]
+    ref = MO.expert_mlp_bwd_ref(d_y, fwd, tpe.cpu(), *bw)
+    assert torch.equal(b[10][:n].view(torch.uint8).cpu(), ref["d_y_fp8"])          # gathered gradient rows, bit-exact
+    tol = 2e-2      # two chained MXFP8 GEMMs on re-quantized activations: bf16 flips move a few E4M3 bytes
+    assert O.rel_frobenius(b[9][:n].cpu(), ref["d_hidden"]) < 1e-2
+    assert O.rel_frobenius(b[1][:n].cpu(), ref["d_x"]) < tol
+    for got, want in ((b[13], ref["d_w_gate"]), (b[15], ref["d_w_up"]), (b[17], ref["d_w_down"])):
+        assert O.rel_frobenius(got.cpu(), want) < tol
+    # d_x: combine + epilogue are exact given the kernel's own d_x_routed
+    buf = MO.combine_ref([b[1][:n].cpu()], [rpr], [rpt], 0, T, k)
+    assert torch.equal(d_x.cpu().view(torch.int16), MO.bwd_epilogue_ref(None, buf, k).view(torch.int16))
