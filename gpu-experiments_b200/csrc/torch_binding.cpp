@@ -226,6 +226,117 @@ at::Tensor fwd_epilogue(const std::optional<at::Tensor>& y_shared, const at::Ten
     return out;
 }
 
+// ---------------------------------------------------------------------------------------------
+// MoE backward (routed experts), blackwell-ultra/022-…-mxfp8-bw.cu:3011-3034
+
+at::Tensor bwd_prologue(const at::Tensor& d_output, const at::Tensor& topk_weights, const at::Tensor& d_combine_buffer) {
+    TORCH_CHECK(topk_weights.dim() == 2 && topk_weights.scalar_type() == at::kFloat && topk_weights.is_contiguous(), "topk_weights float32 [tokens, topk]");
+    c10::cuda::CUDAGuard guard(d_output.device());
+    const int64_t T = topk_weights.size(0), k = topk_weights.size(1), H = d_output.size(1);
+    check(mx8_moe_bwd_prologue(dptr(d_output, "d_output", T * H), topk_weights.data_ptr(),
+                               const_cast<void*>(dptr(d_combine_buffer, "d_combine_buffer", T * k * H)), static_cast<int>(T),
+                               static_cast<int>(H), static_cast<int>(k), stream()),
+          "bwd_prologue");
+    return d_output;   // == d_y_shared; the combine buffer is filled in place
+}
+
+at::Tensor bwd_epilogue(const at::Tensor& d_x_shared, const at::Tensor& d_x_routed_buffer) {
+    c10::cuda::CUDAGuard guard(d_x_shared.device());
+    const int64_t T = d_x_shared.size(0), H = d_x_shared.size(1), k = d_x_routed_buffer.size(0) / T;
+    at::Tensor d_x = at::empty_like(d_x_shared);
+    check(mx8_moe_bwd_epilogue(dptr(d_x_shared, "d_x_shared", T * H), dptr(d_x_routed_buffer, "d_x_routed_buffer", T * k * H),
+                               d_x.data_ptr(), static_cast<int>(T), static_cast<int>(H), static_cast<int>(k), stream()),
+          "bwd_epilogue");
+    return d_x;
+}
+
+using OptT = std::optional<at::Tensor>;
+
+std::vector<at::Tensor> dispatch_mlp_swiglu_combine_bwd(
+    const OptT& d_y_shared, const at::Tensor& d_combine_buffer, const std::vector<int64_t>& d_combine_buffer_ptrs,
+    const at::Tensor& d_x_routed_buffer, const std::vector<int64_t>& d_x_routed_buffer_ptrs, const OptT& w_shared_gate_T,
+    const at::Tensor& w_routed_gate_T, const at::Tensor& w_routed_gate_T_sc, const OptT& w_shared_up_T, const at::Tensor& w_routed_up_T,
+    const at::Tensor& w_routed_up_T_sc, const OptT& w_shared_down_T, const at::Tensor& w_routed_down_T,
+    const at::Tensor& w_routed_down_T_sc, const at::Tensor& x_fp8_t_routed, const at::Tensor& x_sc_t_routed, const OptT& gate_shared,
+    const at::Tensor& gate_fp8_routed, const at::Tensor& gate_sc_routed, const OptT& up_shared, const at::Tensor& up_fp8_routed,
+    const at::Tensor& up_sc_routed, const OptT& hidden_shared, const at::Tensor& hidden_fp8_t_routed,
+    const at::Tensor& hidden_sc_t_routed, const OptT& x_buffer, const std::vector<int64_t>& /*x_buffer_ptrs*/,
+    const OptT& /*w_routed_gate*/, const OptT& /*w_routed_gate_sc*/, const OptT& /*w_routed_up*/, const OptT& /*w_routed_up_sc*/,
+    const at::Tensor& schedule_peer_rank, const at::Tensor& schedule_peer_token_idx, const at::Tensor& num_tokens,
+    const at::Tensor& tokens_per_expert, int /*topk*/, int /*num_comm_sms*/, int /*macrobatch_size*/, int /*minibatch_size*/) {
+    TORCH_CHECK(w_routed_gate_T.dim() == 3, "transposed routed weights must be [E, H, I]");
+    TORCH_CHECK(!d_combine_buffer_ptrs.empty() && d_combine_buffer_ptrs.size() == d_x_routed_buffer_ptrs.size() &&
+                d_combine_buffer_ptrs.size() <= 16, "1..16 ranks");
+    c10::cuda::CUDAGuard guard(d_combine_buffer.device());
+    const int64_t E = w_routed_gate_T.size(0), H = w_routed_gate_T.size(1), I = w_routed_gate_T.size(2), cap = schedule_peer_rank.size(0);
+    const int world = static_cast<int>(d_combine_buffer_ptrs.size());
+    auto bf = d_combine_buffer.options();
+    auto fp8 = bf.dtype(at::kFloat8_e4m3fn);
+    auto u8 = bf.dtype(at::kByte);
+    auto q = [&](int64_t r, int64_t c) { return std::make_tuple(at::empty({r, c}, fp8), at::empty({r / 128, c / 128, 32, 16}, u8)); };
+    auto [d_y_fp8, d_y_sc] = q(cap, H);
+    auto [d_y_fp8_t, d_y_sc_t] = q(H, cap);
+    auto [d_gate_fp8, d_gate_sc] = q(cap, I);
+    auto [d_gate_fp8_t, d_gate_sc_t] = q(I, cap);
+    auto [d_up_fp8, d_up_sc] = q(cap, I);
+    auto [d_up_fp8_t, d_up_sc_t] = q(I, cap);
+    at::Tensor d_hidden = at::empty({cap, I}, bf), d_x_routed = at::empty({cap, H}, bf);
+    at::Tensor d_w_gate = at::empty({E, I, H}, bf), d_w_up = at::empty({E, I, H}, bf), d_w_down = at::empty({E, H, I}, bf);
+    std::vector<const void*> src(world);
+    std::vector<void*> dst(world);
+    for (int i = 0; i < world; ++i) {
+        src[i] = reinterpret_cast<const void*>(d_combine_buffer_ptrs[i]);
+        dst[i] = reinterpret_cast<void*>(d_x_routed_buffer_ptrs[i]);
+    }
+    // gradient rows of the routed outputs: one row per (token, k) pair, hence topk = 1 for the index
+    check(mx8_moe_dispatch_quantize(src.data(), world, static_cast<int>(H), 1, iptr(schedule_peer_rank, "schedule_peer_rank"),
+                                    iptr(schedule_peer_token_idx, "schedule_peer_token_idx"), iptr(num_tokens, "num_tokens"),
+                                    static_cast<int>(cap), d_y_fp8.data_ptr(), d_y_sc.data_ptr(), d_y_fp8_t.data_ptr(), d_y_sc_t.data_ptr(), stream()),
+          "gradient dispatch + quantize");
+    grouped(d_y_fp8, d_y_sc, w_routed_down_T, w_routed_down_T_sc, d_hidden, at::Tensor(), num_tokens, tokens_per_expert);
+    for (int which = 0; which < 2; ++which) {
+        at::Tensor& o = which ? d_up_fp8 : d_gate_fp8;
+        at::Tensor& os = which ? d_up_sc : d_gate_sc;
+        at::Tensor& ot = which ? d_up_fp8_t : d_gate_fp8_t;
+        at::Tensor& ots = which ? d_up_sc_t : d_gate_sc_t;
+        check(mx8_swiglu_bwd_quantize(gate_fp8_routed.data_ptr(), gate_sc_routed.data_ptr(), up_fp8_routed.data_ptr(), up_sc_routed.data_ptr(),
+                                      d_hidden.data_ptr(), static_cast<int>(cap), static_cast<int>(I), num_tokens.data_ptr(), which,
+                                      o.data_ptr(), os.data_ptr(), ot.data_ptr(), ots.data_ptr(), nullptr, stream()),
+              "swiglu backward + quantize");
+    }
+    check(mx8_gemm_grouped_dual(d_gate_fp8.data_ptr(), d_gate_sc.data_ptr(), w_routed_gate_T.data_ptr(), w_routed_gate_T_sc.data_ptr(),
+                                d_up_fp8.data_ptr(), d_up_sc.data_ptr(), w_routed_up_T.data_ptr(), w_routed_up_T_sc.data_ptr(),
+                                d_x_routed.data_ptr(), static_cast<int>(cap), static_cast<int>(H), static_cast<int>(I), static_cast<int>(I),
+                                num_tokens.data_ptr(), tokens_per_expert.data_ptr(), static_cast<int>(E), stream()),
+          "data-gradient gemm");
+    check(mx8_moe_combine(d_x_routed.data_ptr(), schedule_peer_rank.data_ptr(), schedule_peer_token_idx.data_ptr(), num_tokens.data_ptr(),
+                          static_cast<int>(H), dst.data(), world, stream()),
+          "gradient combine");
+    auto wgrad = [&](const at::Tensor& at_, const at::Tensor& ats, const at::Tensor& bt, const at::Tensor& bts, at::Tensor& c) {
+        check(mx8_gemm_wgrad(at_.data_ptr(), ats.data_ptr(), bt.data_ptr(), bts.data_ptr(), c.data_ptr(), static_cast<int>(at_.size(0)),
+                             static_cast<int>(bt.size(0)), static_cast<int>(cap), tokens_per_expert.data_ptr(), static_cast<int>(E), stream()),
+              "weight-gradient gemm");
+    };
+    wgrad(d_gate_fp8_t, d_gate_sc_t, x_fp8_t_routed, x_sc_t_routed, d_w_gate);
+    wgrad(d_up_fp8_t, d_up_sc_t, x_fp8_t_routed, x_sc_t_routed, d_w_up);
+    wgrad(d_y_fp8_t, d_y_sc_t, hidden_fp8_t_routed, hidden_sc_t_routed, d_w_down);
+    // shared expert: bf16, library GEMMs, only when its tensors are given
+    at::Tensor d_x_shared, d_gate_shared, d_up_shared, d_hidden_shared, d_w_sg, d_w_su, d_w_sd;
+    if (d_y_shared && w_shared_gate_T && w_shared_up_T && w_shared_down_T && gate_shared && up_shared && hidden_shared && x_buffer) {
+        d_hidden_shared = at::matmul(*d_y_shared, w_shared_down_T->t());
+        at::Tensor g = gate_shared->to(at::kFloat), den = at::exp(-g) + 1.0, silu = g / den;
+        at::Tensor d_silu = (1.0 - silu) / den + silu;
+        d_gate_shared = (d_hidden_shared.to(at::kFloat) * d_silu * up_shared->to(at::kFloat)).to(at::kBFloat16);
+        d_up_shared = (silu * d_hidden_shared.to(at::kFloat)).to(at::kBFloat16);
+        d_x_shared = at::matmul(d_gate_shared, w_shared_gate_T->t()) + at::matmul(d_up_shared, w_shared_up_T->t());
+        d_w_sg = at::matmul(d_gate_shared.t(), *x_buffer);
+        d_w_su = at::matmul(d_up_shared.t(), *x_buffer);
+        d_w_sd = at::matmul(d_y_shared->t(), *hidden_shared);
+    }
+    return {d_x_shared, d_x_routed, d_gate_shared, d_gate_fp8, d_gate_sc, d_up_shared, d_up_fp8, d_up_sc, d_hidden_shared, d_hidden,
+            d_y_fp8, d_y_sc, d_w_sg, d_w_gate, d_w_su, d_w_up, d_w_sd, d_w_down};
+}
+
 int device_status() {
     int v = 0;
     int rc = mx8_device_status(&v, stream());
@@ -255,6 +366,9 @@ PYBIND11_MODULE(_C, m) {
           pybind11::arg("num_tokens"), pybind11::arg("tokens_per_expert"), pybind11::arg("topk"), pybind11::arg("num_comm_sms") = 0,
           pybind11::arg("macrobatch_size") = 0, pybind11::arg("minibatch_size") = 0);
     m.def("fwd_epilogue", &fwd_epilogue, "", pybind11::arg("y_shared"), pybind11::arg("combine_buffer"), pybind11::arg("topk_weights"));
+    m.def("bwd_prologue", &bwd_prologue);
+    m.def("bwd_epilogue", &bwd_epilogue);
+    m.def("dispatch_mlp_swiglu_combine_bwd", &dispatch_mlp_swiglu_combine_bwd);
     m.def("device_status", &device_status);
     m.def("version", []() { return std::string(mx8_version()); });
 }

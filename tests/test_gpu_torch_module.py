@@ -106,3 +106,41 @@ def test_moe_forward_through_the_cpp_module(C):
     cb_ref = MO.combine_ref([ref["y"]], [rpr], [rpt], 0, T, k)
     ref_out = MO.fwd_epilogue_ref(torch.zeros(T, H, dtype=torch.bfloat16), cb_ref, w)
     assert O.rel_frobenius(out.cpu(), ref_out) < 1e-2
+
+
+def test_moe_backward_through_the_cpp_module(C):
+    # forward then backward through mx8._C; the result must equal the ctypes host path bit for bit
+    import mx8
+    from oracle import moe_oracle as MO
+    T, H, I, k, E = 256, 512, 256, 4, 6
+    g = torch.Generator().manual_seed(4)
+    ids, w = MO.route(torch.randn(T, E, generator=g), k)
+    x = O.make_input(T, H, seed=6).to(DEV)
+    mk = lambda r, c, sd: torch.stack([O.make_input(r, c, seed=sd + e, std=c ** -0.5) for e in range(E)]).to(DEV)
+    wg, wu, wd = mk(I, H, 10), mk(I, H, 20), mk(H, I, 30)
+    fw = [C.mxfp8_quantize(t, True, False)[:2] for t in (wg, wu, wd)]
+    bw = [C.mxfp8_quantize(t.transpose(1, 2).contiguous(), True, False)[:2] for t in (wg, wu, wd)]
+    cap = ((T * k) // 256 + E) * 256
+    pr, pt, nt, tpe = C.schedule(ids.view(1, T, k).to(DEV), E, cap, 0)
+    cb = torch.zeros(T * k, H, dtype=torch.bfloat16, device=DEV)
+    f = C.dispatch_mlp_swiglu_combine_fwd(x, [x.data_ptr()], cb, [cb.data_ptr()], None, *fw[0], None, *fw[1], None, *fw[2], pr, pt, nt, tpe, k)
+    d_out = O.make_input(T, H, seed=7, std=H ** -0.5).to(DEV)
+    results = []
+    for host in (C, mx8):
+        d_cb = torch.zeros(T * k, H, dtype=torch.bfloat16, device=DEV)
+        d_xb = torch.zeros(T * k, H, dtype=torch.bfloat16, device=DEV)
+        d_y_shared = host.bwd_prologue(d_out, w.to(DEV), d_cb)
+        b = host.dispatch_mlp_swiglu_combine_bwd(None, d_cb, [d_cb.data_ptr()], d_xb, [d_xb.data_ptr()], None, *bw[0], None, *bw[1],
+                                                 None, *bw[2], f[0], f[1], None, f[3], f[4], None, f[6], f[7], None, f[9], f[10],
+                                                 x, [x.data_ptr()], *fw[0], *fw[1], pr, pt, nt, tpe, k, 28, 8 * 16384, 16384)
+        d_x = host.bwd_epilogue(torch.zeros(T, H, dtype=torch.bfloat16, device=DEV), d_xb)
+        assert len(b) == 18 and b[0] is None and d_y_shared.data_ptr() == d_out.data_ptr()
+        results.append((b, d_x))
+    assert C.device_status() == 0
+    n = int(nt)
+    (bc, dxc), (bp, dxp) = results
+    assert torch.equal(dxc.view(torch.int16), dxp.view(torch.int16))
+    for i in (1, 9):
+        assert torch.equal(bc[i][:n].view(torch.int16), bp[i][:n].view(torch.int16))
+    for i in (13, 15, 17):
+        assert torch.equal(bc[i].view(torch.int16), bp[i].view(torch.int16))
