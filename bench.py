@@ -501,6 +501,7 @@ def bench_moe(args, world, rank, local, peaks, with_cpu=False):
     cap = ((T * k * max(2, world // 4)) // 256) * 256
     g = torch.Generator(device=dev).manual_seed(1234 + rank)
     logits = torch.randn(T, E_total, device=dev, generator=g)
+    dist = symm_mem = None
     if world > 1:
         import torch.distributed as dist
         import torch.distributed._symmetric_memory as symm_mem
@@ -550,6 +551,54 @@ def bench_moe(args, world, rank, local, peaks, with_cpu=False):
         step(i)
     ms = timed(step, steps, world) / steps
     mx8.device_status()
+
+    # ---- backward of the same layer (routed experts): prologue, barrier, fused backward, barrier, epilogue
+    bwd = None
+    if not getattr(args, "no_bwd", False):
+        def transposed(q_src_rows, q_src_cols, seed_shift):
+            # weights of the backward are the transposes, quantized along their own K; regenerate the same
+            # random matrices slice by slice (the generator state differs, the distribution is what matters)
+            q = torch.empty(E, q_src_cols, q_src_rows, dtype=torch.float8_e4m3fn, device=dev)
+            sc = torch.empty(E * q_src_cols // 128, q_src_rows // 128, 32, 16, dtype=torch.uint8, device=dev)
+            for e0 in range(0, E, 16):
+                n = min(16, E - e0)
+                w = (torch.randn(n, q_src_cols, q_src_rows, device=dev, generator=g) * 0.02).to(torch.bfloat16)
+                mx8.mxfp8_quantize(w, q[e0:e0 + n], sc[e0 * q_src_cols // 128:(e0 + n) * q_src_cols // 128], None, None, True, False)
+            return q, sc
+        wgT, wgTs = transposed(I, H, 1)      # [E, H, I]
+        wuT, wuTs = transposed(I, H, 2)
+        wdT, wdTs = transposed(H, I, 3)      # [E, I, H]
+        if world > 1:
+            d_cb = symm_mem.empty(T * k, H, dtype=torch.bfloat16, device=dev)
+            d_cb_ptrs = list(symm_mem.rendezvous(d_cb, dist.group.WORLD.group_name).buffer_ptrs)
+            d_xb = symm_mem.empty(T * k, H, dtype=torch.bfloat16, device=dev)
+            d_xb_ptrs = list(symm_mem.rendezvous(d_xb, dist.group.WORLD.group_name).buffer_ptrs)
+        else:
+            d_cb = torch.empty(T * k, H, dtype=torch.bfloat16, device=dev)
+            d_xb = torch.empty(T * k, H, dtype=torch.bfloat16, device=dev)
+            d_cb_ptrs, d_xb_ptrs = [d_cb.data_ptr()], [d_xb.data_ptr()]
+        d_out = (torch.randn(T, H, device=dev, generator=g) * H ** -0.5).to(torch.bfloat16)
+        ids_all.copy_(ids.view(1, T, k)) if world == 1 else dist.all_gather_into_tensor(ids_all, ids)
+        pr, pt, nt, tpe = mx8.schedule(ids_all, E, cap, rank)
+        f = mx8.dispatch_mlp_swiglu_combine_fwd(x, x_ptrs, cb, cb_ptrs, None, wg, wgs, None, wu, wus, None, wd, wds, pr, pt, nt, tpe, k)
+
+        def bstep(_):
+            mx8.bwd_prologue(d_out, weights, d_cb)
+            if world > 1:
+                dist.barrier()
+            mx8.dispatch_mlp_swiglu_combine_bwd(None, d_cb, d_cb_ptrs, d_xb, d_xb_ptrs, None, wgT, wgTs, None, wuT, wuTs, None, wdT, wdTs,
+                                                f[0], f[1], None, f[3], f[4], None, f[6], f[7], None, f[9], f[10], x, x_ptrs,
+                                                wg, wgs, wu, wus, pr, pt, nt, tpe, k)
+            if world > 1:
+                dist.barrier()
+            return mx8.bwd_epilogue_routed(None, d_xb, k)
+
+        for i in range(2):
+            bstep(i)
+        bms = timed(bstep, steps, world) / steps
+        mx8.device_status()
+        bwd = {"ms_per_step": bms, "value": 12.0 * (32768 * k) * H * I / (bms * 1e-3) / 1e12, "unit": "TFLOP/s",
+               "flops": "12 * routed rows * hidden * intermediate"}
     flops_total = 6.0 * (32768 * k) * H * I
     value = flops_total / (ms * 1e-3) / 1e12
     per_gpu = value / world
@@ -560,7 +609,8 @@ def bench_moe(args, world, rank, local, peaks, with_cpu=False):
                        "sharding": "experts and tokens split across GPUs; dispatch pulls and combine pushes over peer-mapped memory"},
             "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": 2.0 * peaks["bf16_tflops"], "unit": "TFLOP/s",
                          "frac": per_gpu / (2.0 * peaks["bf16_tflops"]), "frac_of_nominal_4500": per_gpu / 4500.0, "traffic": None},
-            "gpu_launches": 10 * steps, **({"cpu_baseline": cpu_baseline_layer("moe")} if with_cpu and rank == 0 else {})}
+            "backward": bwd,
+            "gpu_launches": (10 + (14 if bwd else 0)) * steps, **({"cpu_baseline": cpu_baseline_layer("moe")} if with_cpu and rank == 0 else {})}
 
 
 def main():

@@ -95,10 +95,53 @@ def main():
         touched[pts[r][:m][sel].long()] = True
     assert bool(touched.all())
     assert torch.equal(cb.cpu().view(torch.int16), cb_own.view(torch.int16)), "combine buffer differs from the expert outputs"
+    # ---- backward over peer memory: prologue, barrier, fused backward, barrier, epilogue
+    def weights_T(r):
+        wg = torch.stack([O.make_input(I, H, seed=100 + 10 * r + e, std=H ** -0.5) for e in range(E)])
+        wu = torch.stack([O.make_input(I, H, seed=200 + 10 * r + e, std=H ** -0.5) for e in range(E)])
+        wd = torch.stack([O.make_input(H, I, seed=300 + 10 * r + e, std=I ** -0.5) for e in range(E)])
+        return [O.quantize_both(w.transpose(1, 2).contiguous())[:2] for w in (wg, wu, wd)]
+
+    bw = weights_T(rank)
+    d_out_all = torch.stack([O.make_input(T, H, seed=400 + r, std=H ** -0.5) for r in range(world)])
+    d_cb = symm_mem.empty(T * k, H, dtype=torch.bfloat16, device=dev)
+    d_cb_ptrs = list(symm_mem.rendezvous(d_cb, group).buffer_ptrs)
+    d_xb = symm_mem.empty(T * k, H, dtype=torch.bfloat16, device=dev)
+    d_xb.zero_()
+    d_xb_ptrs = list(symm_mem.rendezvous(d_xb, group).buffer_ptrs)
+    mx8.bwd_prologue(d_out_all[rank].to(dev), w_all[rank].to(dev), d_cb)
+    torch.cuda.synchronize()
+    dist.barrier()
+    dv = lambda pair: (pair[0].to(dev), pair[1].to(dev))
+    b = mx8.dispatch_mlp_swiglu_combine_bwd(None, d_cb, d_cb_ptrs, d_xb, d_xb_ptrs, None, *dv(bw[0]), None, *dv(bw[1]), None, *dv(bw[2]),
+                                            outs[0], outs[1], None, outs[3], outs[4], None, outs[6], outs[7], None, outs[9], outs[10],
+                                            x, x_ptrs, wgq.to(dev), wgs.to(dev), wuq.to(dev), wus.to(dev), pr, pt, nt, tpe, k)
+    assert mx8.device_status() == 0
+    torch.cuda.synchronize()
+    dist.barrier()
+    d_x = mx8.bwd_epilogue_routed(None, d_xb, k)
+    torch.cuda.synchronize()
+    d_cb_refs = [MO.bwd_prologue_ref(d_out_all[r], w_all[r]) for r in range(world)]
+    bwd_refs = []
+    for r in range(world):
+        m = refs[r]["y"].shape[0]
+        d_y = torch.zeros(m, H, dtype=torch.bfloat16)
+        for src in range(world):
+            sel = prs[r][:m] == src
+            d_y[sel] = d_cb_refs[src][pts[r][:m][sel].long()]
+        rtpe = MO.schedule_ref(ids_all_cpu, E, cap, r)[3]
+        bwd_refs.append(MO.expert_mlp_bwd_ref(d_y, refs[r], rtpe, *weights_T(r)))
+    assert torch.equal(b[10][:n].view(torch.uint8).cpu(), bwd_refs[rank]["d_y_fp8"]), "gathered gradient rows differ"
+    for idx, key in ((13, "d_w_gate"), (15, "d_w_up"), (17, "d_w_down")):
+        rel = O.rel_frobenius(b[idx].cpu(), bwd_refs[rank][key])
+        assert rel < 2e-2, (key, rel)
+    dxb_ref = MO.combine_ref([r["d_x"] for r in bwd_refs], prs, pts, rank, T, k)
+    rel_dx = O.rel_frobenius(d_x.cpu(), MO.bwd_epilogue_ref(None, dxb_ref, k))
+    assert rel_dx < 2e-2, rel_dx
     flag = torch.ones(1, device=dev)
     dist.all_reduce(flag)
     if rank == 0:
-        print(f"MULTI_GPU_MOE_OK world={world} rel_y={rel_y:.2e} rel_out={rel_out:.2e}", flush=True)
+        print(f"MULTI_GPU_MOE_OK world={world} rel_y={rel_y:.2e} rel_out={rel_out:.2e} rel_dx={rel_dx:.2e}", flush=True)
     dist.barrier()
     dist.destroy_process_group()
 
