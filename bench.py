@@ -409,6 +409,30 @@ def bench_gemm(args, world, rank, local, peaks, with_cpu):
     achieved = flops / (per_ms * 1e-3) / 1e12
     value = world * achieved
 
+    # the vendor library on the same operands, for context (not part of the roofline): cuBLAS through
+    # torch._scaled_mm with the same E8M0 block scales, and with per-tensor scales (plain FP8)
+    library = {}
+    if rank == 0 and hasattr(torch, "float8_e8m0fnu"):
+        aq, asc, bq, bsc, c = sets[0]
+        def lib_rate(fn, iters=20):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(iters):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            return flops / (e0.elapsed_time(e1) / iters * 1e-3) / 1e12
+        try:
+            sa, sb = asc.reshape(-1).view(torch.float8_e8m0fnu), bsc.reshape(-1).view(torch.float8_e8m0fnu)
+            library["cublas_mxfp8_tflops"] = lib_rate(lambda: torch._scaled_mm(aq, bq.t(), scale_a=sa, scale_b=sb, out_dtype=torch.bfloat16))
+            one = torch.ones((), device=dev)
+            library["cublas_fp8_per_tensor_tflops"] = lib_rate(lambda: torch._scaled_mm(aq, bq.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16))
+            library["mx8_same_loop_tflops"] = lib_rate(lambda: mx8.kernel(aq, asc, bq, bsc, c))
+        except Exception as ex:
+            library["error"] = f"{type(ex).__name__}: {ex}"[:200]
     aq, asc, bq, bsc, c = sets[0]
     host_in = [t.cpu().pin_memory() for t in (aq, asc, bq, bsc)]
     c_h = torch.empty(c.shape, dtype=c.dtype).pin_memory()
@@ -440,6 +464,7 @@ def bench_gemm(args, world, rank, local, peaks, with_cpu):
         "e2e": {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": e2e_steps},
         "gpu_launches": args.steps,
+        "library": library,
     }
     if sampler:
         line["clocks"] = sampler.summary()
@@ -640,7 +665,7 @@ def main():
         if not args.no_gemm:
             g = bench_gemm(args, world, rank, local, peaks, with_cpu)
             line["gemm"] = {k: g[k] for k in ("metric", "value", "unit", "ms_per_step", "scaling", "config", "roofline", "e2e",
-                                              "gpu_launches", "clocks", "cpu_baseline") if k in g}
+                                              "gpu_launches", "clocks", "cpu_baseline", "library") if k in g}
             line["gpu_launches"] += g["gpu_launches"]
         if not args.no_layers:
             for name, fn in (("ffn", bench_ffn), ("moe", bench_moe)):

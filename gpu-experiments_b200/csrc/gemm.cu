@@ -196,7 +196,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     tc_fence_before();
     if constexpr (CG == 2) cluster_sync_all(); else __syncthreads();
     tc_fence_after();
-    const uint32_t tmem_base = *tmem_ptr;
+    // broadcast from lane 0 so the compiler can keep the value (and everything derived from it) in
+    // uniform registers, which is where tcgen05 and TMA instructions take their operands from
+    const uint32_t tmem_base = __shfl_sync(0xFFFFFFFFu, *tmem_ptr, 0);
     // grouped form: row tiles come from a device-side count and every tile's B rows from its group
     int* seg_end = reinterpret_cast<int*>(base_ptr + C::seg_off);
     int tiles_m = p.tiles_m;
@@ -204,6 +206,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         const int rows = *p.rows_dev;
         tiles_m = min(tiles_m, (rows + 128 * CG - 1) / (128 * CG));
     }
+    tiles_m = __shfl_sync(0xFFFFFFFFu, tiles_m, 0);     // loaded value: make it provably warp-uniform
     if (p.num_groups > 0) {
         if (threadIdx.x == 0) {
             int acc = 0;
@@ -218,29 +221,35 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
 
     if (warp == 0) {
         // ------------------------------------------------------------------ producer
-        if (lane == 0) {
+        // The whole warp walks the loop (uniform control flow, operands in uniform registers); one
+        // elected lane issues the copies.
+        {
+            const bool leader = elect_one();
             uint32_t stage = 0, ph = 0;
             const uint32_t full_leader0 = CG == 2 ? map_to_cta(full0, 0) : full0;
             bool ok = true;
             for (int t = cluster; t < num_tiles && ok; t += num_clusters) {
                 const TileInfo ti = tile_info<CG>(t, p, tiles_m, seg_end);
-                const int a_row = (ti.tm * CG + static_cast<int>(rank)) * 128;
-                const int b_base = ti.b_base;
+                const int a_row = (__shfl_sync(0xFFFFFFFFu, ti.tm, 0) * CG + static_cast<int>(rank)) * 128;
+                const int b_base = __shfl_sync(0xFFFFFFFFu, ti.b_base, 0);
+                const int kcount_t = __shfl_sync(0xFFFFFFFFu, ti.kcount, 0), k0_t = __shfl_sync(0xFFFFFFFFu, ti.k0, 0);
                 const int b_row = b_base + static_cast<int>(rank) * C::B_ROWS;
-                for (int ks = 0; ks < ti.kcount; ++ks) {
-                    if (!mbar_wait(empty0 + stage * 8, ph ^ 1, ab, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
+                for (int ks = 0; ks < kcount_t; ++ks) {
+                    if (!__all_sync(0xFFFFFFFFu, mbar_wait(empty0 + stage * 8, ph ^ 1, ab, DEV_TIMEOUT_EMPTY))) { ok = false; break; }
                     const uint32_t a_dst = base + C::a_off + stage * C::A_BYTES;
                     const uint32_t b_dst = base + C::b_off + stage * C::B_BYTES;
                     const uint32_t sfa_dst = base + C::sfa_off + stage * C::SFA_BYTES;
                     const uint32_t sfb_dst = base + C::sfb_off + stage * C::SFB_BYTES;
                     // K step within the operand pair it belongs to
                     const bool second = ks >= p.k_steps && p.k_steps2 > 0;
-                    const int kk = ti.k0 + (second ? ks - p.k_steps : ks);
+                    const int kk = k0_t + (second ? ks - p.k_steps : ks);
                     const CUtensorMap* ma = second ? &tm_a2 : &tm_a;
                     const CUtensorMap* mb = second ? &tm_b2 : &tm_b;
                     const CUtensorMap* msa = second ? &tm_sfa2 : &tm_sfa;
                     const CUtensorMap* msb = second ? &tm_sfb2 : &tm_sfb;
-                    if constexpr (CG == 2) {
+                    if (!leader) {
+                        // only the elected lane issues
+                    } else if constexpr (CG == 2) {
                         const uint32_t bar = full_leader0 + stage * 8;
                         if (p.dbg & 2) {
                             if (rank == 0) mbar_arrive(full0 + stage * 8);
@@ -269,7 +278,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer (leader CTA only)
-        if (lane == 0 && rank == 0) {
+        if (rank == 0) {
+            const bool leader = elect_one();
             // Everything this loop needs per K step is kept as a running 32-bit value so that the
             // single issuing thread spends its time on tcgen05 instructions, not on address math.
             // The scale copies run one K step ahead of the MMAs (two scale slots in TMEM), so an MMA
@@ -290,9 +300,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             bool ok = true;
             // wait for a stage and copy its scale tiles into the next TMEM scale slot
             auto copy_scales = [&]() -> bool {
-                if (!mbar_wait(full_bar, cph, ab, DEV_TIMEOUT_FULL)) return false;
+                if (!__all_sync(0xFFFFFFFFu, mbar_wait(full_bar, cph, ab, DEV_TIMEOUT_FULL))) return false;
                 tc_fence_after();
-                if (do_cp) {
+                if (do_cp && leader) {
                     tc_cp_scales_lo<CG>(sf_cp, sfa_lo);
                     tc_cp_scales_lo<CG>(sf_cp + 4, sfb_lo);
                     tc_cp_scales_lo<CG>(sf_cp + 8, sfb_lo + (512 >> 4));
@@ -314,24 +324,24 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 if (it > 0) {
                     // the epilogue has emptied the previous-but-one accumulator and the 32 columns
                     // the previous accumulator shares with this one
-                    if (!(p.dbg & 128) && !mbar_wait<true>(drained, (it - 1) & 1, ab, DEV_TIMEOUT_TMEM_FREE)) { ok = false; break; }
+                    if (!(p.dbg & 128) && !__all_sync(0xFFFFFFFFu, mbar_wait<true>(drained, (it - 1) & 1, ab, DEV_TIMEOUT_TMEM_FREE))) { ok = false; break; }
                     tc_fence_after();
                 }
-                const int kcount = tile_info<CG>(cluster + it * num_clusters, p, tiles_m, seg_end).kcount;
+                const int kcount = __shfl_sync(0xFFFFFFFFu, tile_info<CG>(cluster + it * num_clusters, p, tiles_m, seg_end).kcount, 0);
                 for (int ks = 0; ks < kcount; ++ks) {
                     if (ext_copier) {
-                        if (!mbar_wait(sffull0 + (kk & 1) * 8, (kk >> 1) & 1, ab, DEV_TIMEOUT_FULL)) { ok = false; break; }
+                        if (!__all_sync(0xFFFFFFFFu, mbar_wait(sffull0 + (kk & 1) * 8, (kk >> 1) & 1, ab, DEV_TIMEOUT_FULL))) { ok = false; break; }
                         tc_fence_after();
                         ++kk;
                     } else if (remaining > 0 && !copy_scales()) { ok = false; break; }
-                    if (do_mma) {
+                    if (do_mma && leader) {
                         // each K=32 slice lies 32 bytes further inside the swizzle atom: +2 in the address field
                         tc_mma_mxf8_lo<CG, 2>(d_tmem, a_lo, b_lo, ID0, sf_mma, sf_mma + 4, static_cast<uint32_t>(ks));
                         tc_mma_mxf8_lo<CG, 1>(d_tmem, a_lo + 2, b_lo + 2, ID1, sf_mma, sf_mma + 4);
                         tc_mma_mxf8_lo<CG, 1>(d_tmem, a_lo + 4, b_lo + 4, ID2, sf_mma, sf_mma + 4);
                         tc_mma_mxf8_lo<CG, 1>(d_tmem, a_lo + 6, b_lo + 6, ID3, sf_mma, sf_mma + 4);
                     }
-                    tc_commit<CG>(empty_bar);                    // stage reusable once these MMAs retire
+                    if (leader) tc_commit<CG>(empty_bar);        // stage reusable once these MMAs retire
                     sf_mma ^= 16;
                     if (++stage == S) {
                         stage = 0; a_lo = a_lo0; b_lo = b_lo0; empty_bar = empty0;
@@ -339,12 +349,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                         a_lo += C::A_BYTES >> 4; b_lo += C::B_BYTES >> 4; empty_bar += 8;
                     }
                 }
-                if (ok) tc_commit<CG>(accfull0 + (it & 1) * 8);  // accumulator complete
+                if (ok && leader) tc_commit<CG>(accfull0 + (it & 1) * 8);  // accumulator complete
             }
         }
     } else if (warp == 6) {
         // ------------------------------------------------------------------ scale copier (experiment, leader CTA only)
-        if (lane == 0 && rank == 0 && !(p.dbg & 64) && !(p.dbg & (8 | 16))) {
+        if (rank == 0 && !(p.dbg & 64) && !(p.dbg & (8 | 16))) {
+            const bool leader = elect_one();
             const int my_tiles = cluster < num_tiles ? (num_tiles - cluster + num_clusters - 1) / num_clusters : 0;
             long long total = 0;
             for (int t = cluster; t < num_tiles; t += num_clusters) total += tile_info<CG>(t, p, tiles_m, seg_end).kcount;
@@ -352,18 +363,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             const uint32_t sfa_lo0 = desc_scales_lo(base + C::sfa_off), sfb_lo0 = desc_scales_lo(base + C::sfb_off);
             for (long long kk = 0; kk < total; ++kk) {
                 const uint32_t stage = static_cast<uint32_t>(kk % S), ph = static_cast<uint32_t>((kk / S) & 1);
-                if (!mbar_wait(full0 + stage * 8, ph, ab, DEV_TIMEOUT_FULL)) break;
+                if (!__all_sync(0xFFFFFFFFu, mbar_wait(full0 + stage * 8, ph, ab, DEV_TIMEOUT_FULL))) break;
                 if (kk >= 2) {   // the MMAs that read this TMEM scale slot two steps ago have retired
                     const long long k2 = kk - 2;
-                    if (!mbar_wait(empty0 + static_cast<uint32_t>(k2 % S) * 8, static_cast<uint32_t>((k2 / S) & 1), ab, DEV_TIMEOUT_EMPTY)) break;
+                    if (!__all_sync(0xFFFFFFFFu, mbar_wait(empty0 + static_cast<uint32_t>(k2 % S) * 8, static_cast<uint32_t>((k2 / S) & 1), ab, DEV_TIMEOUT_EMPTY))) break;
                 }
                 tc_fence_after();
                 const uint32_t sf = tmem_base + SF_COL + static_cast<uint32_t>(kk & 1) * 16;
                 const uint32_t sfa_lo = sfa_lo0 + stage * (C::SFA_BYTES >> 4), sfb_lo = sfb_lo0 + stage * (C::SFB_BYTES >> 4);
-                tc_cp_scales_lo<CG>(sf, sfa_lo);
-                tc_cp_scales_lo<CG>(sf + 4, sfb_lo);
-                tc_cp_scales_lo<CG>(sf + 8, sfb_lo + (512 >> 4));
-                tc_commit_local<CG>(sffull0 + static_cast<uint32_t>(kk & 1) * 8);
+                if (leader) {
+                    tc_cp_scales_lo<CG>(sf, sfa_lo);
+                    tc_cp_scales_lo<CG>(sf + 4, sfb_lo);
+                    tc_cp_scales_lo<CG>(sf + 8, sfb_lo + (512 >> 4));
+                    tc_commit_local<CG>(sffull0 + static_cast<uint32_t>(kk & 1) * 8);
+                }
             }
         }
     } else {

@@ -135,3 +135,29 @@ def test_full_size_linearity():
     bd = O.dequantize(bq.view(torch.uint8).cpu(), O.scale_unswizzle(bsc.cpu()))
     ref = (a_rows @ bd.t()).to(torch.bfloat16)
     compare(C[rows.to(DEV)].cpu(), ref, "8192^3 sampled rows")
+
+
+def test_full_size_against_library_block_scaled_gemm():
+    # second oracle at the benchmark size: cuBLAS's MXFP8 GEMM (torch._scaled_mm with E8M0 block scales in
+    # the same swizzled layout), as the reference's MoE harness uses it
+    # (blackwell-ultra/022-moe-dispatch-mlp-swiglu-combine-mxfp8-bw.py:79-88)
+    if not hasattr(torch, "float8_e8m0fnu"):
+        pytest.skip("torch has no float8_e8m0fnu")
+    M = N = K = 8192
+    g = torch.Generator(device=DEV).manual_seed(5)
+    a = (torch.randn(M, K, device=DEV, generator=g) * K ** -0.5).to(torch.bfloat16)
+    b = (torch.randn(N, K, device=DEV, generator=g) * K ** -0.5).to(torch.bfloat16)
+    aq, asc, _, _ = mx8.mxfp8_quantize(a, True, False)
+    bq, bsc, _, _ = mx8.mxfp8_quantize(b, True, False)
+    c = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    mx8.kernel(aq, asc, bq, bsc, c)
+    assert mx8.device_status() == 0
+    try:
+        ref = torch._scaled_mm(aq, bq.t(), scale_a=asc.reshape(-1).view(torch.float8_e8m0fnu),
+                               scale_b=bsc.reshape(-1).view(torch.float8_e8m0fnu), out_dtype=torch.bfloat16)
+    except Exception as ex:                       # library without block-scaled support on this box
+        pytest.skip(f"torch._scaled_mm block-scaled path unavailable: {ex}")
+    d = ref.float() - c.float()
+    rel = float(d.norm() / ref.float().norm())
+    assert rel < REL_FRO_TOL
+    assert rel < 1e-3 and float(d.abs().max()) <= float(ref.float().abs().max()) * 2 ** -6
