@@ -1,14 +1,16 @@
 // Block-scaled MXFP8 GEMM for sm_100a:  C[M][N] = dequant(A[M][K]) . dequant(B[N][K])^T.
 //
-// Persistent kernel, one CTA per SM, seven warps:
-//   warp 0  producer   one thread streams A/B tiles (SWIZZLE_128B) and scale tiles with TMA into a
-//                      ring of shared-memory stages; each CTA fetches only its own tiles
-//   warp 6  scales     one thread (of the leader CTA when CG == 2) copies each stage's scale tiles
-//                      into one of two TMEM scale slots with tcgen05.cp and commits to a barrier;
-//                      issued from its own warp the copies overlap the MMAs of the previous K step
-//   warp 1  MMA        one thread (leader CTA) issues four K=32
-//                      tcgen05.mma.kind::mxf8f6f4.block_scale per 128-wide K step; tcgen05.commit
-//                      releases the stage and, after the last K step, publishes the accumulator
+// Persistent kernel, one CTA per SM, six warps.  Producer and MMA warps run their loops with
+// warp-uniform control flow and let one elected lane issue, so that addresses, descriptors and
+// coordinates live in uniform registers (where TMA and tcgen05 instructions read them) instead of
+// being converted for every instruction:
+//   warp 0  producer   streams A/B tiles (SWIZZLE_128B) and scale tiles with TMA into a ring of
+//                      shared-memory stages; each CTA fetches only its own tiles
+//   warp 1  MMA        (leader CTA when CG == 2) copies the scale tiles of the NEXT K step into one of
+//                      two TMEM scale slots with tcgen05.cp, then issues four K=32
+//                      tcgen05.mma.kind::mxf8f6f4.block_scale for the current 128-wide K step;
+//                      tcgen05.commit releases the stage and, after the last K step, publishes the
+//                      accumulator
 //   warps 2-5 epilogue tcgen05.ld the fp32 accumulator (warp q owns TMEM lanes 32q..32q+31),
 //                      round to bf16 (or keep fp32), stage through swizzled shared memory and
 //                      write C with TMA stores
@@ -36,7 +38,7 @@ constexpr int ACC1_COL = 224;           // first column of accumulator 1
 constexpr int SF_COL = 480;             // first scale column; slot s at SF_COL + 16 s: A +0, B +4 and +8
 constexpr int EPI_WARPS = 4;
 constexpr int MAX_GROUPS = 256;          // experts per launch of the grouped form
-constexpr int THREADS = 32 * (3 + EPI_WARPS);   // producer, MMA issuer, 4 epilogue warps, scale copier
+constexpr int THREADS = 32 * (2 + EPI_WARPS);   // producer, MMA issuer, 4 epilogue warps
 
 template <int CG>
 struct Cfg {
@@ -56,7 +58,7 @@ struct Cfg {
     static constexpr int epi_off = (sfb_off + STAGES * SFB_BYTES + 1023) & ~1023;
     static constexpr int bar_off = epi_off + EPI_WARPS * EPI_BYTES;
     // barriers: full[STAGES], empty[STAGES], acc_full[2], drained
-    static constexpr int n_bars = 2 * STAGES + 5;            // + sf_full[2]
+    static constexpr int n_bars = 2 * STAGES + 3;
     static constexpr int tmem_ptr_off = bar_off + n_bars * 8;
     static constexpr int flag_off = tmem_ptr_off + 8;
     static constexpr int seg_off = flag_off + 8;               // end row of every group's segment (grouped GEMM)
@@ -85,7 +87,7 @@ struct Params {
     int group_c_rows;                   // wgrad: rows of C per group (M)
     int dbg;                            // ablation switches (MX8_GEMM_DEBUG, timing only, results are wrong):
                                         // 1 no MMA, 2 no TMA loads, 4 no C stores, 8 no scale traffic, 16 no scale copies,
-                                        // 32 no scale loads, 64 scale copies by the MMA thread, 128 no wait for the epilogue
+                                        // 32 no scale loads, 128 no wait for the epilogue
     int* status;
 };
 
@@ -159,7 +161,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     const uint32_t empty0 = full0 + S * 8;
     const uint32_t accfull0 = empty0 + S * 8;
     const uint32_t drained = accfull0 + 2 * 8;
-    const uint32_t sffull0 = drained + 8;
     volatile uint32_t* tmem_ptr = reinterpret_cast<volatile uint32_t*>(base_ptr + C::tmem_ptr_off);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + C::flag_off);
     const AbortCtl ab{abort_flag, p.status};
@@ -179,8 +180,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         mbar_init(accfull0, 1);
         mbar_init(accfull0 + 8, 1);
         mbar_init(drained, EPI_WARPS * CG);
-        mbar_init(sffull0, 1);
-        mbar_init(sffull0 + 8, 1);
         fence_mbar_init();
         prefetch_tmap(&tm_a);
         prefetch_tmap(&tm_b);
@@ -316,9 +315,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 }
                 return true;
             };
-            const bool ext_copier = (p.dbg & (64 | 8 | 16)) == 0;          // scale copies issued by warp 6 (dbg 64: by this thread)
-            uint32_t kk = 0;
-            if (!ext_copier && remaining > 0) ok = copy_scales();
+            if (remaining > 0) ok = copy_scales();
             for (int it = 0; it < my_tiles && ok; ++it) {
                 const uint32_t d_tmem = tmem_base + ((it & 1) ? ACC1_COL : 0);
                 if (it > 0) {
@@ -329,11 +326,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 }
                 const int kcount = __shfl_sync(0xFFFFFFFFu, tile_info<CG>(cluster + it * num_clusters, p, tiles_m, seg_end).kcount, 0);
                 for (int ks = 0; ks < kcount; ++ks) {
-                    if (ext_copier) {
-                        if (!__all_sync(0xFFFFFFFFu, mbar_wait(sffull0 + (kk & 1) * 8, (kk >> 1) & 1, ab, DEV_TIMEOUT_FULL))) { ok = false; break; }
-                        tc_fence_after();
-                        ++kk;
-                    } else if (remaining > 0 && !copy_scales()) { ok = false; break; }
+                    if (remaining > 0 && !copy_scales()) { ok = false; break; }
                     if (do_mma && leader) {
                         // each K=32 slice lies 32 bytes further inside the swizzle atom: +2 in the address field
                         tc_mma_mxf8_lo<CG, 2>(d_tmem, a_lo, b_lo, ID0, sf_mma, sf_mma + 4, static_cast<uint32_t>(ks));
@@ -350,33 +343,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     }
                 }
                 if (ok && leader) tc_commit<CG>(accfull0 + (it & 1) * 8);  // accumulator complete
-            }
-        }
-    } else if (warp == 6) {
-        // ------------------------------------------------------------------ scale copier (experiment, leader CTA only)
-        if (rank == 0 && !(p.dbg & 64) && !(p.dbg & (8 | 16))) {
-            const bool leader = elect_one();
-            const int my_tiles = cluster < num_tiles ? (num_tiles - cluster + num_clusters - 1) / num_clusters : 0;
-            long long total = 0;
-            for (int t = cluster; t < num_tiles; t += num_clusters) total += tile_info<CG>(t, p, tiles_m, seg_end).kcount;
-            (void)my_tiles;
-            const uint32_t sfa_lo0 = desc_scales_lo(base + C::sfa_off), sfb_lo0 = desc_scales_lo(base + C::sfb_off);
-            for (long long kk = 0; kk < total; ++kk) {
-                const uint32_t stage = static_cast<uint32_t>(kk % S), ph = static_cast<uint32_t>((kk / S) & 1);
-                if (!__all_sync(0xFFFFFFFFu, mbar_wait(full0 + stage * 8, ph, ab, DEV_TIMEOUT_FULL))) break;
-                if (kk >= 2) {   // the MMAs that read this TMEM scale slot two steps ago have retired
-                    const long long k2 = kk - 2;
-                    if (!__all_sync(0xFFFFFFFFu, mbar_wait(empty0 + static_cast<uint32_t>(k2 % S) * 8, static_cast<uint32_t>((k2 / S) & 1), ab, DEV_TIMEOUT_EMPTY))) break;
-                }
-                tc_fence_after();
-                const uint32_t sf = tmem_base + SF_COL + static_cast<uint32_t>(kk & 1) * 16;
-                const uint32_t sfa_lo = sfa_lo0 + stage * (C::SFA_BYTES >> 4), sfb_lo = sfb_lo0 + stage * (C::SFB_BYTES >> 4);
-                if (leader) {
-                    tc_cp_scales_lo<CG>(sf, sfa_lo);
-                    tc_cp_scales_lo<CG>(sf + 4, sfb_lo);
-                    tc_cp_scales_lo<CG>(sf + 8, sfb_lo + (512 >> 4));
-                    tc_commit_local<CG>(sffull0 + static_cast<uint32_t>(kk & 1) * 8);
-                }
             }
         }
     } else {
