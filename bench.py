@@ -30,12 +30,13 @@ sys.path.insert(0, os.path.join(ROOT, "gpu-experiments_b200"))
 import torch  # noqa: E402
 
 QM = QN = 16384
+E2E_BAND_ROWS = 2048          # rows per band of the host-buffer (end-to-end) pipeline
 GM = GN = GK = 8192
 L2_BYTES = 126 * 1024 * 1024
 
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
 # summarised under profiles/; None until a capture exists for that kernel.
-NCU_TRAFFIC_BYTES = {"quantize_16384x16384_both": 1045880000, "gemm_8192": 373310000}
+NCU_TRAFFIC_BYTES = {"quantize_16384x16384_both": 1045880000, "gemm_8192": 370370000}
 
 
 def load_peaks():
@@ -334,16 +335,16 @@ def bench_quantize(args, world, rank, local, peaks, with_cpu):
     value = world * algo_bytes / (per_ms * 1e-3) / 1e9
     achieved = algo_bytes / (per_ms * 1e-3) / 1e9
 
-    # end to end through host buffers: pinned input -> device, quantize, all four outputs -> pinned host
-    outs_h = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in outs]
+    # end to end through host buffers (mx8_quantize_host): pinned input -> device, quantize, all four
+    # outputs -> pinned host, in bands of rows so that the two PCIe directions and the kernel overlap
+    outs_h = [torch.empty(o.shape, dtype=torch.uint8).pin_memory() for o in outs]
     h2d = x_h.numel() * 2
     d2h = sum(o.numel() * o.element_size() for o in outs)
+    ws = torch.empty(mx8.quantize_host_workspace(N, E2E_BAND_ROWS), dtype=torch.uint8, device=dev)
 
     def e2e_step(_):
-        x.copy_(x_h, non_blocking=True)
-        mx8.mxfp8_quantize(x, outs[0], outs[1], outs[2], outs[3], True, True)
-        for o_h, o in zip(outs_h, outs):
-            o_h.copy_(o, non_blocking=True)
+        mx8.mxfp8_quantize_host(x_h, outs_h[0], outs_h[1], outs_h[2], outs_h[3], True, True,
+                                band_rows=E2E_BAND_ROWS, workspace=ws, device=dev)
 
     e2e_steps = max(3, min(args.steps, 10))
     for i in range(2):
@@ -362,9 +363,9 @@ def bench_quantize(args, world, rank, local, peaks, with_cpu):
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": achieved / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC_BYTES["quantize_16384x16384_both"],
                      "peak_source": peaks["source"], "frac_of_nominal_8000": achieved / 8000.0,
-                     "kernel": "quantize_kernel<4,4,true,true>", "algorithmic_bytes_per_launch": algo_bytes},
+                     "kernel": "quantize_kernel<8,1,SRC_DENSE,true,true>", "algorithmic_bytes_per_launch": algo_bytes},
         "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": e2e_ms, "steps": e2e_steps},
+                "ms_per_step": e2e_ms, "steps": e2e_steps, "api": "mx8_quantize_host, bands of %d rows" % E2E_BAND_ROWS},
         "gpu_launches": args.steps,
     }
     if sampler:
@@ -439,11 +440,13 @@ def bench_gemm(args, world, rank, local, peaks, with_cpu):
     h2d = sum(t.numel() * t.element_size() for t in host_in)
     d2h = c.numel() * 2
 
+    band = min(E2E_BAND_ROWS, M)
+    host_in[0] = host_in[0].view(torch.uint8)
+    host_in[2] = host_in[2].view(torch.uint8)
+    ws = torch.empty(mx8.load().mx8_gemm_host_workspace(bq.shape[0], bq.shape[1], band, 0), dtype=torch.uint8, device=dev)
+
     def e2e_step(_):
-        for d, h in zip((aq, asc, bq, bsc), host_in):
-            d.copy_(h, non_blocking=True)
-        mx8.kernel(aq, asc, bq, bsc, c)
-        c_h.copy_(c, non_blocking=True)
+        mx8.kernel_host(host_in[0], host_in[1], host_in[2], host_in[3], c_h, band_rows=band, workspace=ws, device=dev)
 
     e2e_steps = max(3, min(args.steps, 10))
     for i in range(2):
@@ -462,7 +465,7 @@ def bench_gemm(args, world, rank, local, peaks, with_cpu):
                      "peak_source": "2 x cuBLAS bf16 burst (" + peaks["source"] + "); no fp8 peak was measured on this pool",
                      "frac_of_nominal_4500": achieved / 4500.0, "kernel": "gemm_kernel<2>", "algorithmic_flops_per_launch": flops},
         "e2e": {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": e2e_steps},
+                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": e2e_steps, "api": "mx8_gemm_host, bands of %d rows" % band},
         "gpu_launches": args.steps,
         "library": library,
     }

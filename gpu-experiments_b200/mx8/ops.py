@@ -87,6 +87,77 @@ def mxfp8_quantize(x_bf16, *args, scale_mode="rceil"):
     return ret
 
 
+def _chk_host(t, name, dtypes, shape):
+    if not isinstance(t, torch.Tensor) or t.is_cuda:
+        raise ValueError(f"{name} must be a host tensor")
+    if t.dtype not in dtypes:
+        raise ValueError(f"{name} has dtype {t.dtype}, expected one of {dtypes}")
+    if not t.is_contiguous() or t.numel() != _numel(shape):
+        raise ValueError(f"{name} must be contiguous with shape {tuple(shape)}")
+    return t.data_ptr()
+
+
+def _workspace(workspace, need, device):
+    if workspace is None:
+        return torch.empty(need, dtype=torch.uint8, device=device)
+    if not workspace.is_cuda or workspace.numel() * workspace.element_size() < need:
+        raise ValueError(f"workspace must be a CUDA tensor of at least {need} bytes")
+    return workspace
+
+
+def mxfp8_quantize_host(x_bf16, x_fp8, x_sc, x_fp8_t, x_sc_t, return_normal, return_transposed, *,
+                        band_rows=2048, workspace=None, device=None, scale_mode="rceil"):
+    """mxfp8_quantize for a matrix that lives in HOST memory: x_bf16 [M, N] and the requested outputs
+    are host tensors (page-locked for the copies to overlap) with the layouts of `mxfp8_quantize`.
+    Bands of `band_rows` rows flow through copy-in, kernel and copy-out on three streams
+    (mx8_quantize_host).  `workspace` is a CUDA byte tensor of `quantize_host_workspace(N, band_rows)`
+    bytes, allocated per call when omitted.  Returns the workspace so that a caller can keep it."""
+    lib = _lib.load()
+    M, N = x_bf16.shape
+    xp = _chk_host(x_bf16, "x_bf16", (torch.bfloat16,), (M, N))
+    p = [None, None, None, None]
+    if return_normal:
+        p[0] = _chk_host(x_fp8, "x_fp8", _FP8, (M, N))
+        p[1] = _chk_host(x_sc, "x_sc", _SC, (M // 128, N // 128, 512))
+    if return_transposed:
+        p[2] = _chk_host(x_fp8_t, "x_fp8_t", _FP8, (N, M))
+        p[3] = _chk_host(x_sc_t, "x_sc_t", _SC, (N // 128, M // 128, 512))
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    with torch.cuda.device(dev):
+        rows = min(band_rows, M)
+        need = lib.mx8_quantize_host_workspace(N, rows)
+        ws = _workspace(workspace, need, dev)
+        _lib.check(lib.mx8_quantize_host(xp, M, N, p[0], p[1], p[2], p[3], _SCALE_MODES[scale_mode], band_rows,
+                                         ws.data_ptr(), ws.numel() * ws.element_size(), _stream()), "mxfp8_quantize_host")
+    return ws
+
+
+def quantize_host_workspace(N, band_rows):
+    return _lib.load().mx8_quantize_host_workspace(N, band_rows)
+
+
+def kernel_host(A, A_sc, B, B_sc, C, *, band_rows=2048, workspace=None, device=None):
+    """`kernel(A_fp8, A_sc, B_fp8, B_sc, C)` for operands and result in HOST memory (mx8_gemm_host):
+    B and its scales are copied once, then bands of `band_rows` rows of A and C are pipelined."""
+    lib = _lib.load()
+    M, K = A.shape
+    N = B.shape[0]
+    ap = _chk_host(A, "A", _FP8, (M, K))
+    bp = _chk_host(B, "B", _FP8, (N, K))
+    asp = _chk_host(A_sc, "A_sc", _SC, (M // 128, K // 128, 512))
+    bsp = _chk_host(B_sc, "B_sc", _SC, (N // 128, K // 128, 512))
+    cp = _chk_host(C, "C", (torch.bfloat16, torch.float32), (M, N))
+    c_dtype = _lib.C_F32 if C.dtype == torch.float32 else _lib.C_BF16
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    with torch.cuda.device(dev):
+        rows = min(band_rows, M)
+        need = lib.mx8_gemm_host_workspace(N, K, rows, c_dtype)
+        ws = _workspace(workspace, need, dev)
+        _lib.check(lib.mx8_gemm_host(ap, asp, bp, bsp, cp, M, N, K, c_dtype, band_rows, ws.data_ptr(),
+                                     ws.numel() * ws.element_size(), _stream()), "kernel_host")
+    return ws
+
+
 def kernel(A, A_sc, B, B_sc, C, *, cta_group=0, max_ctas=0):
     """kernel(A_fp8, A_sc, B_fp8, B_sc, C) -> None:  C = dequant(A) . dequant(B)^T.
 

@@ -203,6 +203,28 @@ MX8_API int mx8_moe_schedule_static(const void* topk_all, int world, int tokens,
                                     int capacity, int rank, void* peer_rank, void* peer_token_idx, void* num_tokens,
                                     void* tokens_per_expert, void* stream);
 
+/* Host-buffer forms.  The reference's harnesses keep tensors on the device and never move them
+ * inside a timed region (blackwell-ultra/019-mxfp8-quantize.py:59-84,
+ * blackwell/047-mxfp8-mma-2cta-MNK128-polished.py:127-176); a caller whose data lives in host
+ * memory uses these instead of three serial steps (copy in, kernel, copy out).  The matrix is cut
+ * into bands of `band_rows` rows (a multiple of 128); inbound copy, kernel and outbound copy of
+ * successive bands overlap on three streams, so both directions of the PCIe link are busy at once.
+ *   - `*_host` pointers are HOST memory with the layouts of mx8_quantize / mx8_gemm (page-locked
+ *     memory is needed for the copies to be asynchronous);
+ *   - `workspace` is DEVICE memory of at least mx8_*_host_workspace(...) bytes, used for two
+ *     alternating band buffers (and, for the GEMM, B with its scales); the call allocates no memory;
+ *   - earlier work on `stream` precedes the first copy and `stream` waits for the last one.  Two
+ *     copy streams per device are created on first use and kept. */
+#include <stddef.h>
+MX8_API size_t mx8_quantize_host_workspace(int N, int band_rows);
+MX8_API int mx8_quantize_host(const void* x_host, int M, int N, void* fp8_host, void* sc_host, void* fp8_t_host,
+                              void* sc_t_host, int scale_mode, int band_rows, void* workspace,
+                              size_t workspace_bytes, void* stream);
+MX8_API size_t mx8_gemm_host_workspace(int N, int K, int band_rows, int c_dtype);
+MX8_API int mx8_gemm_host(const void* A_host, const void* A_sc_host, const void* B_host, const void* B_sc_host,
+                          void* C_host, int M, int N, int K, int c_dtype, int band_rows, void* workspace,
+                          size_t workspace_bytes, void* stream);
+
 /* Synchronizes `stream`, then reads and clears the current device's status word: 0 = healthy,
  * otherwise the code of the first bounded wait that expired (see csrc/mx8_ptx.cuh).
  * Returns MX8_OK, MX8_ERR_DEVICE_TIMEOUT (status != 0) or MX8_ERR_CUDA. */
