@@ -145,7 +145,9 @@ __device__ __forceinline__ TileInfo tile_info(int t, const Params& p, int tiles_
     return ti;
 }
 
-template <int CG>
+// F16: A and B are bf16 (kind::f16, no scale tiles); the byte images in shared memory, the stage
+// ring and the epilogue are the same, a K step being 128 bytes = 64 bf16 elements of a row.
+template <int CG, bool F16>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
             const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb,
@@ -252,7 +254,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                         const uint32_t bar = full_leader0 + stage * 8;
                         if (p.dbg & 2) {
                             if (rank == 0) mbar_arrive(full0 + stage * 8);
-                        } else if (p.dbg & (8 | 32)) {
+                        } else if (F16 || (p.dbg & (8 | 32))) {
                             if (rank == 0) mbar_arrive_expect_tx(full0 + stage * 8, 2 * (C::A_BYTES + C::B_BYTES));
                             tma_load_2d_pair(a_dst, ma, kk * BK, a_row, bar);
                             tma_load_2d_pair(b_dst, mb, kk * BK, b_row, bar);
@@ -265,11 +267,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                         }
                     } else {
                         const uint32_t bar = full0 + stage * 8;
-                        mbar_arrive_expect_tx(bar, C::STAGE_TX);
+                        mbar_arrive_expect_tx(bar, F16 ? C::A_BYTES + C::B_BYTES : C::STAGE_TX);
                         tma_load_2d(a_dst, ma, kk * BK, a_row, bar);
                         tma_load_2d(b_dst, mb, kk * BK, b_row, bar);
-                        tma_load_3d(sfa_dst, msa, 0, kk, a_row / 128, bar);
-                        tma_load_3d(sfb_dst, msb, 0, kk, b_base / 128, bar);
+                        if constexpr (!F16) {
+                            tma_load_3d(sfa_dst, msa, 0, kk, a_row / 128, bar);
+                            tma_load_3d(sfb_dst, msb, 0, kk, b_base / 128, bar);
+                        }
                     }
                     if (++stage == S) { stage = 0; ph ^= 1; }
                 }
@@ -292,7 +296,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             uint32_t sf_mma = tmem_base + SF_COL, sf_cp = tmem_base + SF_COL;
             constexpr uint32_t ID0 = idesc_mxf8(128 * CG, BN, 0), ID1 = idesc_mxf8(128 * CG, BN, 1);
             constexpr uint32_t ID2 = idesc_mxf8(128 * CG, BN, 2), ID3 = idesc_mxf8(128 * CG, BN, 3);
-            const bool do_cp = !(p.dbg & (8 | 16)), do_mma = !(p.dbg & 1);
+            const bool do_cp = !F16 && !(p.dbg & (8 | 16)), do_mma = !(p.dbg & 1);
             const int my_tiles = cluster < num_tiles ? (num_tiles - cluster + num_clusters - 1) / num_clusters : 0;
             long long remaining = 0;                             // K steps whose scales are not copied yet
             for (int t = cluster; t < num_tiles; t += num_clusters) remaining += tile_info<CG>(t, p, tiles_m, seg_end).kcount;
@@ -327,7 +331,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 const int kcount = __shfl_sync(0xFFFFFFFFu, tile_info<CG>(cluster + it * num_clusters, p, tiles_m, seg_end).kcount, 0);
                 for (int ks = 0; ks < kcount; ++ks) {
                     if (remaining > 0 && !copy_scales()) { ok = false; break; }
-                    if (do_mma && leader) {
+                    if constexpr (F16) {
+                        if (do_mma && leader) {
+                            constexpr uint32_t IDF = idesc_bf16(128 * CG, BN);
+                            tc_mma_bf16_lo<CG, 2>(d_tmem, a_lo, b_lo, IDF, static_cast<uint32_t>(ks));
+                            tc_mma_bf16_lo<CG, 1>(d_tmem, a_lo + 2, b_lo + 2, IDF);
+                            tc_mma_bf16_lo<CG, 1>(d_tmem, a_lo + 4, b_lo + 4, IDF);
+                            tc_mma_bf16_lo<CG, 1>(d_tmem, a_lo + 6, b_lo + 6, IDF);
+                        }
+                    } else if (do_mma && leader) {
                         // each K=32 slice lies 32 bytes further inside the swizzle atom: +2 in the address field
                         tc_mma_mxf8_lo<CG, 2>(d_tmem, a_lo, b_lo, ID0, sf_mma, sf_mma + 4, static_cast<uint32_t>(ks));
                         tc_mma_mxf8_lo<CG, 1>(d_tmem, a_lo + 2, b_lo + 2, ID1, sf_mma, sf_mma + 4);
@@ -506,6 +518,7 @@ struct Maps {
 };
 
 // tensor maps of one operand pair: A [a_rows][K], B [b_rows][K] and their scale tiles
+// (K = bytes per row: the element count for E4M3, twice that for bf16 operands, which have no scales)
 template <int CG>
 static int build_operand_maps(CUtensorMap* ma, CUtensorMap* mb, CUtensorMap* msa, CUtensorMap* msb, const void* A,
                               const void* A_sc, const void* B, const void* B_sc, int a_rows, int b_rows, int K) {
@@ -522,6 +535,11 @@ static int build_operand_maps(CUtensorMap* ma, CUtensorMap* mb, CUtensorMap* msa
         const uint64_t strides[1] = {static_cast<uint64_t>(K)};
         const uint32_t box[2] = {BK, static_cast<uint32_t>(Cfg<CG>::B_ROWS)};
         if ((rc = make_tmap(mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, B, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) != MX8_OK) return rc;
+    }
+    if (!A_sc) {          // bf16 operands: the kernel never touches the scale maps
+        *msa = *ma;
+        *msb = *mb;
+        return MX8_OK;
     }
     {
         // scale tiles [rows/128][K/128][512 bytes] seen as 32-bit words so one box row is a whole tile
@@ -550,7 +568,7 @@ static int build_c_map(CUtensorMap* mc, void* Cp, int c_rows, int N, int c_dtype
     return make_tmap(mc, dt, 2, Cp, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
-template <int CG>
+template <int CG, bool F16>
 static int max_grid() {
     // CTAs that can be resident at once (cluster placement included), cached per device
     static int cached[64] = {};
@@ -558,7 +576,7 @@ static int max_grid() {
     cudaGetDevice(&dev);
     dev &= 63;
     if (cached[dev]) return cached[dev];
-    auto kern = gemm_kernel<CG>;
+    auto kern = gemm_kernel<CG, F16>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<CG>::dynamic);
     if (e != cudaSuccess) {
         note_cuda_error("cudaFuncSetAttribute(gemm)", cudaGetErrorString(e));
@@ -606,7 +624,7 @@ struct Grouping {
     bool wgrad = false;
 };
 
-template <int CG>
+template <int CG, bool F16 = false>
 static int run(const void* A, const void* A_sc, const void* B, const void* B_sc, void* Cp, int M, int N, int K,
                int c_dtype, int max_ctas, const Grouping& gr, cudaStream_t stream) {
     Maps m;
@@ -641,7 +659,7 @@ static int run(const void* A, const void* A_sc, const void* B, const void* B_sc,
     p.dbg = g_ablation_flags;
     p.status = device_status_ptr();
     if (!p.status) return MX8_ERR_CUDA;
-    int grid = max_grid<CG>();
+    int grid = max_grid<CG, F16>();
     if (grid <= 0) return MX8_ERR_CUDA;
     if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
     const int tiles = p.tiles_m * p.tiles_n * (gr.wgrad ? groups : 1);
@@ -661,7 +679,7 @@ static int run(const void* A, const void* A_sc, const void* B, const void* B_sc,
     at[0].val.clusterDim.z = 1;
     cfg.attrs = at;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_kernel<CG>, m.a, m.b, m.sfa, m.sfb, m.a2, m.b2, m.sfa2, m.sfb2, m.c, p);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_kernel<CG, F16>, m.a, m.b, m.sfa, m.sfb, m.a2, m.b2, m.sfa2, m.sfb2, m.c, p);
     if (e != cudaSuccess) {
         note_cuda_error("gemm launch", cudaGetErrorString(e));
         return MX8_ERR_CUDA;
@@ -745,6 +763,32 @@ extern "C" int mx8_gemm_grouped_scatter(const void* A, const void* A_sc, const v
     gr.world = world;
     // the C tensor map is unused by this epilogue; A stands in so that the map encodes
     return gemm::run<2>(A, A_sc, B, B_sc, const_cast<void*>(A), M, N, K, MX8_C_MXFP8, 0, gr, static_cast<cudaStream_t>(stream));
+}
+
+// bf16 operands (shared expert of the MoE layer): the same kernel with kind::f16 MMAs and no scale
+// tiles.  Rows are handed to the common launcher as bytes (2 per element).
+extern "C" int mx8_gemm_bf16_dual(const void* A1, const void* B1, const void* A2, const void* B2, void* C, int M, int N,
+                                  int K1, int K2, int c_dtype, void* stream) {
+    using namespace mx8;
+    if (!A1 || !B1 || !C || (K2 > 0 && (!A2 || !B2))) return MX8_ERR_ARG;
+    if (c_dtype != MX8_C_BF16 && c_dtype != MX8_C_F32) return MX8_ERR_ARG;
+    if (M <= 0 || N <= 0 || K1 <= 0 || K2 < 0 || M % 128 || N % 128 || K1 % 64 || K2 % 64) return MX8_ERR_SHAPE;
+    if (!aligned16(A1) || !aligned16(B1) || !aligned16(C) || !aligned16(A2) || !aligned16(B2)) return MX8_ERR_ALIGN;
+    int rc = check_device_sm100();
+    if (rc != MX8_OK) return rc;
+    gemm::Grouping gr;
+    if (K2 > 0) {
+        gr.A2 = A2;
+        gr.B2 = B2;
+        gr.K2 = 2 * K2;
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (M <= 128) return gemm::run<1, true>(A1, nullptr, B1, nullptr, C, M, N, 2 * K1, c_dtype, 0, gr, st);
+    return gemm::run<2, true>(A1, nullptr, B1, nullptr, C, M, N, 2 * K1, c_dtype, 0, gr, st);
+}
+
+extern "C" int mx8_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int c_dtype, void* stream) {
+    return mx8_gemm_bf16_dual(A, B, nullptr, nullptr, C, M, N, K, 0, c_dtype, stream);
 }
 
 extern "C" int mx8_debug_set_gemm_ablation(int flags) {

@@ -256,6 +256,14 @@ __host__ __device__ constexpr uint32_t idesc_mxf8(int M, int N, int sf_id) {
          | (static_cast<uint32_t>(sf_id) << 29);    // A scale byte within the TMEM word
 }
 
+// Instruction descriptor for kind::f16 with bf16 A and B (K-major) and an fp32 accumulator.
+__host__ __device__ constexpr uint32_t idesc_bf16(int M, int N) {
+    return (1u << 4)                                 // D format f32
+         | (1u << 7) | (1u << 10)                    // A and B format bf16
+         | (static_cast<uint32_t>(N >> 3) << 17)
+         | (static_cast<uint32_t>(M >> 4) << 24);
+}
+
 // The same descriptors split into 32-bit halves: the high word is a constant, the low word carries
 // the address field, so advancing to another stage or K offset is one 32-bit add.
 constexpr uint32_t DESC_SW128_HI = (1024u >> 4) | (1u << 14) | (2u << 29);
@@ -290,6 +298,24 @@ __device__ __forceinline__ void tc_mma_mxf8_lo(uint32_t d, uint32_t a_lo, uint32
             "mov.b64 da, {%1, %7};\n\tmov.b64 db, {%2, %7};\n\tsetp.ne.u32 p, %6, 0;\n\t"
             "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], da, db, %3, [%4], [%5], p;\n\t}"
             ::"r"(d), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(sfa), "r"(sfb), "r"(ACC == 2 ? acc : static_cast<uint32_t>(ACC)), "n"(DESC_SW128_HI)
+            : "memory");
+}
+// bf16 x bf16 -> f32 (kind::f16), K = 16 per instruction; ACC as above
+template <int CG, int ACC>
+__device__ __forceinline__ void tc_mma_bf16_lo(uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t acc = 1) {
+    if constexpr (CG == 2)
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+            "mov.b64 da, {%1, %5};\n\tmov.b64 db, {%2, %5};\n\tsetp.ne.u32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %3, p;\n\t}"
+            ::"r"(d), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(ACC == 2 ? acc : static_cast<uint32_t>(ACC)), "n"(DESC_SW128_HI)
+            : "memory");
+    else
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+            "mov.b64 da, {%1, %5};\n\tmov.b64 db, {%2, %5};\n\tsetp.ne.u32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p;\n\t}"
+            ::"r"(d), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(ACC == 2 ? acc : static_cast<uint32_t>(ACC)), "n"(DESC_SW128_HI)
             : "memory");
 }
 template <int CG>

@@ -157,6 +157,24 @@ void grouped(const at::Tensor& A, const at::Tensor& A_sc, const at::Tensor& B, c
           "expert grouped gemm");
 }
 
+// ---- shared (bf16) expert: the kind::f16 form of the GEMM kernel and its element-wise companions
+at::Tensor bf16_gemm(const at::Tensor& a, const at::Tensor& b, const at::Tensor* a2 = nullptr, const at::Tensor* b2 = nullptr) {
+    const int64_t M = a.size(0), K = a.size(1), N = b.size(0), K2 = a2 ? a2->size(1) : 0;
+    at::Tensor c = at::empty({M, N}, a.options().dtype(at::kBFloat16));
+    check(mx8_gemm_bf16_dual(dptr(a, "A", M * K), dptr(b, "B", N * K), a2 ? dptr(*a2, "A2", M * K2) : nullptr,
+                             b2 ? dptr(*b2, "B2", N * K2) : nullptr, c.data_ptr(), static_cast<int>(M), static_cast<int>(N),
+                             static_cast<int>(K), static_cast<int>(K2), MX8_C_BF16, stream()),
+          "bf16 gemm");
+    return c;
+}
+
+at::Tensor bf16_transpose(const at::Tensor& x) {
+    at::Tensor out = at::empty({x.size(1), x.size(0)}, x.options());
+    check(mx8_transpose_bf16(dptr(x, "x"), out.data_ptr(), static_cast<int>(x.size(0)), static_cast<int>(x.size(1)), stream()),
+          "bf16 transpose");
+    return out;
+}
+
 std::vector<at::Tensor> dispatch_mlp_swiglu_combine_fwd(
     const at::Tensor& x, const std::vector<int64_t>& x_ptrs, const at::Tensor& combine_buffer,
     const std::vector<int64_t>& combine_buffer_ptrs, const std::optional<at::Tensor>& w_shared_gate, const at::Tensor& w_routed_gate,
@@ -199,14 +217,15 @@ std::vector<at::Tensor> dispatch_mlp_swiglu_combine_fwd(
     check(mx8_moe_combine(y_routed.data_ptr(), schedule_peer_rank.data_ptr(), schedule_peer_token_idx.data_ptr(), num_tokens.data_ptr(),
                           static_cast<int>(H), cp.data(), world, stream()),
           "combine");
-    // shared expert: bf16, outside the MXFP8 path; torch's library GEMM when weights are given
+    // shared expert (bf16), when its weights are given
     at::Tensor gate_shared, up_shared, hidden_shared, y_shared;
     if (w_shared_gate.has_value() && w_shared_up.has_value() && w_shared_down.has_value()) {
-        gate_shared = at::matmul(x, w_shared_gate->t());
-        up_shared = at::matmul(x, w_shared_up->t());
-        at::Tensor g = gate_shared.to(at::kFloat);
-        hidden_shared = (g / (at::exp(-g) + 1.0) * up_shared.to(at::kFloat)).to(at::kBFloat16);
-        y_shared = at::matmul(hidden_shared, w_shared_down->t());
+        gate_shared = bf16_gemm(x, *w_shared_gate);
+        up_shared = bf16_gemm(x, *w_shared_up);
+        hidden_shared = at::empty_like(gate_shared);
+        check(mx8_swiglu_bf16(gate_shared.data_ptr(), up_shared.data_ptr(), hidden_shared.data_ptr(), gate_shared.numel(), stream()),
+              "shared swiglu");
+        y_shared = bf16_gemm(hidden_shared, *w_shared_down);
     }
     return {x_fp8_t, x_sc_t, gate_shared, gate_fp8, gate_sc, up_shared, up_fp8, up_sc, hidden_shared, h_fp8_t, h_sc_t, y_shared, y_routed};
 }
@@ -320,18 +339,21 @@ std::vector<at::Tensor> dispatch_mlp_swiglu_combine_bwd(
     wgrad(d_gate_fp8_t, d_gate_sc_t, x_fp8_t_routed, x_sc_t_routed, d_w_gate);
     wgrad(d_up_fp8_t, d_up_sc_t, x_fp8_t_routed, x_sc_t_routed, d_w_up);
     wgrad(d_y_fp8_t, d_y_sc_t, hidden_fp8_t_routed, hidden_sc_t_routed, d_w_down);
-    // shared expert: bf16, library GEMMs, only when its tensors are given
+    // shared expert (bf16), only when its tensors are given
     at::Tensor d_x_shared, d_gate_shared, d_up_shared, d_hidden_shared, d_w_sg, d_w_su, d_w_sd;
     if (d_y_shared && w_shared_gate_T && w_shared_up_T && w_shared_down_T && gate_shared && up_shared && hidden_shared && x_buffer) {
-        d_hidden_shared = at::matmul(*d_y_shared, w_shared_down_T->t());
-        at::Tensor g = gate_shared->to(at::kFloat), den = at::exp(-g) + 1.0, silu = g / den;
-        at::Tensor d_silu = (1.0 - silu) / den + silu;
-        d_gate_shared = (d_hidden_shared.to(at::kFloat) * d_silu * up_shared->to(at::kFloat)).to(at::kBFloat16);
-        d_up_shared = (silu * d_hidden_shared.to(at::kFloat)).to(at::kBFloat16);
-        d_x_shared = at::matmul(d_gate_shared, w_shared_gate_T->t()) + at::matmul(d_up_shared, w_shared_up_T->t());
-        d_w_sg = at::matmul(d_gate_shared.t(), *x_buffer);
-        d_w_su = at::matmul(d_up_shared.t(), *x_buffer);
-        d_w_sd = at::matmul(d_y_shared->t(), *hidden_shared);
+        d_hidden_shared = bf16_gemm(*d_y_shared, *w_shared_down_T);
+        d_gate_shared = at::empty_like(*gate_shared);
+        d_up_shared = at::empty_like(*gate_shared);
+        check(mx8_swiglu_bwd_bf16(dptr(d_hidden_shared, "d_hidden_shared"), dptr(*gate_shared, "gate_shared"), dptr(*up_shared, "up_shared"),
+                                  d_gate_shared.data_ptr(), d_up_shared.data_ptr(), gate_shared->numel(), stream()),
+              "shared swiglu backward");
+        d_x_shared = bf16_gemm(d_gate_shared, *w_shared_gate_T, &d_up_shared, &*w_shared_up_T);
+        // weight gradients: K runs over the tokens, so both operands are transposed to K-major first
+        at::Tensor x_t = bf16_transpose(*x_buffer);
+        d_w_sg = bf16_gemm(bf16_transpose(d_gate_shared), x_t);
+        d_w_su = bf16_gemm(bf16_transpose(d_up_shared), x_t);
+        d_w_sd = bf16_gemm(bf16_transpose(*d_y_shared), bf16_transpose(*hidden_shared));
     }
     return {d_x_shared, d_x_routed, d_gate_shared, d_gate_fp8, d_gate_sc, d_up_shared, d_up_fp8, d_up_sc, d_hidden_shared, d_hidden,
             d_y_fp8, d_y_sc, d_w_sg, d_w_gate, d_w_su, d_w_up, d_w_sd, d_w_down};

@@ -29,6 +29,11 @@ SIGNATURES = {
     "mx8_moe_bwd_epilogue": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "mx8_moe_schedule": (_i, [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "mx8_moe_schedule_static": (_i, [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
+    "mx8_gemm_bf16": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "mx8_gemm_bf16_dual": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "mx8_swiglu_bf16": (_i, [_vp, _vp, _vp, ctypes.c_longlong, _vp]),
+    "mx8_swiglu_bwd_bf16": (_i, [_vp, _vp, _vp, _vp, _vp, ctypes.c_longlong, _vp]),
+    "mx8_transpose_bf16": (_i, [_vp, _vp, _i, _i, _vp]),
     "mx8_quantize_host_workspace": (ctypes.c_size_t, [_i, _i]),
     "mx8_quantize_host": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _vp, ctypes.c_size_t, _vp]),
     "mx8_gemm_host_workspace": (ctypes.c_size_t, [_i, _i, _i, _i]),

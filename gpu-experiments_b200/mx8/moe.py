@@ -12,7 +12,7 @@ import ctypes
 import torch
 
 from . import _lib
-from .ops import _FP8, _SC, _chk, _stream, gemm_grouped
+from .ops import _FP8, _SC, _chk, _stream, gemm_bf16, gemm_grouped, swiglu_bf16, swiglu_bwd_bf16, transpose_bf16
 
 
 def _ptr_array(ptrs):
@@ -103,7 +103,8 @@ def dispatch_mlp_swiglu_combine_fwd(x, x_ptrs, combine_buffer, combine_buffer_pt
        y_shared, y_routed)
     Routed buffers have schedule_capacity rows.  num_comm_sms / macrobatch_size / minibatch_size tune
     the reference's single-kernel schedule and have no effect here.  The shared expert (bf16, outside
-    the MXFP8 path) runs on torch's library GEMM when its weights are given, else those outputs are None.
+    the MXFP8 path) runs on the bf16 form of the same GEMM kernel (gemm_bf16) when its weights are given, else
+    those outputs are None.
     fuse_combine=True (an addition) lets the down projection's epilogue do the combine; y_routed is then None."""
     E, I, H = w_routed_gate.shape
     cap = schedule_peer_rank.numel()
@@ -132,11 +133,11 @@ def dispatch_mlp_swiglu_combine_fwd(x, x_ptrs, combine_buffer, combine_buffer_pt
         combine(y_routed, schedule_peer_rank, schedule_peer_token_idx, num_tokens, combine_buffer_ptrs)
     gate_shared = up_shared = hidden_shared = y_shared = None
     if w_shared_gate is not None:
-        gate_shared = x @ w_shared_gate.t()
-        up_shared = x @ w_shared_up.t()
-        g = gate_shared.float()
-        hidden_shared = ((g / (torch.exp(-g) + 1.0)) * up_shared.float()).to(torch.bfloat16)
-        y_shared = hidden_shared @ w_shared_down.t()
+        Tl, Is = x.shape[0], w_shared_gate.shape[0]
+        gate_shared = gemm_bf16(x, w_shared_gate, torch.empty(Tl, Is, dtype=torch.bfloat16, device=dev))
+        up_shared = gemm_bf16(x, w_shared_up, torch.empty(Tl, Is, dtype=torch.bfloat16, device=dev))
+        hidden_shared = swiglu_bf16(gate_shared, up_shared)
+        y_shared = gemm_bf16(hidden_shared, w_shared_down, torch.empty(Tl, H, dtype=torch.bfloat16, device=dev))
     return (x_fp8_t, x_sc_t, gate_shared, gate_fp8, gate_sc, up_shared, up_fp8, up_sc,
             hidden_shared, h_fp8_t, h_sc_t, y_shared, y_routed)
 
@@ -225,7 +226,7 @@ def dispatch_mlp_swiglu_combine_bwd(d_y_shared, d_combine_buffer, d_combine_buff
     The routed part runs on the MXFP8 kernels; it uses the transposed activations the forward returned
     (x_fp8_t_routed, hidden_fp8_t_routed), so the arguments the reference needs only to replay its
     forward (x_buffer, x_buffer_ptrs, w_routed_gate/up) are accepted and unused.  The shared expert
-    (bf16) runs on torch's library GEMM when its inputs are given, else those outputs are None."""
+    (bf16) runs on gemm_bf16 / swiglu_bwd_bf16 when its inputs are given, else those outputs are None."""
     E, H, I = w_routed_gate_T.shape                      # transposed weights: [E, H, I]
     cap = schedule_peer_rank.numel()
     dev = d_combine_buffer.device
@@ -252,14 +253,16 @@ def dispatch_mlp_swiglu_combine_bwd(d_y_shared, d_combine_buffer, d_combine_buff
     d_x_shared = d_gate_shared = d_up_shared = d_hidden_shared = d_w_sg = d_w_su = d_w_sd = None
     if w_shared_gate_T is not None and d_y_shared is not None:
         x = x_buffer
-        d_hidden_shared = d_y_shared @ w_shared_down_T.t()
-        g = gate_shared.float()
-        den = torch.exp(-g) + 1.0
-        silu = g / den
-        d_silu = (1.0 - silu) / den + silu
-        d_gate_shared = ((d_hidden_shared.float() * d_silu) * up_shared.float()).to(torch.bfloat16)
-        d_up_shared = (silu * d_hidden_shared.float()).to(torch.bfloat16)
-        d_x_shared = d_gate_shared @ w_shared_gate_T.t() + d_up_shared @ w_shared_up_T.t()
-        d_w_sg, d_w_su, d_w_sd = d_gate_shared.t() @ x, d_up_shared.t() @ x, d_y_shared.t() @ hidden_shared
+        Tl, Hs, Is = d_y_shared.shape[0], d_y_shared.shape[1], gate_shared.shape[1]
+        mk = lambda r, c: torch.empty(r, c, dtype=torch.bfloat16, device=dev)
+        d_hidden_shared = gemm_bf16(d_y_shared, w_shared_down_T, mk(Tl, Is))
+        d_gate_shared, d_up_shared = swiglu_bwd_bf16(d_hidden_shared, gate_shared, up_shared)
+        # dgrad: two products accumulated in one tile pass
+        d_x_shared = gemm_bf16(d_gate_shared, w_shared_gate_T, mk(Tl, Hs), d_up_shared, w_shared_up_T)
+        # wgrad: K runs over the tokens, so both operands are transposed to K-major first
+        x_t = transpose_bf16(x)
+        d_w_sg = gemm_bf16(transpose_bf16(d_gate_shared), x_t, mk(Is, Hs))
+        d_w_su = gemm_bf16(transpose_bf16(d_up_shared), x_t, mk(Is, Hs))
+        d_w_sd = gemm_bf16(transpose_bf16(d_y_shared), transpose_bf16(hidden_shared), mk(Hs, Is))
     return (d_x_shared, d_x_routed, d_gate_shared, d_gate_fp8, d_gate_sc, d_up_shared, d_up_fp8, d_up_sc,
             d_hidden_shared, d_hidden, d_y_fp8, d_y_sc, d_w_sg, d_w_gate, d_w_su, d_w_up, d_w_sd, d_w_down)

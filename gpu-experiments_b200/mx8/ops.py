@@ -300,3 +300,56 @@ def gemm_wgrad(A_t, A_t_sc, B_t, B_t_sc, C, group_rows):
                                       _chk(B_t, "B_t", _FP8, (N, R)), _chk(B_t_sc, "B_t_sc", _SC, (N // 128, R // 128, 512)),
                                       _chk(C, "C", (torch.bfloat16,), (G, M, N)), M, N, R,
                                       _chk(group_rows, "group_rows", (torch.int32,)), G, _stream()), "gemm_wgrad")
+
+
+def gemm_bf16(A, B, C, A2=None, B2=None):
+    """C[M, N] = A[M, K] @ B[N, K].T (+ A2[M, K2] @ B2[N, K2].T), bf16 operands, fp32 accumulation on the
+    tensor cores, C bf16 or float32 (mx8_gemm_bf16 / mx8_gemm_bf16_dual): the shared expert's GEMMs,
+    expert_grouped_gemm<true> of blackwell-ultra/022-…-mxfp8-bw.cu:1399-1736."""
+    lib = _lib.load()
+    M, K = A.shape
+    N = B.shape[0]
+    bf = (torch.bfloat16,)
+    ap, bp = _chk(A, "A", bf, (M, K)), _chk(B, "B", bf, (N, K))
+    cp = _chk(C, "C", (torch.bfloat16, torch.float32), (M, N))
+    cd = _lib.C_F32 if C.dtype == torch.float32 else _lib.C_BF16
+    K2, a2p, b2p = 0, None, None
+    if A2 is not None:
+        K2 = A2.shape[1]
+        a2p, b2p = _chk(A2, "A2", bf, (M, K2)), _chk(B2, "B2", bf, (N, K2))
+    with torch.cuda.device(A.device):
+        _lib.check(lib.mx8_gemm_bf16_dual(ap, bp, a2p, b2p, cp, M, N, K, K2, cd, _stream()), "gemm_bf16")
+    return C
+
+
+def swiglu_bf16(gate, up, hidden=None):
+    """hidden = silu(gate) * up on bf16 tensors (swiglu_fwd<true>, blackwell-ultra/022-…-mxfp8-bw.cu:1097-1110)."""
+    lib = _lib.load()
+    bf = (torch.bfloat16,)
+    hidden = torch.empty_like(gate) if hidden is None else hidden
+    n = gate.numel()
+    with torch.cuda.device(gate.device):
+        _lib.check(lib.mx8_swiglu_bf16(_chk(gate, "gate", bf), _chk(up, "up", bf, gate.shape), _chk(hidden, "hidden", bf, gate.shape),
+                                       n, _stream()), "swiglu_bf16")
+    return hidden
+
+
+def swiglu_bwd_bf16(d_hidden, gate, up):
+    """(d_gate, d_up) of hidden = silu(gate) * up (swiglu_bwd<true>, blackwell-ultra/022-…-mxfp8-bw.cu:1354-1375)."""
+    lib = _lib.load()
+    bf = (torch.bfloat16,)
+    d_gate, d_up = torch.empty_like(gate), torch.empty_like(gate)
+    with torch.cuda.device(gate.device):
+        _lib.check(lib.mx8_swiglu_bwd_bf16(_chk(d_hidden, "d_hidden", bf, gate.shape), _chk(gate, "gate", bf), _chk(up, "up", bf, gate.shape),
+                                           d_gate.data_ptr(), d_up.data_ptr(), gate.numel(), _stream()), "swiglu_bwd_bf16")
+    return d_gate, d_up
+
+
+def transpose_bf16(x):
+    """x[rows, cols] -> new contiguous [cols, rows] (mx8_transpose_bf16)."""
+    lib = _lib.load()
+    rows, cols = x.shape
+    out = torch.empty(cols, rows, dtype=torch.bfloat16, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(lib.mx8_transpose_bf16(_chk(x, "x", (torch.bfloat16,)), out.data_ptr(), rows, cols, _stream()), "transpose_bf16")
+    return out

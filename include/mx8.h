@@ -203,6 +203,29 @@ MX8_API int mx8_moe_schedule_static(const void* topk_all, int world, int tokens,
                                     int capacity, int rank, void* peer_rank, void* peer_token_idx, void* num_tokens,
                                     void* tokens_per_expert, void* stream);
 
+/* C[M][N] = A[M][K] . B[N][K]^T with bf16 operands (K contiguous, a multiple of 64), fp32 accumulation
+ * on the tensor cores (tcgen05.mma kind::f16), C bf16 or float.  The dual form adds a second product
+ * A2[M][K2] . B2[N][K2]^T into the same accumulator (K2 = 0: none).
+ * Replaces the shared-expert GEMMs, expert_grouped_gemm<true> of
+ * blackwell-ultra/022-moe-dispatch-mlp-swiglu-combine-mxfp8-bw.cu:1399-1736 (forward gate / up / down,
+ * backward dgrad with two accumulated products; the weight gradients take explicitly transposed
+ * operands, see mx8_transpose_bf16). */
+MX8_API int mx8_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int c_dtype, void* stream);
+MX8_API int mx8_gemm_bf16_dual(const void* A1, const void* B1, const void* A2, const void* B2, void* C, int M, int N,
+                               int K1, int K2, int c_dtype, void* stream);
+
+/* Element-wise pieces of the shared expert (bf16 in, fp32 arithmetic, bf16 out; n elements):
+ *   mx8_swiglu_bf16      hidden = silu(gate) * up       (swiglu_fwd<true>, same file :1097-1110)
+ *   mx8_swiglu_bwd_bf16  d_gate = d_hidden * dsilu(gate) * up, d_up = d_hidden * silu(gate)
+ *                        (swiglu_bwd<true>, same file :1354-1375)
+ *   mx8_transpose_bf16   out[cols][rows] = in[rows][cols]^T (rows, cols multiples of 64): operands of the
+ *                        shared expert's weight-gradient GEMMs, which the reference reads token-major
+ *                        (same file :1547-1550). */
+MX8_API int mx8_swiglu_bf16(const void* gate, const void* up, void* hidden, long long n, void* stream);
+MX8_API int mx8_swiglu_bwd_bf16(const void* d_hidden, const void* gate, const void* up, void* d_gate, void* d_up,
+                                long long n, void* stream);
+MX8_API int mx8_transpose_bf16(const void* in, void* out, int rows, int cols, void* stream);
+
 /* Host-buffer forms.  The reference's harnesses keep tensors on the device and never move them
  * inside a timed region (blackwell-ultra/019-mxfp8-quantize.py:59-84,
  * blackwell/047-mxfp8-mma-2cta-MNK128-polished.py:127-176); a caller whose data lives in host

@@ -206,3 +206,31 @@ def bwd_epilogue_ref(d_x_shared, d_x_routed_buffer, k):
     for j in range(k):
         acc = acc + rb[:, j]
     return acc.to(torch.bfloat16)
+
+
+def shared_mlp_ref(x, w_gate, w_up, w_down):
+    """Shared (bf16) expert forward: gate = x Wg^T, up = x Wu^T, hidden = bf16(silu(gate) * up) in fp32,
+    y = hidden Wd^T; every GEMM accumulates in fp32 and rounds to bf16
+    (blackwell-ultra/022-moe-dispatch-mlp-swiglu-combine-mxfp8-bw.py:98-102).
+    Returns (gate, up, hidden, y)."""
+    mm = lambda a, b: (a.float() @ b.float().t()).to(torch.bfloat16)
+    gate, up = mm(x, w_gate), mm(x, w_up)
+    g = gate.float()
+    hidden = ((g / (torch.exp(-g) + 1.0)) * up.float()).to(torch.bfloat16)
+    return gate, up, hidden, mm(hidden, w_down)
+
+
+def shared_mlp_bwd_ref(d_y, x, gate, up, hidden, w_gate, w_up, w_down):
+    """Shared expert backward (blackwell-ultra/022-moe-dispatch-mlp-swiglu-combine-mxfp8-bw.py:141-151).
+    Weights in forward orientation: w_gate, w_up [I, H], w_down [H, I].
+    Returns (d_x, d_gate, d_up, d_hidden, d_w_gate, d_w_up, d_w_down)."""
+    f = lambda t: t.float()
+    bf = lambda t: t.to(torch.bfloat16)
+    d_hidden = bf(f(d_y) @ f(w_down))
+    den = torch.exp(-f(gate)) + 1.0
+    silu = f(gate) / den
+    d_silu = (1.0 - silu) / den + silu
+    d_gate = bf((f(d_hidden) * d_silu) * f(up))
+    d_up = bf(silu * f(d_hidden))
+    d_x = bf(f(d_gate) @ f(w_gate) + f(d_up) @ f(w_up))
+    return d_x, d_gate, d_up, d_hidden, bf(f(d_gate).t() @ f(x)), bf(f(d_up).t() @ f(x)), bf(f(d_y).t() @ f(hidden))

@@ -144,3 +144,49 @@ def test_moe_backward_through_the_cpp_module(C):
         assert torch.equal(bc[i][:n].view(torch.int16), bp[i][:n].view(torch.int16))
     for i in (13, 15, 17):
         assert torch.equal(bc[i].view(torch.int16), bp[i].view(torch.int16))
+
+
+def test_shared_expert_through_both_hosts(C):
+    # layer forward + backward with shared-expert weights: the C++ module and the ctypes host give the
+    # same bits (same kernels, same launch order) and both agree with the oracle's bf16 expert
+    import mx8
+    from oracle import moe_oracle as MO
+    T, H, I, Is, k, E = 256, 512, 256, 384, 4, 6
+    g = torch.Generator().manual_seed(14)
+    ids, w = MO.route(torch.randn(T, E, generator=g), k)
+    x_cpu = O.make_input(T, H, seed=16)
+    x = x_cpu.to(DEV)
+    mk = lambda r, c, sd: torch.stack([O.make_input(r, c, seed=sd + e, std=c ** -0.5) for e in range(E)]).to(DEV)
+    wg, wu, wd = mk(I, H, 10), mk(I, H, 20), mk(H, I, 30)
+    sg, su, sd = (O.make_input(Is, H, seed=40, std=H ** -0.5), O.make_input(Is, H, seed=41, std=H ** -0.5),
+                  O.make_input(H, Is, seed=42, std=Is ** -0.5))
+    fw = [C.mxfp8_quantize(t, True, False)[:2] for t in (wg, wu, wd)]
+    bw = [C.mxfp8_quantize(t.transpose(1, 2).contiguous(), True, False)[:2] for t in (wg, wu, wd)]
+    cap = ((T * k) // 256 + E) * 256
+    pr, pt, nt, tpe = C.schedule(ids.view(1, T, k).to(DEV), E, cap, 0)
+    d_out = O.make_input(T, H, seed=17, std=H ** -0.5)
+    res = []
+    for host in (C, mx8):
+        cb = torch.zeros(T * k, H, dtype=torch.bfloat16, device=DEV)
+        f = host.dispatch_mlp_swiglu_combine_fwd(x, [x.data_ptr()], cb, [cb.data_ptr()], sg.to(DEV), *fw[0], su.to(DEV), *fw[1],
+                                                 sd.to(DEV), *fw[2], pr, pt, nt, tpe, k)
+        d_cb = torch.zeros(T * k, H, dtype=torch.bfloat16, device=DEV)
+        d_xb = torch.zeros(T * k, H, dtype=torch.bfloat16, device=DEV)
+        d_y_shared = host.bwd_prologue(d_out.to(DEV), w.to(DEV), d_cb)
+        b = host.dispatch_mlp_swiglu_combine_bwd(d_y_shared, d_cb, [d_cb.data_ptr()], d_xb, [d_xb.data_ptr()],
+                                                 sg.t().contiguous().to(DEV), *bw[0], su.t().contiguous().to(DEV), *bw[1],
+                                                 sd.t().contiguous().to(DEV), *bw[2], f[0], f[1], f[2], f[3], f[4], f[5], f[6], f[7],
+                                                 f[8], f[9], f[10], x, [x.data_ptr()], *fw[0], *fw[1], pr, pt, nt, tpe, k, 28, 8 * 16384, 16384)
+        res.append((f, b))
+    assert C.device_status() == 0
+    (fc, bc), (fp, bp) = res
+    for i in (2, 5, 8, 11):
+        assert torch.equal(fc[i].view(torch.int16), fp[i].view(torch.int16)), i
+    for i in (0, 2, 5, 8, 12, 14, 16):
+        assert torch.equal(bc[i].view(torch.int16), bp[i].view(torch.int16)), i
+    gate, up, hidden, y = MO.shared_mlp_ref(x_cpu, sg, su, sd)
+    for got, want in ((fc[2], gate), (fc[5], up), (fc[8], hidden), (fc[11], y)):
+        assert O.rel_frobenius(got.cpu().float(), want.float()) < 1e-2
+    ref = MO.shared_mlp_bwd_ref(d_out, x_cpu, fc[2].cpu(), fc[5].cpu(), fc[8].cpu(), sg, su, sd)
+    for i, want in ((0, ref[0]), (2, ref[1]), (5, ref[2]), (8, ref[3]), (12, ref[4]), (14, ref[5]), (16, ref[6])):
+        assert O.rel_frobenius(bc[i].cpu().float(), want.float()) < 1e-2, i

@@ -48,3 +48,21 @@ def test_layer_composition_shapes_and_padding_rows():
     w = torch.softmax(torch.randn(T, k), -1)
     out = MO.fwd_epilogue_ref(torch.zeros(T, H, dtype=torch.bfloat16), torch.ones(T * k, H, dtype=torch.bfloat16), w)
     assert torch.allclose(out.float(), torch.ones(T, H), atol=1e-2)
+
+
+def test_shared_expert_backward_matches_autograd():
+    # the oracle's hand-written bf16 expert backward against autograd of the same forward in float64
+    # (bf16 rounding of the intermediates bounds the agreement)
+    T, H, I = 64, 96, 80
+    g = torch.Generator().manual_seed(3)
+    r = lambda *s: torch.randn(*s, generator=g)
+    x, wg, wu, wd, d_y = r(T, H).bfloat16(), (r(I, H) * 0.1).bfloat16(), (r(I, H) * 0.1).bfloat16(), (r(H, I) * 0.1).bfloat16(), r(T, H).bfloat16()
+    gate, up, hidden, y = MO.shared_mlp_ref(x, wg, wu, wd)
+    got = MO.shared_mlp_bwd_ref(d_y, x, gate, up, hidden, wg, wu, wd)
+    xs, wgs, wus, wds = [t.double().requires_grad_() for t in (x, wg, wu, wd)]
+    gt, ut = xs @ wgs.t(), xs @ wus.t()
+    out = (torch.nn.functional.silu(gt) * ut) @ wds.t()
+    out.backward(d_y.double())
+    for have, want in ((got[0], xs.grad), (got[4], wgs.grad), (got[5], wus.grad), (got[6], wds.grad)):
+        assert O.rel_frobenius(have.float(), want.float()) < 2e-2
+    assert O.rel_frobenius(y.float(), out.detach().float()) < 2e-2
