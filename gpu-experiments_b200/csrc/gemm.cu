@@ -36,13 +36,16 @@ constexpr int BK = 128;                 // K elements (bytes) per stage
 constexpr int BN = 256;                 // tile columns
 constexpr int ACC1_COL = 224;           // first column of accumulator 1
 constexpr int SF_COL = 480;             // first scale column; slot s at SF_COL + 16 s: A +0, B +4 and +8
+// 4: one warp per TMEM lane quadrant drains all 256 columns.  8 (two warps per quadrant, 128 columns each)
+// also works but costs a pipeline stage of shared memory and measured 3-7 % slower on every shape tried.
 constexpr int EPI_WARPS = 4;
+constexpr int EPI_UNITS = 8 / (EPI_WARPS / 4);   // 32-column units per epilogue warp
 constexpr int MAX_GROUPS = 256;          // experts per launch of the grouped form
-constexpr int THREADS = 32 * (2 + EPI_WARPS);   // producer, MMA issuer, 4 epilogue warps
+constexpr int THREADS = 32 * (2 + EPI_WARPS);   // producer, MMA issuer, epilogue warps
 
 template <int CG>
 struct Cfg {
-    static constexpr int STAGES = CG == 2 ? 6 : 4;
+    static constexpr int STAGES = EPI_WARPS == 4 ? (CG == 2 ? 6 : 4) : (CG == 2 ? 5 : 3);
     static constexpr int A_BYTES = 128 * BK;                 // this CTA's 128 rows of A
     static constexpr int B_ROWS = BN / CG;                   // this CTA's rows of B
     static constexpr int B_BYTES = B_ROWS * BK;
@@ -360,6 +363,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     } else {
         // ------------------------------------------------------------------ epilogue
         const int q = warp & 3;                                  // TMEM lane quadrant this warp may read
+        const int half = (warp - 2) >> 2;                        // which 128 columns of the 256-column tile
         const uint32_t stg = base + C::epi_off + (warp - 2) * C::EPI_BYTES;
         const uint32_t drained_leader = CG == 2 ? map_to_cta(drained, 0) : drained;
         int it = 0;
@@ -377,8 +381,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             uint32_t scword = 0;                                 // four scale bytes of one row (c_mode 2)
             uint8_t* sc_row = nullptr;                           // c_mode 3: where this lane's row goes
 #pragma unroll 1
-            for (int s = 0; s < 8; ++s) {
-                const int u = acc ? s : 7 - s;                   // 32-column unit; the shared unit goes first
+            for (int s = 0; s < EPI_UNITS; ++s) {
+                // 32-column unit of this warp's half; the unit the two accumulators share (the last of
+                // accumulator 0, the first of accumulator 1) is the first one its warp drains
+                const int u = half * EPI_UNITS + (acc ? s : EPI_UNITS - 1 - s);
                 uint32_t r[32];
                 tc_ld_32x32(t_acc + u * 32, r);
                 tc_wait_ld(r);

@@ -52,7 +52,12 @@ struct Params {
     const uint8_t* gate_sc;       // SwiGLU: scale tiles of the two E4M3 inputs
     const uint8_t* up_sc;
     uint8_t* hidden_bf16;         // SwiGLU: optional bf16 copy of the activation (tests), else nullptr
-    int bwd_which;                // SwiGLU backward: 0 = gradient of gate, 1 = gradient of up
+    int bwd_which;                // SwiGLU backward: 0 = gradient of gate, 1 = gradient of up, 2 = both from one
+                                  // pass over the inputs (gate's into out/sc/sc_t, up's into the *2 set)
+    uint8_t* out2;                // second output set of bwd_which == 2
+    uint8_t* sc2;
+    uint8_t* sc_t2;
+    uint8_t* hidden_bf16_2;
     int* status;
 };
 
@@ -94,7 +99,8 @@ __device__ __forceinline__ void tile_coords(int t, const Params& p, int tiles_r,
 template <int W, int D, int SRC, bool ROW, bool COL>
 __global__ void __launch_bounds__((producer_warps(SRC) + W) * 32, 1)
 quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ CUtensorMap tm_in2,
-                const __grid_constant__ CUtensorMap tm_in3, const __grid_constant__ CUtensorMap tm_t, const Params p) {
+                const __grid_constant__ CUtensorMap tm_in3, const __grid_constant__ CUtensorMap tm_t,
+                const __grid_constant__ CUtensorMap tm_t2, const Params p) {
     constexpr int SLOT = slot_bytes(SRC);
     using L = Smem<W, D, SLOT>;
     constexpr int S = L::S;
@@ -198,6 +204,18 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
         tile_coords(t, p, tiles_r, tr, tc);
         if (!mbar_wait(full0 + slot * 8, ph, ab, DEV_TIMEOUT_FULL)) break;
 
+        // SwiGLU backward can emit both gradients from one visit of the slot: two passes over the same
+        // shared-memory inputs, each quantizing into its own output set
+        const int pass_first = (SRC == SRC_SWIGLU_BWD && p.bwd_which != 2) ? p.bwd_which : 0;
+        const int pass_last = SRC == SRC_SWIGLU_BWD ? (p.bwd_which == 2 ? 1 : p.bwd_which) : 0;
+#pragma unroll 1
+        for (int pass = pass_first; pass <= pass_last; ++pass) {
+        const bool second = SRC == SRC_SWIGLU_BWD && p.bwd_which == 2 && pass == 1;
+        uint8_t* const o_out = second ? p.out2 : p.out;
+        uint8_t* const o_sc = second ? p.sc2 : p.sc;
+        uint8_t* const o_sc_t = second ? p.sc_t2 : p.sc_t;
+        uint8_t* const o_bf16 = second ? p.hidden_bf16_2 : p.hidden_bf16;
+        const CUtensorMap* const o_tm_t = second ? &tm_t2 : &tm_t;
         uint32_t c[32][2];                 // c[i] = columns 4l..4l+3 of slab row i (bf16 pairs)
         if constexpr (SRC == SRC_SWIGLU || SRC == SRC_SWIGLU_BWD) {
             // forward: hidden = bf16( silu(dequant(gate)) * dequant(up) ), computed in fp32;
@@ -230,7 +248,7 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
                         const float sig = __fdividef(1.0f, 1.0f + __expf(-g));
                         const float silu = g * sig;
                         const float dsilu = (1.0f - silu) * sig + silu;
-                        h[e] = p.bwd_which ? silu * dh[e] : (dsilu * (uf[e] * us)) * dh[e];
+                        h[e] = pass ? silu * dh[e] : (dsilu * (uf[e] * us)) * dh[e];
                     } else {
                         h[e] = __fdividef(g, 1.0f + __expf(-g)) * (uf[e] * us);
                     }
@@ -238,8 +256,8 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
                 c[i][0] = pack_bf16x2(h[0], h[1]);
                 c[i][1] = pack_bf16x2(h[2], h[3]);
             }
-            if (p.hidden_bf16) {
-                uint8_t* hb = p.hidden_bf16 + ((static_cast<size_t>(tr) * TILE + wq * SLAB_ROWS) * p.N + tc * TILE + l * 4) * 2;
+            if (o_bf16) {
+                uint8_t* hb = o_bf16 + ((static_cast<size_t>(tr) * TILE + wq * SLAB_ROWS) * p.N + tc * TILE + l * 4) * 2;
 #pragma unroll
                 for (int i = 0; i < 32; ++i) *reinterpret_cast<uint2*>(hb + static_cast<size_t>(i) * p.N * 2) = make_uint2(c[i][0], c[i][1]);
             }
@@ -248,10 +266,10 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
             for (int i = 0; i < 32; ++i) ld_shared_v2(slot_addr + i * 256 + l * 8, c[i][0], c[i][1]);
         }
         __syncwarp();
-        if (l == 0) mbar_arrive(empty0 + slot * 8);       // the slot may be refilled now
+        if (l == 0 && pass == pass_last) mbar_arrive(empty0 + slot * 8);       // the slot may be refilled now
 
         if constexpr (ROW) {
-            uint8_t* out_row = p.out + (static_cast<size_t>(tr) * TILE + wq * SLAB_ROWS) * p.N + tc * TILE + l * 4;
+            uint8_t* out_row = o_out + (static_cast<size_t>(tr) * TILE + wq * SLAB_ROWS) * p.N + tc * TILE + l * 4;
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
                 // block amax of rows i and i+1 (one per 16-bit half) over the 8 lanes of a 32-column block
@@ -277,7 +295,7 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
             __syncwarp();
             // row r of the tile keeps its four scale bytes at (r % 32) * 16 + (r / 32) * 4
             const uint32_t word = *reinterpret_cast<const uint32_t*>(scstage_ptr + l * 4);
-            *reinterpret_cast<uint32_t*>(p.sc + (static_cast<size_t>(tr) * p.tiles_c + tc) * 512 + l * 16 + wq * 4) = word;
+            *reinterpret_cast<uint32_t*>(o_sc + (static_cast<size_t>(tr) * p.tiles_c + tc) * 512 + l * 16 + wq * 4) = word;
             __syncwarp();
         }
 
@@ -296,7 +314,7 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
                 c[i][1] = mul_bf16x2(c[i][1], inv23);
             }
             const int e = tr / p.tiles_rm, trm = tr - e * p.tiles_rm;
-            uint8_t* sct = p.sc_t + ((static_cast<size_t>(e) * p.tiles_c + tc) * p.tiles_rm + trm) * 512 + wq;
+            uint8_t* sct = o_sc_t + ((static_cast<size_t>(e) * p.tiles_c + tc) * p.tiles_rm + trm) * 512 + wq;
             // the previous slab's tile stores must have finished reading the staging buffer
             if (l == 0) bulk_wait_read<0>();
             __syncwarp();
@@ -331,17 +349,18 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
             if (l == 0) {
 #pragma unroll
                 for (int k = 0; k < 4; ++k)
-                    tma_store_4d(&tm_t, trm * TILE + wq * SLAB_ROWS, k, tc * 32, e, tstage + k * 1024);
+                    tma_store_4d(o_tm_t, trm * TILE + wq * SLAB_ROWS, k, tc * 32, e, tstage + k * 1024);
                 bulk_commit();
             }
         }
+        }   // pass
     }
     if (COL && l == 0) bulk_wait_all<0>();
 }
 
 template <int W, int D, int SRC, bool ROW, bool COL>
 static int launch(const CUtensorMap& tm_in, const CUtensorMap& tm_in2, const CUtensorMap& tm_in3, const CUtensorMap& tm_t,
-                  const Params& p, int grid, cudaStream_t stream) {
+                  const Params& p, int grid, cudaStream_t stream, const CUtensorMap* tm_t2 = nullptr) {
     auto kern = quantize_kernel<W, D, SRC, ROW, COL>;
     constexpr int smem = Smem<W, D, slot_bytes(SRC)>::dynamic;
     static bool configured[64] = {};
@@ -355,7 +374,7 @@ static int launch(const CUtensorMap& tm_in, const CUtensorMap& tm_in2, const CUt
         }
         configured[dev & 63] = true;
     }
-    kern<<<grid, (producer_warps(SRC) + W) * 32, smem, stream>>>(tm_in, tm_in2, tm_in3, tm_t, p);
+    kern<<<grid, (producer_warps(SRC) + W) * 32, smem, stream>>>(tm_in, tm_in2, tm_in3, tm_t, tm_t2 ? *tm_t2 : tm_t, p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
         note_cuda_error("quantize launch", cudaGetErrorString(e));
@@ -560,4 +579,48 @@ extern "C" int mx8_swiglu_bwd_quantize(const void* gate_fp8, const void* gate_sc
     const int tiles = p.tiles_r * p.tiles_c;
     if (grid > tiles) grid = tiles;
     return launch<8, 1, SRC_SWIGLU_BWD, true, true>(tm_g, tm_u, tm_d, tm_t, p, grid, static_cast<cudaStream_t>(stream));
+}
+
+// Both gradients from one pass over gate, up and d_hidden (each input is read once instead of twice).
+extern "C" int mx8_swiglu_bwd_quantize_both(const void* gate_fp8, const void* gate_sc, const void* up_fp8, const void* up_sc,
+                                            const void* d_hidden, int rows, int cols, const void* num_rows,
+                                            void* d_gate_fp8, void* d_gate_sc, void* d_gate_fp8_t, void* d_gate_sc_t,
+                                            void* d_up_fp8, void* d_up_sc, void* d_up_fp8_t, void* d_up_sc_t, void* stream) {
+    using namespace mx8;
+    using namespace mx8::quant;
+    const void* const all[] = {gate_fp8, gate_sc, up_fp8, up_sc, d_hidden, d_gate_fp8, d_gate_sc, d_gate_fp8_t, d_gate_sc_t,
+                               d_up_fp8, d_up_sc, d_up_fp8_t, d_up_sc_t};
+    for (const void* q : all) {
+        if (!q) return MX8_ERR_ARG;
+        if (!aligned16(q)) return MX8_ERR_ALIGN;
+    }
+    if (rows <= 0 || cols <= 0 || rows % 128 || cols % 128) return MX8_ERR_SHAPE;
+    int rc = check_device_sm100();
+    if (rc != MX8_OK) return rc;
+    Params p{};
+    fill_common(p, d_gate_fp8, d_gate_sc, d_gate_sc_t, rows, cols);
+    p.out2 = static_cast<uint8_t*>(d_up_fp8);
+    p.sc2 = static_cast<uint8_t*>(d_up_sc);
+    p.sc_t2 = static_cast<uint8_t*>(d_up_sc_t);
+    p.rows_dev = static_cast<const int*>(num_rows);
+    p.gate_sc = static_cast<const uint8_t*>(gate_sc);
+    p.up_sc = static_cast<const uint8_t*>(up_sc);
+    p.bwd_which = 2;
+    p.status = device_status_ptr();
+    if (!p.status) return MX8_ERR_CUDA;
+    CUtensorMap tm_g, tm_u, tm_d, tm_t, tm_t2;
+    const uint64_t dims[2] = {static_cast<uint64_t>(cols), static_cast<uint64_t>(rows)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(cols)};
+    const uint64_t strides2[1] = {static_cast<uint64_t>(cols) * 2};
+    const uint32_t box[2] = {128, SLAB_ROWS};
+    if ((rc = make_tmap(&tm_g, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, gate_fp8, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE)) != MX8_OK) return rc;
+    if ((rc = make_tmap(&tm_u, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, up_fp8, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE)) != MX8_OK) return rc;
+    if ((rc = make_tmap(&tm_d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, d_hidden, dims, strides2, box, CU_TENSOR_MAP_SWIZZLE_NONE)) != MX8_OK) return rc;
+    if ((rc = make_transposed_map(&tm_t, d_gate_fp8_t, 1, rows, cols)) != MX8_OK) return rc;
+    if ((rc = make_transposed_map(&tm_t2, d_up_fp8_t, 1, rows, cols)) != MX8_OK) return rc;
+    int grid = sm_count();
+    if (grid <= 0) return MX8_ERR_CUDA;
+    const int tiles = p.tiles_r * p.tiles_c;
+    if (grid > tiles) grid = tiles;
+    return launch<8, 1, SRC_SWIGLU_BWD, true, true>(tm_g, tm_u, tm_d, tm_t, p, grid, static_cast<cudaStream_t>(stream), &tm_t2);
 }

@@ -313,16 +313,11 @@ std::vector<at::Tensor> dispatch_mlp_swiglu_combine_bwd(
                                     static_cast<int>(cap), d_y_fp8.data_ptr(), d_y_sc.data_ptr(), d_y_fp8_t.data_ptr(), d_y_sc_t.data_ptr(), stream()),
           "gradient dispatch + quantize");
     grouped(d_y_fp8, d_y_sc, w_routed_down_T, w_routed_down_T_sc, d_hidden, at::Tensor(), num_tokens, tokens_per_expert);
-    for (int which = 0; which < 2; ++which) {
-        at::Tensor& o = which ? d_up_fp8 : d_gate_fp8;
-        at::Tensor& os = which ? d_up_sc : d_gate_sc;
-        at::Tensor& ot = which ? d_up_fp8_t : d_gate_fp8_t;
-        at::Tensor& ots = which ? d_up_sc_t : d_gate_sc_t;
-        check(mx8_swiglu_bwd_quantize(gate_fp8_routed.data_ptr(), gate_sc_routed.data_ptr(), up_fp8_routed.data_ptr(), up_sc_routed.data_ptr(),
-                                      d_hidden.data_ptr(), static_cast<int>(cap), static_cast<int>(I), num_tokens.data_ptr(), which,
-                                      o.data_ptr(), os.data_ptr(), ot.data_ptr(), ots.data_ptr(), nullptr, stream()),
-              "swiglu backward + quantize");
-    }
+    check(mx8_swiglu_bwd_quantize_both(gate_fp8_routed.data_ptr(), gate_sc_routed.data_ptr(), up_fp8_routed.data_ptr(), up_sc_routed.data_ptr(),
+                                       d_hidden.data_ptr(), static_cast<int>(cap), static_cast<int>(I), num_tokens.data_ptr(),
+                                       d_gate_fp8.data_ptr(), d_gate_sc.data_ptr(), d_gate_fp8_t.data_ptr(), d_gate_sc_t.data_ptr(),
+                                       d_up_fp8.data_ptr(), d_up_sc.data_ptr(), d_up_fp8_t.data_ptr(), d_up_sc_t.data_ptr(), stream()),
+          "swiglu backward + quantize");
     check(mx8_gemm_grouped_dual(d_gate_fp8.data_ptr(), d_gate_sc.data_ptr(), w_routed_gate_T.data_ptr(), w_routed_gate_T_sc.data_ptr(),
                                 d_up_fp8.data_ptr(), d_up_sc.data_ptr(), w_routed_up_T.data_ptr(), w_routed_up_T_sc.data_ptr(),
                                 d_x_routed.data_ptr(), static_cast<int>(cap), static_cast<int>(H), static_cast<int>(I), static_cast<int>(I),

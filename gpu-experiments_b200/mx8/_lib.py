@@ -25,6 +25,7 @@ SIGNATURES = {
     "mx8_gemm_grouped_dual": (_i, [_vp] * 9 + [_i, _i, _i, _i, _vp, _vp, _i, _vp]),
     "mx8_gemm_wgrad": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _i, _vp]),
     "mx8_swiglu_bwd_quantize": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "mx8_swiglu_bwd_quantize_both": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp] + [_vp] * 8 + [_vp]),
     "mx8_moe_bwd_prologue": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "mx8_moe_bwd_epilogue": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "mx8_moe_schedule": (_i, [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),

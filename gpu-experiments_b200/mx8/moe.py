@@ -167,6 +167,27 @@ def swiglu_bwd_quantize(gate_fp8, gate_sc, up_fp8, up_sc, d_hidden, which, num_r
     return (o_fp8, o_sc, o_fp8_t, o_sc_t) + ((o_bf16,) if return_bf16 else ())
 
 
+def swiglu_bwd_quantize_both(gate_fp8, gate_sc, up_fp8, up_sc, d_hidden, num_rows=None):
+    """Both SwiGLU gradients from one pass over the inputs (mx8_swiglu_bwd_quantize_both); same bytes as two
+    calls of swiglu_bwd_quantize.  Returns ((d_gate fp8, sc, fp8_t, sc_t), (d_up fp8, sc, fp8_t, sc_t))."""
+    lib = _lib.load()
+    R, I = gate_fp8.shape
+    dev = gate_fp8.device
+
+    def outs():
+        return (torch.empty(R, I, dtype=torch.float8_e4m3fn, device=dev), torch.empty(R // 128, I // 128, 32, 16, dtype=torch.uint8, device=dev),
+                torch.empty(I, R, dtype=torch.float8_e4m3fn, device=dev), torch.empty(I // 128, R // 128, 32, 16, dtype=torch.uint8, device=dev))
+    dg, du = outs(), outs()
+    with torch.cuda.device(dev):
+        _lib.check(lib.mx8_swiglu_bwd_quantize_both(
+            _chk(gate_fp8, "gate_fp8", _FP8), _chk(gate_sc, "gate_sc", _SC, (R // 128, I // 128, 512)),
+            _chk(up_fp8, "up_fp8", _FP8, (R, I)), _chk(up_sc, "up_sc", _SC, (R // 128, I // 128, 512)),
+            _chk(d_hidden, "d_hidden", (torch.bfloat16,), (R, I)), R, I,
+            _chk(num_rows, "num_rows", (torch.int32,)) if num_rows is not None else None,
+            *[t.data_ptr() for t in dg], *[t.data_ptr() for t in du], _stream()), "swiglu_bwd_quantize_both")
+    return dg, du
+
+
 def bwd_prologue(d_output, topk_weights, d_combine_buffer):
     """bwd_prologue(d_output, topk_weights, d_combine_buffer) -> d_y_shared (== d_output); fills
     d_combine_buffer[t*topk + j] = d_output[t] * w[t, j] in place
@@ -235,10 +256,8 @@ def dispatch_mlp_swiglu_combine_bwd(d_y_shared, d_combine_buffer, d_combine_buff
                                                                schedule_peer_token_idx, num_tokens, cap)
     d_hidden = torch.empty(cap, I, dtype=torch.bfloat16, device=dev)
     gemm_grouped(d_y_fp8, d_y_sc, w_routed_down_T, w_routed_down_T_sc, d_hidden, None, num_tokens, tokens_per_expert)
-    d_gate_fp8, d_gate_sc, d_gate_fp8_t, d_gate_sc_t = swiglu_bwd_quantize(gate_fp8_routed, gate_sc_routed, up_fp8_routed,
-                                                                            up_sc_routed, d_hidden, 0, num_tokens)
-    d_up_fp8, d_up_sc, d_up_fp8_t, d_up_sc_t = swiglu_bwd_quantize(gate_fp8_routed, gate_sc_routed, up_fp8_routed,
-                                                                    up_sc_routed, d_hidden, 1, num_tokens)
+    (d_gate_fp8, d_gate_sc, d_gate_fp8_t, d_gate_sc_t), (d_up_fp8, d_up_sc, d_up_fp8_t, d_up_sc_t) = swiglu_bwd_quantize_both(
+        gate_fp8_routed, gate_sc_routed, up_fp8_routed, up_sc_routed, d_hidden, num_tokens)
     from .ops import gemm_grouped_dual, gemm_wgrad
     d_x_routed = torch.empty(cap, H, dtype=torch.bfloat16, device=dev)
     gemm_grouped_dual(d_gate_fp8, d_gate_sc, w_routed_gate_T, w_routed_gate_T_sc, d_up_fp8, d_up_sc, w_routed_up_T,

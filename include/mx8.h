@@ -167,6 +167,12 @@ MX8_API int mx8_gemm_wgrad(const void* A_t, const void* A_t_sc, const void* B_t,
 MX8_API int mx8_swiglu_bwd_quantize(const void* gate_fp8, const void* gate_sc, const void* up_fp8, const void* up_sc,
                                     const void* d_hidden, int rows, int cols, const void* num_rows, int which, void* out_fp8,
                                     void* out_sc, void* out_fp8_t, void* out_sc_t, void* out_bf16, void* stream);
+/* Both gradients (same arithmetic, same bytes) from one pass over gate, up and d_hidden: each input is
+ * read once, as in the reference's single task (same file :1250-1353). */
+MX8_API int mx8_swiglu_bwd_quantize_both(const void* gate_fp8, const void* gate_sc, const void* up_fp8, const void* up_sc,
+                                         const void* d_hidden, int rows, int cols, const void* num_rows,
+                                         void* d_gate_fp8, void* d_gate_sc, void* d_gate_fp8_t, void* d_gate_sc_t,
+                                         void* d_up_fp8, void* d_up_sc, void* d_up_fp8_t, void* d_up_sc_t, void* stream);
 
 /* d_combine_buffer[t*topk + j] = bf16( d_output[t] * topk_weights[t][j] ) (bf16 [tokens][hidden] in,
  * [tokens*topk][hidden] out).  Replaces bwd_prologue, blackwell-ultra/022-…-mxfp8-bw.cu:2881-2923. */

@@ -385,3 +385,23 @@ def test_moe_backward_layer_single_rank():
     # d_x: combine + epilogue are exact given the kernel's own d_x_routed
     buf = MO.combine_ref([b[1][:n].cpu()], [rpr], [rpt], 0, T, k)
     assert torch.equal(d_x.cpu().view(torch.int16), MO.bwd_epilogue_ref(None, buf, k).view(torch.int16))
+
+
+def test_swiglu_backward_both_equals_two_single_passes():
+    R, I = 512, 384
+    g = O.make_input(R, I, seed=81, std=2.0)
+    u = O.make_input(R, I, seed=82)
+    dh = O.make_input(R, I, seed=83).to(DEV)
+    gq = [t.to(DEV) for t in O.quantize_both(g)[:2]]
+    uq = [t.to(DEV) for t in O.quantize_both(u)[:2]]
+    nr = torch.tensor([384], dtype=torch.int32, device=DEV)
+    one_g = mx8.swiglu_bwd_quantize(gq[0], gq[1], uq[0], uq[1], dh, 0, nr)
+    one_u = mx8.swiglu_bwd_quantize(gq[0], gq[1], uq[0], uq[1], dh, 1, nr)
+    both_g, both_u = mx8.swiglu_bwd_quantize_both(gq[0], gq[1], uq[0], uq[1], dh, nr)
+    assert mx8.device_status() == 0
+    n = 384
+    for single, fused in ((one_g, both_g), (one_u, both_u)):
+        assert torch.equal(single[0][:n].view(torch.uint8), fused[0][:n].view(torch.uint8))
+        assert torch.equal(single[1][:n // 128], fused[1][:n // 128])
+        assert torch.equal(single[2][:, :n].view(torch.uint8), fused[2][:, :n].view(torch.uint8))
+        assert torch.equal(single[3][:, :n // 128], fused[3][:, :n // 128])
