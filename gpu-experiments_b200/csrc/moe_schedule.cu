@@ -12,6 +12,8 @@
 // (blackwell-ultra/022-moe-dispatch-mlp-swiglu-combine-mxfp8-bw.cu:34-147), which this file replaces.
 // Differences: a schedule larger than `capacity` is reported through the device status word
 // (the reference executes `trap`), and the counting scratch is supplied by the caller.
+// Two forms: a counting sort over chunks of the table when the scratch has room for the per-chunk
+// counts (mx8_moe_schedule_scratch_bytes), else one scan of the table per (local expert, source rank).
 #include "mx8_host.cuh"
 #include "mx8_ptx.cuh"
 
@@ -123,6 +125,142 @@ __global__ void sched_place_kernel(SchedParams p) {
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Counting-sort form (used when the scratch buffer is large enough): the table is cut into chunks of
+// CHUNK entries of one source rank; one pass counts every chunk's pairs per local expert, a scan
+// turns the counts into each chunk's first ordinal per (expert, rank), and a second pass places the
+// pairs.  Every entry of the table is read twice in total, instead of once per local expert.
+// Scratch: counts[E*W] | bases[E] | chunk_counts[W * chunks_per_rank * E].
+constexpr int CHUNK = 1024;
+
+__host__ __device__ inline int chunks_per_rank(int tokens, int topk_k) { return (tokens * topk_k + CHUNK - 1) / CHUNK; }
+
+// block (r, c): histogram of chunk c of rank r over the local experts; also clears the outputs
+__global__ void __launch_bounds__(CHUNK) sched_chunk_count_kernel(SchedParams p) {
+    extern __shared__ int hist[];             // [experts]
+    for (int i = blockIdx.x * CHUNK + threadIdx.x; i < p.capacity; i += gridDim.x * CHUNK) p.peer_rank[i] = -1;
+    for (int i = threadIdx.x; i < p.experts; i += CHUNK) hist[i] = 0;
+    __syncthreads();
+    const int cpr = chunks_per_rank(p.tokens, p.topk_k);
+    const int r = blockIdx.x / cpr, c = blockIdx.x % cpr;
+    const int stride = p.tokens * p.topk_k;
+    const int i = c * CHUNK + threadIdx.x;
+    if (i < stride) {
+        const int e = p.topk[static_cast<size_t>(r) * stride + i] - p.rank * p.experts;
+        if (e >= 0 && e < p.experts) atomicAdd(&hist[e], 1);
+    }
+    __syncthreads();
+    int* cc = p.counts + p.experts * p.world + p.experts + static_cast<size_t>(blockIdx.x) * p.experts;
+    for (int e = threadIdx.x; e < p.experts; e += CHUNK) cc[e] = hist[e];
+}
+
+// one block: chunk counts -> exclusive prefix per (expert, rank); totals; padded segments and bases
+__global__ void __launch_bounds__(1024) sched_scan_kernel(SchedParams p) {
+    __shared__ int warp_tot[32];
+    __shared__ int carry;
+    const int cpr = chunks_per_rank(p.tokens, p.topk_k);
+    int* cc = p.counts + p.experts * p.world + p.experts;
+    for (int idx = threadIdx.x; idx < p.experts * p.world; idx += blockDim.x) {
+        const int r = idx / p.experts, e = idx - r * p.experts;     // e fastest: neighbouring threads, neighbouring words
+        int running = 0;
+        for (int c = 0; c < cpr; ++c) {
+            int* q = cc + (static_cast<size_t>(r) * cpr + c) * p.experts + e;
+            const int v = *q;
+            *q = running;
+            running += v;
+        }
+        p.counts[e * p.world + r] = running;
+    }
+    if (threadIdx.x == 0) carry = 0;
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int e0 = 0; e0 < p.experts; e0 += blockDim.x) {
+        const int e = e0 + threadIdx.x;
+        int padded = 0;
+        if (e < p.experts) {
+            int n = 0;
+            for (int r = 0; r < p.world; ++r) n += p.counts[e * p.world + r];
+            padded = (n + PAD - 1) / PAD * PAD;
+            p.tokens_per_expert[e] = padded;
+        }
+        int incl = padded;                                           // inclusive scan inside the warp
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int v = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+            if (lane >= d) incl += v;
+        }
+        if (lane == 31) warp_tot[warp] = incl;
+        __syncthreads();
+        int before = carry;
+        for (int w = 0; w < warp; ++w) before += warp_tot[w];
+        if (e < p.experts) p.counts[p.experts * p.world + e] = before + incl - padded;
+        __syncthreads();
+        if (threadIdx.x == blockDim.x - 1) carry = before + incl;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        p.num_tokens[0] = carry;
+        if (carry > p.capacity) atomicCAS(p.status, 0, DEV_MOE_CAPACITY);
+    }
+}
+
+// block (r, c): ordinal of every pair among the pairs of (expert, rank) in table order, then its row
+__global__ void __launch_bounds__(CHUNK) sched_chunk_place_kernel(SchedParams p) {
+    extern __shared__ int run[];              // [experts] ordinal of the next pair of this rank per expert
+    const int cpr = chunks_per_rank(p.tokens, p.topk_k);
+    const int r = blockIdx.x / cpr, c = blockIdx.x % cpr;
+    const int* cc = p.counts + p.experts * p.world + p.experts + static_cast<size_t>(blockIdx.x) * p.experts;
+    for (int e = threadIdx.x; e < p.experts; e += CHUNK) run[e] = cc[e];
+    const int stride = p.tokens * p.topk_k;
+    const int i = c * CHUNK + threadIdx.x;
+    int e = -1;
+    if (i < stride) {
+        e = p.topk[static_cast<size_t>(r) * stride + i] - p.rank * p.experts;
+        if (e < 0 || e >= p.experts) e = -1;
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const unsigned same = __match_any_sync(0xFFFFFFFFu, e);          // lanes of this warp with the same expert
+    const int in_warp = __popc(same & ((1u << lane) - 1));
+    const bool leader = in_warp == 0;
+    int j = 0;
+    __syncthreads();
+    for (int w = 0; w < CHUNK / 32; ++w) {                           // warps take their ordinals in table order
+        if (warp == w && e >= 0) {
+            j = run[e] + in_warp;
+            __syncwarp(same);
+            if (leader) run[e] += __popc(same);
+        }
+        __syncthreads();
+    }
+    if (e < 0) return;
+    int dst = p.counts[p.experts * p.world + e];
+    for (int q = 0; q < p.world; ++q) {
+        const int n = p.counts[e * p.world + q];
+        dst += min(n, j) + ((q < r && n > j) ? 1 : 0);
+    }
+    if (dst < p.capacity) {
+        p.peer_rank[dst] = r;
+        p.peer_token_idx[dst] = i;
+    }
+}
+
+static long long fast_scratch_ints(int world, int tokens, int topk_k, int experts) {
+    return static_cast<long long>(experts) * (world + 1) + static_cast<long long>(world) * chunks_per_rank(tokens, topk_k) * experts;
+}
+
+static int run_schedule_fast(const SchedParams& p, cudaStream_t st) {
+    const int blocks = p.world * chunks_per_rank(p.tokens, p.topk_k);
+    sched_chunk_count_kernel<<<blocks, CHUNK, p.experts * sizeof(int), st>>>(p);
+    sched_scan_kernel<<<1, 1024, 0, st>>>(p);
+    sched_chunk_place_kernel<<<blocks, CHUNK, p.experts * sizeof(int), st>>>(p);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        note_cuda_error("moe schedule launch", cudaGetErrorString(e));
+        return MX8_ERR_CUDA;
+    }
+    return MX8_OK;
+}
+
 static int run_schedule(const SchedParams& p, cudaStream_t st) {
     const int bins = p.experts * p.world + p.experts;
     const int init_n = p.capacity > bins ? p.capacity : bins;
@@ -146,7 +284,7 @@ static int run_schedule(const SchedParams& p, cudaStream_t st) {
 
 extern "C" int mx8_moe_schedule(const void* topk_all, int world, int tokens, int topk, int num_local_experts, int capacity,
                                 int rank, void* peer_rank, void* peer_token_idx, void* num_tokens, void* tokens_per_expert,
-                                void* scratch, void* stream) {
+                                void* scratch, size_t scratch_bytes, void* stream) {
     using namespace mx8;
     if (!topk_all || !peer_rank || !peer_token_idx || !num_tokens || !tokens_per_expert || !scratch) return MX8_ERR_ARG;
     if (world <= 0 || tokens <= 0 || topk <= 0 || num_local_experts <= 0 || capacity <= 0 || rank < 0 || rank >= world)
@@ -165,7 +303,20 @@ extern "C" int mx8_moe_schedule(const void* topk_all, int world, int tokens, int
     p.counts = static_cast<int*>(scratch);
     p.status = device_status_ptr();
     if (!p.status) return MX8_ERR_CUDA;
+    const long long have = static_cast<long long>(scratch_bytes / sizeof(int));
+    if (have < static_cast<long long>(num_local_experts) * (world + 1)) {
+        note_cuda_error("mx8_moe_schedule", "scratch smaller than num_local_experts * (world + 1) ints");
+        return MX8_ERR_LIMIT;
+    }
+    // the counting-sort form needs room for the per-chunk counts; without it the scan-per-expert form runs
+    if (have >= moe::fast_scratch_ints(world, tokens, topk, num_local_experts))
+        return moe::run_schedule_fast(p, static_cast<cudaStream_t>(stream));
     return moe::run_schedule(p, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" size_t mx8_moe_schedule_scratch_bytes(int world, int tokens, int topk, int num_local_experts) {
+    if (world <= 0 || tokens <= 0 || topk <= 0 || num_local_experts <= 0) return 0;
+    return static_cast<size_t>(mx8::moe::fast_scratch_ints(world, tokens, topk, num_local_experts)) * sizeof(int);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -219,5 +370,5 @@ extern "C" int mx8_moe_schedule_static(const void* topk_all, int world, int toke
     int* scratch = moe::static_scratch_ptr();     // first call on a device resolves the address
     if (!scratch) return MX8_ERR_CUDA;
     return mx8_moe_schedule(topk_all, world, tokens, topk, num_local_experts, capacity, rank, peer_rank, peer_token_idx,
-                            num_tokens, tokens_per_expert, scratch, stream);
+                            num_tokens, tokens_per_expert, scratch, moe::STATIC_SCRATCH_INTS * sizeof(int), stream);
 }

@@ -139,10 +139,12 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> schedule(const at::Te
     auto opt = topk_all.options().dtype(at::kInt);
     at::Tensor peer_rank = at::empty({schedule_capacity}, opt), peer_tok = at::empty({schedule_capacity}, opt);
     at::Tensor num_tokens = at::empty({1}, opt), tpe = at::empty({num_local_experts}, opt);
-    at::Tensor scratch = at::empty({static_cast<int64_t>(num_local_experts) * (world + 1)}, opt);
+    const size_t scratch_bytes = mx8_moe_schedule_scratch_bytes(world, static_cast<int>(topk_all.size(1)), static_cast<int>(topk_all.size(2)),
+                                                                num_local_experts);
+    at::Tensor scratch = at::empty({static_cast<int64_t>(scratch_bytes)}, topk_all.options().dtype(at::kByte));
     check(mx8_moe_schedule(iptr(topk_all, "topk_all"), world, static_cast<int>(topk_all.size(1)), static_cast<int>(topk_all.size(2)),
                            num_local_experts, schedule_capacity, rank, peer_rank.data_ptr(), peer_tok.data_ptr(),
-                           num_tokens.data_ptr(), tpe.data_ptr(), scratch.data_ptr(), stream()),
+                           num_tokens.data_ptr(), tpe.data_ptr(), scratch.data_ptr(), scratch_bytes, stream()),
           "schedule");
     return {peer_rank, peer_tok, num_tokens, tpe};
 }

@@ -28,7 +28,8 @@ SIGNATURES = {
     "mx8_swiglu_bwd_quantize_both": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp] + [_vp] * 8 + [_vp]),
     "mx8_moe_bwd_prologue": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "mx8_moe_bwd_epilogue": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
-    "mx8_moe_schedule": (_i, [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "mx8_moe_schedule": (_i, [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, ctypes.c_size_t, _vp]),
+    "mx8_moe_schedule_scratch_bytes": (ctypes.c_size_t, [_i, _i, _i, _i]),
     "mx8_moe_schedule_static": (_i, [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "mx8_gemm_bf16": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "mx8_gemm_bf16_dual": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),

@@ -224,11 +224,11 @@ def schedule(topk_all, num_local_experts, schedule_capacity, rank):
     peer_tok = torch.empty(schedule_capacity, dtype=torch.int32, device=dev)
     num_tokens = torch.empty(1, dtype=torch.int32, device=dev)
     tpe = torch.empty(num_local_experts, dtype=torch.int32, device=dev)
-    scratch = torch.empty(num_local_experts * (W + 1), dtype=torch.int32, device=dev)
+    scratch = torch.empty(lib.mx8_moe_schedule_scratch_bytes(W, T, k, num_local_experts), dtype=torch.uint8, device=dev)
     with torch.cuda.device(dev):
         _lib.check(lib.mx8_moe_schedule(tp, W, T, k, num_local_experts, schedule_capacity, rank, peer_rank.data_ptr(),
                                         peer_tok.data_ptr(), num_tokens.data_ptr(), tpe.data_ptr(), scratch.data_ptr(),
-                                        _stream()), "schedule")
+                                        scratch.numel(), _stream()), "schedule")
     return peer_rank, peer_tok, num_tokens, tpe
 
 

@@ -26,6 +26,8 @@
 #define MX8_API
 #endif
 
+#include <stddef.h>
+
 #ifdef __cplusplus
 extern "C" {
 #endif
@@ -189,13 +191,16 @@ MX8_API int mx8_moe_bwd_epilogue(const void* d_x_shared, const void* d_x_routed_
  *   this rank owns experts [rank*num_local_experts, (rank+1)*num_local_experts).
  * Outputs: peer_rank[capacity] (source rank per row, -1 = padding/unused), peer_token_idx[capacity]
  * (token*topk + k on the source rank), num_tokens[1] (rows used, every expert padded to 256),
- * tokens_per_expert[num_local_experts] (padded).  `scratch` is num_local_experts*(world+1) ints of
- * device memory, overwritten.  capacity is a multiple of 256; a schedule that does not fit sets the
- * device status word (mx8_device_status) instead of trapping.
+ * tokens_per_expert[num_local_experts] (padded).  `scratch` is `scratch_bytes` of device memory,
+ * overwritten: with mx8_moe_schedule_scratch_bytes(...) bytes the schedule is a counting sort that reads
+ * the routing table twice; with at least num_local_experts*(world+1) ints it still works, scanning the
+ * table once per local expert; less is MX8_ERR_LIMIT.  capacity is a multiple of 256; a schedule that
+ * does not fit sets the device status word (mx8_device_status) instead of trapping.
  * Replaces scheduler::schedule, blackwell-ultra/022-moe-dispatch-mlp-swiglu-combine-mxfp8-bw.cu:149-183. */
+MX8_API size_t mx8_moe_schedule_scratch_bytes(int world, int tokens, int topk, int num_local_experts);
 MX8_API int mx8_moe_schedule(const void* topk_all, int world, int tokens, int topk, int num_local_experts,
                              int capacity, int rank, void* peer_rank, void* peer_token_idx, void* num_tokens,
-                             void* tokens_per_expert, void* scratch, void* stream);
+                             void* tokens_per_expert, void* scratch, size_t scratch_bytes, void* stream);
 
 /* Same schedule, same outputs, for callers that cannot provide scratch memory.  It has no counterpart
  * in the reference.  Hosts whose memory plan is fixed after start-up, or that run under a foreign
@@ -244,7 +249,6 @@ MX8_API int mx8_transpose_bf16(const void* in, void* out, int rows, int cols, vo
  *     alternating band buffers (and, for the GEMM, B with its scales); the call allocates no memory;
  *   - earlier work on `stream` precedes the first copy and `stream` waits for the last one.  Two
  *     copy streams per device are created on first use and kept. */
-#include <stddef.h>
 MX8_API size_t mx8_quantize_host_workspace(int N, int band_rows);
 MX8_API int mx8_quantize_host(const void* x_host, int M, int N, void* fp8_host, void* sc_host, void* fp8_t_host,
                               void* sc_t_host, int scale_mode, int band_rows, void* workspace,

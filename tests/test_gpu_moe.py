@@ -405,3 +405,30 @@ def test_swiglu_backward_both_equals_two_single_passes():
         assert torch.equal(single[1][:n // 128], fused[1][:n // 128])
         assert torch.equal(single[2][:, :n].view(torch.uint8), fused[2][:, :n].view(torch.uint8))
         assert torch.equal(single[3][:, :n // 128], fused[3][:, :n // 128])
+
+
+@pytest.mark.parametrize("W,T,E_local,k,rank", [(1, 512, 8, 4, 0), (4, 300, 6, 3, 2), (8, 1000, 4, 8, 7)])
+def test_schedule_both_forms_agree_with_oracle(W, T, E_local, k, rank):
+    # minimal scratch -> one scan per (expert, rank); full scratch -> counting sort over chunks; T values
+    # that are not multiples of the chunk size exercise the ragged last chunk
+    topk_all, _ = make_topk(W, T, W * E_local, k, seed=W + T)
+    cap = ((W * T * k) // 256 + E_local) * 256
+    want = MO.schedule_ref(topk_all, E_local, cap, rank)
+    lib = mx8.load()
+    dev_topk = topk_all.to(DEV).contiguous()
+    full = lib.mx8_moe_schedule_scratch_bytes(W, T, k, E_local)
+    for nbytes in (E_local * (W + 1) * 4, full):
+        pr = torch.full((cap,), -7, dtype=torch.int32, device=DEV)
+        pt = torch.full((cap,), -7, dtype=torch.int32, device=DEV)
+        nt = torch.zeros(1, dtype=torch.int32, device=DEV)
+        tpe = torch.zeros(E_local, dtype=torch.int32, device=DEV)
+        scratch = torch.empty(nbytes, dtype=torch.uint8, device=DEV)
+        rc = lib.mx8_moe_schedule(dev_topk.data_ptr(), W, T, k, E_local, cap, rank, pr.data_ptr(), pt.data_ptr(), nt.data_ptr(),
+                                  tpe.data_ptr(), scratch.data_ptr(), nbytes, torch.cuda.current_stream().cuda_stream)
+        assert rc == 0 and mx8.device_status() == 0
+        assert torch.equal(nt.cpu(), want[2]) and torch.equal(tpe.cpu(), want[3])
+        assert torch.equal(pr.cpu(), want[0])
+        assert torch.equal(pt.cpu()[want[4]], want[1][want[4]])
+    small = torch.empty(16, dtype=torch.uint8, device=DEV)
+    assert lib.mx8_moe_schedule(dev_topk.data_ptr(), W, T, k, E_local, cap, rank, pr.data_ptr(), pt.data_ptr(), nt.data_ptr(),
+                                tpe.data_ptr(), small.data_ptr(), 16, None) == 7

@@ -38,7 +38,7 @@ def _run(lib, fn_static, topk_all, E_local, cap, rank):
         else:
             scratch = torch.empty(E_local * (W + 1), dtype=torch.int32, device=DEV)
             rc = lib.mx8_moe_schedule(dev_topk.data_ptr(), W, T, k, E_local, cap, rank, pr.data_ptr(), pt.data_ptr(),
-                                      nt.data_ptr(), tpe.data_ptr(), scratch.data_ptr(), stream)
+                                      nt.data_ptr(), tpe.data_ptr(), scratch.data_ptr(), scratch.numel() * 4, stream)
         assert rc == _lib.OK
         assert mx8.device_status() == 0
         outs.append((pr.cpu(), pt.cpu(), nt.cpu(), tpe.cpu()))
