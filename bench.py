@@ -560,6 +560,11 @@ def bench_moe(args, world, rank, local, peaks, with_cpu=False):
     ids = ids.to(torch.int32)
     ids_all = torch.empty(world, T, k, dtype=torch.int32, device=dev)
 
+    # the reference harness's knobs: 28 communication SMs, minibatches of 16384 rows of the schedule
+    comm_sms = args.moe_comm_sms
+    minibatch = args.moe_minibatch if args.moe_minibatch > 0 else -(-cap // (4 * 256)) * 256      # default: four minibatches
+    pipe = [0, 0]
+
     def step(_):
         if world > 1:
             import torch.distributed as dist
@@ -568,7 +573,7 @@ def bench_moe(args, world, rank, local, peaks, with_cpu=False):
             ids_all.copy_(ids.view(1, T, k))
         pr, pt, nt, tpe = mx8.schedule(ids_all, E, cap, rank)
         mx8.dispatch_mlp_swiglu_combine_fwd(x, x_ptrs, cb, cb_ptrs, None, wg, wgs, None, wu, wus, None, wd, wds,
-                                            pr, pt, nt, tpe, k)
+                                            pr, pt, nt, tpe, k, pipe[0], 0, pipe[1])
         if world > 1:
             import torch.distributed as dist
             dist.barrier()
@@ -577,8 +582,18 @@ def bench_moe(args, world, rank, local, peaks, with_cpu=False):
     steps = max(3, args.steps // 40)
     for i in range(3):
         step(i)
-    ms = timed(step, steps, world) / steps
+    ms_single = timed(step, steps, world) / steps
     mx8.device_status()
+    # the same layer with the routed experts cut into minibatches whose transfers overlap the GEMMs
+    pipe[:] = [comm_sms, minibatch]
+    for i in range(3):
+        step(i)
+    ms_pipe = timed(step, steps, world) / steps
+    mx8.device_status()
+    pipe[:] = [0, 0]
+    ms = min(ms_single, ms_pipe)
+    pipeline = {"comm_sms": comm_sms, "minibatch_rows": minibatch, "minibatches": min(E, -(-cap // minibatch)),
+                "ms_per_step": ms_pipe, "single_sequence_ms_per_step": ms_single}
 
     # ---- backward of the same layer (routed experts): prologue, barrier, fused backward, barrier, epilogue
     bwd = None
@@ -637,6 +652,7 @@ def bench_moe(args, world, rank, local, peaks, with_cpu=False):
                        "sharding": "experts and tokens split across GPUs; dispatch pulls and combine pushes over peer-mapped memory"},
             "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": 2.0 * peaks["bf16_tflops"], "unit": "TFLOP/s",
                          "frac": per_gpu / (2.0 * peaks["bf16_tflops"]), "frac_of_nominal_4500": per_gpu / 4500.0, "traffic": None},
+            "pipeline": pipeline,
             "backward": bwd,
             "gpu_launches": (10 + (14 if bwd else 0)) * steps, **({"cpu_baseline": cpu_baseline_layer("moe")} if with_cpu and rank == 0 else {})}
 
@@ -648,6 +664,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="mx8", choices=["mx8", "reference"])
     ap.add_argument("--workload", default="quantize", choices=["quantize", "gemm", "ffn", "moe"])
+    ap.add_argument("--moe-comm-sms", type=int, default=28, help="MoE: multiprocessors left to the dispatch of the next minibatch")
+    ap.add_argument("--moe-minibatch", type=int, default=0,
+                    help="MoE: schedule rows per minibatch of the pipelined layer (0 = a quarter of the schedule capacity; "
+                         "the reference harness uses 16384, which is the same at 8 GPUs)")
     ap.add_argument("--no-layers", action="store_true", help="skip the FFN and MoE objects of the quantize line")
     ap.add_argument("--no-gemm", action="store_true", help="skip the GEMM object of the quantize line")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")

@@ -82,6 +82,7 @@ struct Params {
     int n_cols;                         // N
     int rows_cap;                       // M (rows the C tensors have)
     const int* rows_dev;                // device: rows actually present (nullptr: all tiles_m tiles)
+    const int* row_begin_dev;           // device: first row of the window to compute (multiple of the tile height), nullptr = 0
     const int* group_rows;              // device: rows of every group (multiples of the tile height), nullptr = dense
     int num_groups;
     int group_b_rows;                   // rows of B per group (N)
@@ -118,7 +119,7 @@ struct TileInfo {
 };
 
 template <int CG>
-__device__ __forceinline__ TileInfo tile_info(int t, const Params& p, int tiles_m, const int* seg_end) {
+__device__ __forceinline__ TileInfo tile_info(int t, const Params& p, int tiles_m, const int* seg_end, int tm0 = 0) {
     TileInfo ti;
     if (p.wgrad) {
         const int per_group = tiles_m * p.tiles_n;
@@ -132,6 +133,7 @@ __device__ __forceinline__ TileInfo tile_info(int t, const Params& p, int tiles_
         return ti;
     }
     tile_coords(t, p, tiles_m, ti.tm, ti.tn);
+    ti.tm += tm0;                                     // row window: tile rows are counted from its first row
     ti.b_base = ti.tn * BN;
     if (p.num_groups > 0) {
         const int row0 = ti.tm * 128 * CG;
@@ -210,7 +212,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         const int rows = *p.rows_dev;
         tiles_m = min(tiles_m, (rows + 128 * CG - 1) / (128 * CG));
     }
+    int tm0 = 0;
+    if (p.row_begin_dev) {
+        tm0 = *p.row_begin_dev / (128 * CG);
+        tiles_m = max(tiles_m - tm0, 0);
+    }
     tiles_m = __shfl_sync(0xFFFFFFFFu, tiles_m, 0);     // loaded value: make it provably warp-uniform
+    tm0 = __shfl_sync(0xFFFFFFFFu, tm0, 0);
     if (p.num_groups > 0) {
         if (threadIdx.x == 0) {
             int acc = 0;
@@ -233,7 +241,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             const uint32_t full_leader0 = CG == 2 ? map_to_cta(full0, 0) : full0;
             bool ok = true;
             for (int t = cluster; t < num_tiles && ok; t += num_clusters) {
-                const TileInfo ti = tile_info<CG>(t, p, tiles_m, seg_end);
+                const TileInfo ti = tile_info<CG>(t, p, tiles_m, seg_end, tm0);
                 const int a_row = (__shfl_sync(0xFFFFFFFFu, ti.tm, 0) * CG + static_cast<int>(rank)) * 128;
                 const int b_base = __shfl_sync(0xFFFFFFFFu, ti.b_base, 0);
                 const int kcount_t = __shfl_sync(0xFFFFFFFFu, ti.kcount, 0), k0_t = __shfl_sync(0xFFFFFFFFu, ti.k0, 0);
@@ -302,7 +310,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             const bool do_cp = !F16 && !(p.dbg & (8 | 16)), do_mma = !(p.dbg & 1);
             const int my_tiles = cluster < num_tiles ? (num_tiles - cluster + num_clusters - 1) / num_clusters : 0;
             long long remaining = 0;                             // K steps whose scales are not copied yet
-            for (int t = cluster; t < num_tiles; t += num_clusters) remaining += tile_info<CG>(t, p, tiles_m, seg_end).kcount;
+            for (int t = cluster; t < num_tiles; t += num_clusters) remaining += tile_info<CG>(t, p, tiles_m, seg_end, tm0).kcount;
             bool ok = true;
             // wait for a stage and copy its scale tiles into the next TMEM scale slot
             auto copy_scales = [&]() -> bool {
@@ -331,7 +339,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     if (!(p.dbg & 128) && !__all_sync(0xFFFFFFFFu, mbar_wait<true>(drained, (it - 1) & 1, ab, DEV_TIMEOUT_TMEM_FREE))) { ok = false; break; }
                     tc_fence_after();
                 }
-                const int kcount = __shfl_sync(0xFFFFFFFFu, tile_info<CG>(cluster + it * num_clusters, p, tiles_m, seg_end).kcount, 0);
+                const int kcount = __shfl_sync(0xFFFFFFFFu, tile_info<CG>(cluster + it * num_clusters, p, tiles_m, seg_end, tm0).kcount, 0);
                 for (int ks = 0; ks < kcount; ++ks) {
                     if (remaining > 0 && !copy_scales()) { ok = false; break; }
                     if constexpr (F16) {
@@ -369,7 +377,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         int it = 0;
         bool ok = true;
         for (int t = cluster; t < num_tiles && ok; t += num_clusters, ++it) {
-            const TileInfo ti = tile_info<CG>(t, p, tiles_m, seg_end);
+            const TileInfo ti = tile_info<CG>(t, p, tiles_m, seg_end, tm0);
             const int tn = ti.tn;
             const bool zero_tile = ti.kcount == 0;                // wgrad of a group without rows: nothing was accumulated
             const int acc = it & 1;
@@ -617,6 +625,7 @@ static int max_grid() {
 struct Grouping {
     void* c_sc = nullptr;            // scale tiles of C (MX8_C_MXFP8)
     const int* rows_dev = nullptr;   // device count of rows present
+    const int* row_begin_dev = nullptr; // device: first row of the window
     const int* group_rows = nullptr; // device rows per group
     int num_groups = 0;
     const int* peer_rank = nullptr;  // scatter epilogue
@@ -651,6 +660,7 @@ static int run(const void* A, const void* A_sc, const void* B, const void* B_sc,
     p.wgrad = gr.wgrad ? 1 : 0;
     p.group_c_rows = M;
     p.rows_dev = gr.rows_dev;
+    p.row_begin_dev = gr.row_begin_dev;
     p.group_rows = gr.group_rows;
     p.num_groups = gr.num_groups;
     p.group_b_rows = N;
@@ -716,6 +726,12 @@ extern "C" int mx8_gemm_ex(const void* A, const void* A_sc, const void* B, const
 extern "C" int mx8_gemm_grouped(const void* A, const void* A_sc, const void* B, const void* B_sc, void* C, void* C_sc,
                                 int M, int N, int K, int c_dtype, const void* num_rows, const void* group_rows,
                                 int num_groups, void* stream) {
+    return mx8_gemm_grouped_window(A, A_sc, B, B_sc, C, C_sc, M, N, K, c_dtype, num_rows, group_rows, num_groups, nullptr, stream);
+}
+
+extern "C" int mx8_gemm_grouped_window(const void* A, const void* A_sc, const void* B, const void* B_sc, void* C, void* C_sc,
+                                       int M, int N, int K, int c_dtype, const void* num_rows, const void* group_rows,
+                                       int num_groups, const mx8_window* window, void* stream) {
     using namespace mx8;
     if (!A || !A_sc || !B || !B_sc || !C) return MX8_ERR_ARG;
     if (c_dtype != MX8_C_BF16 && c_dtype != MX8_C_F32 && c_dtype != MX8_C_MXFP8) return MX8_ERR_ARG;
@@ -735,7 +751,13 @@ extern "C" int mx8_gemm_grouped(const void* A, const void* A_sc, const void* B, 
     gr.rows_dev = static_cast<const int*>(num_rows);
     gr.group_rows = static_cast<const int*>(group_rows);
     gr.num_groups = num_groups;
-    return gemm::run<2>(A, A_sc, B, B_sc, C, M, N, K, c_dtype, 0, gr, static_cast<cudaStream_t>(stream));
+    int max_ctas = 0;
+    if (window) {
+        if (window->row_begin) gr.row_begin_dev = static_cast<const int*>(window->row_begin);
+        if (window->row_end) gr.rows_dev = static_cast<const int*>(window->row_end);
+        max_ctas = window->max_sms > 0 ? window->max_sms : 0;
+    }
+    return gemm::run<2>(A, A_sc, B, B_sc, C, M, N, K, c_dtype, max_ctas, gr, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int mx8_gemm(const void* A, const void* A_sc, const void* B, const void* B_sc, void* C, int M, int N, int K,

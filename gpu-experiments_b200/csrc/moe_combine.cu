@@ -20,18 +20,20 @@ struct CombineParams {
     const uint8_t* y;            // [rows][hidden] bf16
     const int* peer_rank;
     const int* peer_token_idx;
-    const int* num_tokens;       // device
+    const int* num_tokens;       // device: one past the last row
+    const int* row_begin;        // device: first row (row window of a minibatch), nullptr = 0
     int hidden;
     uint8_t* dst[16];            // every rank's combine buffer [tokens*topk][hidden] bf16
 };
 
 __global__ void __launch_bounds__(256) combine_kernel(CombineParams p) {
     const int rows = *p.num_tokens;
+    const int row0 = p.row_begin ? *p.row_begin : 0;
     const int lane = threadIdx.x & 31;
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int warps = (gridDim.x * blockDim.x) >> 5;
     const size_t row_bytes = static_cast<size_t>(p.hidden) * 2;
-    for (int r = warp; r < rows; r += warps) {
+    for (int r = row0 + warp; r < rows; r += warps) {
         const int pr = p.peer_rank[r];
         if (pr < 0) continue;
         const uint4* src = reinterpret_cast<const uint4*>(p.y + r * row_bytes);
@@ -125,6 +127,11 @@ __global__ void __launch_bounds__(256) bwd_prologue_kernel(const uint8_t* d_out,
 
 extern "C" int mx8_moe_combine(const void* y_routed, const void* peer_rank, const void* peer_token_idx, const void* num_tokens,
                                int hidden, void* const* combine_ptrs, int world, void* stream) {
+    return mx8_moe_combine_window(y_routed, peer_rank, peer_token_idx, num_tokens, hidden, combine_ptrs, world, nullptr, stream);
+}
+
+extern "C" int mx8_moe_combine_window(const void* y_routed, const void* peer_rank, const void* peer_token_idx, const void* num_tokens,
+                                      int hidden, void* const* combine_ptrs, int world, const mx8_window* window, void* stream) {
     using namespace mx8;
     if (!y_routed || !peer_rank || !peer_token_idx || !num_tokens || !combine_ptrs) return MX8_ERR_ARG;
     if (world <= 0 || world > 16) return MX8_ERR_ARG;
@@ -142,8 +149,13 @@ extern "C" int mx8_moe_combine(const void* y_routed, const void* peer_rank, cons
     p.peer_token_idx = static_cast<const int*>(peer_token_idx);
     p.num_tokens = static_cast<const int*>(num_tokens);
     p.hidden = hidden;
-    const int sms = sm_count();
+    int sms = sm_count();
     if (sms <= 0) return MX8_ERR_CUDA;
+    if (window) {
+        if (window->row_begin) p.row_begin = static_cast<const int*>(window->row_begin);
+        if (window->row_end) p.num_tokens = static_cast<const int*>(window->row_end);
+        if (window->max_sms > 0 && window->max_sms < sms) sms = window->max_sms;
+    }
     moe::combine_kernel<<<sms * 4, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {

@@ -372,3 +372,37 @@ extern "C" int mx8_moe_schedule_static(const void* topk_all, int world, int toke
     return mx8_moe_schedule(topk_all, world, tokens, topk, num_local_experts, capacity, rank, peer_rank, peer_token_idx,
                             num_tokens, tokens_per_expert, scratch, moe::STATIC_SCRATCH_INTS * sizeof(int), stream);
 }
+
+// ---------------------------------------------------------------------------------------------
+// Row bounds of `minibatches` groups of consecutive local experts: bounds[b] = rows before the first
+// expert of minibatch b (experts are split as evenly as the count allows), bounds[minibatches] = all
+// rows.  The windowed entry points take pointers into this array.
+namespace mx8 {
+namespace moe {
+__global__ void minibatch_bounds_kernel(const int* tokens_per_expert, int experts, int minibatches, int* bounds) {
+    if (threadIdx.x != 0) return;
+    int acc = 0, b = 0;
+    for (int e = 0; e <= experts; ++e) {
+        while (b <= minibatches && static_cast<long long>(b) * experts / minibatches == e) bounds[b++] = acc;
+        if (e < experts) acc += tokens_per_expert[e];
+    }
+}
+}  // namespace moe
+}  // namespace mx8
+
+extern "C" int mx8_moe_minibatch_bounds(const void* tokens_per_expert, int num_local_experts, int minibatches, void* bounds,
+                                        void* stream) {
+    using namespace mx8;
+    if (!tokens_per_expert || !bounds) return MX8_ERR_ARG;
+    if (num_local_experts <= 0 || minibatches <= 0 || minibatches > num_local_experts) return MX8_ERR_ARG;
+    int rc = check_device_sm100();
+    if (rc != MX8_OK) return rc;
+    moe::minibatch_bounds_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const int*>(tokens_per_expert),
+                                                                                num_local_experts, minibatches, static_cast<int*>(bounds));
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        note_cuda_error("minibatch bounds launch", cudaGetErrorString(e));
+        return MX8_ERR_CUDA;
+    }
+    return MX8_OK;
+}

@@ -45,6 +45,7 @@ struct Params {
     uint32_t min_byte8_2;// packed per half: smallest scale byte + 8 (rceil 88: amax/448 clamped to 1e-12; floor 0)
     // source modes other than a dense bf16 matrix
     const int* rows_dev;          // device: rows present (gather / SwiGLU); tiles beyond it are skipped
+    const int* row_begin_dev;     // device: first row to process (row window of a minibatch), nullptr = 0
     const int* peer_rank;         // gather: source rank per row, -1 = zero row
     const int* peer_token_idx;    // gather: token * topk + k on the source rank
     int topk;
@@ -126,7 +127,10 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
     __syncthreads();
 
     // this CTA's tiles: blockIdx.x, blockIdx.x + gridDim.x, ...; slab n = 4 * (tile ordinal) + quarter
-    const int tiles_r = p.rows_dev ? min(p.tiles_r, (*p.rows_dev + TILE - 1) / TILE) : p.tiles_r;
+    // row window: tile rows [tile0, tiles_r_end); tile coordinates are computed inside the window
+    const int tile0 = p.row_begin_dev ? *p.row_begin_dev / TILE : 0;
+    const int tiles_r_end = p.rows_dev ? min(p.tiles_r, (*p.rows_dev + TILE - 1) / TILE) : p.tiles_r;
+    const int tiles_r = max(tiles_r_end - tile0, 0);
     const int num_tiles = tiles_r * p.tiles_c;
     const int my_tiles = (num_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
     const int my_slabs = my_tiles * 4;
@@ -144,6 +148,7 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
                 const int t = static_cast<int>(blockIdx.x) + (n >> 2) * static_cast<int>(gridDim.x);
                 int tr, tc;
                 tile_coords(t, p, tiles_r, tr, tc);
+                tr += tile0;
                 const int row = tr * TILE + (n & 3) * SLAB_ROWS + pl;
                 const int pr = p.peer_rank[row];                 // issued before the wait: the look-up overlaps it
                 const int tok = p.peer_token_idx[row];
@@ -170,6 +175,7 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
                 const int t = static_cast<int>(blockIdx.x) + (n >> 2) * static_cast<int>(gridDim.x);
                 int tr, tc;
                 tile_coords(t, p, tiles_r, tr, tc);
+                tr += tile0;
                 const uint32_t dst = base + L::ring + slot * SLOT;
                 mbar_arrive_expect_tx(full0 + slot * 8, SLOT);
                 if constexpr (SRC == SRC_SWIGLU || SRC == SRC_SWIGLU_BWD) {
@@ -202,6 +208,7 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
         const int t = static_cast<int>(blockIdx.x) + (n >> 2) * static_cast<int>(gridDim.x);
         int tr, tc;
         tile_coords(t, p, tiles_r, tr, tc);
+                tr += tile0;
         if (!mbar_wait(full0 + slot * 8, ph, ab, DEV_TIMEOUT_FULL)) break;
 
         // SwiGLU backward can emit both gradients from one visit of the slot: two passes over the same
@@ -475,12 +482,27 @@ static void fill_common(Params& p, void* fp8, void* sc, void* sc_t, int rows, in
     p.min_byte8_2 = RCEIL_MIN_BYTE8_2;
 }
 
+// row window of a minibatch: rows [*row_begin, *row_end) on at most max_sms multiprocessors
+static void apply_window(Params& p, int& grid, const mx8_window* w) {
+    if (!w) return;
+    if (w->row_begin) p.row_begin_dev = static_cast<const int*>(w->row_begin);
+    if (w->row_end) p.rows_dev = static_cast<const int*>(w->row_end);
+    if (w->max_sms > 0 && w->max_sms < grid) grid = w->max_sms;
+}
+
 }  // namespace quant
 }  // namespace mx8
 
 extern "C" int mx8_moe_dispatch_quantize(const void* const* x_ptrs, int world, int hidden, int topk, const void* peer_rank,
                                          const void* peer_token_idx, const void* num_tokens, int capacity, void* fp8,
                                          void* sc, void* fp8_t, void* sc_t, void* stream) {
+    return mx8_moe_dispatch_quantize_window(x_ptrs, world, hidden, topk, peer_rank, peer_token_idx, num_tokens, capacity, fp8, sc,
+                                            fp8_t, sc_t, nullptr, stream);
+}
+
+extern "C" int mx8_moe_dispatch_quantize_window(const void* const* x_ptrs, int world, int hidden, int topk, const void* peer_rank,
+                                         const void* peer_token_idx, const void* num_tokens, int capacity, void* fp8,
+                                         void* sc, void* fp8_t, void* sc_t, const mx8_window* window, void* stream) {
     using namespace mx8;
     using namespace mx8::quant;
     if (!x_ptrs || !peer_rank || !peer_token_idx || !num_tokens || !fp8 || !sc || !fp8_t || !sc_t) return MX8_ERR_ARG;
@@ -506,12 +528,21 @@ extern "C" int mx8_moe_dispatch_quantize(const void* const* x_ptrs, int world, i
     if (grid <= 0) return MX8_ERR_CUDA;
     const int tiles = p.tiles_r * p.tiles_c;
     if (grid > tiles) grid = tiles;
+    apply_window(p, grid, window);
     return launch<8, 1, SRC_GATHER, true, true>(tm_t, tm_t, tm_t, tm_t, p, grid, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int mx8_swiglu_quantize(const void* gate_fp8, const void* gate_sc, const void* up_fp8, const void* up_sc,
                                    int rows, int cols, const void* num_rows, void* hidden_fp8, void* hidden_sc,
                                    void* hidden_fp8_t, void* hidden_sc_t, void* hidden_bf16, void* stream) {
+    return mx8_swiglu_quantize_window(gate_fp8, gate_sc, up_fp8, up_sc, rows, cols, num_rows, hidden_fp8, hidden_sc, hidden_fp8_t,
+                                      hidden_sc_t, hidden_bf16, nullptr, stream);
+}
+
+extern "C" int mx8_swiglu_quantize_window(const void* gate_fp8, const void* gate_sc, const void* up_fp8, const void* up_sc,
+                                          int rows, int cols, const void* num_rows, void* hidden_fp8, void* hidden_sc,
+                                          void* hidden_fp8_t, void* hidden_sc_t, void* hidden_bf16, const mx8_window* window,
+                                          void* stream) {
     using namespace mx8;
     using namespace mx8::quant;
     if (!gate_fp8 || !gate_sc || !up_fp8 || !up_sc || !hidden_fp8 || !hidden_sc || !hidden_fp8_t || !hidden_sc_t) return MX8_ERR_ARG;
@@ -540,6 +571,7 @@ extern "C" int mx8_swiglu_quantize(const void* gate_fp8, const void* gate_sc, co
     if (grid <= 0) return MX8_ERR_CUDA;
     const int tiles = p.tiles_r * p.tiles_c;
     if (grid > tiles) grid = tiles;
+    apply_window(p, grid, window);
     return launch<8, 1, SRC_SWIGLU, true, true>(tm_g, tm_u, tm_u, tm_t, p, grid, static_cast<cudaStream_t>(stream));
 }
 

@@ -13,6 +13,8 @@
 //   schedule(...), dispatch_mlp_swiglu_combine_fwd(...), fwd_epilogue(...)
 //                                                         blackwell-ultra/022-…-mxfp8-bw.cu:2996-3030 (forward, routed experts)
 // Errors raise RuntimeError (the reference prints and exits).
+#include <ATen/cuda/CUDAEvent.h>
+#include <c10/cuda/CUDACachingAllocator.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <c10/cuda/CUDAStream.h>
 #include <torch/extension.h>
@@ -177,14 +179,22 @@ at::Tensor bf16_transpose(const at::Tensor& x) {
     return out;
 }
 
+// two side streams per device for the transfer legs of the pipelined layer, taken from torch's pool once
+std::pair<c10::cuda::CUDAStream, c10::cuda::CUDAStream> side_streams(c10::DeviceIndex dev) {
+    static std::vector<std::optional<std::pair<c10::cuda::CUDAStream, c10::cuda::CUDAStream>>> cache(64);
+    auto& slot = cache[static_cast<size_t>(dev) & 63];
+    if (!slot.has_value()) slot.emplace(c10::cuda::getStreamFromPool(false, dev), c10::cuda::getStreamFromPool(false, dev));
+    return *slot;
+}
+
 std::vector<at::Tensor> dispatch_mlp_swiglu_combine_fwd(
     const at::Tensor& x, const std::vector<int64_t>& x_ptrs, const at::Tensor& combine_buffer,
     const std::vector<int64_t>& combine_buffer_ptrs, const std::optional<at::Tensor>& w_shared_gate, const at::Tensor& w_routed_gate,
     const at::Tensor& w_routed_gate_sc, const std::optional<at::Tensor>& w_shared_up, const at::Tensor& w_routed_up,
     const at::Tensor& w_routed_up_sc, const std::optional<at::Tensor>& w_shared_down, const at::Tensor& w_routed_down,
     const at::Tensor& w_routed_down_sc, const at::Tensor& schedule_peer_rank, const at::Tensor& schedule_peer_token_idx,
-    const at::Tensor& num_tokens, const at::Tensor& tokens_per_expert, int topk, int /*num_comm_sms*/, int /*macrobatch_size*/,
-    int /*minibatch_size*/) {
+    const at::Tensor& num_tokens, const at::Tensor& tokens_per_expert, int topk, int num_comm_sms, int /*macrobatch_size*/,
+    int minibatch_size) {
     TORCH_CHECK(w_routed_gate.dim() == 3 && w_routed_down.dim() == 3, "routed weights must be [E, rows, cols]");
     TORCH_CHECK(x_ptrs.size() == combine_buffer_ptrs.size() && !x_ptrs.empty() && x_ptrs.size() <= 16, "1..16 ranks");
     c10::cuda::CUDAGuard guard(x.device());
@@ -205,20 +215,86 @@ std::vector<at::Tensor> dispatch_mlp_swiglu_combine_fwd(
         cp[i] = reinterpret_cast<void*>(combine_buffer_ptrs[i]);
     }
     const int world = static_cast<int>(x_ptrs.size());
-    check(mx8_moe_dispatch_quantize(xp.data(), world, static_cast<int>(H), topk, iptr(schedule_peer_rank, "schedule_peer_rank"),
-                                    iptr(schedule_peer_token_idx, "schedule_peer_token_idx"), iptr(num_tokens, "num_tokens"),
-                                    static_cast<int>(cap), x_fp8.data_ptr(), x_sc.data_ptr(), x_fp8_t.data_ptr(), x_sc_t.data_ptr(), stream()),
-          "dispatch + quantize");
-    grouped(x_fp8, x_sc, w_routed_gate, w_routed_gate_sc, gate_fp8, gate_sc, num_tokens, tokens_per_expert);
-    grouped(x_fp8, x_sc, w_routed_up, w_routed_up_sc, up_fp8, up_sc, num_tokens, tokens_per_expert);
-    check(mx8_swiglu_quantize(gate_fp8.data_ptr(), gate_sc.data_ptr(), up_fp8.data_ptr(), up_sc.data_ptr(), static_cast<int>(cap),
-                              static_cast<int>(I), num_tokens.data_ptr(), h_fp8.data_ptr(), h_sc.data_ptr(), h_fp8_t.data_ptr(),
-                              h_sc_t.data_ptr(), nullptr, stream()),
-          "swiglu + quantize");
-    grouped(h_fp8, h_sc, w_routed_down, w_routed_down_sc, y_routed, at::Tensor(), num_tokens, tokens_per_expert);
-    check(mx8_moe_combine(y_routed.data_ptr(), schedule_peer_rank.data_ptr(), schedule_peer_token_idx.data_ptr(), num_tokens.data_ptr(),
-                          static_cast<int>(H), cp.data(), world, stream()),
-          "combine");
+    const int E = static_cast<int>(w_routed_gate.size(0));
+    int nb = 1;
+    if (num_comm_sms > 0 && minibatch_size > 0) nb = static_cast<int>(std::min<int64_t>(E, (cap + minibatch_size - 1) / minibatch_size));
+    if (nb > 1) {
+        // Minibatches of consecutive experts: dispatch of group b+1 (num_comm_sms multiprocessors, own stream) and
+        // combine of group b-1 (third stream) run beside the GEMMs of group b.  Same kernels on row windows, so the
+        // outputs are bit-identical to the single sequence below.
+        const c10::cuda::CUDAStream main = c10::cuda::getCurrentCUDAStream();
+        const auto [s_disp, s_comb] = side_streams(main.device_index());
+        at::Tensor bounds = at::empty({nb + 1}, schedule_peer_rank.options());
+        int sms = 0;
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, main.device_index());
+        const int math_sms = std::max(2, (sms - num_comm_sms) & ~1);
+        check(mx8_moe_minibatch_bounds(iptr(tokens_per_expert, "tokens_per_expert"), E, nb, bounds.data_ptr(), main.stream()), "minibatch bounds");
+        const int* bp = static_cast<const int*>(bounds.data_ptr());
+        at::cuda::CUDAEvent start;
+        start.record(main);
+        start.block(s_disp);
+        start.block(s_comb);
+        std::vector<at::cuda::CUDAEvent> disp_done(nb);
+        for (int b = 0; b < nb; ++b) {
+            const mx8_window w{bp + b, bp + b + 1, b == 0 ? 0 : num_comm_sms};
+            check(mx8_moe_dispatch_quantize_window(xp.data(), world, static_cast<int>(H), topk, iptr(schedule_peer_rank, "schedule_peer_rank"),
+                                                   iptr(schedule_peer_token_idx, "schedule_peer_token_idx"), iptr(num_tokens, "num_tokens"),
+                                                   static_cast<int>(cap), x_fp8.data_ptr(), x_sc.data_ptr(), x_fp8_t.data_ptr(),
+                                                   x_sc_t.data_ptr(), &w, s_disp.stream()),
+                  "dispatch + quantize (window)");
+            disp_done[b].record(s_disp);
+        }
+        auto gemm_w = [&](const at::Tensor& a, const at::Tensor& a_sc, const at::Tensor& wt, const at::Tensor& wt_sc, const at::Tensor& c,
+                          const at::Tensor& c_sc, const mx8_window& w) {
+            const bool q = c_sc.defined();
+            check(mx8_gemm_grouped_window(a.data_ptr(), a_sc.data_ptr(), dptr(wt, "w"), dptr(wt_sc, "w_sc"), c.data_ptr(),
+                                          q ? c_sc.data_ptr() : nullptr, static_cast<int>(a.size(0)), static_cast<int>(wt.size(1)),
+                                          static_cast<int>(a.size(1)), q ? MX8_C_MXFP8 : MX8_C_BF16, num_tokens.data_ptr(),
+                                          tokens_per_expert.data_ptr(), E, &w, main.stream()),
+                  "grouped gemm (window)");
+        };
+        for (int b = 0; b < nb; ++b) {
+            disp_done[b].block(main);
+            const mx8_window w{bp + b, bp + b + 1, b == nb - 1 ? 0 : math_sms};
+            gemm_w(x_fp8, x_sc, w_routed_gate, w_routed_gate_sc, gate_fp8, gate_sc, w);
+            gemm_w(x_fp8, x_sc, w_routed_up, w_routed_up_sc, up_fp8, up_sc, w);
+            check(mx8_swiglu_quantize_window(gate_fp8.data_ptr(), gate_sc.data_ptr(), up_fp8.data_ptr(), up_sc.data_ptr(), static_cast<int>(cap),
+                                             static_cast<int>(I), num_tokens.data_ptr(), h_fp8.data_ptr(), h_sc.data_ptr(), h_fp8_t.data_ptr(),
+                                             h_sc_t.data_ptr(), nullptr, &w, main.stream()),
+                  "swiglu + quantize (window)");
+            gemm_w(h_fp8, h_sc, w_routed_down, w_routed_down_sc, y_routed, at::Tensor(), w);
+            at::cuda::CUDAEvent math_done;
+            math_done.record(main);
+            math_done.block(s_comb);
+            const mx8_window wc{bp + b, bp + b + 1, 0};
+            check(mx8_moe_combine_window(y_routed.data_ptr(), schedule_peer_rank.data_ptr(), schedule_peer_token_idx.data_ptr(),
+                                         num_tokens.data_ptr(), static_cast<int>(H), cp.data(), world, &wc, s_comb.stream()),
+                  "combine (window)");
+        }
+        at::cuda::CUDAEvent done;
+        done.record(s_comb);
+        done.block(main);
+        // memory touched by the side streams must not be handed out again before their work has finished
+        for (const at::Tensor* t : {&x_fp8, &x_sc, &x_fp8_t, &x_sc_t, &y_routed, &bounds}) {
+            c10::cuda::CUDACachingAllocator::recordStream(t->storage().data_ptr(), s_disp);
+            c10::cuda::CUDACachingAllocator::recordStream(t->storage().data_ptr(), s_comb);
+        }
+    } else {
+        check(mx8_moe_dispatch_quantize(xp.data(), world, static_cast<int>(H), topk, iptr(schedule_peer_rank, "schedule_peer_rank"),
+                                        iptr(schedule_peer_token_idx, "schedule_peer_token_idx"), iptr(num_tokens, "num_tokens"),
+                                        static_cast<int>(cap), x_fp8.data_ptr(), x_sc.data_ptr(), x_fp8_t.data_ptr(), x_sc_t.data_ptr(), stream()),
+              "dispatch + quantize");
+        grouped(x_fp8, x_sc, w_routed_gate, w_routed_gate_sc, gate_fp8, gate_sc, num_tokens, tokens_per_expert);
+        grouped(x_fp8, x_sc, w_routed_up, w_routed_up_sc, up_fp8, up_sc, num_tokens, tokens_per_expert);
+        check(mx8_swiglu_quantize(gate_fp8.data_ptr(), gate_sc.data_ptr(), up_fp8.data_ptr(), up_sc.data_ptr(), static_cast<int>(cap),
+                                  static_cast<int>(I), num_tokens.data_ptr(), h_fp8.data_ptr(), h_sc.data_ptr(), h_fp8_t.data_ptr(),
+                                  h_sc_t.data_ptr(), nullptr, stream()),
+              "swiglu + quantize");
+        grouped(h_fp8, h_sc, w_routed_down, w_routed_down_sc, y_routed, at::Tensor(), num_tokens, tokens_per_expert);
+        check(mx8_moe_combine(y_routed.data_ptr(), schedule_peer_rank.data_ptr(), schedule_peer_token_idx.data_ptr(), num_tokens.data_ptr(),
+                              static_cast<int>(H), cp.data(), world, stream()),
+              "combine");
+    }
     // shared expert (bf16), when its weights are given
     at::Tensor gate_shared, up_shared, hidden_shared, y_shared;
     if (w_shared_gate.has_value() && w_shared_up.has_value() && w_shared_down.has_value()) {

@@ -12,6 +12,13 @@ C_BF16, C_F32, C_MXFP8 = 0, 1, 2
 
 # every symbol include/mx8.h declares, with its ctypes signature
 _vp, _i = ctypes.c_void_p, ctypes.c_int
+class Window(ctypes.Structure):
+    """mx8_window: rows [*row_begin, *row_end) (device ints) on at most max_sms multiprocessors."""
+    _fields_ = [("row_begin", ctypes.c_void_p), ("row_end", ctypes.c_void_p), ("max_sms", ctypes.c_int)]
+
+
+_wp = ctypes.POINTER(Window)
+
 SIGNATURES = {
     "mx8_quantize": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp]),
     "mx8_gemm": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
@@ -36,6 +43,11 @@ SIGNATURES = {
     "mx8_swiglu_bf16": (_i, [_vp, _vp, _vp, ctypes.c_longlong, _vp]),
     "mx8_swiglu_bwd_bf16": (_i, [_vp, _vp, _vp, _vp, _vp, ctypes.c_longlong, _vp]),
     "mx8_transpose_bf16": (_i, [_vp, _vp, _i, _i, _vp]),
+    "mx8_moe_minibatch_bounds": (_i, [_vp, _i, _i, _vp, _vp]),
+    "mx8_moe_dispatch_quantize_window": (_i, [ctypes.POINTER(_vp), _i, _i, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _wp, _vp]),
+    "mx8_gemm_grouped_window": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _i, _wp, _vp]),
+    "mx8_swiglu_quantize_window": (_i, [_vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _wp, _vp]),
+    "mx8_moe_combine_window": (_i, [_vp, _vp, _vp, _vp, _i, ctypes.POINTER(_vp), _i, _wp, _vp]),
     "mx8_quantize_host_workspace": (ctypes.c_size_t, [_i, _i]),
     "mx8_quantize_host": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _vp, ctypes.c_size_t, _vp]),
     "mx8_gemm_host_workspace": (ctypes.c_size_t, [_i, _i, _i, _i]),

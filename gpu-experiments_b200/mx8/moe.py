@@ -90,6 +90,98 @@ def fwd_epilogue(y_shared, combine_buffer, topk_weights):
     return out
 
 
+_side_streams = {}
+
+
+def _streams(dev):
+    """two side streams per device for the transfer legs of the pipelined layer (created once)"""
+    key = (dev.type, dev.index if dev.index is not None else torch.cuda.current_device())
+    if key not in _side_streams:
+        _side_streams[key] = (torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev))
+    return _side_streams[key]
+
+
+def _window(bounds, b, max_sms):
+    return _lib.Window(bounds.data_ptr() + 4 * b, bounds.data_ptr() + 4 * (b + 1), int(max_sms))
+
+
+def _routed_fwd_pipelined(x_ptrs, combine_buffer_ptrs, w_routed_gate, w_routed_gate_sc, w_routed_up, w_routed_up_sc,
+                          w_routed_down, w_routed_down_sc, schedule_peer_rank, schedule_peer_token_idx, num_tokens,
+                          tokens_per_expert, topk, num_comm_sms, minibatches):
+    """Routed experts in `minibatches` groups of consecutive local experts.  Dispatch of group b+1 (on
+    num_comm_sms multiprocessors, its own stream) and combine of group b-1 (a third stream; a plain copy
+    kernel that shares multiprocessors with the GEMMs) run beside the GEMMs of group b, which keep the
+    remaining multiprocessors.  Every kernel is the windowed form of the one the unsplit layer launches,
+    so all outputs are bit-identical to it.  The stream-and-event counterpart of the reference's
+    single-kernel task queue with communication SMs (blackwell-ultra/022-…-mxfp8-bw.cu:1738-2010)."""
+    lib = _lib.load()
+    E, I, H = w_routed_gate.shape
+    cap = schedule_peer_rank.numel()
+    dev = schedule_peer_rank.device
+    nb = minibatches
+    u8 = lambda *shape: torch.empty(*shape, dtype=torch.uint8, device=dev)
+    f8 = lambda *shape: torch.empty(*shape, dtype=torch.float8_e4m3fn, device=dev)
+    x_fp8, x_sc, x_fp8_t, x_sc_t = f8(cap, H), u8(cap // 128, H // 128, 32, 16), f8(H, cap), u8(H // 128, cap // 128, 32, 16)
+    gate_fp8, gate_sc, up_fp8, up_sc = f8(cap, I), u8(cap // 128, I // 128, 32, 16), f8(cap, I), u8(cap // 128, I // 128, 32, 16)
+    h_fp8, h_sc, h_fp8_t, h_sc_t = f8(cap, I), u8(cap // 128, I // 128, 32, 16), f8(I, cap), u8(I // 128, cap // 128, 32, 16)
+    y_routed = torch.empty(cap, H, dtype=torch.bfloat16, device=dev)
+    bounds = torch.empty(nb + 1, dtype=torch.int32, device=dev)
+    xp, cp = _ptr_array(x_ptrs), _ptr_array(combine_buffer_ptrs)
+    pr, pt, nt, tpe = (schedule_peer_rank.data_ptr(), schedule_peer_token_idx.data_ptr(), num_tokens.data_ptr(),
+                       tokens_per_expert.data_ptr())
+    wts = [(_chk(w, "w", _FP8), _chk(ws, "w_sc", _SC)) for w, ws in ((w_routed_gate, w_routed_gate_sc), (w_routed_up, w_routed_up_sc),
+                                                                      (w_routed_down, w_routed_down_sc))]
+    main = torch.cuda.current_stream(dev)
+    s_disp, s_comb = _streams(dev)
+    with torch.cuda.device(dev):
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        math_sms = max(2, (sms - num_comm_sms) & ~1)
+        _lib.check(lib.mx8_moe_minibatch_bounds(tpe, E, nb, bounds.data_ptr(), main.cuda_stream), "minibatch_bounds")
+        start = torch.cuda.Event()
+        start.record(main)
+        s_disp.wait_event(start)
+        s_comb.wait_event(start)
+        disp_done = []
+        for b in range(nb):
+            # the first group has the device to itself; later ones run beside the GEMMs
+            w = _window(bounds, b, 0 if b == 0 else num_comm_sms)
+            _lib.check(lib.mx8_moe_dispatch_quantize_window(xp, len(x_ptrs), H, topk, pr, pt, nt, cap, x_fp8.data_ptr(), x_sc.data_ptr(),
+                                                            x_fp8_t.data_ptr(), x_sc_t.data_ptr(), ctypes.byref(w), s_disp.cuda_stream),
+                       "dispatch_quantize (window)")
+            ev = torch.cuda.Event()
+            ev.record(s_disp)
+            disp_done.append(ev)
+        for b in range(nb):
+            main.wait_event(disp_done[b])
+            w = _window(bounds, b, 0 if b == nb - 1 else math_sms)
+            wr = ctypes.byref(w)
+            ms = main.cuda_stream
+            _lib.check(lib.mx8_gemm_grouped_window(x_fp8.data_ptr(), x_sc.data_ptr(), wts[0][0], wts[0][1], gate_fp8.data_ptr(),
+                                                   gate_sc.data_ptr(), cap, I, H, _lib.C_MXFP8, nt, tpe, E, wr, ms), "gate gemm (window)")
+            _lib.check(lib.mx8_gemm_grouped_window(x_fp8.data_ptr(), x_sc.data_ptr(), wts[1][0], wts[1][1], up_fp8.data_ptr(),
+                                                   up_sc.data_ptr(), cap, I, H, _lib.C_MXFP8, nt, tpe, E, wr, ms), "up gemm (window)")
+            _lib.check(lib.mx8_swiglu_quantize_window(gate_fp8.data_ptr(), gate_sc.data_ptr(), up_fp8.data_ptr(), up_sc.data_ptr(), cap, I, nt,
+                                                      h_fp8.data_ptr(), h_sc.data_ptr(), h_fp8_t.data_ptr(), h_sc_t.data_ptr(), None, wr, ms),
+                       "swiglu_quantize (window)")
+            _lib.check(lib.mx8_gemm_grouped_window(h_fp8.data_ptr(), h_sc.data_ptr(), wts[2][0], wts[2][1], y_routed.data_ptr(), None,
+                                                   cap, H, I, _lib.C_BF16, nt, tpe, E, wr, ms), "down gemm (window)")
+            ev = torch.cuda.Event()
+            ev.record(main)
+            s_comb.wait_event(ev)
+            wc = _window(bounds, b, 0)
+            _lib.check(lib.mx8_moe_combine_window(y_routed.data_ptr(), pr, pt, nt, H, cp, len(combine_buffer_ptrs), ctypes.byref(wc),
+                                                  s_comb.cuda_stream), "combine (window)")
+        done = torch.cuda.Event()
+        done.record(s_comb)
+        main.wait_event(done)
+    # the side streams used these tensors; tell the caching allocator so that it does not hand the
+    # memory out again before their work has finished
+    for t in (x_fp8, x_sc, x_fp8_t, x_sc_t, y_routed, bounds):
+        t.record_stream(s_disp)
+        t.record_stream(s_comb)
+    return x_fp8, x_sc, x_fp8_t, x_sc_t, gate_fp8, gate_sc, up_fp8, up_sc, h_fp8, h_sc, h_fp8_t, h_sc_t, y_routed
+
+
 def dispatch_mlp_swiglu_combine_fwd(x, x_ptrs, combine_buffer, combine_buffer_ptrs,
                                     w_shared_gate, w_routed_gate, w_routed_gate_sc,
                                     w_shared_up, w_routed_up, w_routed_up_sc,
@@ -101,15 +193,24 @@ def dispatch_mlp_swiglu_combine_fwd(x, x_ptrs, combine_buffer, combine_buffer_pt
       (x_fp8_t_routed, x_sc_t_routed, gate_shared, gate_fp8_routed, gate_sc_routed, up_shared,
        up_fp8_routed, up_sc_routed, hidden_shared, hidden_fp8_t_routed, hidden_sc_t_routed,
        y_shared, y_routed)
-    Routed buffers have schedule_capacity rows.  num_comm_sms / macrobatch_size / minibatch_size tune
-    the reference's single-kernel schedule and have no effect here.  The shared expert (bf16, outside
+    Routed buffers have schedule_capacity rows.  With num_comm_sms > 0 and minibatch_size > 0 the routed
+    experts run in ceil(capacity / minibatch_size) groups whose transfers overlap the other groups' GEMMs
+    (see _routed_fwd_pipelined); with the defaults the layer is one launch sequence on the current stream.
+    macrobatch_size (the backward's replay granularity in the reference) has no effect.  The shared expert (bf16, outside
     the MXFP8 path) runs on the bf16 form of the same GEMM kernel (gemm_bf16) when its weights are given, else
     those outputs are None.
     fuse_combine=True (an addition) lets the down projection's epilogue do the combine; y_routed is then None."""
     E, I, H = w_routed_gate.shape
     cap = schedule_peer_rank.numel()
-    x_fp8, x_sc, x_fp8_t, x_sc_t = dispatch_quantize(x_ptrs, H, topk, schedule_peer_rank, schedule_peer_token_idx, num_tokens, cap)
     dev = x.device
+    nb = min(E, -(-cap // minibatch_size)) if (minibatch_size > 0 and num_comm_sms > 0 and not fuse_combine) else 1
+    if nb > 1:
+        (x_fp8, x_sc, x_fp8_t, x_sc_t, gate_fp8, gate_sc, up_fp8, up_sc, h_fp8, h_sc, h_fp8_t, h_sc_t, y_routed) = _routed_fwd_pipelined(
+            x_ptrs, combine_buffer_ptrs, w_routed_gate, w_routed_gate_sc, w_routed_up, w_routed_up_sc, w_routed_down, w_routed_down_sc,
+            schedule_peer_rank, schedule_peer_token_idx, num_tokens, tokens_per_expert, topk, num_comm_sms, nb)
+        return (x_fp8_t, x_sc_t) + _shared_fwd(x, w_shared_gate, w_shared_up, w_shared_down, gate_fp8, gate_sc, up_fp8, up_sc,
+                                                h_fp8_t, h_sc_t, y_routed)
+    x_fp8, x_sc, x_fp8_t, x_sc_t = dispatch_quantize(x_ptrs, H, topk, schedule_peer_rank, schedule_peer_token_idx, num_tokens, cap)
     gate_fp8 = torch.empty(cap, I, dtype=torch.float8_e4m3fn, device=dev)
     gate_sc = torch.empty(cap // 128, I // 128, 32, 16, dtype=torch.uint8, device=dev)
     up_fp8 = torch.empty_like(gate_fp8)
@@ -131,15 +232,21 @@ def dispatch_mlp_swiglu_combine_fwd(x, x_ptrs, combine_buffer, combine_buffer_pt
         y_routed = torch.empty(cap, H, dtype=torch.bfloat16, device=dev)
         gemm_grouped(h_fp8, h_sc, w_routed_down, w_routed_down_sc, y_routed, None, num_tokens, tokens_per_expert)
         combine(y_routed, schedule_peer_rank, schedule_peer_token_idx, num_tokens, combine_buffer_ptrs)
+    return (x_fp8_t, x_sc_t) + _shared_fwd(x, w_shared_gate, w_shared_up, w_shared_down, gate_fp8, gate_sc, up_fp8, up_sc,
+                                            h_fp8_t, h_sc_t, y_routed)
+
+
+def _shared_fwd(x, w_shared_gate, w_shared_up, w_shared_down, gate_fp8, gate_sc, up_fp8, up_sc, h_fp8_t, h_sc_t, y_routed):
+    """shared (bf16) expert, when its weights are given; returns outputs 2..12 of the forward binding"""
     gate_shared = up_shared = hidden_shared = y_shared = None
     if w_shared_gate is not None:
-        Tl, Is = x.shape[0], w_shared_gate.shape[0]
+        dev = x.device
+        Tl, Is, H = x.shape[0], w_shared_gate.shape[0], x.shape[1]
         gate_shared = gemm_bf16(x, w_shared_gate, torch.empty(Tl, Is, dtype=torch.bfloat16, device=dev))
         up_shared = gemm_bf16(x, w_shared_up, torch.empty(Tl, Is, dtype=torch.bfloat16, device=dev))
         hidden_shared = swiglu_bf16(gate_shared, up_shared)
         y_shared = gemm_bf16(hidden_shared, w_shared_down, torch.empty(Tl, H, dtype=torch.bfloat16, device=dev))
-    return (x_fp8_t, x_sc_t, gate_shared, gate_fp8, gate_sc, up_shared, up_fp8, up_sc,
-            hidden_shared, h_fp8_t, h_sc_t, y_shared, y_routed)
+    return (gate_shared, gate_fp8, gate_sc, up_shared, up_fp8, up_sc, hidden_shared, h_fp8_t, h_sc_t, y_shared, y_routed)
 
 
 # ------------------------------------------------------------------------------------------------

@@ -237,6 +237,37 @@ MX8_API int mx8_swiglu_bwd_bf16(const void* d_hidden, const void* gate, const vo
                                 long long n, void* stream);
 MX8_API int mx8_transpose_bf16(const void* in, void* out, int rows, int cols, void* stream);
 
+/* Row windows: the MoE layer cut into minibatches of consecutive local experts, so that the transfer
+ * legs (dispatch, combine) of one minibatch can run beside the GEMMs of another on a second stream.
+ * The reference does this inside one kernel with a task queue and dedicated communication SMs
+ * (blackwell-ultra/022-…-mxfp8-bw.cu:1738-2010, arguments num_comm_sms / minibatch_size); here every
+ * kernel of the layer has a form that works on rows [*row_begin, *row_end) only, on at most max_sms
+ * multiprocessors, and the host orders the pieces with streams and events.
+ *   row_begin, row_end: device ints (multiples of 256), NULL = 0 / the entry point's own row count;
+ *   max_sms: 0 = the whole device.
+ * mx8_moe_minibatch_bounds fills bounds[0..minibatches] with the row at which each group of
+ * num_local_experts / minibatches consecutive experts starts (from tokens_per_expert). */
+typedef struct mx8_window {
+    const void* row_begin;
+    const void* row_end;
+    int max_sms;
+} mx8_window;
+MX8_API int mx8_moe_minibatch_bounds(const void* tokens_per_expert, int num_local_experts, int minibatches, void* bounds,
+                                     void* stream);
+MX8_API int mx8_moe_dispatch_quantize_window(const void* const* x_ptrs, int world, int hidden, int topk, const void* peer_rank,
+                                             const void* peer_token_idx, const void* num_tokens, int capacity, void* fp8,
+                                             void* sc, void* fp8_t, void* sc_t, const mx8_window* window, void* stream);
+MX8_API int mx8_gemm_grouped_window(const void* A, const void* A_sc, const void* B, const void* B_sc, void* C, void* C_sc,
+                                    int M, int N, int K, int c_dtype, const void* num_rows, const void* group_rows,
+                                    int num_groups, const mx8_window* window, void* stream);
+MX8_API int mx8_swiglu_quantize_window(const void* gate_fp8, const void* gate_sc, const void* up_fp8, const void* up_sc,
+                                       int rows, int cols, const void* num_rows, void* hidden_fp8, void* hidden_sc,
+                                       void* hidden_fp8_t, void* hidden_sc_t, void* hidden_bf16, const mx8_window* window,
+                                       void* stream);
+MX8_API int mx8_moe_combine_window(const void* y_routed, const void* peer_rank, const void* peer_token_idx,
+                                   const void* num_tokens, int hidden, void* const* combine_ptrs, int world,
+                                   const mx8_window* window, void* stream);
+
 /* Host-buffer forms.  The reference's harnesses keep tensors on the device and never move them
  * inside a timed region (blackwell-ultra/019-mxfp8-quantize.py:59-84,
  * blackwell/047-mxfp8-mma-2cta-MNK128-polished.py:127-176); a caller whose data lives in host

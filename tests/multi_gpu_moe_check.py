@@ -95,6 +95,21 @@ def main():
         touched[pts[r][:m][sel].long()] = True
     assert bool(touched.all())
     assert torch.equal(cb.cpu().view(torch.int16), cb_own.view(torch.int16)), "combine buffer differs from the expert outputs"
+    # ---- the same forward cut into minibatches on three streams: same bytes everywhere
+    cb_first = cb.clone()
+    dist.barrier()
+    cb.fill_(-3.0)
+    torch.cuda.synchronize()
+    dist.barrier()
+    outs2 = mx8.dispatch_mlp_swiglu_combine_fwd(x, x_ptrs, cb, cb_ptrs, None, wgq.to(dev), wgs.to(dev), None, wuq.to(dev),
+                                                wus.to(dev), None, wdq.to(dev), wds.to(dev), pr, pt, nt, tpe, k, 28, 0, 512)
+    assert mx8.device_status() == 0
+    torch.cuda.synchronize()
+    dist.barrier()
+    assert torch.equal(cb.view(torch.int16), cb_first.view(torch.int16)), "pipelined forward: combine buffer differs"
+    assert torch.equal(outs2[12][:n].view(torch.int16), outs[12][:n].view(torch.int16)), "pipelined forward: y_routed differs"
+    assert torch.equal(outs2[0][:, :n].view(torch.uint8), outs[0][:, :n].view(torch.uint8)), "pipelined forward: x_fp8_t differs"
+    assert torch.equal(outs2[9][:, :n].view(torch.uint8), outs[9][:, :n].view(torch.uint8)), "pipelined forward: hidden_fp8_t differs"
     # ---- backward over peer memory: prologue, barrier, fused backward, barrier, epilogue
     def weights_T(r):
         wg = torch.stack([O.make_input(I, H, seed=100 + 10 * r + e, std=H ** -0.5) for e in range(E)])

@@ -432,3 +432,39 @@ def test_schedule_both_forms_agree_with_oracle(W, T, E_local, k, rank):
     small = torch.empty(16, dtype=torch.uint8, device=DEV)
     assert lib.mx8_moe_schedule(dev_topk.data_ptr(), W, T, k, E_local, cap, rank, pr.data_ptr(), pt.data_ptr(), nt.data_ptr(),
                                 tpe.data_ptr(), small.data_ptr(), 16, None) == 7
+
+
+@pytest.mark.parametrize("E_local,minibatch", [(5, 512), (4, 256), (3, 100000)])
+def test_pipelined_forward_equals_single_sequence(E_local, minibatch):
+    # minibatches of experts on three streams must leave exactly the bytes of the one-stream layer:
+    # every routed output and both ranks' combine buffers
+    W, T, H, I, k, rank = 2, 384, 512, 256, 4, 1
+    topk_all, _ = make_topk(W, T, W * E_local, k, seed=191)
+    cap = ((W * T * k) // 256 + E_local) * 256
+    pr, pt, nt, tpe = mx8.schedule(topk_all.to(DEV), E_local, cap, rank)
+    xs = [O.make_input(T, H, seed=195 + r).to(DEV) for r in range(W)]
+    ws = []
+    for seed, (r, c) in ((10, (I, H)), (20, (I, H)), (30, (H, I))):
+        wt = torch.stack([O.make_input(r, c, seed=seed + e, std=c ** -0.5) for e in range(E_local)])
+        ws.append(mx8.mxfp8_quantize(wt.to(DEV), True, False)[:2])
+    results = []
+    for comm_sms, mb in ((0, 0), (28, minibatch)):
+        bufs = [torch.full((T * k, H), -1.0, dtype=torch.bfloat16, device=DEV) for _ in range(W)]
+        outs = mx8.dispatch_mlp_swiglu_combine_fwd(xs[rank], [t.data_ptr() for t in xs], bufs[rank], [b.data_ptr() for b in bufs],
+                                                   None, ws[0][0], ws[0][1], None, ws[1][0], ws[1][1], None, ws[2][0], ws[2][1],
+                                                   pr, pt, nt, tpe, k, comm_sms, 0, mb)
+        assert mx8.device_status() == 0
+        results.append((outs, [b.cpu() for b in bufs]))
+    n = int(nt)
+    (o1, b1), (o2, b2) = results
+    for a, b in zip(b1, b2):
+        assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+    for i in (3, 6):            # gate / up bytes, rows
+        assert torch.equal(o1[i][:n].view(torch.uint8), o2[i][:n].view(torch.uint8)), i
+    for i in (4, 7):            # their scale tiles
+        assert torch.equal(o1[i][:n // 128], o2[i][:n // 128]), i
+    for i in (0, 9):            # transposed activations
+        assert torch.equal(o1[i][:, :n].view(torch.uint8), o2[i][:, :n].view(torch.uint8)), i
+    for i in (1, 10):
+        assert torch.equal(o1[i][:, :n // 128], o2[i][:, :n // 128]), i
+    assert torch.equal(o1[12][:n].view(torch.int16), o2[12][:n].view(torch.int16))

@@ -190,3 +190,34 @@ def test_shared_expert_through_both_hosts(C):
     ref = MO.shared_mlp_bwd_ref(d_out, x_cpu, fc[2].cpu(), fc[5].cpu(), fc[8].cpu(), sg, su, sd)
     for i, want in ((0, ref[0]), (2, ref[1]), (5, ref[2]), (8, ref[3]), (12, ref[4]), (14, ref[5]), (16, ref[6])):
         assert O.rel_frobenius(bc[i].cpu().float(), want.float()) < 1e-2, i
+
+
+def test_pipelined_forward_through_the_cpp_module(C):
+    # minibatches on three streams (num_comm_sms, minibatch_size as in the reference's call): same bytes as the
+    # one-stream sequence, from the C++ module and from the ctypes host
+    import mx8
+    from oracle import moe_oracle as MO
+    T, H, I, k, E = 384, 512, 256, 4, 5
+    g = torch.Generator().manual_seed(24)
+    ids, _ = MO.route(torch.randn(T, E, generator=g), k)
+    x = O.make_input(T, H, seed=26).to(DEV)
+    mk = lambda r, c, sd: torch.stack([O.make_input(r, c, seed=sd + e, std=c ** -0.5) for e in range(E)]).to(DEV)
+    fw = [C.mxfp8_quantize(t, True, False)[:2] for t in (mk(I, H, 10), mk(I, H, 20), mk(H, I, 30))]
+    cap = ((T * k) // 256 + E) * 256
+    pr, pt, nt, tpe = C.schedule(ids.view(1, T, k).to(DEV), E, cap, 0)
+    n = int(nt)
+    res = []
+    for host, knobs in ((C, (0, 0, 0)), (C, (28, 0, 512)), (mx8, (28, 0, 512))):
+        cb = torch.full((T * k, H), -2.0, dtype=torch.bfloat16, device=DEV)
+        f = host.dispatch_mlp_swiglu_combine_fwd(x, [x.data_ptr()], cb, [cb.data_ptr()], None, *fw[0], None, *fw[1], None, *fw[2],
+                                                 pr, pt, nt, tpe, k, *knobs)
+        torch.cuda.synchronize()
+        res.append((f, cb))
+    assert C.device_status() == 0
+    for f, cb in res[1:]:
+        assert torch.equal(cb.view(torch.int16), res[0][1].view(torch.int16))
+        assert torch.equal(f[12][:n].view(torch.int16), res[0][0][12][:n].view(torch.int16))
+        for i in (3, 6):
+            assert torch.equal(f[i][:n].view(torch.uint8), res[0][0][i][:n].view(torch.uint8))
+        for i in (0, 9):
+            assert torch.equal(f[i][:, :n].view(torch.uint8), res[0][0][i][:, :n].view(torch.uint8))
