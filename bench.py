@@ -631,15 +631,24 @@ def bench_moe(args, world, rank, local, peaks, with_cpu=False):
                 dist.barrier()
             mx8.dispatch_mlp_swiglu_combine_bwd(None, d_cb, d_cb_ptrs, d_xb, d_xb_ptrs, None, wgT, wgTs, None, wuT, wuTs, None, wdT, wdTs,
                                                 f[0], f[1], None, f[3], f[4], None, f[6], f[7], None, f[9], f[10], x, x_ptrs,
-                                                wg, wgs, wu, wus, pr, pt, nt, tpe, k)
+                                                wg, wgs, wu, wus, pr, pt, nt, tpe, k, pipe[0], 0, pipe[1])
             if world > 1:
                 dist.barrier()
             return mx8.bwd_epilogue_routed(None, d_xb, k)
 
         for i in range(2):
             bstep(i)
-        bms = timed(bstep, steps, world) / steps
+        bms_single = timed(bstep, steps, world) / steps
         mx8.device_status()
+        pipe[:] = [comm_sms, minibatch]
+        for i in range(2):
+            bstep(i)
+        bms_pipe = timed(bstep, steps, world) / steps
+        mx8.device_status()
+        pipe[:] = [0, 0]
+        bms = min(bms_single, bms_pipe)
+        pipeline["backward_ms_per_step"] = bms_pipe
+        pipeline["backward_single_sequence_ms_per_step"] = bms_single
         bwd = {"ms_per_step": bms, "value": 12.0 * (32768 * k) * H * I / (bms * 1e-3) / 1e12, "unit": "TFLOP/s",
                "flops": "12 * routed rows * hidden * intermediate"}
     flops_total = 6.0 * (32768 * k) * H * I

@@ -828,6 +828,14 @@ extern "C" int mx8_debug_set_gemm_ablation(int flags) {
 extern "C" int mx8_gemm_grouped_dual(const void* A1, const void* A1_sc, const void* B1, const void* B1_sc, const void* A2,
                                      const void* A2_sc, const void* B2, const void* B2_sc, void* C, int M, int N, int K1, int K2,
                                      const void* num_rows, const void* group_rows, int num_groups, void* stream) {
+    return mx8_gemm_grouped_dual_window(A1, A1_sc, B1, B1_sc, A2, A2_sc, B2, B2_sc, C, M, N, K1, K2, num_rows, group_rows, num_groups,
+                                        nullptr, stream);
+}
+
+extern "C" int mx8_gemm_grouped_dual_window(const void* A1, const void* A1_sc, const void* B1, const void* B1_sc, const void* A2,
+                                            const void* A2_sc, const void* B2, const void* B2_sc, void* C, int M, int N, int K1,
+                                            int K2, const void* num_rows, const void* group_rows, int num_groups,
+                                            const mx8_window* window, void* stream) {
     using namespace mx8;
     if (!A1 || !A1_sc || !B1 || !B1_sc || !A2 || !A2_sc || !B2 || !B2_sc || !C) return MX8_ERR_ARG;
     if (num_groups < 0 || (num_groups > 0 && !group_rows)) return MX8_ERR_ARG;
@@ -846,7 +854,13 @@ extern "C" int mx8_gemm_grouped_dual(const void* A1, const void* A1_sc, const vo
     gr.group_rows = static_cast<const int*>(group_rows);
     gr.num_groups = num_groups;
     gr.A2 = A2; gr.A2_sc = A2_sc; gr.B2 = B2; gr.B2_sc = B2_sc; gr.K2 = K2;
-    return gemm::run<2>(A1, A1_sc, B1, B1_sc, C, M, N, K1, MX8_C_BF16, 0, gr, static_cast<cudaStream_t>(stream));
+    int max_ctas = 0;
+    if (window) {
+        if (window->row_begin) gr.row_begin_dev = static_cast<const int*>(window->row_begin);
+        if (window->row_end) gr.rows_dev = static_cast<const int*>(window->row_end);
+        max_ctas = window->max_sms > 0 ? window->max_sms : 0;
+    }
+    return gemm::run<2>(A1, A1_sc, B1, B1_sc, C, M, N, K1, MX8_C_BF16, max_ctas, gr, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int mx8_gemm_wgrad(const void* A_t, const void* A_t_sc, const void* B_t, const void* B_t_sc, void* C, int M, int N,

@@ -618,6 +618,15 @@ extern "C" int mx8_swiglu_bwd_quantize_both(const void* gate_fp8, const void* ga
                                             const void* d_hidden, int rows, int cols, const void* num_rows,
                                             void* d_gate_fp8, void* d_gate_sc, void* d_gate_fp8_t, void* d_gate_sc_t,
                                             void* d_up_fp8, void* d_up_sc, void* d_up_fp8_t, void* d_up_sc_t, void* stream) {
+    return mx8_swiglu_bwd_quantize_both_window(gate_fp8, gate_sc, up_fp8, up_sc, d_hidden, rows, cols, num_rows, d_gate_fp8, d_gate_sc,
+                                               d_gate_fp8_t, d_gate_sc_t, d_up_fp8, d_up_sc, d_up_fp8_t, d_up_sc_t, nullptr, stream);
+}
+
+extern "C" int mx8_swiglu_bwd_quantize_both_window(const void* gate_fp8, const void* gate_sc, const void* up_fp8, const void* up_sc,
+                                                   const void* d_hidden, int rows, int cols, const void* num_rows,
+                                                   void* d_gate_fp8, void* d_gate_sc, void* d_gate_fp8_t, void* d_gate_sc_t,
+                                                   void* d_up_fp8, void* d_up_sc, void* d_up_fp8_t, void* d_up_sc_t,
+                                                   const mx8_window* window, void* stream) {
     using namespace mx8;
     using namespace mx8::quant;
     const void* const all[] = {gate_fp8, gate_sc, up_fp8, up_sc, d_hidden, d_gate_fp8, d_gate_sc, d_gate_fp8_t, d_gate_sc_t,
@@ -654,5 +663,6 @@ extern "C" int mx8_swiglu_bwd_quantize_both(const void* gate_fp8, const void* ga
     if (grid <= 0) return MX8_ERR_CUDA;
     const int tiles = p.tiles_r * p.tiles_c;
     if (grid > tiles) grid = tiles;
+    apply_window(p, grid, window);
     return launch<8, 1, SRC_SWIGLU_BWD, true, true>(tm_g, tm_u, tm_d, tm_t, p, grid, static_cast<cudaStream_t>(stream), &tm_t2);
 }

@@ -360,7 +360,7 @@ std::vector<at::Tensor> dispatch_mlp_swiglu_combine_bwd(
     const at::Tensor& hidden_sc_t_routed, const OptT& x_buffer, const std::vector<int64_t>& /*x_buffer_ptrs*/,
     const OptT& /*w_routed_gate*/, const OptT& /*w_routed_gate_sc*/, const OptT& /*w_routed_up*/, const OptT& /*w_routed_up_sc*/,
     const at::Tensor& schedule_peer_rank, const at::Tensor& schedule_peer_token_idx, const at::Tensor& num_tokens,
-    const at::Tensor& tokens_per_expert, int /*topk*/, int /*num_comm_sms*/, int /*macrobatch_size*/, int /*minibatch_size*/) {
+    const at::Tensor& tokens_per_expert, int /*topk*/, int num_comm_sms, int /*macrobatch_size*/, int minibatch_size) {
     TORCH_CHECK(w_routed_gate_T.dim() == 3, "transposed routed weights must be [E, H, I]");
     TORCH_CHECK(!d_combine_buffer_ptrs.empty() && d_combine_buffer_ptrs.size() == d_x_routed_buffer_ptrs.size() &&
                 d_combine_buffer_ptrs.size() <= 16, "1..16 ranks");
@@ -385,25 +385,72 @@ std::vector<at::Tensor> dispatch_mlp_swiglu_combine_bwd(
         src[i] = reinterpret_cast<const void*>(d_combine_buffer_ptrs[i]);
         dst[i] = reinterpret_cast<void*>(d_x_routed_buffer_ptrs[i]);
     }
-    // gradient rows of the routed outputs: one row per (token, k) pair, hence topk = 1 for the index
-    check(mx8_moe_dispatch_quantize(src.data(), world, static_cast<int>(H), 1, iptr(schedule_peer_rank, "schedule_peer_rank"),
-                                    iptr(schedule_peer_token_idx, "schedule_peer_token_idx"), iptr(num_tokens, "num_tokens"),
-                                    static_cast<int>(cap), d_y_fp8.data_ptr(), d_y_sc.data_ptr(), d_y_fp8_t.data_ptr(), d_y_sc_t.data_ptr(), stream()),
-          "gradient dispatch + quantize");
-    grouped(d_y_fp8, d_y_sc, w_routed_down_T, w_routed_down_T_sc, d_hidden, at::Tensor(), num_tokens, tokens_per_expert);
-    check(mx8_swiglu_bwd_quantize_both(gate_fp8_routed.data_ptr(), gate_sc_routed.data_ptr(), up_fp8_routed.data_ptr(), up_sc_routed.data_ptr(),
-                                       d_hidden.data_ptr(), static_cast<int>(cap), static_cast<int>(I), num_tokens.data_ptr(),
-                                       d_gate_fp8.data_ptr(), d_gate_sc.data_ptr(), d_gate_fp8_t.data_ptr(), d_gate_sc_t.data_ptr(),
-                                       d_up_fp8.data_ptr(), d_up_sc.data_ptr(), d_up_fp8_t.data_ptr(), d_up_sc_t.data_ptr(), stream()),
-          "swiglu backward + quantize");
-    check(mx8_gemm_grouped_dual(d_gate_fp8.data_ptr(), d_gate_sc.data_ptr(), w_routed_gate_T.data_ptr(), w_routed_gate_T_sc.data_ptr(),
-                                d_up_fp8.data_ptr(), d_up_sc.data_ptr(), w_routed_up_T.data_ptr(), w_routed_up_T_sc.data_ptr(),
-                                d_x_routed.data_ptr(), static_cast<int>(cap), static_cast<int>(H), static_cast<int>(I), static_cast<int>(I),
-                                num_tokens.data_ptr(), tokens_per_expert.data_ptr(), static_cast<int>(E), stream()),
-          "data-gradient gemm");
-    check(mx8_moe_combine(d_x_routed.data_ptr(), schedule_peer_rank.data_ptr(), schedule_peer_token_idx.data_ptr(), num_tokens.data_ptr(),
-                          static_cast<int>(H), dst.data(), world, stream()),
-          "gradient combine");
+    // With num_comm_sms and minibatch_size set, the experts are cut into minibatches: gradient dispatch of group b+1
+    // (own stream, num_comm_sms multiprocessors) and gradient combine of group b-1 (third stream) run beside the data-
+    // gradient GEMMs of group b; otherwise everything is one sequence on the current stream.  Same kernels, same bytes.
+    int nb = 1;
+    if (num_comm_sms > 0 && minibatch_size > 0) nb = static_cast<int>(std::min<int64_t>(E, (cap + minibatch_size - 1) / minibatch_size));
+    const bool pipe = nb > 1;
+    const c10::cuda::CUDAStream main = c10::cuda::getCurrentCUDAStream();
+    c10::cuda::CUDAStream s_disp = main, s_comb = main;
+    at::Tensor bounds;
+    const int* bp = nullptr;
+    int math_sms = 0;
+    if (pipe) {
+        std::tie(s_disp, s_comb) = side_streams(main.device_index());
+        bounds = at::empty({nb + 1}, schedule_peer_rank.options());
+        bp = static_cast<const int*>(bounds.data_ptr());
+        int sms = 0;
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, main.device_index());
+        math_sms = std::max(2, (sms - num_comm_sms) & ~1);
+        check(mx8_moe_minibatch_bounds(iptr(tokens_per_expert, "tokens_per_expert"), static_cast<int>(E), nb, bounds.data_ptr(), main.stream()),
+              "minibatch bounds");
+        at::cuda::CUDAEvent start;
+        start.record(main);
+        start.block(s_disp);
+        start.block(s_comb);
+    }
+    std::vector<at::cuda::CUDAEvent> disp_done(nb);
+    for (int b = 0; b < nb; ++b) {
+        const mx8_window w{pipe ? bp + b : nullptr, pipe ? bp + b + 1 : nullptr, (pipe && b > 0) ? num_comm_sms : 0};
+        // gradient rows of the routed outputs: one row per (token, k) pair, hence topk = 1 for the index
+        check(mx8_moe_dispatch_quantize_window(src.data(), world, static_cast<int>(H), 1, iptr(schedule_peer_rank, "schedule_peer_rank"),
+                                               iptr(schedule_peer_token_idx, "schedule_peer_token_idx"), iptr(num_tokens, "num_tokens"),
+                                               static_cast<int>(cap), d_y_fp8.data_ptr(), d_y_sc.data_ptr(), d_y_fp8_t.data_ptr(),
+                                               d_y_sc_t.data_ptr(), &w, s_disp.stream()),
+              "gradient dispatch + quantize");
+        if (pipe) disp_done[b].record(s_disp);
+    }
+    for (int b = 0; b < nb; ++b) {
+        if (pipe) disp_done[b].block(main);
+        const mx8_window w{pipe ? bp + b : nullptr, pipe ? bp + b + 1 : nullptr, (pipe && b < nb - 1) ? math_sms : 0};
+        check(mx8_gemm_grouped_window(d_y_fp8.data_ptr(), d_y_sc.data_ptr(), dptr(w_routed_down_T, "w_routed_down_T"),
+                                      dptr(w_routed_down_T_sc, "w_routed_down_T_sc"), d_hidden.data_ptr(), nullptr, static_cast<int>(cap),
+                                      static_cast<int>(I), static_cast<int>(H), MX8_C_BF16, num_tokens.data_ptr(), tokens_per_expert.data_ptr(),
+                                      static_cast<int>(E), &w, main.stream()),
+              "d_hidden gemm");
+        check(mx8_swiglu_bwd_quantize_both_window(gate_fp8_routed.data_ptr(), gate_sc_routed.data_ptr(), up_fp8_routed.data_ptr(),
+                                                  up_sc_routed.data_ptr(), d_hidden.data_ptr(), static_cast<int>(cap), static_cast<int>(I),
+                                                  num_tokens.data_ptr(), d_gate_fp8.data_ptr(), d_gate_sc.data_ptr(), d_gate_fp8_t.data_ptr(),
+                                                  d_gate_sc_t.data_ptr(), d_up_fp8.data_ptr(), d_up_sc.data_ptr(), d_up_fp8_t.data_ptr(),
+                                                  d_up_sc_t.data_ptr(), &w, main.stream()),
+              "swiglu backward + quantize");
+        check(mx8_gemm_grouped_dual_window(d_gate_fp8.data_ptr(), d_gate_sc.data_ptr(), w_routed_gate_T.data_ptr(), w_routed_gate_T_sc.data_ptr(),
+                                           d_up_fp8.data_ptr(), d_up_sc.data_ptr(), w_routed_up_T.data_ptr(), w_routed_up_T_sc.data_ptr(),
+                                           d_x_routed.data_ptr(), static_cast<int>(cap), static_cast<int>(H), static_cast<int>(I),
+                                           static_cast<int>(I), num_tokens.data_ptr(), tokens_per_expert.data_ptr(), static_cast<int>(E), &w,
+                                           main.stream()),
+              "data-gradient gemm");
+        if (pipe) {
+            at::cuda::CUDAEvent math_done;
+            math_done.record(main);
+            math_done.block(s_comb);
+        }
+        const mx8_window wc{pipe ? bp + b : nullptr, pipe ? bp + b + 1 : nullptr, 0};
+        check(mx8_moe_combine_window(d_x_routed.data_ptr(), schedule_peer_rank.data_ptr(), schedule_peer_token_idx.data_ptr(),
+                                     num_tokens.data_ptr(), static_cast<int>(H), dst.data(), world, &wc, s_comb.stream()),
+              "gradient combine");
+    }
     auto wgrad = [&](const at::Tensor& at_, const at::Tensor& ats, const at::Tensor& bt, const at::Tensor& bts, at::Tensor& c) {
         check(mx8_gemm_wgrad(at_.data_ptr(), ats.data_ptr(), bt.data_ptr(), bts.data_ptr(), c.data_ptr(), static_cast<int>(at_.size(0)),
                              static_cast<int>(bt.size(0)), static_cast<int>(cap), tokens_per_expert.data_ptr(), static_cast<int>(E), stream()),
@@ -412,6 +459,15 @@ std::vector<at::Tensor> dispatch_mlp_swiglu_combine_bwd(
     wgrad(d_gate_fp8_t, d_gate_sc_t, x_fp8_t_routed, x_sc_t_routed, d_w_gate);
     wgrad(d_up_fp8_t, d_up_sc_t, x_fp8_t_routed, x_sc_t_routed, d_w_up);
     wgrad(d_y_fp8_t, d_y_sc_t, hidden_fp8_t_routed, hidden_sc_t_routed, d_w_down);
+    if (pipe) {
+        at::cuda::CUDAEvent done;                 // the last gradient combine ran beside the weight gradients
+        done.record(s_comb);
+        done.block(main);
+        for (const at::Tensor* t : {&d_y_fp8, &d_y_sc, &d_y_fp8_t, &d_y_sc_t, &d_x_routed, &bounds}) {
+            c10::cuda::CUDACachingAllocator::recordStream(t->storage().data_ptr(), s_disp);
+            c10::cuda::CUDACachingAllocator::recordStream(t->storage().data_ptr(), s_comb);
+        }
+    }
     // shared expert (bf16), only when its tensors are given
     at::Tensor d_x_shared, d_gate_shared, d_up_shared, d_hidden_shared, d_w_sg, d_w_su, d_w_sd;
     if (d_y_shared && w_shared_gate_T && w_shared_up_T && w_shared_down_T && gate_shared && up_shared && hidden_shared && x_buffer) {

@@ -47,6 +47,8 @@ SIGNATURES = {
     "mx8_moe_dispatch_quantize_window": (_i, [ctypes.POINTER(_vp), _i, _i, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _wp, _vp]),
     "mx8_gemm_grouped_window": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _i, _wp, _vp]),
     "mx8_swiglu_quantize_window": (_i, [_vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _wp, _vp]),
+    "mx8_swiglu_bwd_quantize_both_window": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp] + [_vp] * 8 + [_wp, _vp]),
+    "mx8_gemm_grouped_dual_window": (_i, [_vp] * 9 + [_i, _i, _i, _i, _vp, _vp, _i, _wp, _vp]),
     "mx8_moe_combine_window": (_i, [_vp, _vp, _vp, _vp, _i, ctypes.POINTER(_vp), _i, _wp, _vp]),
     "mx8_quantize_host_workspace": (ctypes.c_size_t, [_i, _i]),
     "mx8_quantize_host": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _vp, ctypes.c_size_t, _vp]),

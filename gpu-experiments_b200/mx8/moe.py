@@ -333,6 +333,79 @@ def bwd_epilogue_routed(d_x_shared, d_x_routed_buffer, topk):
     return d_x
 
 
+def _routed_bwd_pipelined(d_combine_buffer_ptrs, d_x_routed_buffer_ptrs, w_routed_gate_T, w_routed_gate_T_sc, w_routed_up_T,
+                          w_routed_up_T_sc, w_routed_down_T, w_routed_down_T_sc, gate_fp8_routed, gate_sc_routed, up_fp8_routed,
+                          up_sc_routed, schedule_peer_rank, schedule_peer_token_idx, num_tokens, tokens_per_expert,
+                          num_comm_sms, minibatches):
+    """Gradient dispatch, data-gradient GEMMs, SwiGLU backward and gradient combine in minibatches of
+    experts on three streams, like _routed_fwd_pipelined; the weight-gradient GEMMs follow unsplit.
+    Returns the tensors of the one-stream sequence, bit-identical to it."""
+    lib = _lib.load()
+    E, H, I = w_routed_gate_T.shape
+    cap = schedule_peer_rank.numel()
+    dev = schedule_peer_rank.device
+    nb = minibatches
+    u8 = lambda *shape: torch.empty(*shape, dtype=torch.uint8, device=dev)
+    f8 = lambda *shape: torch.empty(*shape, dtype=torch.float8_e4m3fn, device=dev)
+    quad = lambda r, c: (f8(r, c), u8(r // 128, c // 128, 32, 16), f8(c, r), u8(c // 128, r // 128, 32, 16))
+    d_y = quad(cap, H)
+    d_gate, d_up = quad(cap, I), quad(cap, I)
+    d_hidden = torch.empty(cap, I, dtype=torch.bfloat16, device=dev)
+    d_x_routed = torch.empty(cap, H, dtype=torch.bfloat16, device=dev)
+    bounds = torch.empty(nb + 1, dtype=torch.int32, device=dev)
+    src, dst = _ptr_array(d_combine_buffer_ptrs), _ptr_array(d_x_routed_buffer_ptrs)
+    pr, pt, nt, tpe = (schedule_peer_rank.data_ptr(), schedule_peer_token_idx.data_ptr(), num_tokens.data_ptr(),
+                       tokens_per_expert.data_ptr())
+    wts = [(_chk(w, "w", _FP8), _chk(ws, "w_sc", _SC)) for w, ws in ((w_routed_gate_T, w_routed_gate_T_sc), (w_routed_up_T, w_routed_up_T_sc),
+                                                                      (w_routed_down_T, w_routed_down_T_sc))]
+    main = torch.cuda.current_stream(dev)
+    s_disp, s_comb = _streams(dev)
+    with torch.cuda.device(dev):
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        math_sms = max(2, (sms - num_comm_sms) & ~1)
+        _lib.check(lib.mx8_moe_minibatch_bounds(tpe, E, nb, bounds.data_ptr(), main.cuda_stream), "minibatch_bounds")
+        start = torch.cuda.Event()
+        start.record(main)
+        s_disp.wait_event(start)
+        s_comb.wait_event(start)
+        disp_done = []
+        for b in range(nb):
+            w = _window(bounds, b, 0 if b == 0 else num_comm_sms)
+            # one gradient row per (token, k) pair, hence topk = 1 for the index
+            _lib.check(lib.mx8_moe_dispatch_quantize_window(src, len(d_combine_buffer_ptrs), H, 1, pr, pt, nt, cap, d_y[0].data_ptr(),
+                                                            d_y[1].data_ptr(), d_y[2].data_ptr(), d_y[3].data_ptr(), ctypes.byref(w),
+                                                            s_disp.cuda_stream), "gradient dispatch (window)")
+            ev = torch.cuda.Event()
+            ev.record(s_disp)
+            disp_done.append(ev)
+        for b in range(nb):
+            main.wait_event(disp_done[b])
+            # the weight-gradient GEMMs follow the last group, so no group has the whole device for its data gradients
+            w = _window(bounds, b, math_sms if b < nb - 1 else 0)
+            wr, ms = ctypes.byref(w), main.cuda_stream
+            _lib.check(lib.mx8_gemm_grouped_window(d_y[0].data_ptr(), d_y[1].data_ptr(), wts[2][0], wts[2][1], d_hidden.data_ptr(), None,
+                                                   cap, I, H, _lib.C_BF16, nt, tpe, E, wr, ms), "d_hidden gemm (window)")
+            _lib.check(lib.mx8_swiglu_bwd_quantize_both_window(
+                _chk(gate_fp8_routed, "gate_fp8", _FP8), _chk(gate_sc_routed, "gate_sc", _SC), _chk(up_fp8_routed, "up_fp8", _FP8),
+                _chk(up_sc_routed, "up_sc", _SC), d_hidden.data_ptr(), cap, I, nt, *[t.data_ptr() for t in d_gate],
+                *[t.data_ptr() for t in d_up], wr, ms), "swiglu backward (window)")
+            _lib.check(lib.mx8_gemm_grouped_dual_window(d_gate[0].data_ptr(), d_gate[1].data_ptr(), wts[0][0], wts[0][1], d_up[0].data_ptr(),
+                                                        d_up[1].data_ptr(), wts[1][0], wts[1][1], d_x_routed.data_ptr(), cap, H, I, I,
+                                                        nt, tpe, E, wr, ms), "data-gradient gemm (window)")
+            ev = torch.cuda.Event()
+            ev.record(main)
+            s_comb.wait_event(ev)
+            wc = _window(bounds, b, 0)
+            _lib.check(lib.mx8_moe_combine_window(d_x_routed.data_ptr(), pr, pt, nt, H, dst, len(d_x_routed_buffer_ptrs), ctypes.byref(wc),
+                                                  s_comb.cuda_stream), "gradient combine (window)")
+        done = torch.cuda.Event()
+        done.record(s_comb)
+    for t in d_y + (d_x_routed, bounds):
+        t.record_stream(s_disp)
+        t.record_stream(s_comb)
+    return d_y, d_hidden, d_gate, d_up, d_x_routed, done
+
+
 def dispatch_mlp_swiglu_combine_bwd(d_y_shared, d_combine_buffer, d_combine_buffer_ptrs, d_x_routed_buffer, d_x_routed_buffer_ptrs,
                                     w_shared_gate_T, w_routed_gate_T, w_routed_gate_T_sc,
                                     w_shared_up_T, w_routed_up_T, w_routed_up_T_sc,
@@ -358,24 +431,35 @@ def dispatch_mlp_swiglu_combine_bwd(d_y_shared, d_combine_buffer, d_combine_buff
     E, H, I = w_routed_gate_T.shape                      # transposed weights: [E, H, I]
     cap = schedule_peer_rank.numel()
     dev = d_combine_buffer.device
-    # gradient rows of the routed outputs, pulled from the owners' buffers (one row per (token, k) pair)
-    d_y_fp8, d_y_sc, d_y_fp8_t, d_y_sc_t = dispatch_quantize(d_combine_buffer_ptrs, H, 1, schedule_peer_rank,
-                                                               schedule_peer_token_idx, num_tokens, cap)
-    d_hidden = torch.empty(cap, I, dtype=torch.bfloat16, device=dev)
-    gemm_grouped(d_y_fp8, d_y_sc, w_routed_down_T, w_routed_down_T_sc, d_hidden, None, num_tokens, tokens_per_expert)
-    (d_gate_fp8, d_gate_sc, d_gate_fp8_t, d_gate_sc_t), (d_up_fp8, d_up_sc, d_up_fp8_t, d_up_sc_t) = swiglu_bwd_quantize_both(
-        gate_fp8_routed, gate_sc_routed, up_fp8_routed, up_sc_routed, d_hidden, num_tokens)
     from .ops import gemm_grouped_dual, gemm_wgrad
-    d_x_routed = torch.empty(cap, H, dtype=torch.bfloat16, device=dev)
-    gemm_grouped_dual(d_gate_fp8, d_gate_sc, w_routed_gate_T, w_routed_gate_T_sc, d_up_fp8, d_up_sc, w_routed_up_T,
-                      w_routed_up_T_sc, d_x_routed, num_tokens, tokens_per_expert)
-    combine(d_x_routed, schedule_peer_rank, schedule_peer_token_idx, num_tokens, d_x_routed_buffer_ptrs)
+    nb = min(E, -(-cap // minibatch_size)) if (minibatch_size > 0 and num_comm_sms > 0) else 1
+    combine_done = None
+    if nb > 1:
+        ((d_y_fp8, d_y_sc, d_y_fp8_t, d_y_sc_t), d_hidden, (d_gate_fp8, d_gate_sc, d_gate_fp8_t, d_gate_sc_t),
+         (d_up_fp8, d_up_sc, d_up_fp8_t, d_up_sc_t), d_x_routed, combine_done) = _routed_bwd_pipelined(
+            d_combine_buffer_ptrs, d_x_routed_buffer_ptrs, w_routed_gate_T, w_routed_gate_T_sc, w_routed_up_T, w_routed_up_T_sc,
+            w_routed_down_T, w_routed_down_T_sc, gate_fp8_routed, gate_sc_routed, up_fp8_routed, up_sc_routed,
+            schedule_peer_rank, schedule_peer_token_idx, num_tokens, tokens_per_expert, num_comm_sms, nb)
+    else:
+        # gradient rows of the routed outputs, pulled from the owners' buffers (one row per (token, k) pair)
+        d_y_fp8, d_y_sc, d_y_fp8_t, d_y_sc_t = dispatch_quantize(d_combine_buffer_ptrs, H, 1, schedule_peer_rank,
+                                                                   schedule_peer_token_idx, num_tokens, cap)
+        d_hidden = torch.empty(cap, I, dtype=torch.bfloat16, device=dev)
+        gemm_grouped(d_y_fp8, d_y_sc, w_routed_down_T, w_routed_down_T_sc, d_hidden, None, num_tokens, tokens_per_expert)
+        (d_gate_fp8, d_gate_sc, d_gate_fp8_t, d_gate_sc_t), (d_up_fp8, d_up_sc, d_up_fp8_t, d_up_sc_t) = swiglu_bwd_quantize_both(
+            gate_fp8_routed, gate_sc_routed, up_fp8_routed, up_sc_routed, d_hidden, num_tokens)
+        d_x_routed = torch.empty(cap, H, dtype=torch.bfloat16, device=dev)
+        gemm_grouped_dual(d_gate_fp8, d_gate_sc, w_routed_gate_T, w_routed_gate_T_sc, d_up_fp8, d_up_sc, w_routed_up_T,
+                          w_routed_up_T_sc, d_x_routed, num_tokens, tokens_per_expert)
+        combine(d_x_routed, schedule_peer_rank, schedule_peer_token_idx, num_tokens, d_x_routed_buffer_ptrs)
     d_w_gate = torch.empty(E, I, H, dtype=torch.bfloat16, device=dev)
     d_w_up = torch.empty(E, I, H, dtype=torch.bfloat16, device=dev)
     d_w_down = torch.empty(E, H, I, dtype=torch.bfloat16, device=dev)
     gemm_wgrad(d_gate_fp8_t, d_gate_sc_t, x_fp8_t_routed, x_sc_t_routed, d_w_gate, tokens_per_expert)
     gemm_wgrad(d_up_fp8_t, d_up_sc_t, x_fp8_t_routed, x_sc_t_routed, d_w_up, tokens_per_expert)
     gemm_wgrad(d_y_fp8_t, d_y_sc_t, hidden_fp8_t_routed, hidden_sc_t_routed, d_w_down, tokens_per_expert)
+    if combine_done is not None:
+        torch.cuda.current_stream(dev).wait_event(combine_done)     # the last gradient combine ran beside the weight gradients
     d_x_shared = d_gate_shared = d_up_shared = d_hidden_shared = d_w_sg = d_w_su = d_w_sd = None
     if w_shared_gate_T is not None and d_y_shared is not None:
         x = x_buffer

@@ -264,6 +264,15 @@ MX8_API int mx8_swiglu_quantize_window(const void* gate_fp8, const void* gate_sc
                                        int rows, int cols, const void* num_rows, void* hidden_fp8, void* hidden_sc,
                                        void* hidden_fp8_t, void* hidden_sc_t, void* hidden_bf16, const mx8_window* window,
                                        void* stream);
+MX8_API int mx8_swiglu_bwd_quantize_both_window(const void* gate_fp8, const void* gate_sc, const void* up_fp8, const void* up_sc,
+                                                const void* d_hidden, int rows, int cols, const void* num_rows,
+                                                void* d_gate_fp8, void* d_gate_sc, void* d_gate_fp8_t, void* d_gate_sc_t,
+                                                void* d_up_fp8, void* d_up_sc, void* d_up_fp8_t, void* d_up_sc_t,
+                                                const mx8_window* window, void* stream);
+MX8_API int mx8_gemm_grouped_dual_window(const void* A1, const void* A1_sc, const void* B1, const void* B1_sc, const void* A2,
+                                         const void* A2_sc, const void* B2, const void* B2_sc, void* C, int M, int N, int K1,
+                                         int K2, const void* num_rows, const void* group_rows, int num_groups,
+                                         const mx8_window* window, void* stream);
 MX8_API int mx8_moe_combine_window(const void* y_routed, const void* peer_rank, const void* peer_token_idx,
                                    const void* num_tokens, int hidden, void* const* combine_ptrs, int world,
                                    const mx8_window* window, void* stream);

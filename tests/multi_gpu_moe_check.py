@@ -153,6 +153,21 @@ def main():
     dxb_ref = MO.combine_ref([r["d_x"] for r in bwd_refs], prs, pts, rank, T, k)
     rel_dx = O.rel_frobenius(d_x.cpu(), MO.bwd_epilogue_ref(None, dxb_ref, k))
     assert rel_dx < 2e-2, rel_dx
+    # ---- the same backward in minibatches on three streams: same bytes in every rank's gradient buffer
+    d_xb_first = d_xb.clone()
+    dist.barrier()
+    d_xb.fill_(-3.0)
+    torch.cuda.synchronize()
+    dist.barrier()
+    b2 = mx8.dispatch_mlp_swiglu_combine_bwd(None, d_cb, d_cb_ptrs, d_xb, d_xb_ptrs, None, *dv(bw[0]), None, *dv(bw[1]), None, *dv(bw[2]),
+                                             outs[0], outs[1], None, outs[3], outs[4], None, outs[6], outs[7], None, outs[9], outs[10],
+                                             x, x_ptrs, wgq.to(dev), wgs.to(dev), wuq.to(dev), wus.to(dev), pr, pt, nt, tpe, k, 28, 0, 512)
+    assert mx8.device_status() == 0
+    torch.cuda.synchronize()
+    dist.barrier()
+    assert torch.equal(d_xb.view(torch.int16), d_xb_first.view(torch.int16)), "pipelined backward: gradient buffer differs"
+    for idx in (13, 15, 17):
+        assert torch.equal(b2[idx].view(torch.int16), b[idx].view(torch.int16)), "pipelined backward: weight gradient differs"
     flag = torch.ones(1, device=dev)
     dist.all_reduce(flag)
     if rank == 0:

@@ -468,3 +468,39 @@ def test_pipelined_forward_equals_single_sequence(E_local, minibatch):
     for i in (1, 10):
         assert torch.equal(o1[i][:, :n // 128], o2[i][:, :n // 128]), i
     assert torch.equal(o1[12][:n].view(torch.int16), o2[12][:n].view(torch.int16))
+
+
+def test_pipelined_backward_equals_single_sequence():
+    W, T, H, I, k, E = 1, 384, 512, 256, 4, 6
+    topk_all, weights = make_topk(W, T, E, k, seed=271)
+    x = O.make_input(T, H, seed=272).to(DEV)
+    cap = ((T * k) // 256 + E) * 256
+    mk = lambda r, c, sd: torch.stack([O.make_input(r, c, seed=sd + e, std=c ** -0.5) for e in range(E)])
+    wg, wu, wd = mk(I, H, 100), mk(I, H, 200), mk(H, I, 300)
+    q2 = lambda w: tuple(t.to(DEV) for t in O.quantize_both(w)[:2])
+    fw = [q2(wg), q2(wu), q2(wd)]
+    bw = [q2(wg.transpose(1, 2).contiguous()), q2(wu.transpose(1, 2).contiguous()), q2(wd.transpose(1, 2).contiguous())]
+    cb = torch.zeros(T * k, H, dtype=torch.bfloat16, device=DEV)
+    pr, pt, nt, tpe = mx8.schedule(topk_all.to(DEV), E, cap, 0)
+    f = mx8.dispatch_mlp_swiglu_combine_fwd(x, [x.data_ptr()], cb, [cb.data_ptr()], None, *fw[0], None, *fw[1], None, *fw[2], pr, pt, nt, tpe, k)
+    d_out = O.make_input(T, H, seed=273, std=H ** -0.5).to(DEV)
+    d_cb = torch.zeros(T * k, H, dtype=torch.bfloat16, device=DEV)
+    mx8.bwd_prologue(d_out, weights[0].to(DEV), d_cb)
+    res = []
+    for knobs in ((0, 0, 0), (28, 0, 512)):
+        d_xb = torch.full((T * k, H), -5.0, dtype=torch.bfloat16, device=DEV)
+        b = mx8.dispatch_mlp_swiglu_combine_bwd(None, d_cb, [d_cb.data_ptr()], d_xb, [d_xb.data_ptr()], None, *bw[0], None, *bw[1], None, *bw[2],
+                                                f[0], f[1], None, f[3], f[4], None, f[6], f[7], None, f[9], f[10], x, [x.data_ptr()],
+                                                *fw[0], *fw[1], pr, pt, nt, tpe, k, *knobs)
+        torch.cuda.synchronize()
+        assert mx8.device_status() == 0
+        res.append((b, d_xb))
+    n = int(nt)
+    (b1, x1), (b2, x2) = res
+    assert torch.equal(x1.view(torch.int16), x2.view(torch.int16))
+    for i in (1, 9):                                   # d_x_routed, d_hidden
+        assert torch.equal(b1[i][:n].view(torch.int16), b2[i][:n].view(torch.int16)), i
+    for i in (3, 6, 10):                               # d_gate, d_up, d_y bytes
+        assert torch.equal(b1[i][:n].view(torch.uint8), b2[i][:n].view(torch.uint8)), i
+    for i in (13, 15, 17):                             # weight gradients
+        assert torch.equal(b1[i].view(torch.int16), b2[i].view(torch.int16)), i

@@ -221,3 +221,39 @@ def test_pipelined_forward_through_the_cpp_module(C):
             assert torch.equal(f[i][:n].view(torch.uint8), res[0][0][i][:n].view(torch.uint8))
         for i in (0, 9):
             assert torch.equal(f[i][:, :n].view(torch.uint8), res[0][0][i][:, :n].view(torch.uint8))
+
+
+def test_pipelined_backward_through_the_cpp_module(C):
+    import mx8
+    from oracle import moe_oracle as MO
+    T, H, I, k, E = 384, 512, 256, 4, 5
+    g = torch.Generator().manual_seed(34)
+    ids, w = MO.route(torch.randn(T, E, generator=g), k)
+    x = O.make_input(T, H, seed=36).to(DEV)
+    mk = lambda r, c, sd: torch.stack([O.make_input(r, c, seed=sd + e, std=c ** -0.5) for e in range(E)]).to(DEV)
+    wg, wu, wd = mk(I, H, 10), mk(I, H, 20), mk(H, I, 30)
+    fw = [C.mxfp8_quantize(t, True, False)[:2] for t in (wg, wu, wd)]
+    bw = [C.mxfp8_quantize(t.transpose(1, 2).contiguous(), True, False)[:2] for t in (wg, wu, wd)]
+    cap = ((T * k) // 256 + E) * 256
+    pr, pt, nt, tpe = C.schedule(ids.view(1, T, k).to(DEV), E, cap, 0)
+    cb = torch.zeros(T * k, H, dtype=torch.bfloat16, device=DEV)
+    f = C.dispatch_mlp_swiglu_combine_fwd(x, [x.data_ptr()], cb, [cb.data_ptr()], None, *fw[0], None, *fw[1], None, *fw[2], pr, pt, nt, tpe, k)
+    d_out = O.make_input(T, H, seed=37, std=H ** -0.5).to(DEV)
+    d_cb = torch.zeros(T * k, H, dtype=torch.bfloat16, device=DEV)
+    C.bwd_prologue(d_out, w.to(DEV), d_cb)
+    res = []
+    for host, knobs in ((C, (0, 0, 0)), (C, (28, 0, 512)), (mx8, (28, 0, 512))):
+        d_xb = torch.full((T * k, H), -4.0, dtype=torch.bfloat16, device=DEV)
+        b = host.dispatch_mlp_swiglu_combine_bwd(None, d_cb, [d_cb.data_ptr()], d_xb, [d_xb.data_ptr()], None, *bw[0], None, *bw[1],
+                                                 None, *bw[2], f[0], f[1], None, f[3], f[4], None, f[6], f[7], None, f[9], f[10],
+                                                 x, [x.data_ptr()], *fw[0], *fw[1], pr, pt, nt, tpe, k, *knobs)
+        torch.cuda.synchronize()
+        res.append((b, d_xb))
+    assert C.device_status() == 0
+    n = int(nt)
+    for b, d_xb in res[1:]:
+        assert torch.equal(d_xb.view(torch.int16), res[0][1].view(torch.int16))
+        for i in (1, 9):
+            assert torch.equal(b[i][:n].view(torch.int16), res[0][0][i][:n].view(torch.int16))
+        for i in (13, 15, 17):
+            assert torch.equal(b[i].view(torch.int16), res[0][0][i].view(torch.int16))
