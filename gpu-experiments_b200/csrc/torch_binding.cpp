@@ -266,7 +266,8 @@ std::vector<at::Tensor> dispatch_mlp_swiglu_combine_fwd(
             at::cuda::CUDAEvent math_done;
             math_done.record(main);
             math_done.block(s_comb);
-            const mx8_window wc{bp + b, bp + b + 1, 0};
+            // beside GEMMs the combine is held to a few thread blocks: more only queue stores in front of the NVLink ports
+            const mx8_window wc{bp + b, bp + b + 1, b < nb - 1 ? std::max(1, num_comm_sms / 4) : 0};
             check(mx8_moe_combine_window(y_routed.data_ptr(), schedule_peer_rank.data_ptr(), schedule_peer_token_idx.data_ptr(),
                                          num_tokens.data_ptr(), static_cast<int>(H), cp.data(), world, &wc, s_comb.stream()),
                   "combine (window)");
@@ -446,7 +447,7 @@ std::vector<at::Tensor> dispatch_mlp_swiglu_combine_bwd(
             math_done.record(main);
             math_done.block(s_comb);
         }
-        const mx8_window wc{pipe ? bp + b : nullptr, pipe ? bp + b + 1 : nullptr, 0};
+        const mx8_window wc{pipe ? bp + b : nullptr, pipe ? bp + b + 1 : nullptr, (pipe && b < nb - 1) ? std::max(1, num_comm_sms / 4) : 0};
         check(mx8_moe_combine_window(d_x_routed.data_ptr(), schedule_peer_rank.data_ptr(), schedule_peer_token_idx.data_ptr(),
                                      num_tokens.data_ptr(), static_cast<int>(H), dst.data(), world, &wc, s_comb.stream()),
               "gradient combine");

@@ -91,6 +91,20 @@ def fwd_epilogue(y_shared, combine_buffer, topk_weights):
 
 
 _side_streams = {}
+_trace = None       # set to a list to collect (name, start_event, end_event) of every launch of the pipelined layer
+
+
+def _traced(name, stream, call):
+    """run `call()` (one launch on `stream`); with tracing on, bracket it with timing events"""
+    if _trace is None:
+        return call()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record(stream)
+    r = call()
+    b.record(stream)
+    _trace.append((name, a, b))
+    return r
+
 
 
 def _streams(dev):
@@ -110,8 +124,10 @@ def _routed_fwd_pipelined(x_ptrs, combine_buffer_ptrs, w_routed_gate, w_routed_g
                           tokens_per_expert, topk, num_comm_sms, minibatches):
     """Routed experts in `minibatches` groups of consecutive local experts.  Dispatch of group b+1 (on
     num_comm_sms multiprocessors, its own stream) and combine of group b-1 (a third stream; a plain copy
-    kernel that shares multiprocessors with the GEMMs) run beside the GEMMs of group b, which keep the
-    remaining multiprocessors.  Every kernel is the windowed form of the one the unsplit layer launches,
+    kernel that shares multiprocessors with the GEMMs, held to num_comm_sms / 4 multiprocessors' worth of
+    thread blocks: with more, its stores queue up in front of the NVLink ports and slow the GEMMs' operand
+    traffic by as much as the overlap gains) run beside the GEMMs of group b, which keep the remaining
+    multiprocessors.  Every kernel is the windowed form of the one the unsplit layer launches,
     so all outputs are bit-identical to it.  The stream-and-event counterpart of the reference's
     single-kernel task queue with communication SMs (blackwell-ultra/022-…-mxfp8-bw.cu:1738-2010)."""
     lib = _lib.load()
@@ -145,9 +161,9 @@ def _routed_fwd_pipelined(x_ptrs, combine_buffer_ptrs, w_routed_gate, w_routed_g
         for b in range(nb):
             # the first group has the device to itself; later ones run beside the GEMMs
             w = _window(bounds, b, 0 if b == 0 else num_comm_sms)
-            _lib.check(lib.mx8_moe_dispatch_quantize_window(xp, len(x_ptrs), H, topk, pr, pt, nt, cap, x_fp8.data_ptr(), x_sc.data_ptr(),
-                                                            x_fp8_t.data_ptr(), x_sc_t.data_ptr(), ctypes.byref(w), s_disp.cuda_stream),
-                       "dispatch_quantize (window)")
+            _traced("dispatch%d" % b, s_disp, lambda: _lib.check(lib.mx8_moe_dispatch_quantize_window(
+                xp, len(x_ptrs), H, topk, pr, pt, nt, cap, x_fp8.data_ptr(), x_sc.data_ptr(), x_fp8_t.data_ptr(), x_sc_t.data_ptr(),
+                ctypes.byref(w), s_disp.cuda_stream), "dispatch_quantize (window)"))
             ev = torch.cuda.Event()
             ev.record(s_disp)
             disp_done.append(ev)
@@ -156,21 +172,24 @@ def _routed_fwd_pipelined(x_ptrs, combine_buffer_ptrs, w_routed_gate, w_routed_g
             w = _window(bounds, b, 0 if b == nb - 1 else math_sms)
             wr = ctypes.byref(w)
             ms = main.cuda_stream
-            _lib.check(lib.mx8_gemm_grouped_window(x_fp8.data_ptr(), x_sc.data_ptr(), wts[0][0], wts[0][1], gate_fp8.data_ptr(),
-                                                   gate_sc.data_ptr(), cap, I, H, _lib.C_MXFP8, nt, tpe, E, wr, ms), "gate gemm (window)")
-            _lib.check(lib.mx8_gemm_grouped_window(x_fp8.data_ptr(), x_sc.data_ptr(), wts[1][0], wts[1][1], up_fp8.data_ptr(),
-                                                   up_sc.data_ptr(), cap, I, H, _lib.C_MXFP8, nt, tpe, E, wr, ms), "up gemm (window)")
-            _lib.check(lib.mx8_swiglu_quantize_window(gate_fp8.data_ptr(), gate_sc.data_ptr(), up_fp8.data_ptr(), up_sc.data_ptr(), cap, I, nt,
-                                                      h_fp8.data_ptr(), h_sc.data_ptr(), h_fp8_t.data_ptr(), h_sc_t.data_ptr(), None, wr, ms),
-                       "swiglu_quantize (window)")
-            _lib.check(lib.mx8_gemm_grouped_window(h_fp8.data_ptr(), h_sc.data_ptr(), wts[2][0], wts[2][1], y_routed.data_ptr(), None,
-                                                   cap, H, I, _lib.C_BF16, nt, tpe, E, wr, ms), "down gemm (window)")
+            _traced("gate%d" % b, main, lambda: _lib.check(lib.mx8_gemm_grouped_window(
+                x_fp8.data_ptr(), x_sc.data_ptr(), wts[0][0], wts[0][1], gate_fp8.data_ptr(), gate_sc.data_ptr(), cap, I, H, _lib.C_MXFP8,
+                nt, tpe, E, wr, ms), "gate gemm (window)"))
+            _traced("up%d" % b, main, lambda: _lib.check(lib.mx8_gemm_grouped_window(
+                x_fp8.data_ptr(), x_sc.data_ptr(), wts[1][0], wts[1][1], up_fp8.data_ptr(), up_sc.data_ptr(), cap, I, H, _lib.C_MXFP8,
+                nt, tpe, E, wr, ms), "up gemm (window)"))
+            _traced("swiglu%d" % b, main, lambda: _lib.check(lib.mx8_swiglu_quantize_window(
+                gate_fp8.data_ptr(), gate_sc.data_ptr(), up_fp8.data_ptr(), up_sc.data_ptr(), cap, I, nt, h_fp8.data_ptr(), h_sc.data_ptr(),
+                h_fp8_t.data_ptr(), h_sc_t.data_ptr(), None, wr, ms), "swiglu_quantize (window)"))
+            _traced("down%d" % b, main, lambda: _lib.check(lib.mx8_gemm_grouped_window(
+                h_fp8.data_ptr(), h_sc.data_ptr(), wts[2][0], wts[2][1], y_routed.data_ptr(), None, cap, H, I, _lib.C_BF16,
+                nt, tpe, E, wr, ms), "down gemm (window)"))
             ev = torch.cuda.Event()
             ev.record(main)
             s_comb.wait_event(ev)
-            wc = _window(bounds, b, 0)
-            _lib.check(lib.mx8_moe_combine_window(y_routed.data_ptr(), pr, pt, nt, H, cp, len(combine_buffer_ptrs), ctypes.byref(wc),
-                                                  s_comb.cuda_stream), "combine (window)")
+            wc = _window(bounds, b, max(1, num_comm_sms // 4) if b < nb - 1 else 0)
+            _traced("combine%d" % b, s_comb, lambda: _lib.check(lib.mx8_moe_combine_window(
+                y_routed.data_ptr(), pr, pt, nt, H, cp, len(combine_buffer_ptrs), ctypes.byref(wc), s_comb.cuda_stream), "combine (window)"))
         done = torch.cuda.Event()
         done.record(s_comb)
         main.wait_event(done)
@@ -395,7 +414,7 @@ def _routed_bwd_pipelined(d_combine_buffer_ptrs, d_x_routed_buffer_ptrs, w_route
             ev = torch.cuda.Event()
             ev.record(main)
             s_comb.wait_event(ev)
-            wc = _window(bounds, b, 0)
+            wc = _window(bounds, b, max(1, num_comm_sms // 4) if b < nb - 1 else 0)
             _lib.check(lib.mx8_moe_combine_window(d_x_routed.data_ptr(), pr, pt, nt, H, dst, len(d_x_routed_buffer_ptrs), ctypes.byref(wc),
                                                   s_comb.cuda_stream), "gradient combine (window)")
         done = torch.cuda.Event()
