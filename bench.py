@@ -3,7 +3,7 @@
 TFLOP/s (the "gemm" object of the same line), with roofline fractions, clocks, an end-to-end
 number through host buffers and the CPU port of the reference's torch code timed beside it.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl mx8|reference] [--workload quantize|gemm]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl mx8|reference] [--workload quantize|gemm|ffn|moe]
 
 One JSON line on stdout (rank 0).  Under torchrun every rank works on its own shard; there is no
 data-path collective, only the barrier and the max-over-ranks reduction of the timing.
@@ -15,6 +15,11 @@ configurations name):
             its own matrix (weak scaling).
   gemm      M = N = K = 8192, operands quantized from bf16 ~ N(0, 1/sqrt(K)), bf16 output.  With N
             GPUs the rows of A and C are split M/N per rank, B replicated (strong scaling).
+  ffn       X [16384 x 8192] -> quantize -> GEMM with an MXFP8-quantizing epilogue -> GEMM; tokens split.
+  moe       the MoE layer (256 experts, hidden 7168, intermediate 2048, 32768 tokens, top-8): forward as one
+            launch sequence and in minibatches on three streams, and backward, over peer-mapped memory;
+            experts and tokens split across the GPUs.
+The quantize line carries the other three as objects ("gemm", "ffn", "moe") unless --no-gemm / --no-layers.
 """
 import argparse
 import json
