@@ -154,26 +154,63 @@ __global__ void __launch_bounds__(CHUNK) sched_chunk_count_kernel(SchedParams p)
     for (int e = threadIdx.x; e < p.experts; e += CHUNK) cc[e] = hist[e];
 }
 
-// one block: chunk counts -> exclusive prefix per (expert, rank); totals; padded segments and bases
+// one block: chunk counts -> exclusive prefix per (expert, rank); totals; padded segments and bases.
+// Prefix over chunks: 32 (expert, rank) pairs at a time, one per lane (neighbouring lanes read
+// neighbouring words), the chunks split into 32 consecutive ranges, one per warp; warps exchange
+// their range totals through shared memory.
 __global__ void __launch_bounds__(1024) sched_scan_kernel(SchedParams p) {
     __shared__ int warp_tot[32];
+    __shared__ int range_tot[32][33];
     __shared__ int carry;
     const int cpr = chunks_per_rank(p.tokens, p.topk_k);
     int* cc = p.counts + p.experts * p.world + p.experts;
-    for (int idx = threadIdx.x; idx < p.experts * p.world; idx += blockDim.x) {
-        const int r = idx / p.experts, e = idx - r * p.experts;     // e fastest: neighbouring threads, neighbouring words
-        int running = 0;
-        for (int c = 0; c < cpr; ++c) {
-            int* q = cc + (static_cast<size_t>(r) * cpr + c) * p.experts + e;
-            const int v = *q;
-            *q = running;
-            running += v;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int per_warp = (cpr + 31) / 32;
+    const int c_begin = min(cpr, warp * per_warp), c_end = min(cpr, c_begin + per_warp);
+    const int pairs = p.experts * p.world;
+    if (cpr <= 64) {
+        // few chunks: one thread walks the chunks of its pair, no exchange between warps
+        for (int idx = threadIdx.x; idx < pairs; idx += blockDim.x) {
+            const int r = idx / p.experts, e = idx - r * p.experts;
+            int running = 0;
+            for (int c = 0; c < cpr; ++c) {
+                int* cell = cc + (static_cast<size_t>(r) * cpr + c) * p.experts + e;
+                const int v = *cell;
+                *cell = running;
+                running += v;
+            }
+            p.counts[e * p.world + r] = running;
         }
-        p.counts[e * p.world + r] = running;
+    } else
+    for (int g0 = 0; g0 < pairs; g0 += 32) {
+        const int idx = g0 + lane;
+        const bool live = idx < pairs;
+        const int r = live ? idx / p.experts : 0, e = live ? idx - r * p.experts : 0;
+        int* q = cc + (static_cast<size_t>(r) * cpr + c_begin) * p.experts + e;
+        int sum = 0;
+        if (live)
+            for (int c = c_begin; c < c_end; ++c) sum += q[static_cast<size_t>(c - c_begin) * p.experts];
+        range_tot[warp][lane] = sum;
+        __syncthreads();
+        int running = 0, total = 0;
+        for (int w = 0; w < 32; ++w) {
+            const int v = range_tot[w][lane];
+            if (w < warp) running += v;
+            total += v;
+        }
+        if (live) {
+            for (int c = c_begin; c < c_end; ++c) {
+                int* cell = q + static_cast<size_t>(c - c_begin) * p.experts;
+                const int v = *cell;
+                *cell = running;
+                running += v;
+            }
+            if (warp == 0) p.counts[e * p.world + r] = total;
+        }
+        __syncthreads();
     }
     if (threadIdx.x == 0) carry = 0;
     __syncthreads();
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     for (int e0 = 0; e0 < p.experts; e0 += blockDim.x) {
         const int e = e0 + threadIdx.x;
         int padded = 0;
@@ -379,12 +416,16 @@ extern "C" int mx8_moe_schedule_static(const void* topk_all, int world, int toke
 // rows.  The windowed entry points take pointers into this array.
 namespace mx8 {
 namespace moe {
-__global__ void minibatch_bounds_kernel(const int* tokens_per_expert, int experts, int minibatches, int* bounds) {
-    if (threadIdx.x != 0) return;
-    int acc = 0, b = 0;
-    for (int e = 0; e <= experts; ++e) {
-        while (b <= minibatches && static_cast<long long>(b) * experts / minibatches == e) bounds[b++] = acc;
-        if (e < experts) acc += tokens_per_expert[e];
+__global__ void __launch_bounds__(256) minibatch_bounds_kernel(const int* tokens_per_expert, int experts, int minibatches, int* bounds) {
+    // one warp per bound: sum of the segments of the experts before the group's first one
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    for (int b = warp; b <= minibatches; b += warps) {
+        const int first = static_cast<int>(static_cast<long long>(b) * experts / minibatches);
+        int sum = 0;
+        for (int e = lane; e < first; e += 32) sum += tokens_per_expert[e];
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, d);
+        if (lane == 0) bounds[b] = sum;
     }
 }
 }  // namespace moe
@@ -397,7 +438,7 @@ extern "C" int mx8_moe_minibatch_bounds(const void* tokens_per_expert, int num_l
     if (num_local_experts <= 0 || minibatches <= 0 || minibatches > num_local_experts) return MX8_ERR_ARG;
     int rc = check_device_sm100();
     if (rc != MX8_OK) return rc;
-    moe::minibatch_bounds_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const int*>(tokens_per_expert),
+    moe::minibatch_bounds_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const int*>(tokens_per_expert),
                                                                                 num_local_experts, minibatches, static_cast<int*>(bounds));
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {

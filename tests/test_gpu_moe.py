@@ -407,10 +407,11 @@ def test_swiglu_backward_both_equals_two_single_passes():
         assert torch.equal(single[3][:, :n // 128], fused[3][:, :n // 128])
 
 
-@pytest.mark.parametrize("W,T,E_local,k,rank", [(1, 512, 8, 4, 0), (4, 300, 6, 3, 2), (8, 1000, 4, 8, 7)])
+@pytest.mark.parametrize("W,T,E_local,k,rank", [(1, 512, 8, 4, 0), (4, 300, 6, 3, 2), (8, 1000, 4, 8, 7), (2, 8448, 40, 8, 1)])
 def test_schedule_both_forms_agree_with_oracle(W, T, E_local, k, rank):
     # minimal scratch -> one scan per (expert, rank); full scratch -> counting sort over chunks; T values
-    # that are not multiples of the chunk size exercise the ragged last chunk
+    # that are not multiples of the chunk size exercise the ragged last chunk, the last case has more than
+    # 64 chunks per rank (the scan kernel's warp-per-range form) and 40 experts (a ragged group of 32 pairs)
     topk_all, _ = make_topk(W, T, W * E_local, k, seed=W + T)
     cap = ((W * T * k) // 256 + E_local) * 256
     want = MO.schedule_ref(topk_all, E_local, cap, rank)
