@@ -16,7 +16,7 @@ def host_outputs(M, N):
 
 
 @pytest.mark.parametrize("mode", ["rceil", "floor"])
-@pytest.mark.parametrize("shape,band", [((640, 384), 256), ((256, 256), 2048), ((1152, 512), 128)])
+@pytest.mark.parametrize("shape,band", [((640, 384), 256), ((256, 256), 2048), ((1152, 512), 128), ((2304, 256), 512)])
 def test_quantize_host_matches_oracle(shape, band, mode):
     M, N = shape
     x = O.make_input(M, N, seed=M + N, outliers=True, zero_blocks=True).pin_memory()
