@@ -1,5 +1,6 @@
-// Host-buffer forms of the quantizer and the GEMM: the matrix is cut into bands of rows and the
-// three legs of every band (host -> device copy, kernel, device -> host copy) run on three streams,
+// Host-buffer forms of the quantizer and the GEMM: the matrix is cut into bands of rows (the GEMM's C
+// into blocks of an A band by a B band) and the three legs of every band (host -> device copy, kernel,
+// device -> host copy) run on three streams,
 // so that the inbound copy of band b+1 and the outbound copy of band b-1 share the PCIe link's two
 // directions with the kernel of band b.  Two device buffer sets alternate between bands.
 //
@@ -227,37 +228,58 @@ int mx8_gemm_host(const void* A_host, const void* A_sc_host, const void* B_host,
         asc_dev[i] = w; w += align_up(R * Kk / 32);
         c_dev[i] = w;   w += align_up(R * Nn * es);
     }
+    // C is computed in blocks of (band of A rows) x (band of B rows): the first block needs only one band of
+    // each operand, so the outbound copies start after 2 bands have arrived instead of after all of B.
+    // Inbound order: A band 0, every B band, then the other A bands; B stays resident.
     const std::vector<size_t> edges = band_plan(Mm, R);
-    const int bands = static_cast<int>(edges.size()) - 1;
+    const size_t Nb = R < Nn ? R : Nn;
+    const std::vector<size_t> nedges = band_plan(Nn, Nb);
+    const int bands = static_cast<int>(edges.size()) - 1, nbands = static_cast<int>(nedges.size()) - 1;
+    const int blocks = bands * nbands;
     Events evs;
     Check ck;
-    std::vector<cudaEvent_t> in_ready(bands), done(bands), out_done(bands);
+    std::vector<cudaEvent_t> a_ready(bands), band_done(bands), b_ready(nbands), done(blocks), out_done(blocks);
     cudaEvent_t start = evs.make();
-    for (int b = 0; b < bands; ++b) { in_ready[b] = evs.make(); done[b] = evs.make(); out_done[b] = evs.make(); }
+    for (auto* v : {&a_ready, &band_done, &b_ready, &done, &out_done})
+        for (cudaEvent_t& e : *v) e = evs.make();
     if (evs.err != cudaSuccess) { note_cuda_error("cudaEventCreateWithFlags", cudaGetErrorString(evs.err)); return MX8_ERR_CUDA; }
 
     ck(cudaEventRecord(start, s), "cudaEventRecord");
     ck(cudaStreamWaitEvent(cs->in, start, 0), "cudaStreamWaitEvent");
     ck(cudaStreamWaitEvent(cs->out, start, 0), "cudaStreamWaitEvent");
-    // B and its scales first: every band needs them (in-order on the inbound stream)
-    ck(cudaMemcpyAsync(b_dev, B_host, Nn * Kk, cudaMemcpyHostToDevice, cs->in), "cudaMemcpyAsync(h2d)");
-    ck(cudaMemcpyAsync(bsc_dev, B_sc_host, Nn * Kk / 32, cudaMemcpyHostToDevice, cs->in), "cudaMemcpyAsync(h2d)");
-    for (int b = 0; b < bands && ck.err == cudaSuccess; ++b) {
+    for (int b = 0; b < bands && ck.err == cudaSuccess && rc == MX8_OK; ++b) {
         const int i = b & 1;
         const size_t r0 = edges[b], rows = edges[b + 1] - edges[b];
-        if (b >= 2) ck(cudaStreamWaitEvent(cs->in, done[b - 2], 0), "cudaStreamWaitEvent");
+        // the A buffer is free once every block of band b-2 has been computed
+        if (b >= 2) ck(cudaStreamWaitEvent(cs->in, band_done[b - 2], 0), "cudaStreamWaitEvent");
         ck(cudaMemcpyAsync(a_dev[i], static_cast<const uint8_t*>(A_host) + r0 * Kk, rows * Kk, cudaMemcpyHostToDevice, cs->in), "cudaMemcpyAsync(h2d)");
         ck(cudaMemcpyAsync(asc_dev[i], static_cast<const uint8_t*>(A_sc_host) + r0 * Kk / 32, rows * Kk / 32, cudaMemcpyHostToDevice, cs->in), "cudaMemcpyAsync(h2d)");
-        ck(cudaEventRecord(in_ready[b], cs->in), "cudaEventRecord");
-        ck(cudaStreamWaitEvent(s, in_ready[b], 0), "cudaStreamWaitEvent");
-        if (b >= 2) ck(cudaStreamWaitEvent(s, out_done[b - 2], 0), "cudaStreamWaitEvent");
-        if (ck.err != cudaSuccess) break;
-        rc = mx8_gemm(a_dev[i], asc_dev[i], b_dev, bsc_dev, c_dev[i], static_cast<int>(rows), N, K, c_dtype, s);
-        if (rc != MX8_OK) break;
-        ck(cudaEventRecord(done[b], s), "cudaEventRecord");
-        ck(cudaStreamWaitEvent(cs->out, done[b], 0), "cudaStreamWaitEvent");
-        ck(cudaMemcpyAsync(static_cast<uint8_t*>(C_host) + r0 * Nn * es, c_dev[i], rows * Nn * es, cudaMemcpyDeviceToHost, cs->out), "cudaMemcpyAsync(d2h)");
-        ck(cudaEventRecord(out_done[b], cs->out), "cudaEventRecord");
+        ck(cudaEventRecord(a_ready[b], cs->in), "cudaEventRecord");
+        if (b == 0) {
+            for (int j = 0; j < nbands; ++j) {
+                const size_t c0 = nedges[j], cols = nedges[j + 1] - nedges[j];
+                ck(cudaMemcpyAsync(b_dev + c0 * Kk, static_cast<const uint8_t*>(B_host) + c0 * Kk, cols * Kk, cudaMemcpyHostToDevice, cs->in), "cudaMemcpyAsync(h2d)");
+                ck(cudaMemcpyAsync(bsc_dev + c0 * Kk / 32, static_cast<const uint8_t*>(B_sc_host) + c0 * Kk / 32, cols * Kk / 32, cudaMemcpyHostToDevice, cs->in), "cudaMemcpyAsync(h2d)");
+                ck(cudaEventRecord(b_ready[j], cs->in), "cudaEventRecord");
+            }
+        }
+        ck(cudaStreamWaitEvent(s, a_ready[b], 0), "cudaStreamWaitEvent");
+        for (int j = 0; j < nbands && ck.err == cudaSuccess; ++j) {
+            const int k = b * nbands + j, cb = k & 1;
+            const size_t c0 = nedges[j], cols = nedges[j + 1] - nedges[j];
+            if (b == 0) ck(cudaStreamWaitEvent(s, b_ready[j], 0), "cudaStreamWaitEvent");
+            if (k >= 2) ck(cudaStreamWaitEvent(s, out_done[k - 2], 0), "cudaStreamWaitEvent");   // the C buffer has left the device
+            if (ck.err != cudaSuccess) break;
+            rc = mx8_gemm(a_dev[i], asc_dev[i], b_dev + c0 * Kk, bsc_dev + c0 * Kk / 32, c_dev[cb], static_cast<int>(rows), static_cast<int>(cols), K,
+                          c_dtype, s);
+            if (rc != MX8_OK) break;
+            ck(cudaEventRecord(done[k], s), "cudaEventRecord");
+            ck(cudaStreamWaitEvent(cs->out, done[k], 0), "cudaStreamWaitEvent");
+            ck(cudaMemcpy2DAsync(static_cast<uint8_t*>(C_host) + (r0 * Nn + c0) * es, Nn * es, c_dev[cb], cols * es, cols * es, rows,
+                                 cudaMemcpyDeviceToHost, cs->out), "cudaMemcpy2DAsync(d2h)");
+            ck(cudaEventRecord(out_done[k], cs->out), "cudaEventRecord");
+        }
+        ck(cudaEventRecord(band_done[b], s), "cudaEventRecord");
     }
     cudaEvent_t tail_in = evs.make(), tail_out = evs.make();
     if (tail_in && tail_out) {

@@ -287,6 +287,8 @@ MX8_API int mx8_moe_combine_window(const void* y_routed, const void* peer_rank, 
  *     memory is needed for the copies to be asynchronous);
  *   - `workspace` is DEVICE memory of at least mx8_*_host_workspace(...) bytes, used for two
  *     alternating band buffers (and, for the GEMM, B with its scales); the call allocates no memory;
+ *   - the GEMM form computes C in blocks of band_rows rows of A by band_rows rows of B and sends A band 0
+ *     and the B bands first, so its outbound copies begin once two bands have arrived;
  *   - earlier work on `stream` precedes the first copy and `stream` waits for the last one.  Two
  *     copy streams per device are created on first use and kept. */
 MX8_API size_t mx8_quantize_host_workspace(int N, int band_rows);
