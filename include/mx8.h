@@ -300,6 +300,15 @@ MX8_API int mx8_gemm_host(const void* A_host, const void* A_sc_host, const void*
                           void* C_host, int M, int N, int K, int c_dtype, int band_rows, void* workspace,
                           size_t workspace_bytes, void* stream);
 
+/* C = dequant(quantize(A_bf16)) . dequant(B)^T: the GEMM for an activation that is still bf16 [M][K].
+ * A is quantized row-wise (reference rule) into `workspace` (DEVICE memory, mx8_gemm_a_bf16_workspace(M, K)
+ * bytes: the E4M3 bytes, then the scale tiles), then mx8_gemm runs; two launches on `stream`, same result
+ * as calling mx8_quantize and mx8_gemm.  Stands in for a GEMM with a quantizing prologue; the reference
+ * quantizes in separate kernels too (blackwell-ultra/022-…-mxfp8-bw.cu:717-828 before :1399-1736). */
+MX8_API size_t mx8_gemm_a_bf16_workspace(int M, int K);
+MX8_API int mx8_gemm_a_bf16(const void* A_bf16, const void* B, const void* B_sc, void* C, int M, int N, int K, int c_dtype,
+                            void* workspace, size_t workspace_bytes, void* stream);
+
 /* Synchronizes `stream`, then reads and clears the current device's status word: 0 = healthy,
  * otherwise the code of the first bounded wait that expired (see csrc/mx8_ptx.cuh).
  * Returns MX8_OK, MX8_ERR_DEVICE_TIMEOUT (status != 0) or MX8_ERR_CUDA. */

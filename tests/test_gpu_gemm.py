@@ -161,3 +161,18 @@ def test_full_size_against_library_block_scaled_gemm():
     rel = float(d.norm() / ref.float().norm())
     assert rel < REL_FRO_TOL
     assert rel < 1e-3 and float(d.abs().max()) <= float(ref.float().abs().max()) * 2 ** -6
+
+
+def test_gemm_with_bf16_activation_equals_quantize_then_gemm():
+    M, N, K = 384, 256, 512
+    a = O.make_input(M, K, seed=31, std=K ** -0.5, outliers=True, zero_blocks=True).to(DEV)
+    b = O.make_input(N, K, seed=32, std=K ** -0.5).to(DEV)
+    bq, bsc, _, _ = mx8.mxfp8_quantize(b, True, False)
+    aq, asc, _, _ = mx8.mxfp8_quantize(a, True, False)
+    want = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    mx8.kernel(aq, asc, bq, bsc, want)
+    got = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ws = mx8.kernel_a_bf16(a, bq, bsc, got)
+    assert mx8.device_status() == 0
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+    assert torch.equal(ws[:M * K], aq.view(torch.uint8).reshape(-1))
