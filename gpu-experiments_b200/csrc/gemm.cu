@@ -43,9 +43,14 @@ constexpr int EPI_UNITS = 8 / (EPI_WARPS / 4);   // 32-column units per epilogue
 constexpr int MAX_GROUPS = 256;          // experts per launch of the grouped form
 constexpr int THREADS = 32 * (2 + EPI_WARPS);   // producer, MMA issuer, epilogue warps
 
-template <int CG>
+constexpr int CONV_WARPS = 8;            // A16 form: two threads per A row convert bf16 -> E4M3 + scales in shared memory
+constexpr int A16_BYTES = 128 * BK * 2;  // A16 form: one bf16 A tile (two 128-byte-wide TMA boxes)
+
+// A16: the A operand arrives as bf16 and is quantized inside the main loop (three pipeline stages, each
+// with a bf16 staging buffer, instead of six)
+template <int CG, bool A16 = false>
 struct Cfg {
-    static constexpr int STAGES = EPI_WARPS == 4 ? (CG == 2 ? 6 : 4) : (CG == 2 ? 5 : 3);
+    static constexpr int STAGES = A16 ? 3 : (EPI_WARPS == 4 ? (CG == 2 ? 6 : 4) : (CG == 2 ? 5 : 3));
     static constexpr int A_BYTES = 128 * BK;                 // this CTA's 128 rows of A
     static constexpr int B_ROWS = BN / CG;                   // this CTA's rows of B
     static constexpr int B_BYTES = B_ROWS * BK;
@@ -58,10 +63,12 @@ struct Cfg {
     static constexpr int b_off = a_off + STAGES * A_BYTES;
     static constexpr int sfa_off = b_off + STAGES * B_BYTES;
     static constexpr int sfb_off = sfa_off + STAGES * SFA_BYTES;
-    static constexpr int epi_off = (sfb_off + STAGES * SFB_BYTES + 1023) & ~1023;
+    static constexpr int a16_off = (sfb_off + STAGES * SFB_BYTES + 1023) & ~1023;     // bf16 staging ring (A16 only)
+    static constexpr int epi_off = a16_off + (A16 ? STAGES * A16_BYTES : 0);
     static constexpr int bar_off = epi_off + EPI_WARPS * EPI_BYTES;
-    // barriers: full[STAGES], empty[STAGES], acc_full[2], drained
-    static constexpr int n_bars = 2 * STAGES + 3;
+    // barriers: full[STAGES], empty[STAGES], acc_full[2], drained; A16: a_full[STAGES], a_empty[STAGES], conv_done[STAGES]
+    static constexpr int n_bars = 2 * STAGES + 3 + (A16 ? 3 * STAGES : 0);
+    static constexpr int threads = THREADS + (A16 ? 32 * (CONV_WARPS + 1) : 0);   // A16: converters + the bf16 tile producer
     static constexpr int tmem_ptr_off = bar_off + n_bars * 8;
     static constexpr int flag_off = tmem_ptr_off + 8;
     static constexpr int seg_off = flag_off + 8;               // end row of every group's segment (grouped GEMM)
@@ -152,15 +159,16 @@ __device__ __forceinline__ TileInfo tile_info(int t, const Params& p, int tiles_
 
 // F16: A and B are bf16 (kind::f16, no scale tiles); the byte images in shared memory, the stage
 // ring and the epilogue are the same, a K step being 128 bytes = 64 bf16 elements of a row.
-template <int CG, bool F16>
-__global__ void __launch_bounds__(THREADS, 1)
+template <int CG, bool F16, bool A16 = false>
+__global__ void __launch_bounds__((Cfg<CG, A16>::threads), 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
             const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb,
             const __grid_constant__ CUtensorMap tm_a2, const __grid_constant__ CUtensorMap tm_b2,
             const __grid_constant__ CUtensorMap tm_sfa2, const __grid_constant__ CUtensorMap tm_sfb2,
             const __grid_constant__ CUtensorMap tm_c, const Params p) {
-    using C = Cfg<CG>;
+    using C = Cfg<CG, A16>;
     constexpr int S = C::STAGES;
+    static_assert(!A16 || (CG == 2 && !F16), "the bf16-activation form exists for the 2-CTA MXFP8 kernel only");
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
@@ -168,6 +176,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     const uint32_t empty0 = full0 + S * 8;
     const uint32_t accfull0 = empty0 + S * 8;
     const uint32_t drained = accfull0 + 2 * 8;
+    const uint32_t afull0 = drained + 8;            // A16 only: bf16 tile landed / staging free / fp8 tile + scales written
+    const uint32_t aempty0 = afull0 + S * 8;
+    const uint32_t convdone0 = aempty0 + S * 8;
     volatile uint32_t* tmem_ptr = reinterpret_cast<volatile uint32_t*>(base_ptr + C::tmem_ptr_off);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + C::flag_off);
     const AbortCtl ab{abort_flag, p.status};
@@ -187,6 +198,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         mbar_init(accfull0, 1);
         mbar_init(accfull0 + 8, 1);
         mbar_init(drained, EPI_WARPS * CG);
+        if constexpr (A16) {
+            for (int s = 0; s < S; ++s) {
+                mbar_init(afull0 + s * 8, 1);               // this CTA's producer
+                mbar_init(aempty0 + s * 8, CONV_WARPS);     // this CTA's converter warps
+                mbar_init(convdone0 + s * 8, CONV_WARPS * CG);   // (leader's copy is the one waited on) both CTAs' converters
+            }
+        }
         fence_mbar_init();
         prefetch_tmap(&tm_a);
         prefetch_tmap(&tm_b);
@@ -261,6 +279,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     const CUtensorMap* msb = second ? &tm_sfb2 : &tm_sfb;
                     if (!leader) {
                         // only the elected lane issues
+                    } else if constexpr (A16) {
+                        // B and its scales as usual (signalling the leader's barrier); A as bf16 into this CTA's own
+                        // staging slot, two 128-byte-wide boxes, signalling this CTA's a_full
+                        const uint32_t bar = full_leader0 + stage * 8;
+                        if (rank == 0) mbar_arrive_expect_tx(full0 + stage * 8, 2 * (C::B_BYTES + C::SFB_BYTES));
+                        tma_load_2d_pair(b_dst, mb, kk * BK, b_row, bar);
+                        tma_load_3d_pair(sfb_dst, msb, 0, kk, b_base / 128, bar);
                     } else if constexpr (CG == 2) {
                         const uint32_t bar = full_leader0 + stage * 8;
                         if (p.dbg & 2) {
@@ -315,6 +340,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             // wait for a stage and copy its scale tiles into the next TMEM scale slot
             auto copy_scales = [&]() -> bool {
                 if (!__all_sync(0xFFFFFFFFu, mbar_wait(full_bar, cph, ab, DEV_TIMEOUT_FULL))) return false;
+                if constexpr (A16) {
+                    // both CTAs' converters have written this stage's E4M3 tile and A scales
+                    if (!__all_sync(0xFFFFFFFFu, mbar_wait<true>(convdone0 + cstage * 8, cph, ab, DEV_TIMEOUT_FULL))) return false;
+                }
                 tc_fence_after();
                 if (do_cp && leader) {
                     tc_cp_scales_lo<CG>(sf_cp, sfa_lo);
@@ -366,6 +395,86 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     }
                 }
                 if (ok && leader) tc_commit<CG>(accfull0 + (it & 1) * 8);  // accumulator complete
+            }
+        }
+    } else if (A16 && warp == 2 + EPI_WARPS + CONV_WARPS) {
+        // ------------------------------------------------------------------ bf16 tile producer (A16 form)
+        // Its own warp, so that the bf16 tiles run ahead by the depth of the staging ring no matter how far the
+        // MMAs are behind: a staging slot is free as soon as the converters have read it.
+        if constexpr (A16) {
+            const bool leader = elect_one();
+            uint32_t stage = 0, ph = 0;
+            bool ok = true;
+            for (int t = cluster; t < num_tiles && ok; t += num_clusters) {
+                const TileInfo ti = tile_info<CG>(t, p, tiles_m, seg_end, tm0);
+                const int a_row = (__shfl_sync(0xFFFFFFFFu, ti.tm, 0) * CG + static_cast<int>(rank)) * 128;
+                const int kcount_t = __shfl_sync(0xFFFFFFFFu, ti.kcount, 0), k0_t = __shfl_sync(0xFFFFFFFFu, ti.k0, 0);
+                for (int ks = 0; ks < kcount_t; ++ks) {
+                    if (!__all_sync(0xFFFFFFFFu, mbar_wait(aempty0 + stage * 8, ph ^ 1, ab, DEV_TIMEOUT_EMPTY))) { ok = false; break; }
+                    if (leader) {
+                        const uint32_t a16 = base + C::a16_off + stage * A16_BYTES, abar = afull0 + stage * 8;
+                        mbar_arrive_expect_tx(abar, A16_BYTES);
+                        tma_load_2d(a16, &tm_a, (k0_t + ks) * 2 * BK, a_row, abar);
+                        tma_load_2d(a16 + A16_BYTES / 2, &tm_a, (k0_t + ks) * 2 * BK + BK, a_row, abar);
+                    }
+                    if (++stage == S) { stage = 0; ph ^= 1; }
+                }
+            }
+        }
+    } else if (A16 && warp >= 2 + EPI_WARPS) {
+        // ------------------------------------------------------------------ converter (A16 form)
+        // Two threads share row r of this CTA's A tile, one per 64-column half: 128 bf16 of a K step arrive in the
+        // staging slot (two SWIZZLE_128B boxes of 64 columns); per 32-column block a thread takes the amax, the
+        // scale byte (the reference's rule) and writes 32 E4M3 bytes into the stage's A tile in the layout a TMA
+        // load with SWIZZLE_128B would have produced, then its two scale bytes into the stage's scale tile.
+        if constexpr (A16) {
+            using namespace qmath;
+            const int ct = static_cast<int>(threadIdx.x) - 32 * (2 + EPI_WARPS);
+            const int r = ct & 127, half = ct >> 7;
+            const uint32_t sw = static_cast<uint32_t>(r & 7);
+            const uint32_t convdone_leader0 = map_to_cta(convdone0, 0);
+            uint32_t stage = 0, ph = 0;
+            bool ok = true;
+            for (int t = cluster; t < num_tiles && ok; t += num_clusters) {
+                const int kcount_t = tile_info<CG>(t, p, tiles_m, seg_end, tm0).kcount;
+                for (int ks = 0; ks < kcount_t; ++ks) {
+                    if (!mbar_wait(afull0 + stage * 8, ph, ab, DEV_TIMEOUT_FULL)) { ok = false; break; }
+                    if (!mbar_wait(empty0 + stage * 8, ph ^ 1, ab, DEV_TIMEOUT_EMPTY)) { ok = false; break; }   // MMAs of the previous use retired
+                    const uint32_t src = base + C::a16_off + stage * A16_BYTES + half * (A16_BYTES / 2) + r * 128;
+                    const uint32_t a8 = base + C::a_off + stage * C::A_BYTES + r * 128;
+                    uint32_t scword = 0;
+#pragma unroll
+                    for (int b2 = 0; b2 < 2; ++b2) {
+                        const int kb = 2 * half + b2;
+                        const uint32_t c0 = b2 * 4;
+                        uint32_t v[16];
+#pragma unroll
+                        for (int c = 0; c < 4; ++c)
+                            ld_shared_v4(src + (((c0 + c) ^ sw) << 4), v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+                        uint32_t m = maxabs_bf16x2(v[0], v[1]);
+#pragma unroll
+                        for (int j = 2; j < 16; ++j) m = maxabs_bf16x2(m, v[j]);
+                        m &= 0x7FFF7FFFu;
+                        const uint32_t amax = max(m & 0xFFFFu, m >> 16);
+                        const uint32_t byte = scale_bytes2(amax, RCEIL_ROUND_ADD2, RCEIL_MIN_BYTE8_2) & 0xFFu;
+                        const uint32_t inv = inv_scales2(byte | (byte << 16));
+                        uint32_t w[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) w[j] = cvt4(mul_bf16x2(v[2 * j], inv), mul_bf16x2(v[2 * j + 1], inv));
+                        st_shared_v4(a8 + (((2 * kb) ^ sw) << 4), w[0], w[1], w[2], w[3]);
+                        st_shared_v4(a8 + (((2 * kb + 1) ^ sw) << 4), w[4], w[5], w[6], w[7]);
+                        scword |= byte << (8 * b2);
+                    }
+                    asm volatile("st.shared.b16 [%0], %1;" ::"r"(base + C::sfa_off + stage * C::SFA_BYTES + (r & 31) * 16 + (r >> 5) * 4 + 2 * half),
+                                 "h"(static_cast<uint16_t>(scword)) : "memory");
+                    fence_proxy_async_smem();                 // generic-proxy writes -> visible to tcgen05 / tcgen05.cp
+                    __syncwarp();
+                    if (lane == 0) {
+                        mbar_arrive(aempty0 + stage * 8);                         // staging slot may be refilled
+                        mbar_arrive_remote(convdone_leader0 + stage * 8);          // tile + scales ready for the MMA warp
+                    }
+                    if (++stage == S) { stage = 0; ph ^= 1; }
+                }
             }
         }
     } else {
@@ -582,7 +691,7 @@ static int build_c_map(CUtensorMap* mc, void* Cp, int c_rows, int N, int c_dtype
     return make_tmap(mc, dt, 2, Cp, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
-template <int CG, bool F16>
+template <int CG, bool F16, bool A16 = false>
 static int max_grid() {
     // CTAs that can be resident at once (cluster placement included), cached per device
     static int cached[64] = {};
@@ -590,8 +699,8 @@ static int max_grid() {
     cudaGetDevice(&dev);
     dev &= 63;
     if (cached[dev]) return cached[dev];
-    auto kern = gemm_kernel<CG, F16>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<CG>::dynamic);
+    auto kern = gemm_kernel<CG, F16, A16>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<CG, A16>::dynamic);
     if (e != cudaSuccess) {
         note_cuda_error("cudaFuncSetAttribute(gemm)", cudaGetErrorString(e));
         return 0;
@@ -600,8 +709,8 @@ static int max_grid() {
     if (CG == 2) {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(static_cast<unsigned>(n & ~1));
-        cfg.blockDim = dim3(THREADS);
-        cfg.dynamicSmemBytes = Cfg<CG>::dynamic;
+        cfg.blockDim = dim3(Cfg<CG, A16>::threads);
+        cfg.dynamicSmemBytes = Cfg<CG, A16>::dynamic;
         cudaLaunchAttribute at[1];
         at[0].id = cudaLaunchAttributeClusterDimension;
         at[0].val.clusterDim.x = 2;
@@ -639,14 +748,25 @@ struct Grouping {
     bool wgrad = false;
 };
 
-template <int CG, bool F16 = false>
+template <int CG, bool F16 = false, bool A16 = false>
 static int run(const void* A, const void* A_sc, const void* B, const void* B_sc, void* Cp, int M, int N, int K,
                int c_dtype, int max_ctas, const Grouping& gr, cudaStream_t stream) {
     Maps m;
     const int groups = gr.num_groups > 0 ? gr.num_groups : 1;
     const int b_rows = gr.wgrad ? N : groups * N;              // wgrad: B^T is one [N][K] matrix
     const int c_rows = gr.wgrad ? groups * M : M;
-    int rc = build_operand_maps<CG>(&m.a, &m.b, &m.sfa, &m.sfb, A, A_sc, B, B_sc, M, b_rows, K);
+    int rc;
+    if constexpr (A16) {
+        // A is bf16 [M][K]: its rows are 2K bytes and arrive in 128-byte-wide boxes; there are no A scale tiles
+        rc = build_operand_maps<CG>(&m.a, &m.b, &m.sfa, &m.sfb, B, B_sc, B, B_sc, b_rows, b_rows, K);
+        if (rc != MX8_OK) return rc;
+        const uint64_t dims[2] = {2 * static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
+        const uint64_t strides[1] = {2 * static_cast<uint64_t>(K)};
+        const uint32_t box[2] = {BK, 128};
+        rc = make_tmap(&m.a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, A, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    } else {
+        rc = build_operand_maps<CG>(&m.a, &m.b, &m.sfa, &m.sfb, A, A_sc, B, B_sc, M, b_rows, K);
+    }
     if (rc != MX8_OK) return rc;
     if (gr.K2 > 0) rc = build_operand_maps<CG>(&m.a2, &m.b2, &m.sfa2, &m.sfb2, gr.A2, gr.A2_sc, gr.B2, gr.B2_sc, M, b_rows, gr.K2);
     else { m.a2 = m.a; m.b2 = m.b; m.sfa2 = m.sfa; m.sfb2 = m.sfb; }
@@ -675,7 +795,7 @@ static int run(const void* A, const void* A_sc, const void* B, const void* B_sc,
     p.dbg = g_ablation_flags;
     p.status = device_status_ptr();
     if (!p.status) return MX8_ERR_CUDA;
-    int grid = max_grid<CG, F16>();
+    int grid = max_grid<CG, F16, A16>();
     if (grid <= 0) return MX8_ERR_CUDA;
     if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
     const int tiles = p.tiles_m * p.tiles_n * (gr.wgrad ? groups : 1);
@@ -685,8 +805,8 @@ static int run(const void* A, const void* A_sc, const void* B, const void* B_sc,
 
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(grid));
-    cfg.blockDim = dim3(THREADS);
-    cfg.dynamicSmemBytes = Cfg<CG>::dynamic;
+    cfg.blockDim = dim3(Cfg<CG, A16>::threads);
+    cfg.dynamicSmemBytes = Cfg<CG, A16>::dynamic;
     cfg.stream = stream;
     cudaLaunchAttribute at[1];
     at[0].id = cudaLaunchAttributeClusterDimension;
@@ -695,7 +815,7 @@ static int run(const void* A, const void* A_sc, const void* B, const void* B_sc,
     at[0].val.clusterDim.z = 1;
     cfg.attrs = at;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_kernel<CG, F16>, m.a, m.b, m.sfa, m.sfb, m.a2, m.b2, m.sfa2, m.sfb2, m.c, p);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_kernel<CG, F16, A16>, m.a, m.b, m.sfa, m.sfb, m.a2, m.b2, m.sfa2, m.sfb2, m.c, p);
     if (e != cudaSuccess) {
         note_cuda_error("gemm launch", cudaGetErrorString(e));
         return MX8_ERR_CUDA;
@@ -817,6 +937,20 @@ extern "C" int mx8_gemm_bf16_dual(const void* A1, const void* B1, const void* A2
 
 extern "C" int mx8_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int c_dtype, void* stream) {
     return mx8_gemm_bf16_dual(A, B, nullptr, nullptr, C, M, N, K, 0, c_dtype, stream);
+}
+
+// A bf16, quantized row-wise inside the main loop (see the converter role in the kernel)
+extern "C" int mx8_gemm_a_bf16_fused(const void* A_bf16, const void* B, const void* B_sc, void* C, int M, int N, int K, int c_dtype,
+                                     void* stream) {
+    using namespace mx8;
+    if (!A_bf16 || !B || !B_sc || !C) return MX8_ERR_ARG;
+    if (c_dtype != MX8_C_BF16 && c_dtype != MX8_C_F32) return MX8_ERR_ARG;
+    if (M <= 0 || N <= 0 || K <= 0 || M % 128 || N % 128 || K % 128) return MX8_ERR_SHAPE;
+    if (!aligned16(A_bf16) || !aligned16(B) || !aligned16(B_sc) || !aligned16(C)) return MX8_ERR_ALIGN;
+    int rc = check_device_sm100();
+    if (rc != MX8_OK) return rc;
+    const gemm::Grouping none;
+    return gemm::run<2, false, true>(A_bf16, nullptr, B, B_sc, C, M, N, K, c_dtype, 0, none, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int mx8_debug_set_gemm_ablation(int flags) {

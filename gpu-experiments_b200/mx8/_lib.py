@@ -55,6 +55,7 @@ SIGNATURES = {
     "mx8_gemm_host_workspace": (ctypes.c_size_t, [_i, _i, _i, _i]),
     "mx8_gemm_host": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, ctypes.c_size_t, _vp]),
     "mx8_gemm_a_bf16_workspace": (ctypes.c_size_t, [_i, _i]),
+    "mx8_gemm_a_bf16_fused": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "mx8_gemm_a_bf16": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, ctypes.c_size_t, _vp]),
     "mx8_debug_set_gemm_ablation": (_i, [_i]),
     "mx8_device_status": (_i, [ctypes.POINTER(_i), _vp]),

@@ -158,10 +158,12 @@ def kernel_host(A, A_sc, B, B_sc, C, *, band_rows=2048, workspace=None, device=N
     return ws
 
 
-def kernel_a_bf16(A_bf16, B, B_sc, C, workspace=None):
+def kernel_a_bf16(A_bf16, B, B_sc, C, workspace=None, fused=False):
     """`kernel` for an A operand that is still bf16 [M, K]: quantized row-wise into `workspace` (a CUDA byte
     tensor of mx8_gemm_a_bf16_workspace(M, K) bytes, allocated here when omitted), then the block-scaled GEMM
-    (mx8_gemm_a_bf16).  Returns the workspace: its first M*K bytes are A's E4M3 bytes, the scale tiles follow."""
+    (mx8_gemm_a_bf16).  Returns the workspace: its first M*K bytes are A's E4M3 bytes, the scale tiles follow.
+    fused=True quantizes inside the GEMM's main loop instead (mx8_gemm_a_bf16_fused): one launch, no workspace,
+    same bits; returns None."""
     lib = _lib.load()
     M, K = A_bf16.shape
     N = B.shape[0]
@@ -169,6 +171,10 @@ def kernel_a_bf16(A_bf16, B, B_sc, C, workspace=None):
     bp, bsp = _chk(B, "B", _FP8, (N, K)), _chk(B_sc, "B_sc", _SC, (N // 128, K // 128, 512))
     cp = _chk(C, "C", (torch.bfloat16, torch.float32), (M, N))
     cd = _lib.C_F32 if C.dtype == torch.float32 else _lib.C_BF16
+    if fused:
+        with torch.cuda.device(A_bf16.device):
+            _lib.check(lib.mx8_gemm_a_bf16_fused(ap, bp, bsp, cp, M, N, K, cd, _stream()), "kernel_a_bf16 (fused)")
+        return None
     with torch.cuda.device(A_bf16.device):
         ws = _workspace(workspace, lib.mx8_gemm_a_bf16_workspace(M, K), A_bf16.device)
         _lib.check(lib.mx8_gemm_a_bf16(ap, bp, bsp, cp, M, N, K, cd, ws.data_ptr(), ws.numel() * ws.element_size(), _stream()),

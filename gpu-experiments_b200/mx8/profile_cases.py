@@ -2,6 +2,7 @@
 
     python gpu-experiments_b200/mx8/profile_cases.py quantize [M N [launches]]
     python gpu-experiments_b200/mx8/profile_cases.py gemm [M N K [launches]]
+    python gpu-experiments_b200/mx8/profile_cases.py gemm_fused [M N K [launches]]   (bf16 A quantized in the main loop)
 
 Defaults keep the inputs larger than L2 and the device footprint well under 1 GiB so that a
 multi-pass capture of one to three launches ends by itself within a minute or two.
@@ -38,7 +39,10 @@ def main():
         bq, bsc, _, _ = mx8.mxfp8_quantize(b, True, False)
         c = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
         for _ in range(launches):
-            mx8.kernel(aq, asc, bq, bsc, c)
+            if what == "gemm_fused":
+                mx8.kernel_a_bf16(a, bq, bsc, c, fused=True)
+            else:
+                mx8.kernel(aq, asc, bq, bsc, c)
     print("device status", mx8.device_status())
 
 

@@ -304,7 +304,12 @@ MX8_API int mx8_gemm_host(const void* A_host, const void* A_sc_host, const void*
  * A is quantized row-wise (reference rule) into `workspace` (DEVICE memory, mx8_gemm_a_bf16_workspace(M, K)
  * bytes: the E4M3 bytes, then the scale tiles), then mx8_gemm runs; two launches on `stream`, same result
  * as calling mx8_quantize and mx8_gemm.  Stands in for a GEMM with a quantizing prologue; the reference
- * quantizes in separate kernels too (blackwell-ultra/022-…-mxfp8-bw.cu:717-828 before :1399-1736). */
+ * quantizes in separate kernels too (blackwell-ultra/022-…-mxfp8-bw.cu:717-828 before :1399-1736).
+ * mx8_gemm_a_bf16_fused is the same product with the quantization done inside the GEMM's main loop (four
+ * extra warps convert every bf16 A tile to E4M3 + scale bytes in shared memory): no workspace and one launch,
+ * bit-identical output, at the price of three pipeline stages instead of six. */
+MX8_API int mx8_gemm_a_bf16_fused(const void* A_bf16, const void* B, const void* B_sc, void* C, int M, int N, int K,
+                                  int c_dtype, void* stream);
 MX8_API size_t mx8_gemm_a_bf16_workspace(int M, int K);
 MX8_API int mx8_gemm_a_bf16(const void* A_bf16, const void* B, const void* B_sc, void* C, int M, int N, int K, int c_dtype,
                             void* workspace, size_t workspace_bytes, void* stream);

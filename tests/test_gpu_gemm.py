@@ -176,3 +176,20 @@ def test_gemm_with_bf16_activation_equals_quantize_then_gemm():
     assert mx8.device_status() == 0
     assert torch.equal(got.view(torch.int16), want.view(torch.int16))
     assert torch.equal(ws[:M * K], aq.view(torch.uint8).reshape(-1))
+
+
+@pytest.mark.parametrize("shape", [(256, 256, 128), (384, 640, 1024), (128, 256, 512), (1024, 512, 2048)])
+def test_gemm_with_quantizing_prologue_equals_quantize_then_gemm(shape):
+    # A quantized inside the GEMM's main loop (converter warps) must give the bits of quantize -> GEMM
+    M, N, K = shape
+    a = O.make_input(M, K, seed=41, std=K ** -0.5, outliers=True, zero_blocks=True).to(DEV)
+    b = O.make_input(N, K, seed=42, std=K ** -0.5).to(DEV)
+    bq, bsc, _, _ = mx8.mxfp8_quantize(b, True, False)
+    for dt in (torch.bfloat16, torch.float32):
+        want = torch.empty(M, N, dtype=dt, device=DEV)
+        mx8.kernel_a_bf16(a, bq, bsc, want)
+        got = torch.full((M, N), float("nan"), dtype=dt, device=DEV)
+        assert mx8.kernel_a_bf16(a, bq, bsc, got, fused=True) is None
+        assert mx8.device_status() == 0
+        assert torch.equal(got.view(torch.int32 if dt == torch.float32 else torch.int16),
+                           want.view(torch.int32 if dt == torch.float32 else torch.int16))
