@@ -64,7 +64,8 @@ struct Params {
 
 constexpr int SRC_DENSE = 0, SRC_GATHER = 1, SRC_SWIGLU = 2, SRC_SWIGLU_BWD = 3;
 // bytes of one ring slot: the backward of SwiGLU also needs the bf16 gradient of the activation
-__host__ __device__ constexpr int slot_bytes(int src) { return src == SRC_SWIGLU_BWD ? 2 * SLOT_BYTES : SLOT_BYTES; }
+// (and the gather source fetches 512-byte row pieces, two column tiles wide: half as many bulk copies)
+__host__ __device__ constexpr int slot_bytes(int src) { return (src == SRC_SWIGLU_BWD || src == SRC_GATHER) ? 2 * SLOT_BYTES : SLOT_BYTES; }
 // producer warps: the gather source looks two indices up per row before it can issue a copy, so
 // several warps work on different slabs to keep enough copies in flight
 __host__ __device__ constexpr int producer_warps(int src) { return src == SRC_GATHER ? 4 : 1; }
@@ -88,8 +89,8 @@ using namespace qmath;
 // tiles in flight at any time then form a patch about group_r tiles tall, so each input row, each
 // row-wise output row AND each transposed output row receives a contiguous run of a kilobyte or
 // more within a short time window, which keeps DRAM pages open for all three streams.
-__device__ __forceinline__ void tile_coords(int t, const Params& p, int tiles_r, int& tr, int& tc) {
-    const int per_group = p.group_r * p.tiles_c;
+__device__ __forceinline__ void tile_coords(int t, const Params& p, int tiles_r, int tiles_c, int& tr, int& tc) {
+    const int per_group = p.group_r * tiles_c;
     const int grp = t / per_group;
     const int in_grp = t - grp * per_group;
     const int rows = min(p.group_r, tiles_r - grp * p.group_r);
@@ -131,7 +132,9 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
     const int tile0 = p.row_begin_dev ? *p.row_begin_dev / TILE : 0;
     const int tiles_r_end = p.rows_dev ? min(p.tiles_r, (*p.rows_dev + TILE - 1) / TILE) : p.tiles_r;
     const int tiles_r = max(tiles_r_end - tile0, 0);
-    const int num_tiles = tiles_r * p.tiles_c;
+    // the gather source walks tiles two columns wide (the odd last column, if any, alone)
+    const int tiles_ce = SRC == SRC_GATHER ? (p.tiles_c + 1) / 2 : p.tiles_c;
+    const int num_tiles = tiles_r * tiles_ce;
     const int my_tiles = (num_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
     const int my_slabs = my_tiles * 4;
 
@@ -139,15 +142,15 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
     if (tid < 32 * P) {
         // ---------------------------------------------------------------- producer
         if constexpr (SRC == SRC_GATHER) {
-            // every lane fetches one row of the slab (256 bytes) from the rank that owns the token,
-            // straight from that rank's memory; rows without a source are filled with zeros
+            // every lane fetches one row of the slot (512 bytes = two column tiles) from the rank that owns
+            // the token, straight from that rank's memory; rows without a source are filled with zeros
             const int pw = tid >> 5, pl = tid & 31;              // producer warp pw takes slabs pw, pw + P, ...
             for (int n = pw; n < my_slabs; n += P) {
                 const int slot = n % S;
                 const uint32_t ph = (n / S) & 1;
                 const int t = static_cast<int>(blockIdx.x) + (n >> 2) * static_cast<int>(gridDim.x);
                 int tr, tc;
-                tile_coords(t, p, tiles_r, tr, tc);
+                tile_coords(t, p, tiles_r, tiles_ce, tr, tc);
                 tr += tile0;
                 const int row = tr * TILE + (n & 3) * SLAB_ROWS + pl;
                 const int pr = p.peer_rank[row];                 // issued before the wait: the look-up overlaps it
@@ -156,14 +159,16 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
                 if (pl == 0) ok = mbar_wait(empty0 + slot * 8, ph ^ 1, ab, DEV_TIMEOUT_EMPTY) ? 1 : 0;
                 ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
                 if (!ok) break;
-                const uint32_t dst = base + L::ring + slot * SLOT + pl * 256;
+                // this row's piece: two column tiles (512 bytes), one if the row of tiles ends here
+                const uint32_t dst = base + L::ring + slot * SLOT + pl * 512;
+                const uint32_t piece = (2 * tc + 1 < p.tiles_c) ? 512u : 256u;
                 if (pr >= 0) {
-                    const uint8_t* s = p.src[pr] + (static_cast<size_t>(tok / p.topk) * p.N + tc * TILE) * 2;
-                    mbar_arrive_expect_tx(full0 + slot * 8, 256);
-                    bulk_load_1d(dst, s, 256, full0 + slot * 8);
+                    const uint8_t* s = p.src[pr] + (static_cast<size_t>(tok / p.topk) * p.N + 2 * tc * TILE) * 2;
+                    mbar_arrive_expect_tx(full0 + slot * 8, piece);
+                    bulk_load_1d(dst, s, piece, full0 + slot * 8);
                 } else {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) st_shared_v4(dst + j * 16, 0, 0, 0, 0);
+                    for (int j = 0; j < 32; ++j) st_shared_v4(dst + j * 16, 0, 0, 0, 0);
                     mbar_arrive(full0 + slot * 8);
                 }
             }
@@ -174,7 +179,7 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
                 if (!mbar_wait(empty0 + slot * 8, ph ^ 1, ab, DEV_TIMEOUT_EMPTY)) break;
                 const int t = static_cast<int>(blockIdx.x) + (n >> 2) * static_cast<int>(gridDim.x);
                 int tr, tc;
-                tile_coords(t, p, tiles_r, tr, tc);
+                tile_coords(t, p, tiles_r, tiles_ce, tr, tc);
                 tr += tile0;
                 const uint32_t dst = base + L::ring + slot * SLOT;
                 mbar_arrive_expect_tx(full0 + slot * 8, SLOT);
@@ -207,14 +212,17 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
         const int wq = n & 3;
         const int t = static_cast<int>(blockIdx.x) + (n >> 2) * static_cast<int>(gridDim.x);
         int tr, tc;
-        tile_coords(t, p, tiles_r, tr, tc);
+        tile_coords(t, p, tiles_r, tiles_ce, tr, tc);
                 tr += tile0;
         if (!mbar_wait(full0 + slot * 8, ph, ab, DEV_TIMEOUT_FULL)) break;
 
         // SwiGLU backward can emit both gradients from one visit of the slot: two passes over the same
         // shared-memory inputs, each quantizing into its own output set
+        // The gather source visits a slot twice as well: its two 128-column halves are two tiles.
         const int pass_first = (SRC == SRC_SWIGLU_BWD && p.bwd_which != 2) ? p.bwd_which : 0;
-        const int pass_last = SRC == SRC_SWIGLU_BWD ? (p.bwd_which == 2 ? 1 : p.bwd_which) : 0;
+        const int pass_last = SRC == SRC_SWIGLU_BWD ? (p.bwd_which == 2 ? 1 : p.bwd_which)
+                            : (SRC == SRC_GATHER ? ((2 * tc + 1 < p.tiles_c) ? 1 : 0) : 0);
+        const int tc_pair = tc;
 #pragma unroll 1
         for (int pass = pass_first; pass <= pass_last; ++pass) {
         const bool second = SRC == SRC_SWIGLU_BWD && p.bwd_which == 2 && pass == 1;
@@ -223,6 +231,7 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
         uint8_t* const o_sc_t = second ? p.sc_t2 : p.sc_t;
         uint8_t* const o_bf16 = second ? p.hidden_bf16_2 : p.hidden_bf16;
         const CUtensorMap* const o_tm_t = second ? &tm_t2 : &tm_t;
+        if constexpr (SRC == SRC_GATHER) tc = 2 * tc_pair + pass;
         uint32_t c[32][2];                 // c[i] = columns 4l..4l+3 of slab row i (bf16 pairs)
         if constexpr (SRC == SRC_SWIGLU || SRC == SRC_SWIGLU_BWD) {
             // forward: hidden = bf16( silu(dequant(gate)) * dequant(up) ), computed in fp32;
@@ -270,7 +279,10 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
             }
         } else {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) ld_shared_v2(slot_addr + i * 256 + l * 8, c[i][0], c[i][1]);
+            for (int i = 0; i < 32; ++i) {
+                if constexpr (SRC == SRC_GATHER) ld_shared_v2(slot_addr + i * 512 + pass * 256 + l * 8, c[i][0], c[i][1]);
+                else ld_shared_v2(slot_addr + i * 256 + l * 8, c[i][0], c[i][1]);
+            }
         }
         __syncwarp();
         if (l == 0 && pass == pass_last) mbar_arrive(empty0 + slot * 8);       // the slot may be refilled now
@@ -526,7 +538,7 @@ extern "C" int mx8_moe_dispatch_quantize_window(const void* const* x_ptrs, int w
     if ((rc = make_transposed_map(&tm_t, fp8_t, 1, capacity, hidden)) != MX8_OK) return rc;
     int grid = sm_count();
     if (grid <= 0) return MX8_ERR_CUDA;
-    const int tiles = p.tiles_r * p.tiles_c;
+    const int tiles = p.tiles_r * ((p.tiles_c + 1) / 2);       // slots are two column tiles wide
     if (grid > tiles) grid = tiles;
     apply_window(p, grid, window);
     return launch<8, 1, SRC_GATHER, true, true>(tm_t, tm_t, tm_t, tm_t, p, grid, static_cast<cudaStream_t>(stream));
