@@ -45,12 +45,13 @@ constexpr int THREADS = 32 * (2 + EPI_WARPS);   // producer, MMA issuer, epilogu
 
 constexpr int CONV_WARPS = 8;            // A16 form: two threads per A row convert bf16 -> E4M3 + scales in shared memory
 constexpr int A16_BYTES = 128 * BK * 2;  // A16 form: one bf16 A tile (two 128-byte-wide TMA boxes)
+constexpr int A16_SLOTS = 2;             // A16 form: depth of the bf16 staging ring (the E4M3 stage ring is deeper)
 
-// A16: the A operand arrives as bf16 and is quantized inside the main loop (three pipeline stages, each
-// with a bf16 staging buffer, instead of six)
+// A16: the A operand arrives as bf16 and is quantized inside the main loop (four pipeline stages and a
+// two-slot bf16 staging ring instead of six stages)
 template <int CG, bool A16 = false>
 struct Cfg {
-    static constexpr int STAGES = A16 ? 3 : (EPI_WARPS == 4 ? (CG == 2 ? 6 : 4) : (CG == 2 ? 5 : 3));
+    static constexpr int STAGES = A16 ? 4 : (EPI_WARPS == 4 ? (CG == 2 ? 6 : 4) : (CG == 2 ? 5 : 3));
     static constexpr int A_BYTES = 128 * BK;                 // this CTA's 128 rows of A
     static constexpr int B_ROWS = BN / CG;                   // this CTA's rows of B
     static constexpr int B_BYTES = B_ROWS * BK;
@@ -64,10 +65,10 @@ struct Cfg {
     static constexpr int sfa_off = b_off + STAGES * B_BYTES;
     static constexpr int sfb_off = sfa_off + STAGES * SFA_BYTES;
     static constexpr int a16_off = (sfb_off + STAGES * SFB_BYTES + 1023) & ~1023;     // bf16 staging ring (A16 only)
-    static constexpr int epi_off = a16_off + (A16 ? STAGES * A16_BYTES : 0);
+    static constexpr int epi_off = a16_off + (A16 ? A16_SLOTS * A16_BYTES : 0);
     static constexpr int bar_off = epi_off + EPI_WARPS * EPI_BYTES;
-    // barriers: full[STAGES], empty[STAGES], acc_full[2], drained; A16: a_full[STAGES], a_empty[STAGES], conv_done[STAGES]
-    static constexpr int n_bars = 2 * STAGES + 3 + (A16 ? 3 * STAGES : 0);
+    // barriers: full[STAGES], empty[STAGES], acc_full[2], drained; A16: a_full[A16_SLOTS], a_empty[A16_SLOTS], conv_done[STAGES]
+    static constexpr int n_bars = 2 * STAGES + 3 + (A16 ? 2 * A16_SLOTS + STAGES : 0);
     static constexpr int threads = THREADS + (A16 ? 32 * (CONV_WARPS + 1) : 0);   // A16: converters + the bf16 tile producer
     static constexpr int tmem_ptr_off = bar_off + n_bars * 8;
     static constexpr int flag_off = tmem_ptr_off + 8;
@@ -177,8 +178,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     const uint32_t accfull0 = empty0 + S * 8;
     const uint32_t drained = accfull0 + 2 * 8;
     const uint32_t afull0 = drained + 8;            // A16 only: bf16 tile landed / staging free / fp8 tile + scales written
-    const uint32_t aempty0 = afull0 + S * 8;
-    const uint32_t convdone0 = aempty0 + S * 8;
+    const uint32_t aempty0 = afull0 + A16_SLOTS * 8;
+    const uint32_t convdone0 = aempty0 + A16_SLOTS * 8;
     volatile uint32_t* tmem_ptr = reinterpret_cast<volatile uint32_t*>(base_ptr + C::tmem_ptr_off);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + C::flag_off);
     const AbortCtl ab{abort_flag, p.status};
@@ -199,11 +200,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         mbar_init(accfull0 + 8, 1);
         mbar_init(drained, EPI_WARPS * CG);
         if constexpr (A16) {
-            for (int s = 0; s < S; ++s) {
-                mbar_init(afull0 + s * 8, 1);               // this CTA's producer
+            for (int s = 0; s < A16_SLOTS; ++s) {
+                mbar_init(afull0 + s * 8, 1);               // this CTA's bf16 tile producer
                 mbar_init(aempty0 + s * 8, CONV_WARPS);     // this CTA's converter warps
-                mbar_init(convdone0 + s * 8, CONV_WARPS * CG);   // (leader's copy is the one waited on) both CTAs' converters
             }
+            for (int s = 0; s < S; ++s) mbar_init(convdone0 + s * 8, CONV_WARPS * CG);   // both CTAs' converters (leader's copy is waited on)
         }
         fence_mbar_init();
         prefetch_tmap(&tm_a);
@@ -403,21 +404,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         // MMAs are behind: a staging slot is free as soon as the converters have read it.
         if constexpr (A16) {
             const bool leader = elect_one();
-            uint32_t stage = 0, ph = 0;
+            uint32_t slot = 0, ph = 0;
             bool ok = true;
             for (int t = cluster; t < num_tiles && ok; t += num_clusters) {
                 const TileInfo ti = tile_info<CG>(t, p, tiles_m, seg_end, tm0);
                 const int a_row = (__shfl_sync(0xFFFFFFFFu, ti.tm, 0) * CG + static_cast<int>(rank)) * 128;
                 const int kcount_t = __shfl_sync(0xFFFFFFFFu, ti.kcount, 0), k0_t = __shfl_sync(0xFFFFFFFFu, ti.k0, 0);
                 for (int ks = 0; ks < kcount_t; ++ks) {
-                    if (!__all_sync(0xFFFFFFFFu, mbar_wait(aempty0 + stage * 8, ph ^ 1, ab, DEV_TIMEOUT_EMPTY))) { ok = false; break; }
+                    if (!__all_sync(0xFFFFFFFFu, mbar_wait(aempty0 + slot * 8, ph ^ 1, ab, DEV_TIMEOUT_EMPTY))) { ok = false; break; }
                     if (leader) {
-                        const uint32_t a16 = base + C::a16_off + stage * A16_BYTES, abar = afull0 + stage * 8;
+                        const uint32_t a16 = base + C::a16_off + slot * A16_BYTES, abar = afull0 + slot * 8;
                         mbar_arrive_expect_tx(abar, A16_BYTES);
                         tma_load_2d(a16, &tm_a, (k0_t + ks) * 2 * BK, a_row, abar);
                         tma_load_2d(a16 + A16_BYTES / 2, &tm_a, (k0_t + ks) * 2 * BK + BK, a_row, abar);
                     }
-                    if (++stage == S) { stage = 0; ph ^= 1; }
+                    if (++slot == A16_SLOTS) { slot = 0; ph ^= 1; }
                 }
             }
         }
@@ -433,14 +434,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             const int r = ct & 127, half = ct >> 7;
             const uint32_t sw = static_cast<uint32_t>(r & 7);
             const uint32_t convdone_leader0 = map_to_cta(convdone0, 0);
-            uint32_t stage = 0, ph = 0;
+            uint32_t stage = 0, ph = 0;        // E4M3 stage ring
+            uint32_t slot = 0, sph = 0;        // bf16 staging ring
             bool ok = true;
             for (int t = cluster; t < num_tiles && ok; t += num_clusters) {
                 const int kcount_t = tile_info<CG>(t, p, tiles_m, seg_end, tm0).kcount;
                 for (int ks = 0; ks < kcount_t; ++ks) {
-                    if (!mbar_wait(afull0 + stage * 8, ph, ab, DEV_TIMEOUT_FULL)) { ok = false; break; }
+                    if (!mbar_wait(afull0 + slot * 8, sph, ab, DEV_TIMEOUT_FULL)) { ok = false; break; }
                     if (!mbar_wait(empty0 + stage * 8, ph ^ 1, ab, DEV_TIMEOUT_EMPTY)) { ok = false; break; }   // MMAs of the previous use retired
-                    const uint32_t src = base + C::a16_off + stage * A16_BYTES + half * (A16_BYTES / 2) + r * 128;
+                    const uint32_t src = base + C::a16_off + slot * A16_BYTES + half * (A16_BYTES / 2) + r * 128;
                     const uint32_t a8 = base + C::a_off + stage * C::A_BYTES + r * 128;
                     uint32_t scword = 0;
 #pragma unroll
@@ -470,10 +472,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     fence_proxy_async_smem();                 // generic-proxy writes -> visible to tcgen05 / tcgen05.cp
                     __syncwarp();
                     if (lane == 0) {
-                        mbar_arrive(aempty0 + stage * 8);                         // staging slot may be refilled
+                        mbar_arrive(aempty0 + slot * 8);                          // staging slot may be refilled
                         mbar_arrive_remote(convdone_leader0 + stage * 8);          // tile + scales ready for the MMA warp
                     }
                     if (++stage == S) { stage = 0; ph ^= 1; }
+                    if (++slot == A16_SLOTS) { slot = 0; sph ^= 1; }
                 }
             }
         }
