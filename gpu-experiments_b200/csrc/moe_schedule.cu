@@ -7,9 +7,14 @@
 //   peer_rank[row]      source rank of the row, -1 for padding and unused rows
 //   peer_token_idx[row] token * topk + k on the source rank
 //   tokens_per_expert[e] padded segment length, num_tokens[0] their sum
-// Order inside a segment: round j takes the j-th pair (in token*topk+k order) of every source rank
-// that still has one, ranks ascending — the placement rule of the reference's scheduler
+// Order inside a segment: round j takes the j-th pair of every source rank that still has one, ranks
+// ascending — the placement rule of the reference's scheduler
 // (blackwell-ultra/022-moe-dispatch-mlp-swiglu-combine-mxfp8-bw.cu:34-147), which this file replaces.
+// "The j-th pair of a source rank" is the reference's order too: its placement kernel gives entry
+// idx = token*topk+k of a rank's table to thread idx % 1024 of a 1024-thread block, and the threads
+// take consecutive ordinals in thread order (:99-146), so the pairs of one (expert, source rank) are
+// ordered by (idx % 1024, idx / 1024).  For tables of at most 1024 entries per rank that is table
+// order; for larger ones it is not, and every routed tensor of the layer depends on it.
 // Differences: a schedule larger than `capacity` is reported through the device status word
 // (the reference executes `trap`), and the counting scratch is supplied by the caller.
 // Two forms: a counting sort over chunks of the table when the scratch has room for the per-chunk
@@ -78,14 +83,14 @@ __global__ void sched_pad_kernel(SchedParams p) {
     }
 }
 
-// block (expert e, source rank r): rank the pairs of r that chose e and place them
-__global__ void sched_place_kernel(SchedParams p) {
+// block (expert e, source rank r): thread t owns the entries t, t + 1024, ... of rank r's table; the
+// pairs that chose e take ordinals thread by thread (an exclusive prefix over the threads' hit
+// counts), entries of one thread in ascending order
+__global__ void __launch_bounds__(THREADS) sched_place_kernel(SchedParams p) {
     extern __shared__ int n_from[];           // [world] pairs per source rank for this expert
     __shared__ int warp_sums[THREADS / 32];
-    __shared__ int running;
     const int e = blockIdx.x / p.world, r = blockIdx.x % p.world;
     for (int i = threadIdx.x; i < p.world; i += blockDim.x) n_from[i] = p.counts[e * p.world + i];
-    if (threadIdx.x == 0) running = 0;
     __syncthreads();
     if (n_from[r] == 0) return;
     const int base = p.counts[p.experts * p.world + e];
@@ -93,47 +98,61 @@ __global__ void sched_place_kernel(SchedParams p) {
     const int stride = p.tokens * p.topk_k;
     const int* src = p.topk + static_cast<size_t>(r) * stride;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    for (int i0 = 0; i0 < stride; i0 += blockDim.x) {
-        const int i = i0 + threadIdx.x;
-        const int hit = (i < stride && src[i] == want) ? 1 : 0;
-        // exclusive rank of this pair among the block's hits
-        const unsigned ballot = __ballot_sync(0xFFFFFFFFu, hit);
-        const int in_warp = __popc(ballot & ((1u << lane) - 1));
-        if (lane == 0) warp_sums[warp] = __popc(ballot);
-        __syncthreads();
-        int before = running;
-        for (int w = 0; w < warp; ++w) before += warp_sums[w];
-        if (hit) {
-            const int j = before + in_warp;
-            int dst = base;
-            for (int q = 0; q < p.world; ++q) {
-                const int n = n_from[q];
-                dst += min(n, j) + ((q < r && n > j) ? 1 : 0);
-            }
-            if (dst < p.capacity) {
-                p.peer_rank[dst] = r;
-                p.peer_token_idx[dst] = i;
-            }
+    int mine = 0;
+    for (int i = threadIdx.x; i < stride; i += THREADS) mine += (src[i] == want) ? 1 : 0;
+    int incl = mine;                                                 // inclusive scan over the block
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const int v = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+        if (lane >= d) incl += v;
+    }
+    if (lane == 31) warp_sums[warp] = incl;
+    __syncthreads();
+    int j = incl - mine;
+    for (int w = 0; w < warp; ++w) j += warp_sums[w];
+    if (mine == 0) return;
+    for (int i = threadIdx.x; i < stride; i += THREADS) {
+        if (src[i] != want) continue;
+        int dst = base;
+        for (int q = 0; q < p.world; ++q) {
+            const int n = n_from[q];
+            dst += min(n, j) + ((q < r && n > j) ? 1 : 0);
         }
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            int s = 0;
-            for (int w = 0; w < THREADS / 32; ++w) s += warp_sums[w];
-            running += s;
+        if (dst < p.capacity) {
+            p.peer_rank[dst] = r;
+            p.peer_token_idx[dst] = i;
         }
-        __syncthreads();
+        ++j;
     }
 }
 
 // ---------------------------------------------------------------------------------------------
-// Counting-sort form (used when the scratch buffer is large enough): the table is cut into chunks of
-// CHUNK entries of one source rank; one pass counts every chunk's pairs per local expert, a scan
-// turns the counts into each chunk's first ordinal per (expert, rank), and a second pass places the
-// pairs.  Every entry of the table is read twice in total, instead of once per local expert.
+// Counting-sort form (used when the scratch buffer is large enough).  A rank's table is read as a
+// matrix of `rows` x 1024 entries (entry idx at row idx / 1024, column idx % 1024) and the order of the
+// pairs is column-major over it.  A chunk is a band of consecutive columns holding about 1024 entries;
+// inside a chunk, position pos = (column - first column) * rows + row.  One pass counts every chunk's
+// pairs per local expert, a scan turns the counts into each chunk's first ordinal per (expert, rank),
+// and a second pass places the pairs.  Every entry of the table is read twice in total, instead of
+// once per local expert.
 // Scratch: counts[E*W] | bases[E] | chunk_counts[W * chunks_per_rank * E].
 constexpr int CHUNK = 1024;
 
-__host__ __device__ inline int chunks_per_rank(int tokens, int topk_k) { return (tokens * topk_k + CHUNK - 1) / CHUNK; }
+struct ChunkGeom {
+    int rows;      // entries per column = ceil(stride / 1024)
+    int cols;      // columns per chunk
+    int chunks;    // chunks per rank
+};
+
+__host__ __device__ inline ChunkGeom chunk_geom(int tokens, int topk_k) {
+    ChunkGeom g;
+    const long long stride = static_cast<long long>(tokens) * topk_k;
+    g.rows = static_cast<int>((stride + THREADS - 1) / THREADS);
+    g.cols = g.rows >= CHUNK ? 1 : CHUNK / g.rows;
+    g.chunks = (THREADS + g.cols - 1) / g.cols;
+    return g;
+}
+
+__host__ __device__ inline int chunks_per_rank(int tokens, int topk_k) { return chunk_geom(tokens, topk_k).chunks; }
 
 // block (r, c): histogram of chunk c of rank r over the local experts; also clears the outputs
 __global__ void __launch_bounds__(CHUNK) sched_chunk_count_kernel(SchedParams p) {
@@ -141,13 +160,18 @@ __global__ void __launch_bounds__(CHUNK) sched_chunk_count_kernel(SchedParams p)
     for (int i = blockIdx.x * CHUNK + threadIdx.x; i < p.capacity; i += gridDim.x * CHUNK) p.peer_rank[i] = -1;
     for (int i = threadIdx.x; i < p.experts; i += CHUNK) hist[i] = 0;
     __syncthreads();
-    const int cpr = chunks_per_rank(p.tokens, p.topk_k);
-    const int r = blockIdx.x / cpr, c = blockIdx.x % cpr;
+    const ChunkGeom g = chunk_geom(p.tokens, p.topk_k);
+    const int r = blockIdx.x / g.chunks, c = blockIdx.x % g.chunks;
     const int stride = p.tokens * p.topk_k;
-    const int i = c * CHUNK + threadIdx.x;
-    if (i < stride) {
-        const int e = p.topk[static_cast<size_t>(r) * stride + i] - p.rank * p.experts;
-        if (e >= 0 && e < p.experts) atomicAdd(&hist[e], 1);
+    const int col0 = c * g.cols, ncols = min(g.cols, THREADS - col0);
+    const int* src = p.topk + static_cast<size_t>(r) * stride;
+    // the order inside the chunk does not matter for counting: walk it row by row (contiguous reads)
+    for (int q = threadIdx.x; q < ncols * g.rows; q += CHUNK) {
+        const int i = (q / ncols) * THREADS + col0 + q % ncols;
+        if (i < stride) {
+            const int e = src[i] - p.rank * p.experts;
+            if (e >= 0 && e < p.experts) atomicAdd(&hist[e], 1);
+        }
     }
     __syncthreads();
     int* cc = p.counts + p.experts * p.world + p.experts + static_cast<size_t>(blockIdx.x) * p.experts;
@@ -241,43 +265,52 @@ __global__ void __launch_bounds__(1024) sched_scan_kernel(SchedParams p) {
     }
 }
 
-// block (r, c): ordinal of every pair among the pairs of (expert, rank) in table order, then its row
+// block (r, c): ordinal of every pair of the chunk among the pairs of its (expert, rank), in the
+// chunk's column-major order, then its row.  A chunk of more than 1024 entries (a table of more than
+// a million entries per rank) is walked in windows of 1024 positions.
 __global__ void __launch_bounds__(CHUNK) sched_chunk_place_kernel(SchedParams p) {
     extern __shared__ int run[];              // [experts] ordinal of the next pair of this rank per expert
-    const int cpr = chunks_per_rank(p.tokens, p.topk_k);
-    const int r = blockIdx.x / cpr, c = blockIdx.x % cpr;
+    const ChunkGeom g = chunk_geom(p.tokens, p.topk_k);
+    const int r = blockIdx.x / g.chunks, c = blockIdx.x % g.chunks;
     const int* cc = p.counts + p.experts * p.world + p.experts + static_cast<size_t>(blockIdx.x) * p.experts;
     for (int e = threadIdx.x; e < p.experts; e += CHUNK) run[e] = cc[e];
     const int stride = p.tokens * p.topk_k;
-    const int i = c * CHUNK + threadIdx.x;
-    int e = -1;
-    if (i < stride) {
-        e = p.topk[static_cast<size_t>(r) * stride + i] - p.rank * p.experts;
-        if (e < 0 || e >= p.experts) e = -1;
-    }
+    const int col0 = c * g.cols, ncols = min(g.cols, THREADS - col0);
+    const int entries = ncols * g.rows;
+    const int* src = p.topk + static_cast<size_t>(r) * stride;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const unsigned same = __match_any_sync(0xFFFFFFFFu, e);          // lanes of this warp with the same expert
-    const int in_warp = __popc(same & ((1u << lane) - 1));
-    const bool leader = in_warp == 0;
-    int j = 0;
     __syncthreads();
-    for (int w = 0; w < CHUNK / 32; ++w) {                           // warps take their ordinals in table order
-        if (warp == w && e >= 0) {
-            j = run[e] + in_warp;
-            __syncwarp(same);
-            if (leader) run[e] += __popc(same);
+    for (int pos0 = 0; pos0 < entries; pos0 += CHUNK) {
+        const int pos = pos0 + threadIdx.x;
+        int e = -1, i = 0;
+        if (pos < entries) {
+            i = (pos % g.rows) * THREADS + col0 + pos / g.rows;
+            if (i < stride) {
+                e = src[i] - p.rank * p.experts;
+                if (e < 0 || e >= p.experts) e = -1;
+            }
         }
-        __syncthreads();
-    }
-    if (e < 0) return;
-    int dst = p.counts[p.experts * p.world + e];
-    for (int q = 0; q < p.world; ++q) {
-        const int n = p.counts[e * p.world + q];
-        dst += min(n, j) + ((q < r && n > j) ? 1 : 0);
-    }
-    if (dst < p.capacity) {
-        p.peer_rank[dst] = r;
-        p.peer_token_idx[dst] = i;
+        const unsigned same = __match_any_sync(0xFFFFFFFFu, e);      // lanes of this warp with the same expert
+        const int in_warp = __popc(same & ((1u << lane) - 1));
+        int j = 0;
+        for (int w = 0; w < CHUNK / 32; ++w) {                       // warps take their ordinals in position order
+            if (warp == w && e >= 0) {
+                j = run[e] + in_warp;
+                __syncwarp(same);
+                if (in_warp == 0) run[e] += __popc(same);
+            }
+            __syncthreads();
+        }
+        if (e < 0) continue;
+        int dst = p.counts[p.experts * p.world + e];
+        for (int q = 0; q < p.world; ++q) {
+            const int n = p.counts[e * p.world + q];
+            dst += min(n, j) + ((q < r && n > j) ? 1 : 0);
+        }
+        if (dst < p.capacity) {
+            p.peer_rank[dst] = r;
+            p.peer_token_idx[dst] = i;
+        }
     }
 }
 

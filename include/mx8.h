@@ -191,7 +191,11 @@ MX8_API int mx8_moe_bwd_epilogue(const void* d_x_shared, const void* d_x_routed_
  *   this rank owns experts [rank*num_local_experts, (rank+1)*num_local_experts).
  * Outputs: peer_rank[capacity] (source rank per row, -1 = padding/unused), peer_token_idx[capacity]
  * (token*topk + k on the source rank), num_tokens[1] (rows used, every expert padded to 256),
- * tokens_per_expert[num_local_experts] (padded).  `scratch` is `scratch_bytes` of device memory,
+ * tokens_per_expert[num_local_experts] (padded).  Rows of an expert: round j holds the j-th pair of every
+ * source rank that still has one, ranks ascending, where the pairs of one source rank are counted in the
+ * reference kernel's order: entry idx = token*topk + k belongs to thread idx % 1024 of a 1024-thread
+ * block and threads number their hits one after the other, i.e. by (idx % 1024, idx / 1024)
+ * (blackwell-ultra/022-moe-dispatch-mlp-swiglu-combine-mxfp8-bw.cu:99-146).  `scratch` is `scratch_bytes` of device memory,
  * overwritten: with mx8_moe_schedule_scratch_bytes(...) bytes the schedule is a counting sort that reads
  * the routing table twice; with at least num_local_experts*(world+1) ints it still works, scanning the
  * table once per local expert; less is MX8_ERR_LIMIT.  capacity is a multiple of 256; a schedule that

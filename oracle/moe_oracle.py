@@ -20,34 +20,93 @@ from . import mx8_oracle as O
 PAD = 256
 
 
+SCHED_THREADS = 1024   # scheduler::config::NUM_THREADS, ...-mxfp8-bw.cu:15
+
+
 def schedule_ref(topk_all: torch.Tensor, num_local_experts: int, capacity: int, rank: int):
     """topk_all int32 [W, T, k] -> (peer_rank[capacity], peer_token_idx[capacity], num_tokens[1],
-    tokens_per_expert[E]).  Rows of an expert: round j takes the j-th routed pair (token*k + kk order)
-    of every source rank that still has one, ranks ascending; segments padded to 256 rows."""
+    tokens_per_expert[E], written[capacity]).
+
+    Transcription of the reference's three scheduler kernels (...-mxfp8-bw.cu:34-147), with the thread
+    loops of its placement kernel (:99-146) written out as array operations over a [rows, 1024] view of
+    a rank's table: block (expert, peer) has 1024 threads; thread t visits entries t, t + 1024, ...
+    (:108, :133); its first hit takes the ordinal `exclusive prefix over threads of the hit counts`
+    (:112-131) and later hits of the same thread the following ordinals (:145); ordinal j of peer r
+    lands on row base + sum_q min(n_q, j) + #{q < r : n_q > j} (:136-141).  Segments are padded to 256
+    rows (:68-71).  `schedule_ref_threads` below is the same thing as plain loops, for small cases."""
     W, T, k = topk_all.shape
-    flat = topk_all.reshape(W, T * k).numpy()
+    stride = T * k
+    flat = topk_all.reshape(W, stride).numpy()
+    rows = (stride + SCHED_THREADS - 1) // SCHED_THREADS
     peer_rank = np.full(capacity, -1, np.int32)
     peer_tok = np.zeros(capacity, np.int32)
     tpe = np.zeros(num_local_experts, np.int32)
-    base = 0
     written = np.zeros(capacity, bool)
+    entry = np.arange(rows * SCHED_THREADS, dtype=np.int64).reshape(rows, SCHED_THREADS)
+    base = 0
     for e in range(num_local_experts):
         g = rank * num_local_experts + e
-        lists = [np.nonzero(flat[r] == g)[0] for r in range(W)]
-        n = sum(len(x) for x in lists)
-        row = base
-        for j in range(max((len(x) for x in lists), default=0)):
-            for r in range(W):
-                if j < len(lists[r]):
-                    if row < capacity:
-                        peer_rank[row] = r
-                        peer_tok[row] = lists[r][j]
-                        written[row] = True
-                    row += 1
-        tpe[e] = (n + PAD - 1) // PAD * PAD
+        hits = np.zeros((W, rows * SCHED_THREADS), bool)
+        hits[:, :stride] = flat == g
+        hits = hits.reshape(W, rows, SCHED_THREADS)
+        n_from = hits.sum(axis=(1, 2))                                   # count_kernel
+        for r in range(W):
+            h = hits[r]
+            per_thread = h.sum(axis=0)
+            first = np.cumsum(per_thread) - per_thread                   # exclusive prefix over threads
+            j = first[None, :] + np.cumsum(h, axis=0) - h                # ordinal of every entry that hits
+            jj = j[h]
+            dst = base + np.minimum(n_from[None, :], jj[:, None]).sum(axis=1) \
+                + (n_from[None, :r] > jj[:, None]).sum(axis=1)
+            ok = dst < capacity
+            peer_rank[dst[ok]] = r
+            peer_tok[dst[ok]] = entry[h][ok]
+            written[dst[ok]] = True
+        tpe[e] = (int(n_from.sum()) + PAD - 1) // PAD * PAD               # pad_kernel
         base += int(tpe[e])
     return (torch.from_numpy(peer_rank), torch.from_numpy(peer_tok), torch.tensor([base], dtype=torch.int32),
             torch.from_numpy(tpe), torch.from_numpy(written))
+
+
+def schedule_ref_threads(topk_all: torch.Tensor, num_local_experts: int, capacity: int, rank: int):
+    """The reference's placement kernel executed thread by thread in plain Python (small cases only):
+    one pass per block (expert, peer) in which every thread counts its hits, then one in which it
+    places them.  Same outputs as schedule_ref without `written`."""
+    W, T, k = topk_all.shape
+    stride = T * k
+    flat = topk_all.reshape(W, stride).tolist()
+    first_expert = rank * num_local_experts
+    n_ep = [[0] * W for _ in range(num_local_experts)]
+    for r in range(W):
+        for v in flat[r]:
+            if first_expert <= v < first_expert + num_local_experts:
+                n_ep[v - first_expert][r] += 1
+    tpe = [(sum(n_ep[e]) + PAD - 1) // PAD * PAD for e in range(num_local_experts)]
+    peer_rank = [-1] * capacity
+    peer_tok = [0] * capacity
+    for e in range(num_local_experts):
+        expert_base = sum(tpe[:e])
+        for r in range(W):
+            counts = [0] * SCHED_THREADS
+            for t in range(SCHED_THREADS):
+                for i in range(t, stride, SCHED_THREADS):
+                    counts[t] += 1 if flat[r][i] - first_expert == e else 0
+            j_of = [0] * SCHED_THREADS
+            for t in range(1, SCHED_THREADS):
+                j_of[t] = j_of[t - 1] + counts[t - 1]
+            for t in range(SCHED_THREADS):
+                j = j_of[t]
+                for i in range(t, stride, SCHED_THREADS):
+                    if flat[r][i] - first_expert == e:
+                        dst = expert_base
+                        for q in range(W):
+                            dst += min(n_ep[e][q], j) + (1 if q < r and n_ep[e][q] > j else 0)
+                        if dst < capacity:
+                            peer_rank[dst] = r
+                            peer_tok[dst] = i
+                        j += 1
+    return (torch.tensor(peer_rank, dtype=torch.int32), torch.tensor(peer_tok, dtype=torch.int32),
+            torch.tensor([sum(tpe)], dtype=torch.int32), torch.tensor(tpe, dtype=torch.int32))
 
 
 def route(logits: torch.Tensor, k: int):

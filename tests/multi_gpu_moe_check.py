@@ -27,7 +27,7 @@ def main():
             symm_mem.enable_symm_mem_for_group(group)
         except Exception:
             pass
-    T, H, I, k, E = 256, 512, 256, 4, 3
+    T, H, I, k, E = 384, 512, 256, 4, 3      # 1536 routed pairs per rank: above the scheduler's 1024-thread stride
     cap = ((world * T * k) // 256 + E) * 256
     g = torch.Generator().manual_seed(7)
     logits = torch.randn(world * T, world * E, generator=g)

@@ -17,7 +17,12 @@ def make_topk(W, T, E_total, k, seed):
     return ids.view(W, T, k), w.view(W, T, k)
 
 
-@pytest.mark.parametrize("W,T,E_local,k,rank", [(1, 512, 8, 4, 0), (4, 256, 4, 8, 2), (8, 512, 32, 8, 5), (2, 1024, 3, 2, 1)])
+# entries per rank: at or below 1024 (table order), and above (the reference's thread-strided order), up to the
+# benchmark's own table (8 x 4096 x 8, 32 local experts), its one-GPU form (256 local experts) and the
+# reference harness's own sizes (4 x 7168 x 8, 4 local experts)
+@pytest.mark.parametrize("W,T,E_local,k,rank", [(1, 128, 8, 4, 0), (4, 128, 4, 8, 2), (1, 512, 8, 4, 0), (4, 256, 4, 8, 2),
+                                                (8, 512, 32, 8, 5), (2, 1024, 3, 2, 1), (8, 4096, 32, 8, 3),
+                                                (1, 32768, 256, 8, 0), (4, 7168, 4, 8, 1)])
 def test_schedule_matches_oracle(W, T, E_local, k, rank):
     topk_all, _ = make_topk(W, T, W * E_local, k, seed=W * 100 + T)
     cap = ((W * T * k) // 256 + E_local) * 256            # every pair could land here, plus padding
@@ -407,11 +412,15 @@ def test_swiglu_backward_both_equals_two_single_passes():
         assert torch.equal(single[3][:, :n // 128], fused[3][:, :n // 128])
 
 
-@pytest.mark.parametrize("W,T,E_local,k,rank", [(1, 512, 8, 4, 0), (4, 300, 6, 3, 2), (8, 1000, 4, 8, 7), (2, 8448, 40, 8, 1)])
+@pytest.mark.parametrize("W,T,E_local,k,rank", [(1, 512, 8, 4, 0), (2, 100, 6, 3, 1), (4, 300, 6, 3, 2), (8, 1000, 4, 8, 7),
+                                                (2, 8448, 40, 8, 1), (8, 4096, 32, 8, 6), (1, 32768, 256, 8, 0),
+                                                (4, 7168, 4, 8, 3), (1, 140000, 8, 8, 0)])
 def test_schedule_both_forms_agree_with_oracle(W, T, E_local, k, rank):
-    # minimal scratch -> one scan per (expert, rank); full scratch -> counting sort over chunks; T values
-    # that are not multiples of the chunk size exercise the ragged last chunk, the last case has more than
-    # 64 chunks per rank (the scan kernel's warp-per-range form) and 40 experts (a ragged group of 32 pairs)
+    # minimal scratch -> one scan per (expert, rank); full scratch -> counting sort over chunks.  T values that
+    # are not multiples of 1024 leave ragged columns in the [rows, 1024] view of a rank's table; (2, 8448, 40, 8)
+    # and (4, 7168, 4, 8) have more than 64 chunks per rank (the scan kernel's warp-per-range form), 40 experts
+    # leave a ragged group of 32 pairs, and the last case has more than 1024 rows, so a chunk is one column
+    # walked in windows
     topk_all, _ = make_topk(W, T, W * E_local, k, seed=W + T)
     cap = ((W * T * k) // 256 + E_local) * 256
     want = MO.schedule_ref(topk_all, E_local, cap, rank)

@@ -20,6 +20,32 @@ def test_schedule_interleaves_source_ranks_round_by_round():
     assert int(nt) == 256 and tpe.tolist() == [256] and bool((pr[5:] == -1).all())
 
 
+def test_schedule_transcription_equals_thread_by_thread_execution():
+    # the array form of the reference's placement kernel against the same kernel run thread by thread,
+    # below, at and above 1024 entries per rank (where the order stops being table order)
+    for (W, T, k, E_local, rank, seed) in ((2, 64, 4, 2, 1, 1), (1, 128, 8, 16, 0, 2), (2, 512, 4, 2, 0, 3), (3, 700, 3, 2, 2, 4)):
+        topk_all = _topk(W, T, W * E_local, k, seed)
+        cap = (W * T * k + 256 * E_local + 255) // 256 * 256
+        a = MO.schedule_ref(topk_all, E_local, cap, rank)
+        b = MO.schedule_ref_threads(topk_all, E_local, cap, rank)
+        n = int(a[2])
+        assert int(b[2]) == n and torch.equal(a[3], b[3])
+        assert torch.equal(a[0], b[0])
+        assert torch.equal(a[1][a[4]], b[1][a[4]])
+
+
+def test_schedule_order_is_thread_strided_above_1024_entries():
+    # one rank, one expert, every pair routed to it: 2048 entries -> thread t holds entries t and t + 1024,
+    # so the rows read 0, 1024, 1, 1025, ...
+    topk_all = torch.zeros(1, 512, 4, dtype=torch.int32)
+    pr, pt, nt, tpe, written = MO.schedule_ref(topk_all, 1, 2048, 0)
+    assert int(nt) == 2048 and bool(written.all())
+    assert pt[:6].tolist() == [0, 1024, 1, 1025, 2, 1026]
+    # at 1024 entries the order is table order
+    pr, pt, nt, tpe, written = MO.schedule_ref(torch.zeros(1, 256, 4, dtype=torch.int32), 1, 1024, 0)
+    assert pt.tolist() == list(range(1024))
+
+
 def test_schedule_segments_are_padded_and_complete():
     W, T, E_local, k = 4, 128, 4, 4
     topk_all = _topk(W, T, W * E_local, k, 3)

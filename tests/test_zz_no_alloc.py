@@ -2,9 +2,10 @@
 
 Such hosts (a serving process with a memory plan frozen at start-up, a plugin living under another
 component's allocator) call this entry point instead of mx8_moe_schedule; its scratch is an array
-inside the library.  The test calls it through the C ABI twice in a row on different inputs and
+inside the library.  The test calls it through the C ABI several times in a row on different inputs and
 requires exactly the outputs of the caller-scratch entry point, which shows that nothing left in
-the shared array by one call leaks into the next."""
+the shared array by one call leaks into the next; it also reads the device's free memory around the
+calls, which an allocation on the way would lower."""
 import ctypes
 
 import pytest
@@ -48,15 +49,40 @@ def _run(lib, fn_static, topk_all, E_local, cap, rank):
 def test_static_scratch_schedule_matches_and_repeats():
     lib = mx8.load()
     fn = lib.mx8_moe_schedule_static
-    # two calls in a row: a large problem first, then a smaller one with other routing, so stale
-    # counts from the first call would corrupt the second if they were not cleared
-    for (W, T, E_local, k, rank, seed) in ((8, 512, 32, 8, 3, 1), (2, 256, 4, 4, 1, 2)):
+    # calls in a row: a large problem first, then a smaller one with other routing, so stale counts from
+    # the first call would corrupt the second if they were not cleared.  The first two fit the
+    # counting-sort form into the built-in array; the third needs 16672 ints for it (64 chunks per rank
+    # x 8 ranks x 32 experts + 288), so the entry point takes the scan-per-expert form there, which must
+    # clear the counters the earlier calls left dirty
+    for (W, T, E_local, k, rank, seed) in ((8, 512, 32, 8, 3, 1), (2, 256, 4, 4, 1, 2), (8, 8192, 32, 8, 5, 3)):
         topk_all = _routing(W, T, W * E_local, k, seed)
         cap = ((W * T * k) // 256 + E_local) * 256
         ref, got = _run(lib, fn, topk_all, E_local, cap, rank)
         valid = ref[0] >= 0
         assert torch.equal(got[0], ref[0]) and torch.equal(got[2], ref[2]) and torch.equal(got[3], ref[3])
         assert torch.equal(got[1][valid], ref[1][valid])
+
+
+def test_static_scratch_schedule_leaves_free_memory_alone():
+    lib = mx8.load()
+    W, T, E_local, k, rank = 4, 1024, 8, 4, 2
+    topk_all = _routing(W, T, W * E_local, k, 7).to(DEV)
+    cap = ((W * T * k) // 256 + E_local) * 256
+    pr = torch.empty(cap, dtype=torch.int32, device=DEV)
+    pt = torch.empty(cap, dtype=torch.int32, device=DEV)
+    nt = torch.empty(1, dtype=torch.int32, device=DEV)
+    tpe = torch.empty(E_local, dtype=torch.int32, device=DEV)
+    stream = torch.cuda.current_stream().cuda_stream
+    call = lambda: lib.mx8_moe_schedule_static(topk_all.data_ptr(), W, T, k, E_local, cap, rank, pr.data_ptr(), pt.data_ptr(),
+                                               nt.data_ptr(), tpe.data_ptr(), stream)
+    assert call() == _lib.OK            # the first call on a device resolves the array's address
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info(0)[0]
+    for _ in range(3):
+        assert call() == _lib.OK
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info(0)[0] == free_before
+    assert mx8.device_status() == 0
 
 
 def test_static_scratch_limit_is_an_error():
