@@ -1,9 +1,13 @@
 """CPU oracle for the expert-parallel MoE layer built on the MXFP8 path.  TEST INFRASTRUCTURE ONLY
 (same rules as mx8_oracle.py: imported by tests, the smoke check and the benchmark's CPU leg only).
 
-Parity status: the quantize and GEMM pieces are pinned through mx8_oracle.py; the routing schedule
-and the layer composition are restatements of reference code that only runs on a multi-GPU box
-("parity unpinned" for those two: no reference output could be generated here).  They follow
+Parity status: the quantize and GEMM pieces are pinned through mx8_oracle.py.  The expert MLP (routed
+and shared, forward and backward) is pinned by tests/golden/moe_fwd_bwd.npz, which
+tests/golden/make_golden.py produces by executing the reference harness's own mlp_swiglu_fwd_ref /
+mlp_swiglu_bwd_ref on CPU (with its GPU-only block-scaled GEMM wrapper bound to dequantize -> fp32
+product); tests/test_oracle_moe.py requires the functions below to reproduce it.  The routing schedule is
+a transcription of the reference's CUDA kernels, which cannot run here; it is checked against a
+thread-by-thread execution of the same kernel source logic, not against reference output.  They follow
 
 * schedule ............ blackwell-ultra/022-moe-dispatch-mlp-swiglu-combine-mxfp8-bw.cu:34-147
 * routed forward ...... blackwell-ultra/022-moe-dispatch-mlp-swiglu-combine-mxfp8-bw.py:91-126
@@ -239,9 +243,11 @@ def expert_mlp_bwd_ref(d_y_routed, fwd, tokens_per_expert, wg_T, wu_T, wd_T):
         if n:
             rows, tiles = slice(off, off + n), slice(off // 128, (off + n) // 128)
             hs = slice(e * H // 128, (e + 1) * H // 128)
-            acc = O.dequantize(dgq[rows], O.scale_unswizzle(dgsc[tiles])) @ O.dequantize(wg_q[e], O.scale_unswizzle(wg_sc[hs])).t()
-            acc = acc + O.dequantize(duq[rows], O.scale_unswizzle(dusc[tiles])) @ O.dequantize(wu_q[e], O.scale_unswizzle(wu_sc[hs])).t()
-            d_x[rows] = acc.to(torch.bfloat16)
+            # one product over the concatenated K dimension [d_gate | d_up] x [Wg^T | Wu^T] (…-mxfp8-bw.py:178-186)
+            a = torch.cat((O.dequantize(dgq[rows], O.scale_unswizzle(dgsc[tiles])),
+                           O.dequantize(duq[rows], O.scale_unswizzle(dusc[tiles]))), 1)
+            b = torch.cat((O.dequantize(wg_q[e], O.scale_unswizzle(wg_sc[hs])), O.dequantize(wu_q[e], O.scale_unswizzle(wu_sc[hs]))), 1)
+            d_x[rows] = (a @ b.t()).to(torch.bfloat16)
     deq_t = lambda q, sc: O.dequantize(q, O.scale_unswizzle(sc))          # [cols, R]
     dg_t, du_t, dy_t = deq_t(dgqt, dgsct), deq_t(duqt, dusct), deq_t(dyqt, dysct)
     x_t, h_t = deq_t(fwd["x_fp8_t"], fwd["x_sc_t"]), deq_t(fwd["hidden_fp8_t"], fwd["hidden_sc_t"])
@@ -285,11 +291,11 @@ def shared_mlp_bwd_ref(d_y, x, gate, up, hidden, w_gate, w_up, w_down):
     Returns (d_x, d_gate, d_up, d_hidden, d_w_gate, d_w_up, d_w_down)."""
     f = lambda t: t.float()
     bf = lambda t: t.to(torch.bfloat16)
-    d_hidden = bf(f(d_y) @ f(w_down))
+    d_hidden = d_y @ w_down                                  # bf16 products with fp32 accumulation, as in the reference
     den = torch.exp(-f(gate)) + 1.0
     silu = f(gate) / den
     d_silu = (1.0 - silu) / den + silu
     d_gate = bf((f(d_hidden) * d_silu) * f(up))
     d_up = bf(silu * f(d_hidden))
-    d_x = bf(f(d_gate) @ f(w_gate) + f(d_up) @ f(w_up))
-    return d_x, d_gate, d_up, d_hidden, bf(f(d_gate).t() @ f(x)), bf(f(d_up).t() @ f(x)), bf(f(d_y).t() @ f(hidden))
+    d_x = torch.cat((d_gate, d_up), 1) @ torch.cat((w_gate, w_up), 0)
+    return d_x, d_gate, d_up, d_hidden, d_gate.t() @ x, d_up.t() @ x, d_y.t() @ hidden

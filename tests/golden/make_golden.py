@@ -12,6 +12,17 @@ stores inputs and outputs.  The functions taken are
     blackwell-ultra/019-mxfp8-quantize.py     mxfp8_quantize_ref, scale_unswizzle
     blackwell/047-mxfp8-mma-2cta-MNK128-polished.py
                                               quantize_2d, dequantize_2d, reshape_sc
+    blackwell-ultra/022-moe-dispatch-mlp-swiglu-combine-mxfp8-bw.py
+                                              mxfp8_quantize_ref, scale_unswizzle, dequant, quant_and_dequant,
+                                              mlp_swiglu_fwd_ref, mlp_swiglu_bwd_ref
+
+The MoE functions call the harness's mxfp8_gemm_ref, which wraps torch._scaled_mm with block scales and
+needs a GPU.  Here that one name is bound to a CPU stand-in of the same contract (operands given as
+(fp8, scales) or quantized on the fly by the reference's mxfp8_quantize_ref, scales unswizzled or in
+128 x 4 tiles; result = fp32 product of the dequantized operands, rounded to the output type), so the
+fixture pins everything the reference's functions do around the GEMMs — the order of the steps, what
+is rounded to bf16 and where, which operand is quantized along which axis — and the GEMM itself is
+pinned separately by gemm_256x384x512.npz.
 
 The test-suite only reads the stored .npz files; it never needs the reference.
 """
@@ -25,10 +36,11 @@ import torch
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def extract(path, names):
+def extract(path, names, extra=None):
     src = open(path).read()
     tree = ast.parse(src)
     ns = {"torch": torch, "np": np}
+    ns.update(extra or {})
     for node in tree.body:
         if isinstance(node, ast.FunctionDef) and node.name in names:
             code = compile(ast.Module(body=[node], type_ignores=[]), path, "exec")
@@ -111,8 +123,84 @@ def main(ref_root):
                         a_fp8=u8(A_fp8), b_fp8=u8(B_fp8),
                         a_sc=g47["reshape_sc"](A_sc_kmajor).numpy(), b_sc=g47["reshape_sc"](B_sc_kmajor).numpy(),
                         c_bits=bf16_bits(C))
+    moe_fixture(ref_root)
     print("golden vectors written to", HERE)
 
 
+def moe_fixture(ref_root):
+    """Routed + shared expert MLP, forward and backward, through the reference's own torch functions."""
+    path = os.path.join(ref_root, "blackwell-ultra/022-moe-dispatch-mlp-swiglu-combine-mxfp8-bw.py")
+    ns = extract(path, ["mxfp8_quantize_ref", "scale_unswizzle", "dequant", "quant_and_dequant"])
+
+    def mxfp8_gemm_ref(x, w, out_dtype=torch.bfloat16):
+        def operand(o):
+            fp8, sc = o if isinstance(o, tuple) else ns["mxfp8_quantize_ref"](o)
+            if sc.dim() != 2:
+                sc = ns["scale_unswizzle"](sc)
+            rows, K = fp8.shape
+            return (fp8.float().reshape(rows, K // 32, 32) * (2.0 ** (sc.float() - 127.0)).unsqueeze(-1)).reshape(rows, K)
+        return (operand(x) @ operand(w).t()).to(out_dtype)
+
+    ns = extract(path, ["mxfp8_quantize_ref", "scale_unswizzle", "dequant", "quant_and_dequant", "mlp_swiglu_fwd_ref",
+                        "mlp_swiglu_bwd_ref"], extra={"mxfp8_gemm_ref": mxfp8_gemm_ref})
+    quant = ns["mxfp8_quantize_ref"]
+
+    def quant_tiles(w):
+        """[E, R, C] bf16 -> (fp8 [E, R, C], scale tiles [E*R/128, C/128, 32, 16]) as the reference's quantize kernel
+        lays them out; the tile permutation is the one its mxfp8_gemm_ref applies to unswizzled scales."""
+        E, R, C = w.shape
+        fp8, sc = zip(*(quant(w[e]) for e in range(E)))
+        sc = torch.stack(sc).reshape(E * R, C // 32)
+        sc = sc.view(E * R // 128, 4, 32, C // 128, 4).permute(0, 3, 2, 1, 4).contiguous().view(E * R // 128, C // 128, 32, 16)
+        return torch.stack(fp8), sc
+
+    E, H, I, Ts, Is = 2, 256, 128, 32, 64
+    tokens_per_expert = torch.tensor([256, 256], dtype=torch.int32)
+    valid_rows = [200, 130]                                     # the rest of every segment is padding: zero rows
+    R = int(tokens_per_expert.sum())
+    g = torch.Generator().manual_seed(2022)
+    rn = lambda *shape: torch.randn(*shape, generator=g)
+    x_routed = rn(R, H).to(torch.bfloat16)
+    d_y_routed = (rn(R, H) * H ** -0.5).to(torch.bfloat16)
+    off = 0
+    for n, v in zip(tokens_per_expert.tolist(), valid_rows):
+        x_routed[off + v:off + n] = 0
+        d_y_routed[off + v:off + n] = 0
+        off += n
+    w_gate = (rn(E, I, H) * H ** -0.5).to(torch.bfloat16)
+    w_up = (rn(E, I, H) * H ** -0.5).to(torch.bfloat16)
+    w_down = (rn(E, H, I) * I ** -0.5).to(torch.bfloat16)
+    x_shared = rn(Ts, H).to(torch.bfloat16)
+    d_y_shared = (rn(Ts, H) * H ** -0.5).to(torch.bfloat16)
+    ws_gate = (rn(Is, H) * H ** -0.5).to(torch.bfloat16)
+    ws_up = (rn(Is, H) * H ** -0.5).to(torch.bfloat16)
+    ws_down = (rn(H, Is) * Is ** -0.5).to(torch.bfloat16)
+    wq = {n: quant_tiles(w) for n, w in (("gate", w_gate), ("up", w_up), ("down", w_down))}
+    wq_T = {n: quant_tiles(w.transpose(-2, -1).contiguous()) for n, w in (("gate", w_gate), ("up", w_up), ("down", w_down))}
+
+    fwd_names = ["gate_shared", "gate_routed", "up_shared", "up_routed", "hidden_shared", "hidden_routed", "y_shared", "y_routed"]
+    fwd = dict(zip(fwd_names, ns["mlp_swiglu_fwd_ref"](x_shared, x_routed, ws_gate, wq["gate"], ws_up, wq["up"], ws_down, wq["down"],
+                                                        tokens_per_expert)))
+    bwd_names = ["d_x_shared", "d_x_routed", "d_gate_shared", "d_gate_routed", "d_up_shared", "d_up_routed", "d_hidden_shared",
+                 "d_hidden_routed", "d_w_shared_gate", "d_w_routed_gate", "d_w_shared_up", "d_w_routed_up", "d_w_shared_down",
+                 "d_w_routed_down"]
+    bwd = dict(zip(bwd_names, ns["mlp_swiglu_bwd_ref"](
+        d_y_shared, d_y_routed, x_shared, x_routed, fwd["gate_shared"], fwd["gate_routed"], fwd["up_shared"], fwd["up_routed"],
+        fwd["hidden_shared"], fwd["hidden_routed"], ws_gate, wq_T["gate"], ws_up, wq_T["up"], ws_down, wq_T["down"], tokens_per_expert)))
+    out = dict(tokens_per_expert=tokens_per_expert.numpy(), valid_rows=np.array(valid_rows, np.int32),
+               x_routed=bf16_bits(x_routed), d_y_routed=bf16_bits(d_y_routed), x_shared=bf16_bits(x_shared),
+               d_y_shared=bf16_bits(d_y_shared), w_shared_gate=bf16_bits(ws_gate), w_shared_up=bf16_bits(ws_up),
+               w_shared_down=bf16_bits(ws_down))
+    for n in ("gate", "up", "down"):
+        out["w_%s_fp8" % n], out["w_%s_sc" % n] = u8(wq[n][0]), wq[n][1].numpy()
+        out["w_%s_T_fp8" % n], out["w_%s_T_sc" % n] = u8(wq_T[n][0]), wq_T[n][1].numpy()
+    for d in (fwd, bwd):
+        for n, t in d.items():
+            out[n] = bf16_bits(t)
+    np.savez_compressed(os.path.join(HERE, "moe_fwd_bwd.npz"), **out)
+
+
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: python tests/golden/make_golden.py /path/to/reference")
+    main(sys.argv[1])

@@ -92,3 +92,57 @@ def test_shared_expert_backward_matches_autograd():
     for have, want in ((got[0], xs.grad), (got[4], wgs.grad), (got[5], wus.grad), (got[6], wds.grad)):
         assert O.rel_frobenius(have.float(), want.float()) < 2e-2
     assert O.rel_frobenius(y.float(), out.detach().float()) < 2e-2
+
+
+def _fixture(golden_dir):
+    import os
+
+    import numpy as np
+    z = np.load(os.path.join(golden_dir, "moe_fwd_bwd.npz"))
+    bf = lambda n: torch.from_numpy(z[n].view(np.int16)).view(torch.bfloat16)
+    w = lambda n: (torch.from_numpy(z["w_%s_fp8" % n]), torch.from_numpy(z["w_%s_sc" % n]))
+    return z, bf, w
+
+
+def test_expert_mlp_oracle_reproduces_the_reference_functions(golden_dir):
+    # moe_fwd_bwd.npz holds inputs and outputs of the reference harness's mlp_swiglu_fwd_ref / mlp_swiglu_bwd_ref
+    # (two experts, segments of 256 rows with 200 and 130 live rows).  Both sides run the same fp32 products on CPU,
+    # so bf16 results may differ only where an fp32 sum lands on a rounding boundary: equality is asked of the
+    # quantized bytes and of nearly all bf16 elements, closeness of the rest.
+    z, bf, w = _fixture(golden_dir)
+    tpe = torch.from_numpy(z["tokens_per_expert"])
+    fwd = MO.expert_mlp_ref(bf("x_routed"), tpe, w("gate"), w("up"), w("down"))
+
+    def close(have, want, name):
+        assert have.shape == want.shape, name
+        diff = (have.view(torch.int16) != want.view(torch.int16)).float().mean().item()
+        assert diff < 1e-3 and O.rel_frobenius(have, want) < 1e-4, (name, diff)
+
+    for name in ("gate", "up"):
+        q, sc = O.quantize_tiled(bf(name + "_routed"))
+        same = (q == fwd[name + "_fp8"]).float().mean().item()
+        assert same > 0.999 and torch.equal(sc, fwd[name + "_sc"]), name
+    close(fwd["hidden"], bf("hidden_routed"), "hidden")
+    close(fwd["y"], bf("y_routed"), "y")
+    bwd = MO.expert_mlp_bwd_ref(bf("d_y_routed"), fwd, tpe, w("gate_T"), w("up_T"), w("down_T"))
+    for mine, theirs in (("d_hidden", "d_hidden_routed"), ("d_gate", "d_gate_routed"), ("d_up", "d_up_routed"), ("d_x", "d_x_routed"),
+                         ("d_w_gate", "d_w_routed_gate"), ("d_w_up", "d_w_routed_up"), ("d_w_down", "d_w_routed_down")):
+        close(bwd[mine], bf(theirs), mine)
+    # padding rows stay zero through the layer, as in the reference
+    off = 0
+    for n, v in zip(tpe.tolist(), z["valid_rows"].tolist()):
+        assert not fwd["y"][off + v:off + n].any() and not bwd["d_x"][off + v:off + n].any()
+        off += n
+
+
+def test_shared_expert_oracle_reproduces_the_reference_functions(golden_dir):
+    z, bf, w = _fixture(golden_dir)
+    names = ("gate_shared", "up_shared", "hidden_shared", "y_shared")
+    fwd = MO.shared_mlp_ref(bf("x_shared"), bf("w_shared_gate"), bf("w_shared_up"), bf("w_shared_down"))
+    for have, name in zip(fwd, names):
+        assert O.rel_frobenius(have, bf(name)) < 1e-4, name
+    bwd = MO.shared_mlp_bwd_ref(bf("d_y_shared"), bf("x_shared"), bf("gate_shared"), bf("up_shared"), bf("hidden_shared"),
+                                bf("w_shared_gate"), bf("w_shared_up"), bf("w_shared_down"))
+    for have, name in zip(bwd, ("d_x_shared", "d_gate_shared", "d_up_shared", "d_hidden_shared", "d_w_shared_gate",
+                                "d_w_shared_up", "d_w_shared_down")):
+        assert O.rel_frobenius(have, bf(name)) < 1e-4, name
