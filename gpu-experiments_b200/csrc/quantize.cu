@@ -23,6 +23,41 @@
 #include "mx8_ptx.cuh"
 #include "mx8_qmath.cuh"
 
+// Consumer warps (W), ring slots per warp (D) and the row-wise store flavour (RTMA: staged TMA tile store
+// instead of one 4-byte global store per lane and row) of the dense quantizer: build-time tunables, set
+// from measurements at 16384 x 16384 with the GPU idle before each run (SM clock at its maximum):
+//   both orientations  W=8 D=1 per-lane stores 181 us; W=7 or 9 are 2-6 % slower, TMA row stores 4 % slower
+//   one orientation    W=7 D=2: row-wise with TMA stores 135 us (per-lane stores 143 us), transposed 132 us
+// Under sustained load the SM clock drops under the power cap and the TMA row store wins for both
+// orientations as well (185 vs 193 us), which is why the MoE kernels, which run inside long steps, use it.
+#ifndef MX8_Q_BOTH_W
+#define MX8_Q_BOTH_W 8
+#endif
+#ifndef MX8_Q_BOTH_D
+#define MX8_Q_BOTH_D 1
+#endif
+#ifndef MX8_Q_BOTH_RTMA
+#define MX8_Q_BOTH_RTMA 0
+#endif
+#ifndef MX8_Q_ONE_W
+#define MX8_Q_ONE_W 7
+#endif
+#ifndef MX8_Q_ONE_D
+#define MX8_Q_ONE_D 2
+#endif
+#ifndef MX8_Q_ONE_RTMA
+#define MX8_Q_ONE_RTMA 1
+#endif
+#ifndef MX8_Q_COL_W
+#define MX8_Q_COL_W 7
+#endif
+#ifndef MX8_Q_COL_D
+#define MX8_Q_COL_D 2
+#endif
+#ifndef MX8_Q_MOE_RTMA
+#define MX8_Q_MOE_RTMA 1
+#endif
+
 namespace mx8 {
 namespace quant {
 
@@ -30,6 +65,7 @@ constexpr int TILE = 128;
 constexpr int SLAB_ROWS = 32;
 constexpr int SLOT_BYTES = SLAB_ROWS * TILE * 2;   // one bf16 slab (or two E4M3 slabs)
 constexpr int TSTAGE_BYTES = SLAB_ROWS * TILE;     // transposed fp8 staging per warp
+constexpr int RSTAGE_BYTES = SLAB_ROWS * TILE;     // row-wise fp8 staging per warp
 constexpr int SCSTAGE_BYTES = 128;                 // row-wise scale bytes of one slab: [row][kb]
 
 struct Params {
@@ -70,12 +106,13 @@ __host__ __device__ constexpr int slot_bytes(int src) { return (src == SRC_SWIGL
 // several warps work on different slabs to keep enough copies in flight
 __host__ __device__ constexpr int producer_warps(int src) { return src == SRC_GATHER ? 4 : 1; }
 
-template <int W, int D, int SLOT = SLOT_BYTES>
+template <int W, int D, int SLOT = SLOT_BYTES, bool RTMA = true>
 struct Smem {
     static constexpr int S = W * D;                               // slots in the ring
     static constexpr int ring = 0;
     static constexpr int tstage = ring + S * SLOT;
-    static constexpr int scstage = tstage + W * TSTAGE_BYTES;
+    static constexpr int rstage = tstage + W * TSTAGE_BYTES;
+    static constexpr int scstage = rstage + (RTMA ? W * RSTAGE_BYTES : 0);
     static constexpr int bars = scstage + W * SCSTAGE_BYTES;      // full[S], empty[S]
     static constexpr int flag = bars + 2 * S * 8;
     static constexpr int total = flag + 16;
@@ -98,13 +135,14 @@ __device__ __forceinline__ void tile_coords(int t, const Params& p, int tiles_r,
     tr = grp * p.group_r + (in_grp - tc * rows);
 }
 
-template <int W, int D, int SRC, bool ROW, bool COL>
+template <int W, int D, int SRC, bool ROW, bool COL, bool RTMA>
 __global__ void __launch_bounds__((producer_warps(SRC) + W) * 32, 1)
 quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ CUtensorMap tm_in2,
                 const __grid_constant__ CUtensorMap tm_in3, const __grid_constant__ CUtensorMap tm_t,
-                const __grid_constant__ CUtensorMap tm_t2, const Params p) {
+                const __grid_constant__ CUtensorMap tm_t2, const __grid_constant__ CUtensorMap tm_r,
+                const __grid_constant__ CUtensorMap tm_r2, const Params p) {
     constexpr int SLOT = slot_bytes(SRC);
-    using L = Smem<W, D, SLOT>;
+    using L = Smem<W, D, SLOT, RTMA>;
     constexpr int S = L::S;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -124,6 +162,7 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
         fence_mbar_init();
         prefetch_tmap(&tm_in);
         if (COL) prefetch_tmap(&tm_t);
+        if (ROW) prefetch_tmap(&tm_r);
     }
     __syncthreads();
 
@@ -201,6 +240,7 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
     const int w = (tid >> 5) - P;
     const int l = tid & 31;
     const uint32_t tstage = base + L::tstage + w * TSTAGE_BYTES;
+    const uint32_t rstage = base + L::rstage + w * RSTAGE_BYTES;
     uint8_t* scstage_ptr = base_ptr + L::scstage + w * SCSTAGE_BYTES;
     const int hswap = (l >> 2) & 1;     // staging stores: which 16-byte half goes first (bank spreading)
 
@@ -231,6 +271,7 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
         uint8_t* const o_sc_t = second ? p.sc_t2 : p.sc_t;
         uint8_t* const o_bf16 = second ? p.hidden_bf16_2 : p.hidden_bf16;
         const CUtensorMap* const o_tm_t = second ? &tm_t2 : &tm_t;
+        const CUtensorMap* const o_tm_r = second ? &tm_r2 : &tm_r;
         if constexpr (SRC == SRC_GATHER) tc = 2 * tc_pair + pass;
         uint32_t c[32][2];                 // c[i] = columns 4l..4l+3 of slab row i (bf16 pairs)
         if constexpr (SRC == SRC_SWIGLU || SRC == SRC_SWIGLU_BWD) {
@@ -287,7 +328,15 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
         __syncwarp();
         if (l == 0 && pass == pass_last) mbar_arrive(empty0 + slot * 8);       // the slot may be refilled now
 
+        // the previous slab's tile stores must have finished reading the staging buffers
+        if ((COL || RTMA) && l == 0) bulk_wait_read<0>();
+        __syncwarp();
+
         if constexpr (ROW) {
+            // RTMA: the E4M3 bytes of the slab are staged as 32 rows of 128 bytes (one conflict-free row per warp
+            // instruction) and leave with one TMA tile store; otherwise every lane stores its 4 bytes of a row
+            // directly (128 contiguous bytes per warp instruction).  Which is faster depends on what else the
+            // memory system is doing; the launchers choose per use from measurements.
             uint8_t* out_row = o_out + (static_cast<size_t>(tr) * TILE + wq * SLAB_ROWS) * p.N + tc * TILE + l * 4;
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
@@ -303,15 +352,25 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
                 const uint32_t inv_a = __byte_perm(inv2, inv2, 0x1010), inv_b = __byte_perm(inv2, inv2, 0x3232);
                 const uint32_t qa = cvt4(mul_bf16x2(c[i][0], inv_a), mul_bf16x2(c[i][1], inv_a));
                 const uint32_t qb = cvt4(mul_bf16x2(c[i + 1][0], inv_b), mul_bf16x2(c[i + 1][1], inv_b));
-                // streaming stores: the bytes are not read again by this kernel
-                __stcs(reinterpret_cast<uint32_t*>(out_row + static_cast<size_t>(i) * p.N), qa);
-                __stcs(reinterpret_cast<uint32_t*>(out_row + static_cast<size_t>(i + 1) * p.N), qb);
+                if constexpr (RTMA) {
+                    asm volatile("st.shared.b32 [%0], %1;" ::"r"(rstage + i * 128 + l * 4), "r"(qa) : "memory");
+                    asm volatile("st.shared.b32 [%0], %1;" ::"r"(rstage + (i + 1) * 128 + l * 4), "r"(qb) : "memory");
+                } else {
+                    // streaming stores: the bytes are not read again by this kernel
+                    __stcs(reinterpret_cast<uint32_t*>(out_row + static_cast<size_t>(i) * p.N), qa);
+                    __stcs(reinterpret_cast<uint32_t*>(out_row + static_cast<size_t>(i + 1) * p.N), qb);
+                }
                 if ((l & 7) == 0) {
                     scstage_ptr[i * 4 + (l >> 3)] = static_cast<uint8_t>(b2);
                     scstage_ptr[(i + 1) * 4 + (l >> 3)] = static_cast<uint8_t>(b2 >> 16);
                 }
             }
+            if constexpr (RTMA) fence_proxy_async_smem();
             __syncwarp();
+            if (RTMA && l == 0) {
+                tma_store_2d(o_tm_r, tc * TILE, tr * TILE + wq * SLAB_ROWS, rstage);
+                if (!COL) bulk_commit();
+            }
             // row r of the tile keeps its four scale bytes at (r % 32) * 16 + (r / 32) * 4
             const uint32_t word = *reinterpret_cast<const uint32_t*>(scstage_ptr + l * 4);
             *reinterpret_cast<uint32_t*>(o_sc + (static_cast<size_t>(tr) * p.tiles_c + tc) * 512 + l * 16 + wq * 4) = word;
@@ -334,9 +393,6 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
             }
             const int e = tr / p.tiles_rm, trm = tr - e * p.tiles_rm;
             uint8_t* sct = o_sc_t + ((static_cast<size_t>(e) * p.tiles_c + tc) * p.tiles_rm + trm) * 512 + wq;
-            // the previous slab's tile stores must have finished reading the staging buffer
-            if (l == 0) bulk_wait_read<0>();
-            __syncwarp();
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
                 uint32_t wd[8];
@@ -374,14 +430,15 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
         }
         }   // pass
     }
-    if (COL && l == 0) bulk_wait_all<0>();
+    if ((COL || RTMA) && l == 0) bulk_wait_all<0>();
 }
 
-template <int W, int D, int SRC, bool ROW, bool COL>
+template <int W, int D, int SRC, bool ROW, bool COL, bool RTMA = true>
 static int launch(const CUtensorMap& tm_in, const CUtensorMap& tm_in2, const CUtensorMap& tm_in3, const CUtensorMap& tm_t,
-                  const Params& p, int grid, cudaStream_t stream, const CUtensorMap* tm_t2 = nullptr) {
-    auto kern = quantize_kernel<W, D, SRC, ROW, COL>;
-    constexpr int smem = Smem<W, D, slot_bytes(SRC)>::dynamic;
+                  const CUtensorMap& tm_r, const Params& p, int grid, cudaStream_t stream, const CUtensorMap* tm_t2 = nullptr,
+                  const CUtensorMap* tm_r2 = nullptr) {
+    auto kern = quantize_kernel<W, D, SRC, ROW, COL, RTMA>;
+    constexpr int smem = Smem<W, D, slot_bytes(SRC), RTMA>::dynamic;
     static bool configured[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -393,7 +450,8 @@ static int launch(const CUtensorMap& tm_in, const CUtensorMap& tm_in2, const CUt
         }
         configured[dev & 63] = true;
     }
-    kern<<<grid, (producer_warps(SRC) + W) * 32, smem, stream>>>(tm_in, tm_in2, tm_in3, tm_t, tm_t2 ? *tm_t2 : tm_t, p);
+    kern<<<grid, (producer_warps(SRC) + W) * 32, smem, stream>>>(tm_in, tm_in2, tm_in3, tm_t, tm_t2 ? *tm_t2 : tm_t, tm_r,
+                                                                 tm_r2 ? *tm_r2 : tm_r, p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
         note_cuda_error("quantize launch", cudaGetErrorString(e));
@@ -402,6 +460,13 @@ static int launch(const CUtensorMap& tm_in, const CUtensorMap& tm_in2, const CUt
     return MX8_OK;
 }
 
+}  // namespace quant
+}  // namespace mx8
+
+namespace mx8 {
+namespace quant {
+static int make_transposed_map(CUtensorMap* tm, void* fp8_t, int E, int M, int N);
+static int make_row_map(CUtensorMap* tm, void* fp8, long long rows, int N);
 }  // namespace quant
 }  // namespace mx8
 
@@ -442,17 +507,16 @@ extern "C" int mx8_quantize(const void* x_bf16, int E, int M, int N, void* fp8, 
         rc = make_tmap(&tm_in, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x_bf16, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
         if (rc != MX8_OK) return rc;
     }
+    CUtensorMap tm_r;
     if (col) {
-        // transposed bytes [E][N][M] seen as (M, 4, N/4, E): column c = 4q + k lives at (k, q), so
-        // one store covers the 32 columns a staging buffer holds (k fixed, q = 0..31), 32 bytes each
-        const uint64_t dims[4] = {static_cast<uint64_t>(M), 4, static_cast<uint64_t>(N) / 4, static_cast<uint64_t>(E)};
-        const uint64_t strides[3] = {static_cast<uint64_t>(M), static_cast<uint64_t>(M) * 4, static_cast<uint64_t>(M) * N};
-        const uint32_t box[4] = {SLAB_ROWS, 1, 32, 1};
-        rc = make_tmap(&tm_t, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, fp8_t, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE,
-                       CU_TENSOR_MAP_L2_PROMOTION_NONE);
-        if (rc != MX8_OK) return rc;
+        if ((rc = make_transposed_map(&tm_t, fp8_t, E, M, N)) != MX8_OK) return rc;
     } else {
         tm_t = tm_in;
+    }
+    if (row) {
+        if ((rc = make_row_map(&tm_r, fp8, static_cast<long long>(E) * M, N)) != MX8_OK) return rc;
+    } else {
+        tm_r = tm_in;
     }
 
     const int tiles = p.tiles_r * p.tiles_c;
@@ -462,10 +526,10 @@ extern "C" int mx8_quantize(const void* x_bf16, int E, int M, int N, void* fp8, 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     // Both orientations: 8 consumer warps with one slot each measured best (deeper prefetch lowers
     // throughput once reads and both write streams compete); a single orientation does less
-    // arithmetic per slab and prefers 6 warps with two slots each.
-    if (row && col) return launch<8, 1, SRC_DENSE, true, true>(tm_in, tm_in, tm_in, tm_t, p, grid, st);
-    if (row) return launch<6, 2, SRC_DENSE, true, false>(tm_in, tm_in, tm_in, tm_t, p, grid, st);
-    return launch<6, 2, SRC_DENSE, false, true>(tm_in, tm_in, tm_in, tm_t, p, grid, st);
+    // arithmetic per slab and prefers 7 warps with two slots each.
+    if (row && col) return launch<MX8_Q_BOTH_W, MX8_Q_BOTH_D, SRC_DENSE, true, true, (MX8_Q_BOTH_RTMA != 0)>(tm_in, tm_in, tm_in, tm_t, tm_r, p, grid, st);
+    if (row) return launch<MX8_Q_ONE_W, MX8_Q_ONE_D, SRC_DENSE, true, false, (MX8_Q_ONE_RTMA != 0)>(tm_in, tm_in, tm_in, tm_t, tm_r, p, grid, st);
+    return launch<MX8_Q_COL_W, MX8_Q_COL_D, SRC_DENSE, false, true, false>(tm_in, tm_in, tm_in, tm_t, tm_r, p, grid, st);
 }
 
 namespace mx8 {
@@ -478,6 +542,15 @@ static int make_transposed_map(CUtensorMap* tm, void* fp8_t, int E, int M, int N
     const uint64_t strides[3] = {static_cast<uint64_t>(M), static_cast<uint64_t>(M) * 4, static_cast<uint64_t>(M) * N};
     const uint32_t box[4] = {SLAB_ROWS, 1, 32, 1};
     return make_tmap(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, fp8_t, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE,
+                     CU_TENSOR_MAP_L2_PROMOTION_NONE);
+}
+
+// row-wise bytes [rows][N]: a slab leaves as one store of 32 rows of 128 bytes
+static int make_row_map(CUtensorMap* tm, void* fp8, long long rows, int N) {
+    const uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(rows)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(N)};
+    const uint32_t box[2] = {TILE, SLAB_ROWS};
+    return make_tmap(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, fp8, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE,
                      CU_TENSOR_MAP_L2_PROMOTION_NONE);
 }
 
@@ -534,14 +607,15 @@ extern "C" int mx8_moe_dispatch_quantize_window(const void* const* x_ptrs, int w
     for (int r = 0; r < world; ++r) p.src[r] = static_cast<const uint8_t*>(x_ptrs[r]);
     p.status = device_status_ptr();
     if (!p.status) return MX8_ERR_CUDA;
-    CUtensorMap tm_t;
+    CUtensorMap tm_t, tm_r;
     if ((rc = make_transposed_map(&tm_t, fp8_t, 1, capacity, hidden)) != MX8_OK) return rc;
+    if ((rc = make_row_map(&tm_r, fp8, capacity, hidden)) != MX8_OK) return rc;
     int grid = sm_count();
     if (grid <= 0) return MX8_ERR_CUDA;
     const int tiles = p.tiles_r * ((p.tiles_c + 1) / 2);       // slots are two column tiles wide
     if (grid > tiles) grid = tiles;
     apply_window(p, grid, window);
-    return launch<8, 1, SRC_GATHER, true, true>(tm_t, tm_t, tm_t, tm_t, p, grid, static_cast<cudaStream_t>(stream));
+    return launch<8, 1, SRC_GATHER, true, true, (MX8_Q_MOE_RTMA != 0)>(tm_t, tm_t, tm_t, tm_t, tm_r, p, grid, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int mx8_swiglu_quantize(const void* gate_fp8, const void* gate_sc, const void* up_fp8, const void* up_sc,
@@ -579,12 +653,14 @@ extern "C" int mx8_swiglu_quantize_window(const void* gate_fp8, const void* gate
     if ((rc = make_tmap(&tm_g, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, gate_fp8, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE)) != MX8_OK) return rc;
     if ((rc = make_tmap(&tm_u, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, up_fp8, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE)) != MX8_OK) return rc;
     if ((rc = make_transposed_map(&tm_t, hidden_fp8_t, 1, rows, cols)) != MX8_OK) return rc;
+    CUtensorMap tm_r;
+    if ((rc = make_row_map(&tm_r, hidden_fp8, rows, cols)) != MX8_OK) return rc;
     int grid = sm_count();
     if (grid <= 0) return MX8_ERR_CUDA;
     const int tiles = p.tiles_r * p.tiles_c;
     if (grid > tiles) grid = tiles;
     apply_window(p, grid, window);
-    return launch<8, 1, SRC_SWIGLU, true, true>(tm_g, tm_u, tm_u, tm_t, p, grid, static_cast<cudaStream_t>(stream));
+    return launch<8, 1, SRC_SWIGLU, true, true, (MX8_Q_MOE_RTMA != 0)>(tm_g, tm_u, tm_u, tm_t, tm_r, p, grid, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int mx8_swiglu_bwd_quantize(const void* gate_fp8, const void* gate_sc, const void* up_fp8, const void* up_sc,
@@ -618,11 +694,13 @@ extern "C" int mx8_swiglu_bwd_quantize(const void* gate_fp8, const void* gate_sc
     if ((rc = make_tmap(&tm_u, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, up_fp8, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE)) != MX8_OK) return rc;
     if ((rc = make_tmap(&tm_d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, d_hidden, dims, strides2, box, CU_TENSOR_MAP_SWIZZLE_NONE)) != MX8_OK) return rc;
     if ((rc = make_transposed_map(&tm_t, out_fp8_t, 1, rows, cols)) != MX8_OK) return rc;
+    CUtensorMap tm_r;
+    if ((rc = make_row_map(&tm_r, out_fp8, rows, cols)) != MX8_OK) return rc;
     int grid = sm_count();
     if (grid <= 0) return MX8_ERR_CUDA;
     const int tiles = p.tiles_r * p.tiles_c;
     if (grid > tiles) grid = tiles;
-    return launch<8, 1, SRC_SWIGLU_BWD, true, true>(tm_g, tm_u, tm_d, tm_t, p, grid, static_cast<cudaStream_t>(stream));
+    return launch<8, 1, SRC_SWIGLU_BWD, true, true, (MX8_Q_MOE_RTMA != 0)>(tm_g, tm_u, tm_d, tm_t, tm_r, p, grid, static_cast<cudaStream_t>(stream));
 }
 
 // Both gradients from one pass over gate, up and d_hidden (each input is read once instead of twice).
@@ -671,10 +749,13 @@ extern "C" int mx8_swiglu_bwd_quantize_both_window(const void* gate_fp8, const v
     if ((rc = make_tmap(&tm_d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, d_hidden, dims, strides2, box, CU_TENSOR_MAP_SWIZZLE_NONE)) != MX8_OK) return rc;
     if ((rc = make_transposed_map(&tm_t, d_gate_fp8_t, 1, rows, cols)) != MX8_OK) return rc;
     if ((rc = make_transposed_map(&tm_t2, d_up_fp8_t, 1, rows, cols)) != MX8_OK) return rc;
+    CUtensorMap tm_r, tm_r2;
+    if ((rc = make_row_map(&tm_r, d_gate_fp8, rows, cols)) != MX8_OK) return rc;
+    if ((rc = make_row_map(&tm_r2, d_up_fp8, rows, cols)) != MX8_OK) return rc;
     int grid = sm_count();
     if (grid <= 0) return MX8_ERR_CUDA;
     const int tiles = p.tiles_r * p.tiles_c;
     if (grid > tiles) grid = tiles;
     apply_window(p, grid, window);
-    return launch<8, 1, SRC_SWIGLU_BWD, true, true>(tm_g, tm_u, tm_d, tm_t, p, grid, static_cast<cudaStream_t>(stream), &tm_t2);
+    return launch<8, 1, SRC_SWIGLU_BWD, true, true, (MX8_Q_MOE_RTMA != 0)>(tm_g, tm_u, tm_d, tm_t, tm_r, p, grid, static_cast<cudaStream_t>(stream), &tm_t2, &tm_r2);
 }

@@ -80,8 +80,10 @@ MX8_API int mx8_gemm(const void* A, const void* A_sc, const void* B, const void*
 
 /* Same contract as mx8_gemm with the kernel variant chosen by the caller:
  *   cta_group 2 = one 256x256 tile per CTA pair (cluster of 2), 1 = one 128x256 tile per CTA,
- *   0 = library default; max_ctas caps the persistent grid (0 = all SMs). Used by the tests and
- *   the benchmark's ablations. */
+ *   0 = library default, 3 = as 2 but the tiles of a short last round are never cut into two
+ *   128-column halves (the default does that when the last round of the persistent schedule would
+ *   occupy at most half of the CTA pairs); max_ctas caps the persistent grid (0 = all SMs).
+ *   Used by the tests and the benchmark's ablations. */
 MX8_API int mx8_gemm_ex(const void* A, const void* A_sc, const void* B, const void* B_sc, void* C,
                 int M, int N, int K, int c_dtype, int cta_group, int max_ctas, void* stream);
 

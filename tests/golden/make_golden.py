@@ -154,9 +154,9 @@ def moe_fixture(ref_root):
         sc = sc.view(E * R // 128, 4, 32, C // 128, 4).permute(0, 3, 2, 1, 4).contiguous().view(E * R // 128, C // 128, 32, 16)
         return torch.stack(fp8), sc
 
-    E, H, I, Ts, Is = 2, 256, 128, 32, 64
+    E, H, I, Ts, Is = 2, 256, 256, 32, 64             # the grouped GEMM wants whole 256-column tiles
     tokens_per_expert = torch.tensor([256, 256], dtype=torch.int32)
-    valid_rows = [200, 130]                                     # the rest of every segment is padding: zero rows
+    valid_rows = [96, 40]                                       # the rest of every segment is padding: zero rows
     R = int(tokens_per_expert.sum())
     g = torch.Generator().manual_seed(2022)
     rn = lambda *shape: torch.randn(*shape, generator=g)

@@ -106,7 +106,7 @@ def _fixture(golden_dir):
 
 def test_expert_mlp_oracle_reproduces_the_reference_functions(golden_dir):
     # moe_fwd_bwd.npz holds inputs and outputs of the reference harness's mlp_swiglu_fwd_ref / mlp_swiglu_bwd_ref
-    # (two experts, segments of 256 rows with 200 and 130 live rows).  Both sides run the same fp32 products on CPU,
+    # (two experts, segments of 256 rows with 96 and 40 live rows).  Both sides run the same fp32 products on CPU,
     # so bf16 results may differ only where an fp32 sum lands on a rounding boundary: equality is asked of the
     # quantized bytes and of nearly all bf16 elements, closeness of the rest.
     z, bf, w = _fixture(golden_dir)
