@@ -95,7 +95,6 @@ struct Params {
     int num_groups;
     int group_b_rows;                   // rows of B per group (N)
     int k_steps2;                       // second operand pair accumulated into the same tile (0 = none)
-    int split_tail;                     // 1: the tiles of a short last wave are computed as two 128-column halves each
     int wgrad;                          // 1: one output matrix per group, K runs over the group's rows of A^T / B^T
     int group_c_rows;                   // wgrad: rows of C per group (M)
     int dbg;                            // ablation switches (MX8_GEMM_DEBUG, timing only, results are wrong):
@@ -125,40 +124,11 @@ struct TileInfo {
     int b_base;        // first row of B for this tile (before the CTA's own offset)
     int c_row;         // first row of C for this tile (before the CTA's own offset)
     int k0, kcount;    // first K step and number of K steps
-    int n_off;         // first column inside the 256-column tile (128 for the second half of a split tile)
-    int units;         // 32-column units of the accumulator in use: 8, or 4 for half a tile
 };
-
-// Work list of a launch.  The tiles are dealt out round-robin, `clusters` at a time; when the last round would
-// occupy at most half of the clusters, each of its tiles is cut into two 128-column halves (the MMAs take
-// N = 128), so that round lasts about half as long.  Work item w < split_from is tile w; above it, items
-// come in pairs: tile split_from + (w - split_from) / 2, half (w - split_from) % 2.
-struct WorkList {
-    int items;         // work items in total
-    int split_from;    // first tile that is cut in two (== number of tiles when nothing is cut)
-};
-
-__device__ __forceinline__ WorkList work_list(int num_tiles, int clusters, int split_tail) {
-    WorkList wl{num_tiles, num_tiles};
-    const int tail = num_tiles % clusters;
-    if (split_tail && tail > 0 && 2 * tail <= clusters) {
-        wl.split_from = num_tiles - tail;
-        wl.items = num_tiles + tail;
-    }
-    return wl;
-}
 
 template <int CG>
-__device__ __forceinline__ TileInfo tile_info(int w, const WorkList& wl, const Params& p, int tiles_m, const int* seg_end, int tm0 = 0) {
+__device__ __forceinline__ TileInfo tile_info(int t, const Params& p, int tiles_m, const int* seg_end, int tm0 = 0) {
     TileInfo ti;
-    int t = w;
-    ti.n_off = 0;
-    ti.units = BN / 32;
-    if (w >= wl.split_from) {
-        t = wl.split_from + ((w - wl.split_from) >> 1);
-        ti.n_off = ((w - wl.split_from) & 1) * (BN / 2);
-        ti.units = BN / 64;
-    }
     if (p.wgrad) {
         const int per_group = tiles_m * p.tiles_n;
         const int e = t / per_group;
@@ -278,8 +248,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         }
         __syncthreads();
     }
-    const WorkList wl = work_list(tiles_m * p.tiles_n * (p.wgrad ? p.num_groups : 1), num_clusters, p.split_tail);
-    const int num_tiles = wl.items;                     // work items: whole tiles, then the halves of a split last round
+    const int num_tiles = tiles_m * p.tiles_n * (p.wgrad ? p.num_groups : 1);
 
     if (warp == 0) {
         // ------------------------------------------------------------------ producer
@@ -291,14 +260,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             const uint32_t full_leader0 = CG == 2 ? map_to_cta(full0, 0) : full0;
             bool ok = true;
             for (int t = cluster; t < num_tiles && ok; t += num_clusters) {
-                const TileInfo ti = tile_info<CG>(t, wl, p, tiles_m, seg_end, tm0);
+                const TileInfo ti = tile_info<CG>(t, p, tiles_m, seg_end, tm0);
                 const int a_row = (__shfl_sync(0xFFFFFFFFu, ti.tm, 0) * CG + static_cast<int>(rank)) * 128;
                 const int b_base = __shfl_sync(0xFFFFFFFFu, ti.b_base, 0);
                 const int kcount_t = __shfl_sync(0xFFFFFFFFu, ti.kcount, 0), k0_t = __shfl_sync(0xFFFFFFFFu, ti.k0, 0);
-                // half a tile: the MMA reads the first N/2 rows of each CTA's B tile, so the box starts at the half's
-                // rows (it still fetches a full box; the rows beyond the half are not used)
-                const int n_off = __shfl_sync(0xFFFFFFFFu, ti.n_off, 0), units_t = __shfl_sync(0xFFFFFFFFu, ti.units, 0);
-                const int b_row = b_base + n_off + static_cast<int>(rank) * (C::B_ROWS * units_t / 8);
+                const int b_row = b_base + static_cast<int>(rank) * C::B_ROWS;
                 for (int ks = 0; ks < kcount_t; ++ks) {
                     if (!__all_sync(0xFFFFFFFFu, mbar_wait(empty0 + stage * 8, ph ^ 1, ab, DEV_TIMEOUT_EMPTY))) { ok = false; break; }
                     const uint32_t a_dst = base + C::a_off + stage * C::A_BYTES;
@@ -370,7 +336,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             const bool do_cp = !F16 && !(p.dbg & (8 | 16)), do_mma = !(p.dbg & 1);
             const int my_tiles = cluster < num_tiles ? (num_tiles - cluster + num_clusters - 1) / num_clusters : 0;
             long long remaining = 0;                             // K steps whose scales are not copied yet
-            for (int t = cluster; t < num_tiles; t += num_clusters) remaining += tile_info<CG>(t, wl, p, tiles_m, seg_end, tm0).kcount;
+            for (int t = cluster; t < num_tiles; t += num_clusters) remaining += tile_info<CG>(t, p, tiles_m, seg_end, tm0).kcount;
             bool ok = true;
             // wait for a stage and copy its scale tiles into the next TMEM scale slot
             auto copy_scales = [&]() -> bool {
@@ -403,17 +369,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     if (!(p.dbg & 128) && !__all_sync(0xFFFFFFFFu, mbar_wait<true>(drained, (it - 1) & 1, ab, DEV_TIMEOUT_TMEM_FREE))) { ok = false; break; }
                     tc_fence_after();
                 }
-                const TileInfo ti = tile_info<CG>(cluster + it * num_clusters, wl, p, tiles_m, seg_end, tm0);
-                const int kcount = __shfl_sync(0xFFFFFFFFu, ti.kcount, 0);
-                // half a tile: N = 128 in the instruction descriptor, B scales of the half's 128 columns
-                const uint32_t half_tile = __shfl_sync(0xFFFFFFFFu, ti.units, 0) == BN / 64 ? 1u : 0u;
-                const uint32_t id_n = half_tile ? (static_cast<uint32_t>((BN >> 3) ^ (BN >> 4)) << 17) : 0u;
-                const uint32_t sfb_col = 4u + static_cast<uint32_t>(__shfl_sync(0xFFFFFFFFu, ti.n_off, 0)) / 32u;
+                const int kcount = __shfl_sync(0xFFFFFFFFu, tile_info<CG>(cluster + it * num_clusters, p, tiles_m, seg_end, tm0).kcount, 0);
                 for (int ks = 0; ks < kcount; ++ks) {
                     if (remaining > 0 && !copy_scales()) { ok = false; break; }
                     if constexpr (F16) {
                         if (do_mma && leader) {
-                            const uint32_t IDF = idesc_bf16(128 * CG, BN) ^ id_n;
+                            constexpr uint32_t IDF = idesc_bf16(128 * CG, BN);
                             tc_mma_bf16_lo<CG, 2>(d_tmem, a_lo, b_lo, IDF, static_cast<uint32_t>(ks));
                             tc_mma_bf16_lo<CG, 1>(d_tmem, a_lo + 2, b_lo + 2, IDF);
                             tc_mma_bf16_lo<CG, 1>(d_tmem, a_lo + 4, b_lo + 4, IDF);
@@ -421,10 +382,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                         }
                     } else if (do_mma && leader) {
                         // each K=32 slice lies 32 bytes further inside the swizzle atom: +2 in the address field
-                        tc_mma_mxf8_lo<CG, 2>(d_tmem, a_lo, b_lo, ID0 ^ id_n, sf_mma, sf_mma + sfb_col, static_cast<uint32_t>(ks));
-                        tc_mma_mxf8_lo<CG, 1>(d_tmem, a_lo + 2, b_lo + 2, ID1 ^ id_n, sf_mma, sf_mma + sfb_col);
-                        tc_mma_mxf8_lo<CG, 1>(d_tmem, a_lo + 4, b_lo + 4, ID2 ^ id_n, sf_mma, sf_mma + sfb_col);
-                        tc_mma_mxf8_lo<CG, 1>(d_tmem, a_lo + 6, b_lo + 6, ID3 ^ id_n, sf_mma, sf_mma + sfb_col);
+                        tc_mma_mxf8_lo<CG, 2>(d_tmem, a_lo, b_lo, ID0, sf_mma, sf_mma + 4, static_cast<uint32_t>(ks));
+                        tc_mma_mxf8_lo<CG, 1>(d_tmem, a_lo + 2, b_lo + 2, ID1, sf_mma, sf_mma + 4);
+                        tc_mma_mxf8_lo<CG, 1>(d_tmem, a_lo + 4, b_lo + 4, ID2, sf_mma, sf_mma + 4);
+                        tc_mma_mxf8_lo<CG, 1>(d_tmem, a_lo + 6, b_lo + 6, ID3, sf_mma, sf_mma + 4);
                     }
                     if (leader) tc_commit<CG>(empty_bar);        // stage reusable once these MMAs retire
                     sf_mma ^= 16;
@@ -446,7 +407,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             uint32_t slot = 0, ph = 0;
             bool ok = true;
             for (int t = cluster; t < num_tiles && ok; t += num_clusters) {
-                const TileInfo ti = tile_info<CG>(t, wl, p, tiles_m, seg_end, tm0);
+                const TileInfo ti = tile_info<CG>(t, p, tiles_m, seg_end, tm0);
                 const int a_row = (__shfl_sync(0xFFFFFFFFu, ti.tm, 0) * CG + static_cast<int>(rank)) * 128;
                 const int kcount_t = __shfl_sync(0xFFFFFFFFu, ti.kcount, 0), k0_t = __shfl_sync(0xFFFFFFFFu, ti.k0, 0);
                 for (int ks = 0; ks < kcount_t; ++ks) {
@@ -477,7 +438,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             uint32_t slot = 0, sph = 0;        // bf16 staging ring
             bool ok = true;
             for (int t = cluster; t < num_tiles && ok; t += num_clusters) {
-                const int kcount_t = tile_info<CG>(t, wl, p, tiles_m, seg_end, tm0).kcount;
+                const int kcount_t = tile_info<CG>(t, p, tiles_m, seg_end, tm0).kcount;
                 for (int ks = 0; ks < kcount_t; ++ks) {
                     if (!mbar_wait(afull0 + slot * 8, sph, ab, DEV_TIMEOUT_FULL)) { ok = false; break; }
                     if (!mbar_wait(empty0 + stage * 8, ph ^ 1, ab, DEV_TIMEOUT_EMPTY)) { ok = false; break; }   // MMAs of the previous use retired
@@ -528,7 +489,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         int it = 0;
         bool ok = true;
         for (int t = cluster; t < num_tiles && ok; t += num_clusters, ++it) {
-            const TileInfo ti = tile_info<CG>(t, wl, p, tiles_m, seg_end, tm0);
+            const TileInfo ti = tile_info<CG>(t, p, tiles_m, seg_end, tm0);
             const int tn = ti.tn;
             const bool zero_tile = ti.kcount == 0;                // wgrad of a group without rows: nothing was accumulated
             const int acc = it & 1;
@@ -536,15 +497,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             tc_fence_after();
             const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + (acc ? ACC1_COL : 0);
             const int row0 = ti.c_row + static_cast<int>(rank) * 128 + q * 32;
-            const int col0 = tn * BN + ti.n_off;
-            const int units = EPI_WARPS == 4 ? ti.units : EPI_UNITS;   // half a tile fills the first four units only
+            const int col0 = tn * BN;
             uint32_t scword = 0;                                 // four scale bytes of one row (c_mode 2)
             uint8_t* sc_row = nullptr;                           // c_mode 3: where this lane's row goes
 #pragma unroll 1
-            for (int s = 0; s < units; ++s) {
+            for (int s = 0; s < EPI_UNITS; ++s) {
                 // 32-column unit of this warp's half; the unit the two accumulators share (the last of
                 // accumulator 0, the first of accumulator 1) is the first one its warp drains
-                const int u = half * EPI_UNITS + (acc ? s : units - 1 - s);
+                const int u = half * EPI_UNITS + (acc ? s : EPI_UNITS - 1 - s);
                 uint32_t r[32];
                 tc_ld_32x32(t_acc + u * 32, r);
                 tc_wait_ld(r);
@@ -789,7 +749,6 @@ struct Grouping {
     int K2 = 0;
     // weight-gradient form: A is A^T [M][K], B is B^T [N][K] with K = all rows; one C [M][N] per group
     bool wgrad = false;
-    bool no_split = false;           // never cut the tiles of a short last round in two (comparisons only)
 };
 
 template <int CG, bool F16 = false, bool A16 = false>
@@ -822,7 +781,6 @@ static int run(const void* A, const void* A_sc, const void* B, const void* B_sc,
     p.rows_cap = c_rows;
     p.k_steps2 = gr.K2 / BK;
     p.wgrad = gr.wgrad ? 1 : 0;
-    p.split_tail = (EPI_WARPS == 4 && !A16 && !gr.no_split) ? 1 : 0;
     p.group_c_rows = M;
     p.rows_dev = gr.rows_dev;
     p.row_begin_dev = gr.row_begin_dev;
@@ -844,9 +802,7 @@ static int run(const void* A, const void* A_sc, const void* B, const void* B_sc,
     if (grid <= 0) return MX8_ERR_CUDA;
     if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
     const int tiles = p.tiles_m * p.tiles_n * (gr.wgrad ? groups : 1);
-    // a launch with fewer tiles than half the clusters is all "last round": keep two clusters per tile
-    const int want = p.split_tail ? 2 * tiles : tiles;
-    if (grid > want * CG) grid = want * CG;
+    if (grid > tiles * CG) grid = tiles * CG;
     grid = (grid / CG) * CG;
     if (grid <= 0) grid = CG;
 
@@ -878,16 +834,15 @@ extern "C" int mx8_gemm_ex(const void* A, const void* A_sc, const void* B, const
     using namespace mx8;
     if (!A || !A_sc || !B || !B_sc || !C) return MX8_ERR_ARG;
     if (c_dtype != MX8_C_BF16 && c_dtype != MX8_C_F32) return MX8_ERR_ARG;
-    if (cta_group < 0 || cta_group > 3 || max_ctas < 0) return MX8_ERR_ARG;
+    if (cta_group < 0 || cta_group > 2 || max_ctas < 0) return MX8_ERR_ARG;
     if (M <= 0 || N <= 0 || K <= 0 || M % 128 || N % 128 || K % 128) return MX8_ERR_SHAPE;
     if (!aligned16(A) || !aligned16(A_sc) || !aligned16(B) || !aligned16(B_sc) || !aligned16(C)) return MX8_ERR_ALIGN;
     int rc = check_device_sm100();
     if (rc != MX8_OK) return rc;
     if (cta_group == 0) cta_group = (M <= 128) ? 1 : 2;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    gemm::Grouping none;
-    none.no_split = cta_group == 3;
-    if (cta_group >= 2) return gemm::run<2>(A, A_sc, B, B_sc, C, M, N, K, c_dtype, max_ctas, none, st);
+    const gemm::Grouping none;
+    if (cta_group == 2) return gemm::run<2>(A, A_sc, B, B_sc, C, M, N, K, c_dtype, max_ctas, none, st);
     return gemm::run<1>(A, A_sc, B, B_sc, C, M, N, K, c_dtype, max_ctas, none, st);
 }
 

@@ -2,7 +2,9 @@
 // finishes the layer.
 //
 // combine: row r of y_routed (bf16, `hidden` wide) goes to row peer_token_idx[r] of the combine
-// buffer of rank peer_rank[r]; rows with peer_rank < 0 (padding) are skipped.  The destination is
+// buffer of rank peer_rank[r]; rows with peer_rank < 0 (padding) are skipped, and so is everything a
+// schedule that overflowed its capacity could make the kernel touch: rows at or beyond `capacity`, a
+// rank outside [0, world), a destination row outside the buffer.  The destination is
 // that rank's memory, written directly with 16-byte stores over NVLink (one warp per row, 512 bytes
 // per warp instruction).  The copy is exact.  Replaces combine_kernel,
 // blackwell-ultra/022-moe-dispatch-mlp-swiglu-combine-mxfp8-bw.cu:830-922.
@@ -23,11 +25,14 @@ struct CombineParams {
     const int* num_tokens;       // device: one past the last row
     const int* row_begin;        // device: first row (row window of a minibatch), nullptr = 0
     int hidden;
+    int capacity;                // rows y_routed and the two index arrays have
+    int world;
+    long long dst_rows;          // rows of every destination buffer
     uint8_t* dst[16];            // every rank's combine buffer [tokens*topk][hidden] bf16
 };
 
 __global__ void __launch_bounds__(256) combine_kernel(CombineParams p) {
-    const int rows = *p.num_tokens;
+    const int rows = min(*p.num_tokens, p.capacity);
     const int row0 = p.row_begin ? *p.row_begin : 0;
     const int lane = threadIdx.x & 31;
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -35,9 +40,11 @@ __global__ void __launch_bounds__(256) combine_kernel(CombineParams p) {
     const size_t row_bytes = static_cast<size_t>(p.hidden) * 2;
     for (int r = row0 + warp; r < rows; r += warps) {
         const int pr = p.peer_rank[r];
-        if (pr < 0) continue;
+        if (pr < 0 || pr >= p.world) continue;
+        const int pt = p.peer_token_idx[r];
+        if (pt < 0 || pt >= p.dst_rows) continue;
         const uint4* src = reinterpret_cast<const uint4*>(p.y + r * row_bytes);
-        uint4* dst = reinterpret_cast<uint4*>(p.dst[pr] + static_cast<size_t>(p.peer_token_idx[r]) * row_bytes);
+        uint4* dst = reinterpret_cast<uint4*>(p.dst[pr] + static_cast<size_t>(pt) * row_bytes);
         const int n16 = p.hidden / 8;
         for (int i = lane; i < n16; i += 128) {
             // four independent 16-byte copies in flight per lane
@@ -126,15 +133,17 @@ __global__ void __launch_bounds__(256) bwd_prologue_kernel(const uint8_t* d_out,
 }  // namespace mx8
 
 extern "C" int mx8_moe_combine(const void* y_routed, const void* peer_rank, const void* peer_token_idx, const void* num_tokens,
-                               int hidden, void* const* combine_ptrs, int world, void* stream) {
-    return mx8_moe_combine_window(y_routed, peer_rank, peer_token_idx, num_tokens, hidden, combine_ptrs, world, nullptr, stream);
+                               int capacity, int hidden, void* const* combine_ptrs, int world, long long combine_rows, void* stream) {
+    return mx8_moe_combine_window(y_routed, peer_rank, peer_token_idx, num_tokens, capacity, hidden, combine_ptrs, world, combine_rows,
+                                  nullptr, stream);
 }
 
 extern "C" int mx8_moe_combine_window(const void* y_routed, const void* peer_rank, const void* peer_token_idx, const void* num_tokens,
-                                      int hidden, void* const* combine_ptrs, int world, const mx8_window* window, void* stream) {
+                                      int capacity, int hidden, void* const* combine_ptrs, int world, long long combine_rows,
+                                      const mx8_window* window, void* stream) {
     using namespace mx8;
     if (!y_routed || !peer_rank || !peer_token_idx || !num_tokens || !combine_ptrs) return MX8_ERR_ARG;
-    if (world <= 0 || world > 16) return MX8_ERR_ARG;
+    if (world <= 0 || world > 16 || capacity <= 0 || combine_rows <= 0) return MX8_ERR_ARG;
     if (hidden <= 0 || hidden % 8) return MX8_ERR_SHAPE;
     if (!aligned16(y_routed)) return MX8_ERR_ALIGN;
     moe::CombineParams p{};
@@ -149,6 +158,9 @@ extern "C" int mx8_moe_combine_window(const void* y_routed, const void* peer_ran
     p.peer_token_idx = static_cast<const int*>(peer_token_idx);
     p.num_tokens = static_cast<const int*>(num_tokens);
     p.hidden = hidden;
+    p.capacity = capacity;
+    p.world = world;
+    p.dst_rows = combine_rows;
     int sms = sm_count();
     if (sms <= 0) return MX8_ERR_CUDA;
     if (window) {

@@ -449,11 +449,16 @@ extern "C" int mx8_moe_schedule_static(const void* topk_all, int world, int toke
 // rows.  The windowed entry points take pointers into this array.
 namespace mx8 {
 namespace moe {
-__global__ void __launch_bounds__(256) minibatch_bounds_kernel(const int* tokens_per_expert, int experts, int minibatches, int* bounds) {
+struct ExpertSplit {
+    int first[65];       // first expert of every group, first[minibatches] = experts; first[0] < 0: even split
+};
+
+__global__ void __launch_bounds__(256) minibatch_bounds_kernel(const int* tokens_per_expert, int experts, int minibatches, int* bounds,
+                                                               const ExpertSplit split) {
     // one warp per bound: sum of the segments of the experts before the group's first one
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     for (int b = warp; b <= minibatches; b += warps) {
-        const int first = static_cast<int>(static_cast<long long>(b) * experts / minibatches);
+        const int first = split.first[0] < 0 ? static_cast<int>(static_cast<long long>(b) * experts / minibatches) : split.first[b];
         int sum = 0;
         for (int e = lane; e < first; e += 32) sum += tokens_per_expert[e];
 #pragma unroll
@@ -466,13 +471,28 @@ __global__ void __launch_bounds__(256) minibatch_bounds_kernel(const int* tokens
 
 extern "C" int mx8_moe_minibatch_bounds(const void* tokens_per_expert, int num_local_experts, int minibatches, void* bounds,
                                         void* stream) {
+    return mx8_moe_minibatch_bounds_split(tokens_per_expert, num_local_experts, minibatches, nullptr, bounds, stream);
+}
+
+extern "C" int mx8_moe_minibatch_bounds_split(const void* tokens_per_expert, int num_local_experts, int minibatches,
+                                              const int* first_expert, void* bounds, void* stream) {
     using namespace mx8;
     if (!tokens_per_expert || !bounds) return MX8_ERR_ARG;
-    if (num_local_experts <= 0 || minibatches <= 0 || minibatches > num_local_experts) return MX8_ERR_ARG;
+    if (num_local_experts <= 0 || minibatches <= 0 || minibatches > num_local_experts || minibatches > 64) return MX8_ERR_ARG;
+    moe::ExpertSplit split;
+    split.first[0] = -1;
+    if (first_expert) {
+        if (first_expert[0] != 0 || first_expert[minibatches] != num_local_experts) return MX8_ERR_ARG;
+        for (int b = 0; b <= minibatches; ++b) {
+            if (b > 0 && first_expert[b] < first_expert[b - 1]) return MX8_ERR_ARG;
+            split.first[b] = first_expert[b];
+        }
+    }
     int rc = check_device_sm100();
     if (rc != MX8_OK) return rc;
     moe::minibatch_bounds_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const int*>(tokens_per_expert),
-                                                                                num_local_experts, minibatches, static_cast<int*>(bounds));
+                                                                                num_local_experts, minibatches, static_cast<int*>(bounds),
+                                                                                split);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
         note_cuda_error("minibatch bounds launch", cudaGetErrorString(e));

@@ -13,8 +13,6 @@
 //   schedule(...), dispatch_mlp_swiglu_combine_fwd(...), fwd_epilogue(...)
 //                                                         blackwell-ultra/022-…-mxfp8-bw.cu:2996-3030 (forward, routed experts)
 // Errors raise RuntimeError (the reference prints and exits).
-#include <ATen/cuda/CUDAEvent.h>
-#include <c10/cuda/CUDACachingAllocator.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <c10/cuda/CUDAStream.h>
 #include <torch/extension.h>
@@ -151,42 +149,28 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> schedule(const at::Te
     return {peer_rank, peer_tok, num_tokens, tpe};
 }
 
-void grouped(const at::Tensor& A, const at::Tensor& A_sc, const at::Tensor& B, const at::Tensor& B_sc, const at::Tensor& C,
-             const at::Tensor& C_sc, const at::Tensor& num_tokens, const at::Tensor& tokens_per_expert) {
-    const bool q = C_sc.defined();
-    check(mx8_gemm_grouped(A.data_ptr(), A_sc.data_ptr(), B.data_ptr(), B_sc.data_ptr(), C.data_ptr(), q ? C_sc.data_ptr() : nullptr,
-                           static_cast<int>(A.size(0)), static_cast<int>(B.size(1)), static_cast<int>(A.size(1)),
-                           q ? MX8_C_MXFP8 : MX8_C_BF16, num_tokens.data_ptr(), tokens_per_expert.data_ptr(),
-                           static_cast<int>(B.size(0)), stream()),
-          "expert grouped gemm");
+// pointer of an optional / possibly undefined tensor
+const void* optr(const std::optional<at::Tensor>& t) { return (t.has_value() && t->defined()) ? t->data_ptr() : nullptr; }
+void* mptr(const at::Tensor& t) { return t.defined() ? t.data_ptr() : nullptr; }
+
+mx8_moe_dims moe_dims(int world, int64_t tokens, int64_t H, int64_t I, int64_t Is, int64_t E, int topk, int64_t cap, int num_comm_sms,
+                      int minibatch_size) {
+    mx8_moe_dims d{};
+    d.world = world;
+    d.tokens = static_cast<int>(tokens);
+    d.hidden = static_cast<int>(H);
+    d.intermediate = static_cast<int>(I);
+    d.shared_intermediate = static_cast<int>(Is);
+    d.num_local_experts = static_cast<int>(E);
+    d.topk = topk;
+    d.capacity = static_cast<int>(cap);
+    d.num_comm_sms = num_comm_sms;
+    d.minibatch_size = minibatch_size;
+    return d;
 }
 
-// ---- shared (bf16) expert: the kind::f16 form of the GEMM kernel and its element-wise companions
-at::Tensor bf16_gemm(const at::Tensor& a, const at::Tensor& b, const at::Tensor* a2 = nullptr, const at::Tensor* b2 = nullptr) {
-    const int64_t M = a.size(0), K = a.size(1), N = b.size(0), K2 = a2 ? a2->size(1) : 0;
-    at::Tensor c = at::empty({M, N}, a.options().dtype(at::kBFloat16));
-    check(mx8_gemm_bf16_dual(dptr(a, "A", M * K), dptr(b, "B", N * K), a2 ? dptr(*a2, "A2", M * K2) : nullptr,
-                             b2 ? dptr(*b2, "B2", N * K2) : nullptr, c.data_ptr(), static_cast<int>(M), static_cast<int>(N),
-                             static_cast<int>(K), static_cast<int>(K2), MX8_C_BF16, stream()),
-          "bf16 gemm");
-    return c;
-}
-
-at::Tensor bf16_transpose(const at::Tensor& x) {
-    at::Tensor out = at::empty({x.size(1), x.size(0)}, x.options());
-    check(mx8_transpose_bf16(dptr(x, "x"), out.data_ptr(), static_cast<int>(x.size(0)), static_cast<int>(x.size(1)), stream()),
-          "bf16 transpose");
-    return out;
-}
-
-// two side streams per device for the transfer legs of the pipelined layer, taken from torch's pool once
-std::pair<c10::cuda::CUDAStream, c10::cuda::CUDAStream> side_streams(c10::DeviceIndex dev) {
-    static std::vector<std::optional<std::pair<c10::cuda::CUDAStream, c10::cuda::CUDAStream>>> cache(64);
-    auto& slot = cache[static_cast<size_t>(dev) & 63];
-    if (!slot.has_value()) slot.emplace(c10::cuda::getStreamFromPool(false, dev), c10::cuda::getStreamFromPool(false, dev));
-    return *slot;
-}
-
+// The layer itself is one C-ABI call (mx8_moe_fwd); this function allocates what the reference's host function
+// allocates (blackwell-ultra/022-…-mxfp8-bw.cu:2040-2075) and returns its thirteen tensors.
 std::vector<at::Tensor> dispatch_mlp_swiglu_combine_fwd(
     const at::Tensor& x, const std::vector<int64_t>& x_ptrs, const at::Tensor& combine_buffer,
     const std::vector<int64_t>& combine_buffer_ptrs, const std::optional<at::Tensor>& w_shared_gate, const at::Tensor& w_routed_gate,
@@ -197,115 +181,62 @@ std::vector<at::Tensor> dispatch_mlp_swiglu_combine_fwd(
     int minibatch_size) {
     TORCH_CHECK(w_routed_gate.dim() == 3 && w_routed_down.dim() == 3, "routed weights must be [E, rows, cols]");
     TORCH_CHECK(x_ptrs.size() == combine_buffer_ptrs.size() && !x_ptrs.empty() && x_ptrs.size() <= 16, "1..16 ranks");
+    TORCH_CHECK(x.dim() == 2 && x.scalar_type() == at::kBFloat16, "x must be bf16 [tokens, hidden]");
+    (void)combine_buffer;
     c10::cuda::CUDAGuard guard(x.device());
-    const int64_t I = w_routed_gate.size(1), H = w_routed_gate.size(2), cap = schedule_peer_rank.size(0);
+    const int64_t E = w_routed_gate.size(0), I = w_routed_gate.size(1), H = w_routed_gate.size(2), cap = schedule_peer_rank.size(0);
+    const int64_t T = x.size(0);
+    const bool shared = optr(w_shared_gate) && optr(w_shared_up) && optr(w_shared_down);
+    const int64_t Is = shared ? w_shared_gate->size(0) : 0;
     auto fp8 = x.options().dtype(at::kFloat8_e4m3fn);
     auto u8 = x.options().dtype(at::kByte);
-    at::Tensor x_fp8 = at::empty({cap, H}, fp8), x_sc = at::empty({cap / 128, H / 128, 32, 16}, u8);
     at::Tensor x_fp8_t = at::empty({H, cap}, fp8), x_sc_t = at::empty({H / 128, cap / 128, 32, 16}, u8);
     at::Tensor gate_fp8 = at::empty({cap, I}, fp8), gate_sc = at::empty({cap / 128, I / 128, 32, 16}, u8);
     at::Tensor up_fp8 = at::empty({cap, I}, fp8), up_sc = at::empty({cap / 128, I / 128, 32, 16}, u8);
-    at::Tensor h_fp8 = at::empty({cap, I}, fp8), h_sc = at::empty({cap / 128, I / 128, 32, 16}, u8);
     at::Tensor h_fp8_t = at::empty({I, cap}, fp8), h_sc_t = at::empty({I / 128, cap / 128, 32, 16}, u8);
     at::Tensor y_routed = at::empty({cap, H}, x.options());
+    at::Tensor gate_shared, up_shared, hidden_shared, y_shared;
+    if (shared) {
+        gate_shared = at::empty({T, Is}, x.options());
+        up_shared = at::empty({T, Is}, x.options());
+        hidden_shared = at::empty({T, Is}, x.options());
+        y_shared = at::empty({T, H}, x.options());
+    }
     std::vector<const void*> xp(x_ptrs.size());
     std::vector<void*> cp(x_ptrs.size());
     for (size_t i = 0; i < x_ptrs.size(); ++i) {
         xp[i] = reinterpret_cast<const void*>(x_ptrs[i]);
         cp[i] = reinterpret_cast<void*>(combine_buffer_ptrs[i]);
     }
-    const int world = static_cast<int>(x_ptrs.size());
-    const int E = static_cast<int>(w_routed_gate.size(0));
-    int nb = 1;
-    if (num_comm_sms > 0 && minibatch_size > 0) nb = static_cast<int>(std::min<int64_t>(E, (cap + minibatch_size - 1) / minibatch_size));
-    if (nb > 1) {
-        // Minibatches of consecutive experts: dispatch of group b+1 (num_comm_sms multiprocessors, own stream) and
-        // combine of group b-1 (third stream) run beside the GEMMs of group b.  Same kernels on row windows, so the
-        // outputs are bit-identical to the single sequence below.
-        const c10::cuda::CUDAStream main = c10::cuda::getCurrentCUDAStream();
-        const auto [s_disp, s_comb] = side_streams(main.device_index());
-        at::Tensor bounds = at::empty({nb + 1}, schedule_peer_rank.options());
-        int sms = 0;
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, main.device_index());
-        const int math_sms = std::max(2, (sms - num_comm_sms) & ~1);
-        check(mx8_moe_minibatch_bounds(iptr(tokens_per_expert, "tokens_per_expert"), E, nb, bounds.data_ptr(), main.stream()), "minibatch bounds");
-        const int* bp = static_cast<const int*>(bounds.data_ptr());
-        at::cuda::CUDAEvent start;
-        start.record(main);
-        start.block(s_disp);
-        start.block(s_comb);
-        std::vector<at::cuda::CUDAEvent> disp_done(nb);
-        for (int b = 0; b < nb; ++b) {
-            const mx8_window w{bp + b, bp + b + 1, b == 0 ? 0 : num_comm_sms};
-            check(mx8_moe_dispatch_quantize_window(xp.data(), world, static_cast<int>(H), topk, iptr(schedule_peer_rank, "schedule_peer_rank"),
-                                                   iptr(schedule_peer_token_idx, "schedule_peer_token_idx"), iptr(num_tokens, "num_tokens"),
-                                                   static_cast<int>(cap), x_fp8.data_ptr(), x_sc.data_ptr(), x_fp8_t.data_ptr(),
-                                                   x_sc_t.data_ptr(), &w, s_disp.stream()),
-                  "dispatch + quantize (window)");
-            disp_done[b].record(s_disp);
-        }
-        auto gemm_w = [&](const at::Tensor& a, const at::Tensor& a_sc, const at::Tensor& wt, const at::Tensor& wt_sc, const at::Tensor& c,
-                          const at::Tensor& c_sc, const mx8_window& w) {
-            const bool q = c_sc.defined();
-            check(mx8_gemm_grouped_window(a.data_ptr(), a_sc.data_ptr(), dptr(wt, "w"), dptr(wt_sc, "w_sc"), c.data_ptr(),
-                                          q ? c_sc.data_ptr() : nullptr, static_cast<int>(a.size(0)), static_cast<int>(wt.size(1)),
-                                          static_cast<int>(a.size(1)), q ? MX8_C_MXFP8 : MX8_C_BF16, num_tokens.data_ptr(),
-                                          tokens_per_expert.data_ptr(), E, &w, main.stream()),
-                  "grouped gemm (window)");
-        };
-        for (int b = 0; b < nb; ++b) {
-            disp_done[b].block(main);
-            const mx8_window w{bp + b, bp + b + 1, b == nb - 1 ? 0 : math_sms};
-            gemm_w(x_fp8, x_sc, w_routed_gate, w_routed_gate_sc, gate_fp8, gate_sc, w);
-            gemm_w(x_fp8, x_sc, w_routed_up, w_routed_up_sc, up_fp8, up_sc, w);
-            check(mx8_swiglu_quantize_window(gate_fp8.data_ptr(), gate_sc.data_ptr(), up_fp8.data_ptr(), up_sc.data_ptr(), static_cast<int>(cap),
-                                             static_cast<int>(I), num_tokens.data_ptr(), h_fp8.data_ptr(), h_sc.data_ptr(), h_fp8_t.data_ptr(),
-                                             h_sc_t.data_ptr(), nullptr, &w, main.stream()),
-                  "swiglu + quantize (window)");
-            gemm_w(h_fp8, h_sc, w_routed_down, w_routed_down_sc, y_routed, at::Tensor(), w);
-            at::cuda::CUDAEvent math_done;
-            math_done.record(main);
-            math_done.block(s_comb);
-            // beside GEMMs the combine is held to a few thread blocks: more only queue stores in front of the NVLink ports
-            const mx8_window wc{bp + b, bp + b + 1, b < nb - 1 ? std::max(1, num_comm_sms / 4) : 0};
-            check(mx8_moe_combine_window(y_routed.data_ptr(), schedule_peer_rank.data_ptr(), schedule_peer_token_idx.data_ptr(),
-                                         num_tokens.data_ptr(), static_cast<int>(H), cp.data(), world, &wc, s_comb.stream()),
-                  "combine (window)");
-        }
-        at::cuda::CUDAEvent done;
-        done.record(s_comb);
-        done.block(main);
-        // memory touched by the side streams must not be handed out again before their work has finished
-        for (const at::Tensor* t : {&x_fp8, &x_sc, &x_fp8_t, &x_sc_t, &y_routed, &bounds}) {
-            c10::cuda::CUDACachingAllocator::recordStream(t->storage().data_ptr(), s_disp);
-            c10::cuda::CUDACachingAllocator::recordStream(t->storage().data_ptr(), s_comb);
-        }
-    } else {
-        check(mx8_moe_dispatch_quantize(xp.data(), world, static_cast<int>(H), topk, iptr(schedule_peer_rank, "schedule_peer_rank"),
-                                        iptr(schedule_peer_token_idx, "schedule_peer_token_idx"), iptr(num_tokens, "num_tokens"),
-                                        static_cast<int>(cap), x_fp8.data_ptr(), x_sc.data_ptr(), x_fp8_t.data_ptr(), x_sc_t.data_ptr(), stream()),
-              "dispatch + quantize");
-        grouped(x_fp8, x_sc, w_routed_gate, w_routed_gate_sc, gate_fp8, gate_sc, num_tokens, tokens_per_expert);
-        grouped(x_fp8, x_sc, w_routed_up, w_routed_up_sc, up_fp8, up_sc, num_tokens, tokens_per_expert);
-        check(mx8_swiglu_quantize(gate_fp8.data_ptr(), gate_sc.data_ptr(), up_fp8.data_ptr(), up_sc.data_ptr(), static_cast<int>(cap),
-                                  static_cast<int>(I), num_tokens.data_ptr(), h_fp8.data_ptr(), h_sc.data_ptr(), h_fp8_t.data_ptr(),
-                                  h_sc_t.data_ptr(), nullptr, stream()),
-              "swiglu + quantize");
-        grouped(h_fp8, h_sc, w_routed_down, w_routed_down_sc, y_routed, at::Tensor(), num_tokens, tokens_per_expert);
-        check(mx8_moe_combine(y_routed.data_ptr(), schedule_peer_rank.data_ptr(), schedule_peer_token_idx.data_ptr(), num_tokens.data_ptr(),
-                              static_cast<int>(H), cp.data(), world, stream()),
-              "combine");
-    }
-    // shared expert (bf16), when its weights are given
-    at::Tensor gate_shared, up_shared, hidden_shared, y_shared;
-    if (w_shared_gate.has_value() && w_shared_up.has_value() && w_shared_down.has_value()) {
-        gate_shared = bf16_gemm(x, *w_shared_gate);
-        up_shared = bf16_gemm(x, *w_shared_up);
-        hidden_shared = at::empty_like(gate_shared);
-        check(mx8_swiglu_bf16(gate_shared.data_ptr(), up_shared.data_ptr(), hidden_shared.data_ptr(), gate_shared.numel(), stream()),
-              "shared swiglu");
-        y_shared = bf16_gemm(hidden_shared, *w_shared_down);
-    }
+    mx8_moe_fwd_args a{};
+    a.dims = moe_dims(static_cast<int>(x_ptrs.size()), T, H, I, Is, E, topk, cap, num_comm_sms, minibatch_size);
+    a.x = dptr(x, "x");
+    a.x_ptrs = xp.data();
+    a.combine_ptrs = cp.data();
+    a.w_shared_gate = shared ? optr(w_shared_gate) : nullptr;
+    a.w_shared_up = shared ? optr(w_shared_up) : nullptr;
+    a.w_shared_down = shared ? optr(w_shared_down) : nullptr;
+    a.w_gate = dptr(w_routed_gate, "w_routed_gate");
+    a.w_gate_sc = dptr(w_routed_gate_sc, "w_routed_gate_sc", E * I * H / 32);
+    a.w_up = dptr(w_routed_up, "w_routed_up", E * I * H);
+    a.w_up_sc = dptr(w_routed_up_sc, "w_routed_up_sc", E * I * H / 32);
+    a.w_down = dptr(w_routed_down, "w_routed_down", E * I * H);
+    a.w_down_sc = dptr(w_routed_down_sc, "w_routed_down_sc", E * I * H / 32);
+    a.peer_rank = iptr(schedule_peer_rank, "schedule_peer_rank");
+    a.peer_token_idx = iptr(schedule_peer_token_idx, "schedule_peer_token_idx");
+    a.num_tokens = iptr(num_tokens, "num_tokens");
+    a.tokens_per_expert = iptr(tokens_per_expert, "tokens_per_expert");
+    a.x_fp8_t = x_fp8_t.data_ptr(); a.x_sc_t = x_sc_t.data_ptr();
+    a.gate_shared = mptr(gate_shared); a.gate_fp8 = gate_fp8.data_ptr(); a.gate_sc = gate_sc.data_ptr();
+    a.up_shared = mptr(up_shared); a.up_fp8 = up_fp8.data_ptr(); a.up_sc = up_sc.data_ptr();
+    a.hidden_shared = mptr(hidden_shared); a.hidden_fp8_t = h_fp8_t.data_ptr(); a.hidden_sc_t = h_sc_t.data_ptr();
+    a.y_shared = mptr(y_shared); a.y_routed = y_routed.data_ptr();
+    const size_t need = mx8_moe_fwd_workspace_bytes(&a.dims);
+    TORCH_CHECK(need > 0, "dispatch_mlp_swiglu_combine_fwd: hidden, intermediate and capacity must be multiples of 256");
+    at::Tensor ws = at::empty({static_cast<int64_t>(need)}, u8);
+    a.workspace = ws.data_ptr();
+    a.workspace_bytes = need;
+    check(mx8_moe_fwd(&a, stream()), "dispatch_mlp_swiglu_combine_fwd");
     return {x_fp8_t, x_sc_t, gate_shared, gate_fp8, gate_sc, up_shared, up_fp8, up_sc, hidden_shared, h_fp8_t, h_sc_t, y_shared, y_routed};
 }
 
@@ -350,6 +281,7 @@ at::Tensor bwd_epilogue(const at::Tensor& d_x_shared, const at::Tensor& d_x_rout
 
 using OptT = std::optional<at::Tensor>;
 
+// One C-ABI call (mx8_moe_bwd); allocates and returns the eighteen tensors of the reference's backward binding.
 std::vector<at::Tensor> dispatch_mlp_swiglu_combine_bwd(
     const OptT& d_y_shared, const at::Tensor& d_combine_buffer, const std::vector<int64_t>& d_combine_buffer_ptrs,
     const at::Tensor& d_x_routed_buffer, const std::vector<int64_t>& d_x_routed_buffer_ptrs, const OptT& w_shared_gate_T,
@@ -361,130 +293,81 @@ std::vector<at::Tensor> dispatch_mlp_swiglu_combine_bwd(
     const at::Tensor& hidden_sc_t_routed, const OptT& x_buffer, const std::vector<int64_t>& /*x_buffer_ptrs*/,
     const OptT& /*w_routed_gate*/, const OptT& /*w_routed_gate_sc*/, const OptT& /*w_routed_up*/, const OptT& /*w_routed_up_sc*/,
     const at::Tensor& schedule_peer_rank, const at::Tensor& schedule_peer_token_idx, const at::Tensor& num_tokens,
-    const at::Tensor& tokens_per_expert, int /*topk*/, int num_comm_sms, int /*macrobatch_size*/, int minibatch_size) {
+    const at::Tensor& tokens_per_expert, int topk, int num_comm_sms, int /*macrobatch_size*/, int minibatch_size) {
     TORCH_CHECK(w_routed_gate_T.dim() == 3, "transposed routed weights must be [E, H, I]");
     TORCH_CHECK(!d_combine_buffer_ptrs.empty() && d_combine_buffer_ptrs.size() == d_x_routed_buffer_ptrs.size() &&
                 d_combine_buffer_ptrs.size() <= 16, "1..16 ranks");
+    TORCH_CHECK(topk > 0 && d_combine_buffer.dim() == 2 && d_combine_buffer.size(0) % topk == 0, "d_combine_buffer must be [tokens * topk, hidden]");
+    (void)d_x_routed_buffer;
     c10::cuda::CUDAGuard guard(d_combine_buffer.device());
     const int64_t E = w_routed_gate_T.size(0), H = w_routed_gate_T.size(1), I = w_routed_gate_T.size(2), cap = schedule_peer_rank.size(0);
+    const int64_t T = d_combine_buffer.size(0) / topk;
     const int world = static_cast<int>(d_combine_buffer_ptrs.size());
+    const bool shared = optr(d_y_shared) && optr(w_shared_gate_T) && optr(w_shared_up_T) && optr(w_shared_down_T) && optr(gate_shared) &&
+                        optr(up_shared) && optr(hidden_shared) && optr(x_buffer);
+    const int64_t Is = shared ? gate_shared->size(1) : 0;
     auto bf = d_combine_buffer.options();
     auto fp8 = bf.dtype(at::kFloat8_e4m3fn);
     auto u8 = bf.dtype(at::kByte);
-    auto q = [&](int64_t r, int64_t c) { return std::make_tuple(at::empty({r, c}, fp8), at::empty({r / 128, c / 128, 32, 16}, u8)); };
-    auto [d_y_fp8, d_y_sc] = q(cap, H);
-    auto [d_y_fp8_t, d_y_sc_t] = q(H, cap);
-    auto [d_gate_fp8, d_gate_sc] = q(cap, I);
-    auto [d_gate_fp8_t, d_gate_sc_t] = q(I, cap);
-    auto [d_up_fp8, d_up_sc] = q(cap, I);
-    auto [d_up_fp8_t, d_up_sc_t] = q(I, cap);
+    at::Tensor d_y_fp8 = at::empty({cap, H}, fp8), d_y_sc = at::empty({cap / 128, H / 128, 32, 16}, u8);
+    at::Tensor d_gate_fp8 = at::empty({cap, I}, fp8), d_gate_sc = at::empty({cap / 128, I / 128, 32, 16}, u8);
+    at::Tensor d_up_fp8 = at::empty({cap, I}, fp8), d_up_sc = at::empty({cap / 128, I / 128, 32, 16}, u8);
     at::Tensor d_hidden = at::empty({cap, I}, bf), d_x_routed = at::empty({cap, H}, bf);
     at::Tensor d_w_gate = at::empty({E, I, H}, bf), d_w_up = at::empty({E, I, H}, bf), d_w_down = at::empty({E, H, I}, bf);
+    at::Tensor d_x_shared, d_gate_shared, d_up_shared, d_hidden_shared, d_w_sg, d_w_su, d_w_sd;
+    if (shared) {
+        d_x_shared = at::empty({T, H}, bf);
+        d_gate_shared = at::empty({T, Is}, bf);
+        d_up_shared = at::empty({T, Is}, bf);
+        d_hidden_shared = at::empty({T, Is}, bf);
+        d_w_sg = at::empty({Is, H}, bf);
+        d_w_su = at::empty({Is, H}, bf);
+        d_w_sd = at::empty({H, Is}, bf);
+    }
     std::vector<const void*> src(world);
     std::vector<void*> dst(world);
     for (int i = 0; i < world; ++i) {
         src[i] = reinterpret_cast<const void*>(d_combine_buffer_ptrs[i]);
         dst[i] = reinterpret_cast<void*>(d_x_routed_buffer_ptrs[i]);
     }
-    // With num_comm_sms and minibatch_size set, the experts are cut into minibatches: gradient dispatch of group b+1
-    // (own stream, num_comm_sms multiprocessors) and gradient combine of group b-1 (third stream) run beside the data-
-    // gradient GEMMs of group b; otherwise everything is one sequence on the current stream.  Same kernels, same bytes.
-    int nb = 1;
-    if (num_comm_sms > 0 && minibatch_size > 0) nb = static_cast<int>(std::min<int64_t>(E, (cap + minibatch_size - 1) / minibatch_size));
-    const bool pipe = nb > 1;
-    const c10::cuda::CUDAStream main = c10::cuda::getCurrentCUDAStream();
-    c10::cuda::CUDAStream s_disp = main, s_comb = main;
-    at::Tensor bounds;
-    const int* bp = nullptr;
-    int math_sms = 0;
-    if (pipe) {
-        std::tie(s_disp, s_comb) = side_streams(main.device_index());
-        bounds = at::empty({nb + 1}, schedule_peer_rank.options());
-        bp = static_cast<const int*>(bounds.data_ptr());
-        int sms = 0;
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, main.device_index());
-        math_sms = std::max(2, (sms - num_comm_sms) & ~1);
-        check(mx8_moe_minibatch_bounds(iptr(tokens_per_expert, "tokens_per_expert"), static_cast<int>(E), nb, bounds.data_ptr(), main.stream()),
-              "minibatch bounds");
-        at::cuda::CUDAEvent start;
-        start.record(main);
-        start.block(s_disp);
-        start.block(s_comb);
-    }
-    std::vector<at::cuda::CUDAEvent> disp_done(nb);
-    for (int b = 0; b < nb; ++b) {
-        const mx8_window w{pipe ? bp + b : nullptr, pipe ? bp + b + 1 : nullptr, (pipe && b > 0) ? num_comm_sms : 0};
-        // gradient rows of the routed outputs: one row per (token, k) pair, hence topk = 1 for the index
-        check(mx8_moe_dispatch_quantize_window(src.data(), world, static_cast<int>(H), 1, iptr(schedule_peer_rank, "schedule_peer_rank"),
-                                               iptr(schedule_peer_token_idx, "schedule_peer_token_idx"), iptr(num_tokens, "num_tokens"),
-                                               static_cast<int>(cap), d_y_fp8.data_ptr(), d_y_sc.data_ptr(), d_y_fp8_t.data_ptr(),
-                                               d_y_sc_t.data_ptr(), &w, s_disp.stream()),
-              "gradient dispatch + quantize");
-        if (pipe) disp_done[b].record(s_disp);
-    }
-    for (int b = 0; b < nb; ++b) {
-        if (pipe) disp_done[b].block(main);
-        const mx8_window w{pipe ? bp + b : nullptr, pipe ? bp + b + 1 : nullptr, (pipe && b < nb - 1) ? math_sms : 0};
-        check(mx8_gemm_grouped_window(d_y_fp8.data_ptr(), d_y_sc.data_ptr(), dptr(w_routed_down_T, "w_routed_down_T"),
-                                      dptr(w_routed_down_T_sc, "w_routed_down_T_sc"), d_hidden.data_ptr(), nullptr, static_cast<int>(cap),
-                                      static_cast<int>(I), static_cast<int>(H), MX8_C_BF16, num_tokens.data_ptr(), tokens_per_expert.data_ptr(),
-                                      static_cast<int>(E), &w, main.stream()),
-              "d_hidden gemm");
-        check(mx8_swiglu_bwd_quantize_both_window(gate_fp8_routed.data_ptr(), gate_sc_routed.data_ptr(), up_fp8_routed.data_ptr(),
-                                                  up_sc_routed.data_ptr(), d_hidden.data_ptr(), static_cast<int>(cap), static_cast<int>(I),
-                                                  num_tokens.data_ptr(), d_gate_fp8.data_ptr(), d_gate_sc.data_ptr(), d_gate_fp8_t.data_ptr(),
-                                                  d_gate_sc_t.data_ptr(), d_up_fp8.data_ptr(), d_up_sc.data_ptr(), d_up_fp8_t.data_ptr(),
-                                                  d_up_sc_t.data_ptr(), &w, main.stream()),
-              "swiglu backward + quantize");
-        check(mx8_gemm_grouped_dual_window(d_gate_fp8.data_ptr(), d_gate_sc.data_ptr(), w_routed_gate_T.data_ptr(), w_routed_gate_T_sc.data_ptr(),
-                                           d_up_fp8.data_ptr(), d_up_sc.data_ptr(), w_routed_up_T.data_ptr(), w_routed_up_T_sc.data_ptr(),
-                                           d_x_routed.data_ptr(), static_cast<int>(cap), static_cast<int>(H), static_cast<int>(I),
-                                           static_cast<int>(I), num_tokens.data_ptr(), tokens_per_expert.data_ptr(), static_cast<int>(E), &w,
-                                           main.stream()),
-              "data-gradient gemm");
-        if (pipe) {
-            at::cuda::CUDAEvent math_done;
-            math_done.record(main);
-            math_done.block(s_comb);
-        }
-        const mx8_window wc{pipe ? bp + b : nullptr, pipe ? bp + b + 1 : nullptr, (pipe && b < nb - 1) ? std::max(1, num_comm_sms / 4) : 0};
-        check(mx8_moe_combine_window(d_x_routed.data_ptr(), schedule_peer_rank.data_ptr(), schedule_peer_token_idx.data_ptr(),
-                                     num_tokens.data_ptr(), static_cast<int>(H), dst.data(), world, &wc, s_comb.stream()),
-              "gradient combine");
-    }
-    auto wgrad = [&](const at::Tensor& at_, const at::Tensor& ats, const at::Tensor& bt, const at::Tensor& bts, at::Tensor& c) {
-        check(mx8_gemm_wgrad(at_.data_ptr(), ats.data_ptr(), bt.data_ptr(), bts.data_ptr(), c.data_ptr(), static_cast<int>(at_.size(0)),
-                             static_cast<int>(bt.size(0)), static_cast<int>(cap), tokens_per_expert.data_ptr(), static_cast<int>(E), stream()),
-              "weight-gradient gemm");
-    };
-    wgrad(d_gate_fp8_t, d_gate_sc_t, x_fp8_t_routed, x_sc_t_routed, d_w_gate);
-    wgrad(d_up_fp8_t, d_up_sc_t, x_fp8_t_routed, x_sc_t_routed, d_w_up);
-    wgrad(d_y_fp8_t, d_y_sc_t, hidden_fp8_t_routed, hidden_sc_t_routed, d_w_down);
-    if (pipe) {
-        at::cuda::CUDAEvent done;                 // the last gradient combine ran beside the weight gradients
-        done.record(s_comb);
-        done.block(main);
-        for (const at::Tensor* t : {&d_y_fp8, &d_y_sc, &d_y_fp8_t, &d_y_sc_t, &d_x_routed, &bounds}) {
-            c10::cuda::CUDACachingAllocator::recordStream(t->storage().data_ptr(), s_disp);
-            c10::cuda::CUDACachingAllocator::recordStream(t->storage().data_ptr(), s_comb);
-        }
-    }
-    // shared expert (bf16), only when its tensors are given
-    at::Tensor d_x_shared, d_gate_shared, d_up_shared, d_hidden_shared, d_w_sg, d_w_su, d_w_sd;
-    if (d_y_shared && w_shared_gate_T && w_shared_up_T && w_shared_down_T && gate_shared && up_shared && hidden_shared && x_buffer) {
-        d_hidden_shared = bf16_gemm(*d_y_shared, *w_shared_down_T);
-        d_gate_shared = at::empty_like(*gate_shared);
-        d_up_shared = at::empty_like(*gate_shared);
-        check(mx8_swiglu_bwd_bf16(dptr(d_hidden_shared, "d_hidden_shared"), dptr(*gate_shared, "gate_shared"), dptr(*up_shared, "up_shared"),
-                                  d_gate_shared.data_ptr(), d_up_shared.data_ptr(), gate_shared->numel(), stream()),
-              "shared swiglu backward");
-        d_x_shared = bf16_gemm(d_gate_shared, *w_shared_gate_T, &d_up_shared, &*w_shared_up_T);
-        // weight gradients: K runs over the tokens, so both operands are transposed to K-major first
-        at::Tensor x_t = bf16_transpose(*x_buffer);
-        d_w_sg = bf16_gemm(bf16_transpose(d_gate_shared), x_t);
-        d_w_su = bf16_gemm(bf16_transpose(d_up_shared), x_t);
-        d_w_sd = bf16_gemm(bf16_transpose(*d_y_shared), bf16_transpose(*hidden_shared));
-    }
+    mx8_moe_bwd_args a{};
+    a.dims = moe_dims(world, T, H, I, Is, E, topk, cap, num_comm_sms, minibatch_size);
+    a.d_y_shared = shared ? optr(d_y_shared) : nullptr;
+    a.d_combine_ptrs = src.data();
+    a.d_x_routed_ptrs = dst.data();
+    a.w_shared_gate_T = shared ? optr(w_shared_gate_T) : nullptr;
+    a.w_shared_up_T = shared ? optr(w_shared_up_T) : nullptr;
+    a.w_shared_down_T = shared ? optr(w_shared_down_T) : nullptr;
+    a.w_gate_T = dptr(w_routed_gate_T, "w_routed_gate_T"); a.w_gate_T_sc = dptr(w_routed_gate_T_sc, "w_routed_gate_T_sc", E * I * H / 32);
+    a.w_up_T = dptr(w_routed_up_T, "w_routed_up_T", E * I * H); a.w_up_T_sc = dptr(w_routed_up_T_sc, "w_routed_up_T_sc", E * I * H / 32);
+    a.w_down_T = dptr(w_routed_down_T, "w_routed_down_T", E * I * H); a.w_down_T_sc = dptr(w_routed_down_T_sc, "w_routed_down_T_sc", E * I * H / 32);
+    a.x_fp8_t = dptr(x_fp8_t_routed, "x_fp8_t_routed", cap * H); a.x_sc_t = dptr(x_sc_t_routed, "x_sc_t_routed", cap * H / 32);
+    a.gate_shared = shared ? optr(gate_shared) : nullptr;
+    a.gate_fp8 = dptr(gate_fp8_routed, "gate_fp8_routed", cap * I); a.gate_sc = dptr(gate_sc_routed, "gate_sc_routed", cap * I / 32);
+    a.up_shared = shared ? optr(up_shared) : nullptr;
+    a.up_fp8 = dptr(up_fp8_routed, "up_fp8_routed", cap * I); a.up_sc = dptr(up_sc_routed, "up_sc_routed", cap * I / 32);
+    a.hidden_shared = shared ? optr(hidden_shared) : nullptr;
+    a.hidden_fp8_t = dptr(hidden_fp8_t_routed, "hidden_fp8_t_routed", cap * I);
+    a.hidden_sc_t = dptr(hidden_sc_t_routed, "hidden_sc_t_routed", cap * I / 32);
+    a.x = shared ? optr(x_buffer) : nullptr;
+    a.peer_rank = iptr(schedule_peer_rank, "schedule_peer_rank");
+    a.peer_token_idx = iptr(schedule_peer_token_idx, "schedule_peer_token_idx");
+    a.num_tokens = iptr(num_tokens, "num_tokens");
+    a.tokens_per_expert = iptr(tokens_per_expert, "tokens_per_expert");
+    a.d_x_shared = mptr(d_x_shared); a.d_x_routed = d_x_routed.data_ptr();
+    a.d_gate_shared = mptr(d_gate_shared); a.d_gate_fp8 = d_gate_fp8.data_ptr(); a.d_gate_sc = d_gate_sc.data_ptr();
+    a.d_up_shared = mptr(d_up_shared); a.d_up_fp8 = d_up_fp8.data_ptr(); a.d_up_sc = d_up_sc.data_ptr();
+    a.d_hidden_shared = mptr(d_hidden_shared); a.d_hidden_routed = d_hidden.data_ptr();
+    a.d_y_fp8 = d_y_fp8.data_ptr(); a.d_y_sc = d_y_sc.data_ptr();
+    a.d_w_shared_gate = mptr(d_w_sg); a.d_w_gate = d_w_gate.data_ptr();
+    a.d_w_shared_up = mptr(d_w_su); a.d_w_up = d_w_up.data_ptr();
+    a.d_w_shared_down = mptr(d_w_sd); a.d_w_down = d_w_down.data_ptr();
+    const size_t need = mx8_moe_bwd_workspace_bytes(&a.dims);
+    TORCH_CHECK(need > 0, "dispatch_mlp_swiglu_combine_bwd: hidden, intermediate and capacity must be multiples of 256");
+    at::Tensor ws = at::empty({static_cast<int64_t>(need)}, u8);
+    a.workspace = ws.data_ptr();
+    a.workspace_bytes = need;
+    check(mx8_moe_bwd(&a, stream()), "dispatch_mlp_swiglu_combine_bwd");
     return {d_x_shared, d_x_routed, d_gate_shared, d_gate_fp8, d_gate_sc, d_up_shared, d_up_fp8, d_up_sc, d_hidden_shared, d_hidden,
             d_y_fp8, d_y_sc, d_w_sg, d_w_gate, d_w_su, d_w_up, d_w_sd, d_w_down};
 }

@@ -18,6 +18,39 @@ class Window(ctypes.Structure):
 
 
 _wp = ctypes.POINTER(Window)
+_pp = ctypes.POINTER(ctypes.c_void_p)
+
+
+class MoeDims(ctypes.Structure):
+    """mx8_moe_dims"""
+    _fields_ = [(n, ctypes.c_int) for n in ("world", "tokens", "hidden", "intermediate", "shared_intermediate", "num_local_experts",
+                                            "topk", "capacity", "num_comm_sms", "minibatch_size", "minibatches", "ramp", "combine_sms")]
+
+
+FWD_IN = ("w_shared_gate", "w_shared_up", "w_shared_down", "w_gate", "w_gate_sc", "w_up", "w_up_sc", "w_down", "w_down_sc",
+          "peer_rank", "peer_token_idx", "num_tokens", "tokens_per_expert")
+FWD_OUT = ("x_fp8_t", "x_sc_t", "gate_shared", "gate_fp8", "gate_sc", "up_shared", "up_fp8", "up_sc", "hidden_shared", "hidden_fp8_t",
+           "hidden_sc_t", "y_shared", "y_routed")
+
+
+class MoeFwdArgs(ctypes.Structure):
+    """mx8_moe_fwd_args"""
+    _fields_ = ([("dims", MoeDims), ("fuse_combine", ctypes.c_int), ("x", ctypes.c_void_p), ("x_ptrs", _pp), ("combine_ptrs", _pp)]
+                + [(n, ctypes.c_void_p) for n in FWD_IN + FWD_OUT] + [("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_size_t)])
+
+
+BWD_IN = ("w_shared_gate_T", "w_shared_up_T", "w_shared_down_T", "w_gate_T", "w_gate_T_sc", "w_up_T", "w_up_T_sc", "w_down_T", "w_down_T_sc",
+          "x_fp8_t", "x_sc_t", "gate_shared", "gate_fp8", "gate_sc", "up_shared", "up_fp8", "up_sc", "hidden_shared", "hidden_fp8_t",
+          "hidden_sc_t", "x", "peer_rank", "peer_token_idx", "num_tokens", "tokens_per_expert")
+BWD_OUT = ("d_x_shared", "d_x_routed", "d_gate_shared", "d_gate_fp8", "d_gate_sc", "d_up_shared", "d_up_fp8", "d_up_sc", "d_hidden_shared",
+           "d_hidden_routed", "d_y_fp8", "d_y_sc", "d_w_shared_gate", "d_w_gate", "d_w_shared_up", "d_w_up", "d_w_shared_down", "d_w_down")
+
+
+class MoeBwdArgs(ctypes.Structure):
+    """mx8_moe_bwd_args"""
+    _fields_ = ([("dims", MoeDims), ("d_y_shared", ctypes.c_void_p), ("d_combine_ptrs", _pp), ("d_x_routed_ptrs", _pp)]
+                + [(n, ctypes.c_void_p) for n in BWD_IN + BWD_OUT] + [("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_size_t)])
+
 
 SIGNATURES = {
     "mx8_quantize": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp]),
@@ -26,7 +59,7 @@ SIGNATURES = {
     "mx8_gemm_grouped": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _i, _vp]),
     "mx8_moe_dispatch_quantize": (_i, [ctypes.POINTER(_vp), _i, _i, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp]),
     "mx8_swiglu_quantize": (_i, [_vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
-    "mx8_moe_combine": (_i, [_vp, _vp, _vp, _vp, _i, ctypes.POINTER(_vp), _i, _vp]),
+    "mx8_moe_combine": (_i, [_vp, _vp, _vp, _vp, _i, _i, ctypes.POINTER(_vp), _i, ctypes.c_longlong, _vp]),
     "mx8_moe_fwd_epilogue": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "mx8_gemm_grouped_scatter": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _i, _vp, _vp, ctypes.POINTER(_vp), _i, _vp]),
     "mx8_gemm_grouped_dual": (_i, [_vp] * 9 + [_i, _i, _i, _i, _vp, _vp, _i, _vp]),
@@ -49,7 +82,12 @@ SIGNATURES = {
     "mx8_swiglu_quantize_window": (_i, [_vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _wp, _vp]),
     "mx8_swiglu_bwd_quantize_both_window": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp] + [_vp] * 8 + [_wp, _vp]),
     "mx8_gemm_grouped_dual_window": (_i, [_vp] * 9 + [_i, _i, _i, _i, _vp, _vp, _i, _wp, _vp]),
-    "mx8_moe_combine_window": (_i, [_vp, _vp, _vp, _vp, _i, ctypes.POINTER(_vp), _i, _wp, _vp]),
+    "mx8_moe_combine_window": (_i, [_vp, _vp, _vp, _vp, _i, _i, ctypes.POINTER(_vp), _i, ctypes.c_longlong, _wp, _vp]),
+    "mx8_moe_minibatch_bounds_split": (_i, [_vp, _i, _i, ctypes.POINTER(_i), _vp, _vp]),
+    "mx8_moe_fwd_workspace_bytes": (ctypes.c_size_t, [ctypes.POINTER(MoeDims)]),
+    "mx8_moe_fwd": (_i, [ctypes.POINTER(MoeFwdArgs), _vp]),
+    "mx8_moe_bwd_workspace_bytes": (ctypes.c_size_t, [ctypes.POINTER(MoeDims)]),
+    "mx8_moe_bwd": (_i, [ctypes.POINTER(MoeBwdArgs), _vp]),
     "mx8_quantize_host_workspace": (ctypes.c_size_t, [_i, _i]),
     "mx8_quantize_host": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _vp, ctypes.c_size_t, _vp]),
     "mx8_gemm_host_workspace": (ctypes.c_size_t, [_i, _i, _i, _i]),

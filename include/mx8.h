@@ -80,10 +80,8 @@ MX8_API int mx8_gemm(const void* A, const void* A_sc, const void* B, const void*
 
 /* Same contract as mx8_gemm with the kernel variant chosen by the caller:
  *   cta_group 2 = one 256x256 tile per CTA pair (cluster of 2), 1 = one 128x256 tile per CTA,
- *   0 = library default, 3 = as 2 but the tiles of a short last round are never cut into two
- *   128-column halves (the default does that when the last round of the persistent schedule would
- *   occupy at most half of the CTA pairs); max_ctas caps the persistent grid (0 = all SMs).
- *   Used by the tests and the benchmark's ablations. */
+ *   0 = library default; max_ctas caps the persistent grid (0 = all SMs). Used by the tests and
+ *   the benchmark's ablations. */
 MX8_API int mx8_gemm_ex(const void* A, const void* A_sc, const void* B, const void* B_sc, void* C,
                 int M, int N, int K, int c_dtype, int cta_group, int max_ctas, void* stream);
 
@@ -120,13 +118,16 @@ MX8_API int mx8_swiglu_quantize(const void* gate_fp8, const void* gate_sc, const
                                 int rows, int cols, const void* num_rows, void* hidden_fp8, void* hidden_sc,
                                 void* hidden_fp8_t, void* hidden_sc_t, void* hidden_bf16, void* stream);
 
-/* MoE combine: row r (< *num_tokens, peer_rank[r] >= 0) of y_routed [rows][hidden] bf16 is written to
- * row peer_token_idx[r] of combine_ptrs[peer_rank[r]] (HOST array of `world` device pointers to every
- * rank's [tokens*topk][hidden] bf16 buffer, peer-mapped for other GPUs).  The caller orders this call
+/* MoE combine: row r (< min(*num_tokens, capacity), peer_rank[r] >= 0) of y_routed [capacity][hidden] bf16 is
+ * written to row peer_token_idx[r] of combine_ptrs[peer_rank[r]] (HOST array of `world` device pointers to
+ * every rank's [combine_rows][hidden] bf16 buffer, combine_rows = tokens*topk, peer-mapped for other GPUs).
+ * A schedule that overflowed its capacity (device status word set by mx8_moe_schedule) cannot make this call
+ * read or write out of bounds: rows beyond capacity, ranks outside [0, world) and destination rows outside
+ * [0, combine_rows) are skipped; the reference traps in that case (same file :86).  The caller orders this call
  * against the readers of those buffers (a cross-rank barrier), as the reference's harness does.
  * Replaces combine_kernel, blackwell-ultra/022-…-mxfp8-bw.cu:830-922. */
 MX8_API int mx8_moe_combine(const void* y_routed, const void* peer_rank, const void* peer_token_idx, const void* num_tokens,
-                            int hidden, void* const* combine_ptrs, int world, void* stream);
+                            int capacity, int hidden, void* const* combine_ptrs, int world, long long combine_rows, void* stream);
 
 /* out[t] = bf16( y_shared[t] + sum_j topk_weights[t][j] * combine_buffer[t*topk + j] ); y_shared may be
  * NULL (no shared expert).  topk_weights float32 [tokens][topk]; the other tensors bf16.
@@ -280,8 +281,72 @@ MX8_API int mx8_gemm_grouped_dual_window(const void* A1, const void* A1_sc, cons
                                          int K2, const void* num_rows, const void* group_rows, int num_groups,
                                          const mx8_window* window, void* stream);
 MX8_API int mx8_moe_combine_window(const void* y_routed, const void* peer_rank, const void* peer_token_idx,
-                                   const void* num_tokens, int hidden, void* const* combine_ptrs, int world,
-                                   const mx8_window* window, void* stream);
+                                   const void* num_tokens, int capacity, int hidden, void* const* combine_ptrs, int world,
+                                   long long combine_rows, const mx8_window* window, void* stream);
+/* As mx8_moe_minibatch_bounds with the groups given explicitly: first_expert is a HOST array of minibatches + 1
+ * ascending expert indices, first_expert[0] = 0, first_expert[minibatches] = num_local_experts (NULL = even split);
+ * at most 64 minibatches. */
+MX8_API int mx8_moe_minibatch_bounds_split(const void* tokens_per_expert, int num_local_experts, int minibatches,
+                                           const int* first_expert, void* bounds, void* stream);
+
+/* The whole layer in one call.
+ *
+ * mx8_moe_fwd = the reference's dispatch_mlp_swiglu_combine_fwd (blackwell-ultra/022-…-mxfp8-bw.cu:2016-2136): tokens
+ * are pulled from every rank's x (x_ptrs), quantized, run through the local experts' gate / up / SwiGLU / down, and
+ * the result rows are pushed into the owners' combine buffers (combine_ptrs); the shared expert (bf16) runs on this
+ * rank's own tokens when shared_intermediate > 0.  The reference allocates its outputs itself; here the caller
+ * passes them (the thirteen tensors its binding returns, same names, capacity rows for the routed ones) plus a
+ * workspace of mx8_moe_fwd_workspace_bytes(dims) bytes of device memory for the tensors it keeps internal.
+ *   num_comm_sms, minibatch_size: the reference's arguments.  Both > 0: the local experts are cut into
+ *   ceil(capacity / minibatch_size) minibatches whose transfers overlap the other minibatches' GEMMs on two side
+ *   streams the library creates once per device; outputs do not depend on the split.  Otherwise one launch
+ *   sequence on `stream`.  Tuning (all may be 0): minibatches overrides the count; ramp = 1 makes the first and
+ *   last minibatch half as large; combine_sms caps a combine that runs beside GEMMs (default num_comm_sms / 4).
+ *   fuse_combine = 1: the down projection's epilogue writes the owners' buffers directly (one sequence; y_routed
+ *   may be NULL).
+ * mx8_moe_bwd = dispatch_mlp_swiglu_combine_bwd (same file :2556-2760) in the same style: the eighteen tensors its
+ * binding returns are passed by the caller, the transposed gradients live in the workspace.
+ * Both return after queueing; `stream` waits for the side streams' last work.  x_ptrs / combine_ptrs /
+ * d_combine_ptrs / d_x_routed_ptrs are HOST arrays of `world` device pointers. */
+typedef struct mx8_moe_dims {
+    int world, tokens, hidden, intermediate, shared_intermediate, num_local_experts, topk, capacity;
+    int num_comm_sms, minibatch_size;
+    int minibatches, ramp, combine_sms;
+} mx8_moe_dims;
+typedef struct mx8_moe_fwd_args {
+    mx8_moe_dims dims;
+    int fuse_combine;
+    const void* x;                          /* this rank's [tokens][hidden] bf16 (shared expert input) */
+    const void* const* x_ptrs;
+    void* const* combine_ptrs;
+    const void *w_shared_gate, *w_shared_up, *w_shared_down;       /* bf16 [Is][H], [Is][H], [H][Is] or NULL */
+    const void *w_gate, *w_gate_sc, *w_up, *w_up_sc, *w_down, *w_down_sc;
+    const void *peer_rank, *peer_token_idx, *num_tokens, *tokens_per_expert;
+    void *x_fp8_t, *x_sc_t, *gate_shared, *gate_fp8, *gate_sc, *up_shared, *up_fp8, *up_sc, *hidden_shared, *hidden_fp8_t,
+         *hidden_sc_t, *y_shared, *y_routed;
+    void* workspace;
+    size_t workspace_bytes;
+} mx8_moe_fwd_args;
+typedef struct mx8_moe_bwd_args {
+    mx8_moe_dims dims;
+    const void* d_y_shared;                 /* [tokens][hidden] bf16 or NULL */
+    const void* const* d_combine_ptrs;
+    void* const* d_x_routed_ptrs;
+    const void *w_shared_gate_T, *w_shared_up_T, *w_shared_down_T;
+    const void *w_gate_T, *w_gate_T_sc, *w_up_T, *w_up_T_sc, *w_down_T, *w_down_T_sc;
+    const void *x_fp8_t, *x_sc_t, *gate_shared, *gate_fp8, *gate_sc, *up_shared, *up_fp8, *up_sc, *hidden_shared, *hidden_fp8_t,
+               *hidden_sc_t;
+    const void* x;                          /* this rank's tokens (shared expert weight gradients) */
+    const void *peer_rank, *peer_token_idx, *num_tokens, *tokens_per_expert;
+    void *d_x_shared, *d_x_routed, *d_gate_shared, *d_gate_fp8, *d_gate_sc, *d_up_shared, *d_up_fp8, *d_up_sc, *d_hidden_shared,
+         *d_hidden_routed, *d_y_fp8, *d_y_sc, *d_w_shared_gate, *d_w_gate, *d_w_shared_up, *d_w_up, *d_w_shared_down, *d_w_down;
+    void* workspace;
+    size_t workspace_bytes;
+} mx8_moe_bwd_args;
+MX8_API size_t mx8_moe_fwd_workspace_bytes(const mx8_moe_dims* dims);
+MX8_API int mx8_moe_fwd(const mx8_moe_fwd_args* args, void* stream);
+MX8_API size_t mx8_moe_bwd_workspace_bytes(const mx8_moe_dims* dims);
+MX8_API int mx8_moe_bwd(const mx8_moe_bwd_args* args, void* stream);
 
 /* Host-buffer forms.  The reference's harnesses keep tensors on the device and never move them
  * inside a timed region (blackwell-ultra/019-mxfp8-quantize.py:59-84,

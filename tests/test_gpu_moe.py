@@ -176,7 +176,7 @@ def test_combine_and_epilogue_exact():
     for rank in range(W):
         pr, pt, nt, tpe = mx8.schedule(topk_all.to(DEV), E_local, cap, rank)
         y = O.make_input(cap, H, seed=60 + rank).to(DEV)
-        mx8.combine(y, pr, pt, nt, [b.data_ptr() for b in bufs])
+        mx8.combine(y, pr, pt, nt, [b.data_ptr() for b in bufs], T * k)
         n = int(nt)
         ys.append(y[:n].cpu()); prs.append(pr.cpu()); pts.append(pt.cpu())
     assert mx8.device_status() == 0
@@ -190,6 +190,33 @@ def test_combine_and_epilogue_exact():
         out0 = mx8.fwd_epilogue(None, bufs[owner], weights[owner].to(DEV))
         ref0 = MO.fwd_epilogue_ref(torch.zeros(T, H, dtype=torch.bfloat16), want, weights[owner])
         assert torch.equal(out0.cpu().view(torch.int16), ref0.view(torch.int16))
+
+
+def test_combine_after_an_overflowed_schedule_stays_in_bounds():
+    # a schedule that does not fit its capacity reports through the status word and still stores the full row count;
+    # the combine must then touch nothing beyond `capacity` rows, a rank outside the world or a row outside the buffers
+    W, T, H, k, E_local = 2, 512, 256, 2, 2
+    topk_all, _ = make_topk(W, T, W * E_local, k, seed=9)
+    cap = 256
+    pr, pt, nt, tpe = mx8.schedule(topk_all.to(DEV), E_local, cap, 0)
+    with pytest.raises(mx8.Mx8Error):
+        mx8.device_status()
+    assert int(nt) > cap
+    guard = 4
+    bufs = [torch.full((T * k + guard, H), -3.0, dtype=torch.bfloat16, device=DEV) for _ in range(W)]
+    y = O.make_input(cap, H, seed=3).to(DEV)
+    # poison one entry each way: a rank beyond the world and a destination row beyond the buffer
+    pr2, pt2 = pr.clone(), pt.clone()
+    valid = torch.nonzero(pr2 >= 0).squeeze(1)
+    pr2[valid[0]] = 7
+    pt2[valid[1]] = T * k + 1
+    mx8.combine(y, pr2, pt2, nt, [b.data_ptr() for b in bufs], T * k)
+    assert mx8.device_status() == 0
+    torch.cuda.synchronize()
+    for b in bufs:
+        assert bool((b[T * k:] == -3.0).all())                      # nothing landed beyond the buffers' rows
+    written = sum(int((b[:T * k, 0] != -3.0).sum()) for b in bufs)
+    assert written == int(valid.numel()) - 2
 
 
 def test_moe_forward_layer_two_emulated_ranks():
