@@ -35,6 +35,7 @@ sys.path.insert(0, os.path.join(ROOT, "gpu-experiments_b200"))
 import torch  # noqa: E402
 
 QM = QN = 16384
+LAYER_STEPS = 20            # timed steps of the FFN and MoE objects, whatever --steps says
 E2E_BAND_ROWS = 2048          # rows per band of the host-buffer (end-to-end) pipeline
 GM = GN = GK = 8192
 L2_BYTES = 126 * 1024 * 1024
@@ -50,6 +51,51 @@ def load_peaks():
         d = json.load(open(path))
         return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "source": "measured"}
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+_fp8_roof = {}
+
+
+def measure_fp8_roof(local):
+    """Tensor-core roof for the MXFP8 GEMM, measured on this GPU right now: the kernel's own MMA instruction issued
+    back to back from shared memory by every CTA pair (mx8_probe_mma_peak), three launches of about a millisecond
+    after an idle moment, i.e. at the clock a short burst gets.  Cached per device."""
+    if local in _fp8_roof:
+        return _fp8_roof[local]
+    import ctypes
+    import mx8
+    lib = mx8.load()
+    st = torch.cuda.current_stream().cuda_stream
+    fl = ctypes.c_double()
+    k_steps = 4096
+    for _ in range(2):
+        mx8._lib.check(lib.mx8_probe_mma_peak(k_steps, ctypes.byref(fl), st), "mx8_probe_mma_peak")
+    torch.cuda.synchronize()
+    time.sleep(0.3)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(3):
+        lib.mx8_probe_mma_peak(k_steps, ctypes.byref(fl), st)
+    e1.record()
+    torch.cuda.synchronize()
+    mx8.device_status()
+    _fp8_roof[local] = {"tflops": 3 * fl.value / (e0.elapsed_time(e1) * 1e-3) / 1e12,
+                        "source": "measured on this GPU in this run: tcgen05.mma kind::mxf8f6f4.block_scale 256x256x32 issued back to "
+                                  "back from shared memory by all CTA pairs (mx8_probe_mma_peak), 3 launches of ~1 ms"}
+    time.sleep(0.3)
+    return _fp8_roof[local]
+
+
+def tensor_roofline(achieved, local, clocks=None, **extra):
+    roof = measure_fp8_roof(local)
+    r = {"bound": "tensor", "achieved": achieved, "peak": roof["tflops"], "unit": "TFLOP/s", "frac": achieved / roof["tflops"],
+         "peak_source": roof["source"], "frac_of_nominal_4500": achieved / 4500.0}
+    if clocks and clocks.get("sm_mhz") and clocks.get("sm_max_mhz"):
+        # what the same cycle count would give at the maximum SM clock (the power cap lowers the clock inside long runs)
+        r["achieved_at_max_clock"] = achieved * clocks["sm_max_mhz"] / clocks["sm_mhz"]
+        r["median_sm_mhz"] = clocks["sm_mhz"]
+    r.update(extra)
+    return r
 
 
 class ClockSampler:
@@ -457,7 +503,14 @@ def bench_gemm(args, world, rank, local, peaks, with_cpu):
     for i in range(2):
         e2e_step(i)
     e2e_ms = timed(e2e_step, e2e_steps, world) / e2e_steps
-    fp8_peak = 2.0 * peaks["bf16_tflops"]
+    # a sustained figure next to the burst above: 200 launches back to back (the power cap lowers the clock)
+    sus_sampler = ClockSampler(local) if rank == 0 else None
+    sus_steps = 200
+    sus_ms = timed(step, sus_steps, world, sus_sampler) / sus_steps
+    sustained = {"tflops_per_gpu": flops / (sus_ms * 1e-3) / 1e12, "launches": sus_steps, "ms_per_launch": sus_ms}
+    if sus_sampler:
+        sustained["clocks"] = sus_sampler.summary()
+    clocks = sampler.summary() if sampler else None
     line = {
         "metric": "mxfp8_gemm_throughput", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": per_ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
@@ -465,17 +518,16 @@ def bench_gemm(args, world, rank, local, peaks, with_cpu):
         "config": {"workload": f"MXFP8 GEMM M=N=K=8192 (per GPU {M}x{N}x{K}), operands quantized from bf16 N(0,1/sqrt(K)), bf16 out",
                    "l2": "three operand/output sets (256 MiB each at 1 GPU) used in rotation", "tile": "256x256x128, 2-CTA cluster, 6 stages",
                    "sharding": "rows of A and C split across GPUs, B replicated, no collective"},
-        "roofline": {"bound": "tensor", "achieved": achieved, "peak": fp8_peak, "unit": "TFLOP/s", "frac": achieved / fp8_peak,
-                     "traffic": NCU_TRAFFIC_BYTES["gemm_8192"],
-                     "peak_source": "2 x cuBLAS bf16 burst (" + peaks["source"] + "); no fp8 peak was measured on this pool",
-                     "frac_of_nominal_4500": achieved / 4500.0, "kernel": "gemm_kernel<2>", "algorithmic_flops_per_launch": flops},
+        "roofline": tensor_roofline(achieved, local, clocks, traffic=NCU_TRAFFIC_BYTES["gemm_8192"], kernel="gemm_kernel<2>",
+                                    algorithmic_flops_per_launch=flops, frac_of_2x_bf16_burst=achieved / (2.0 * peaks["bf16_tflops"])),
+        "sustained": sustained,
         "e2e": {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": e2e_steps, "api": "mx8_gemm_host, bands of %d rows" % band},
-        "gpu_launches": args.steps,
+        "gpu_launches": args.steps + sus_steps,
         "library": library,
     }
-    if sampler:
-        line["clocks"] = sampler.summary()
+    if clocks:
+        line["clocks"] = clocks
     if with_cpu and rank == 0:
         line["cpu_baseline"] = cpu_baseline_gemm()
     return line
@@ -508,10 +560,11 @@ def bench_ffn(args, world, rank, local, peaks, with_cpu=False):
         mx8.gemm_grouped(xq, xs, w1q, w1s, hq, hs)       # H = X W1^T, emitted as MXFP8
         mx8.kernel(hq, hs, w2q, w2s, y)                  # Y = H W2^T
 
-    steps = max(3, args.steps // 20)
+    steps = LAYER_STEPS
     for i in range(3):
         step(i)
-    ms = timed(step, steps, world) / steps
+    sampler = ClockSampler(local) if rank == 0 else None
+    ms = timed(step, steps, world, sampler) / steps
     mx8.device_status()
     flops = 2.0 * 2.0 * T * H * F
     achieved = flops / (ms * 1e-3) / 1e12
@@ -519,8 +572,8 @@ def bench_ffn(args, world, rank, local, peaks, with_cpu=False):
             "scaling": "strong",
             "config": {"workload": f"FFN X[{T}x{H}] bf16 -> quantize -> [{F}x{H}] GEMM with MXFP8-quantizing epilogue -> [{H}x{F}] GEMM -> bf16, per GPU",
                        "sharding": "tokens split across GPUs, weights replicated, no collective"},
-            "roofline": {"bound": "tensor", "achieved": achieved, "peak": 2.0 * peaks["bf16_tflops"], "unit": "TFLOP/s",
-                         "frac": achieved / (2.0 * peaks["bf16_tflops"]), "frac_of_nominal_4500": achieved / 4500.0, "traffic": None},
+            "roofline": tensor_roofline(achieved, local, sampler.summary() if sampler else None, traffic=None),
+            **({"clocks": sampler.summary()} if sampler else {}),
             "gpu_launches": 3 * steps, **({"cpu_baseline": cpu_baseline_layer("ffn")} if with_cpu and rank == 0 else {})}
 
 
@@ -565,10 +618,16 @@ def bench_moe(args, world, rank, local, peaks, with_cpu=False):
     ids = ids.to(torch.int32)
     ids_all = torch.empty(world, T, k, dtype=torch.int32, device=dev)
 
-    # the reference harness's knobs: 28 communication SMs, minibatches of 16384 rows of the schedule
+    # the reference harness's knobs: communication SMs and rows of the schedule per minibatch
     comm_sms = args.moe_comm_sms
-    minibatch = args.moe_minibatch if args.moe_minibatch > 0 else -(-cap // (4 * 256)) * 256      # default: four minibatches
+    nb_default = args.moe_minibatches
+    minibatch = args.moe_minibatch if args.moe_minibatch > 0 else -(-cap // (nb_default * 256)) * 256
+    tuning = {"ramp": args.moe_ramp, "combine_sms": args.moe_combine_sms}
     pipe = [0, 0]
+
+    def layer(pr, pt, nt, tpe):
+        return mx8.dispatch_mlp_swiglu_combine_fwd(x, x_ptrs, cb, cb_ptrs, None, wg, wgs, None, wu, wus, None, wd, wds,
+                                                   pr, pt, nt, tpe, k, pipe[0], 0, pipe[1], tuning=tuning)
 
     def step(_):
         if world > 1:
@@ -577,14 +636,76 @@ def bench_moe(args, world, rank, local, peaks, with_cpu=False):
         else:
             ids_all.copy_(ids.view(1, T, k))
         pr, pt, nt, tpe = mx8.schedule(ids_all, E, cap, rank)
-        mx8.dispatch_mlp_swiglu_combine_fwd(x, x_ptrs, cb, cb_ptrs, None, wg, wgs, None, wu, wus, None, wd, wds,
-                                            pr, pt, nt, tpe, k, pipe[0], 0, pipe[1])
+        layer(pr, pt, nt, tpe)
         if world > 1:
             import torch.distributed as dist
             dist.barrier()
         return mx8.fwd_epilogue(None, cb, weights)
 
-    steps = max(3, args.steps // 40)
+    # ---- parity, before anything is timed: (1) the layer in minibatches on three streams leaves the bytes of the
+    # one-sequence layer, in this rank's routed outputs and in its combine buffer after every rank's pushes;
+    # (2) sampled rows of this rank's expert outputs against the CPU oracle of the expert MLP (every step of the
+    # chain is row-wise, so a row can be checked alone); (3) the weighted sum of the combine buffer against the
+    # oracle's epilogue on sampled tokens.  Rank 0 reports the worst rank.
+    parity = None
+    if not args.no_parity:
+        step(0)
+        barrier(world)
+        pr, pt, nt, tpe = mx8.schedule(ids_all, E, cap, rank)
+        cb.zero_()
+        barrier(world)
+        single = layer(pr, pt, nt, tpe)
+        barrier(world)
+        cb_single = cb.clone()
+        out_single = mx8.fwd_epilogue(None, cb, weights)
+        cb.zero_()
+        barrier(world)
+        pipe[:] = [comm_sms, minibatch]
+        piped = layer(pr, pt, nt, tpe)
+        pipe[:] = [0, 0]
+        barrier(world)
+        n = int(nt)
+        same = torch.equal(cb, cb_single)
+        # the thirteen outputs, cut to the rows in use: (index, which axis holds the routed rows, rows per index step)
+        for idx, axis, unit in ((0, 1, 1), (1, 1, 128), (3, 0, 1), (4, 0, 128), (6, 0, 1), (7, 0, 128), (9, 1, 1), (10, 1, 128), (12, 0, 1)):
+            a_, b_ = single[idx].narrow(axis, 0, n // unit), piped[idx].narrow(axis, 0, n // unit)
+            view = torch.int16 if a_.dtype == torch.bfloat16 else torch.uint8
+            same = same and torch.equal(a_.contiguous().view(view), b_.contiguous().view(view))
+        from oracle import moe_oracle as MO
+        from oracle import mx8_oracle as O
+        if world > 1:
+            x_all = torch.empty(world, T, H, dtype=torch.bfloat16, device=dev)
+            dist.all_gather_into_tensor(x_all, x)
+        else:
+            x_all = x.view(1, T, H)
+        tpe_c, pr_c, pt_c = tpe.cpu(), pr.cpu(), pt.cpu()
+        live = torch.nonzero(tpe_c > 0).squeeze(1)
+        worst, checked = 0.0, 0
+        for e in [int(live[0]), int(live[len(live) // 2]), int(live[-1])]:
+            r0 = int(tpe_c[:e].sum())
+            rows = slice(r0, r0 + 128)
+            src_r, src_t = pr_c[rows].long(), pt_c[rows].long() // k
+            xr = torch.zeros(128, H, dtype=torch.bfloat16)
+            ok = src_r >= 0
+            xr[ok] = x_all[src_r[ok].to(dev), src_t[ok].to(dev)].cpu()
+            one = lambda wq, ws, r_: (wq[e:e + 1].view(torch.uint8).cpu(), ws[e * r_ // 128:(e + 1) * r_ // 128].cpu())
+            ref = MO.expert_mlp_ref(xr, torch.tensor([128], dtype=torch.int32), one(wg, wgs, I), one(wu, wus, I), one(wd, wds, H))
+            worst = max(worst, O.rel_frobenius(single[12][rows].cpu(), ref["y"]))
+            checked += 128
+        tok = torch.arange(0, T, max(1, T // 16))[:16]
+        ref_out = MO.fwd_epilogue_ref(torch.zeros(len(tok), H, dtype=torch.bfloat16),
+                                      cb_single.view(T, k, H)[tok.to(dev)].reshape(-1, H).cpu(), weights[tok.to(dev)].cpu())
+        epi_exact = torch.equal(out_single[tok.to(dev)].cpu().view(torch.int16), ref_out.view(torch.int16))
+        flags = torch.tensor([0.0 if same else 1.0, 0.0 if epi_exact else 1.0, worst, float(mx8.device_status())], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(flags, op=dist.ReduceOp.MAX)
+        parity = {"pipelined_equals_single_sequence": flags[0].item() == 0.0, "epilogue_exact_on_sampled_tokens": flags[1].item() == 0.0,
+                  "expert_rows_checked_per_gpu": checked, "max_rel_frobenius_vs_oracle": flags[2].item(), "tolerance": 1e-2,
+                  "device_status": int(flags[3].item()),
+                  "ok": flags[0].item() == 0.0 and flags[1].item() == 0.0 and flags[2].item() < 1e-2 and flags[3].item() == 0.0}
+        del single, piped, cb_single, out_single
+
+    steps = LAYER_STEPS
     for i in range(3):
         step(i)
     ms_single = timed(step, steps, world) / steps
@@ -593,11 +714,16 @@ def bench_moe(args, world, rank, local, peaks, with_cpu=False):
     pipe[:] = [comm_sms, minibatch]
     for i in range(3):
         step(i)
-    ms_pipe = timed(step, steps, world) / steps
+    sampler = ClockSampler(local) if rank == 0 else None
+    ms_pipe = timed(step, steps, world, sampler) / steps
     mx8.device_status()
     pipe[:] = [0, 0]
-    ms = min(ms_single, ms_pipe)
-    pipeline = {"comm_sms": comm_sms, "minibatch_rows": minibatch, "minibatches": min(E, -(-cap // minibatch)),
+    # the figure reported is the form a multi-GPU job uses (minibatches, as the reference's harness asks for); at one GPU
+    # there is nothing to overlap and the default arguments (one sequence) are the form to report
+    use_pipe = world > 1
+    ms = ms_pipe if use_pipe else ms_single
+    pipeline = {"reported": "minibatches" if use_pipe else "single sequence", "comm_sms": comm_sms, "minibatch_rows": minibatch,
+                "minibatches": min(E, -(-cap // minibatch)), "ramp": args.moe_ramp, "combine_sms": args.moe_combine_sms,
                 "ms_per_step": ms_pipe, "single_sequence_ms_per_step": ms_single}
 
     # ---- backward of the same layer (routed experts): prologue, barrier, fused backward, barrier, epilogue
@@ -636,7 +762,7 @@ def bench_moe(args, world, rank, local, peaks, with_cpu=False):
                 dist.barrier()
             mx8.dispatch_mlp_swiglu_combine_bwd(None, d_cb, d_cb_ptrs, d_xb, d_xb_ptrs, None, wgT, wgTs, None, wuT, wuTs, None, wdT, wdTs,
                                                 f[0], f[1], None, f[3], f[4], None, f[6], f[7], None, f[9], f[10], x, x_ptrs,
-                                                wg, wgs, wu, wus, pr, pt, nt, tpe, k, pipe[0], 0, pipe[1])
+                                                wg, wgs, wu, wus, pr, pt, nt, tpe, k, pipe[0], 0, pipe[1], tuning=tuning)
             if world > 1:
                 dist.barrier()
             return mx8.bwd_epilogue_routed(None, d_xb, k)
@@ -651,7 +777,7 @@ def bench_moe(args, world, rank, local, peaks, with_cpu=False):
         bms_pipe = timed(bstep, steps, world) / steps
         mx8.device_status()
         pipe[:] = [0, 0]
-        bms = min(bms_single, bms_pipe)
+        bms = bms_pipe if use_pipe else bms_single
         pipeline["backward_ms_per_step"] = bms_pipe
         pipeline["backward_single_sequence_ms_per_step"] = bms_single
         bwd = {"ms_per_step": bms, "value": 12.0 * (32768 * k) * H * I / (bms * 1e-3) / 1e12, "unit": "TFLOP/s",
@@ -664,11 +790,41 @@ def bench_moe(args, world, rank, local, peaks, with_cpu=False):
             "config": {"workload": f"MoE forward, {E_total} experts / {world} GPUs, hidden {H}, intermediate {I}, 32768 tokens, top-{k}, routed experts only",
                        "flops": "6 * routed rows * hidden * intermediate (padding rows not counted)",
                        "sharding": "experts and tokens split across GPUs; dispatch pulls and combine pushes over peer-mapped memory"},
-            "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": 2.0 * peaks["bf16_tflops"], "unit": "TFLOP/s",
-                         "frac": per_gpu / (2.0 * peaks["bf16_tflops"]), "frac_of_nominal_4500": per_gpu / 4500.0, "traffic": None},
+            "roofline": tensor_roofline(per_gpu, local, sampler.summary() if sampler else None, traffic=None),
+            **({"clocks": sampler.summary()} if sampler else {}),
+            "parity": parity,
             "pipeline": pipeline,
             "backward": bwd,
             "gpu_launches": (10 + (14 if bwd else 0)) * steps, **({"cpu_baseline": cpu_baseline_layer("moe")} if with_cpu and rank == 0 else {})}
+
+
+def summary_of(line, world):
+    """the figures of every object of the line in one short object"""
+    def rnd(v, nd=4):
+        return round(v, nd) if isinstance(v, (int, float)) else v
+    out = {"n_gpus": world}
+    objs = {line.get("metric", "").replace("mxfp8_", "").split("_")[0]: line}
+    for k in ("gemm", "ffn", "moe"):
+        if isinstance(line.get(k), dict):
+            objs[k] = line[k]
+    for name, o in objs.items():
+        if "error" in o:
+            out[name] = {"error": o["error"][:120]}
+            continue
+        e = {"value": rnd(o.get("value"), 1), "unit": o.get("unit"), "ms_per_step": rnd(o.get("ms_per_step")),
+             "frac_of_measured_roof": rnd(o.get("roofline", {}).get("frac"))}
+        if "sustained" in o:
+            e["sustained_tflops_per_gpu"] = rnd(o["sustained"]["tflops_per_gpu"], 1)
+        if o.get("parity"):
+            e["parity_ok"] = o["parity"]["ok"]
+            e["max_rel_vs_oracle"] = rnd(o["parity"]["max_rel_frobenius_vs_oracle"], 6)
+        if isinstance(o.get("backward"), dict):
+            e["backward_ms_per_step"] = rnd(o["backward"]["ms_per_step"])
+        if isinstance(o.get("pipeline"), dict):
+            e["single_sequence_ms_per_step"] = rnd(o["pipeline"]["single_sequence_ms_per_step"])
+            e["minibatches_ms_per_step"] = rnd(o["pipeline"]["ms_per_step"])
+        out[name] = e
+    return out
 
 
 def main():
@@ -682,6 +838,11 @@ def main():
     ap.add_argument("--moe-minibatch", type=int, default=0,
                     help="MoE: schedule rows per minibatch of the pipelined layer (0 = a quarter of the schedule capacity; "
                          "the reference harness uses 16384, which is the same at 8 GPUs)")
+    ap.add_argument("--moe-minibatches", type=int, default=4, help="MoE: minibatches when --moe-minibatch is 0")
+    ap.add_argument("--moe-ramp", type=int, default=0, help="MoE: 1 = first and last minibatch half as large")
+    ap.add_argument("--moe-combine-sms", type=int, default=0, help="MoE: multiprocessors' worth of blocks for a combine beside GEMMs (0 = comm SMs / 4)")
+    ap.add_argument("--no-parity", action="store_true", help="MoE: skip the parity checks that precede the timing")
+    ap.add_argument("--no-bwd", action="store_true", help="MoE: skip the backward")
     ap.add_argument("--no-layers", action="store_true", help="skip the FFN and MoE objects of the quantize line")
     ap.add_argument("--no-gemm", action="store_true", help="skip the GEMM object of the quantize line")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
@@ -702,7 +863,7 @@ def main():
         if not args.no_gemm:
             g = bench_gemm(args, world, rank, local, peaks, with_cpu)
             line["gemm"] = {k: g[k] for k in ("metric", "value", "unit", "ms_per_step", "scaling", "config", "roofline", "e2e",
-                                              "gpu_launches", "clocks", "cpu_baseline", "library") if k in g}
+                                              "gpu_launches", "clocks", "cpu_baseline", "library", "sustained") if k in g}
             line["gpu_launches"] += g["gpu_launches"]
         if not args.no_layers:
             for name, fn in (("ffn", bench_ffn), ("moe", bench_moe)):
@@ -719,6 +880,7 @@ def main():
         line.update({"n_gpus": world, "warmup": args.warmup, "higher_is_better": True, "vs_baseline": None, "dtype": "fp8_e4m3 x ue8m0",
                      "data": "synthetic"})
     if rank == 0:
+        line["summary"] = summary_of(line, world)       # last key: the part of the line a log tail keeps
         print(json.dumps(line), flush=True)
     if world > 1:
         import torch.distributed as dist

@@ -13,7 +13,7 @@ CSRC = os.path.join(HERE, "csrc")
 OUT_DIR = os.path.join(HERE, "mx8")
 OBJ_DIR = os.path.join(HERE, "build")
 LIB = os.path.join(OUT_DIR, "libmx8.so")
-SOURCES = ["mx8_host.cu", "quantize.cu", "gemm.cu", "moe_schedule.cu", "moe_combine.cu", "moe_layer.cu", "host_pipeline.cu", "shared_expert.cu"]
+SOURCES = ["mx8_host.cu", "quantize.cu", "gemm.cu", "moe_schedule.cu", "moe_combine.cu", "moe_layer.cu", "host_pipeline.cu", "shared_expert.cu", "peak_probe.cu"]
 HEADERS = ["mx8_host.cuh", "mx8_ptx.cuh", "mx8_qmath.cuh", os.path.join("..", "..", "include", "mx8.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]

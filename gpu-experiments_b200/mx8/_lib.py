@@ -96,6 +96,7 @@ SIGNATURES = {
     "mx8_gemm_a_bf16_fused": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "mx8_gemm_a_bf16": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, ctypes.c_size_t, _vp]),
     "mx8_debug_set_gemm_ablation": (_i, [_i]),
+    "mx8_probe_mma_peak": (_i, [_i, ctypes.POINTER(ctypes.c_double), _vp]),
     "mx8_device_status": (_i, [ctypes.POINTER(_i), _vp]),
     "mx8_strerror": (ctypes.c_char_p, [_i]),
     "mx8_last_cuda_error": (ctypes.c_char_p, []),

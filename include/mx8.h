@@ -385,6 +385,13 @@ MX8_API size_t mx8_gemm_a_bf16_workspace(int M, int K);
 MX8_API int mx8_gemm_a_bf16(const void* A_bf16, const void* B, const void* B_sc, void* C, int M, int N, int K, int c_dtype,
                             void* workspace, size_t workspace_bytes, void* stream);
 
+/* Measurement aid, no counterpart in the reference: queues one launch in which every CTA pair of the device
+ * issues k_steps (a multiple of 8) K steps of the GEMM's main loop, four tcgen05.mma.cta_group::2.kind::mxf8f6f4
+ * .block_scale of a 256 x 256 tile each, on operands resident in shared memory; no global traffic, no epilogue.
+ * *flops_out = operations of the launch; timed by the caller with events it gives the tensor-core roof the
+ * benchmark reports the GEMM against (the data sheet's 4.5 PFLOP/s assumes a clock the power cap does not allow). */
+MX8_API int mx8_probe_mma_peak(int k_steps, double* flops_out, void* stream);
+
 /* Synchronizes `stream`, then reads and clears the current device's status word: 0 = healthy,
  * otherwise the code of the first bounded wait that expired (see csrc/mx8_ptx.cuh).
  * Returns MX8_OK, MX8_ERR_DEVICE_TIMEOUT (status != 0) or MX8_ERR_CUDA. */
