@@ -398,10 +398,13 @@ def bench_quantize(args, world, rank, local, peaks, with_cpu):
                                 band_rows=E2E_BAND_ROWS, workspace=ws, device=dev)
 
     e2e_steps = max(3, min(args.steps, 10))
-    for i in range(2):
-        e2e_step(i)
-    e2e_ms = timed(e2e_step, e2e_steps, world) / e2e_steps
-    e2e_val = world * algo_bytes / (e2e_ms * 1e-3) / 1e9
+    if args.quick:
+        e2e_steps, e2e_ms, e2e_val = 0, None, None
+    else:
+        for i in range(2):
+            e2e_step(i)
+        e2e_ms = timed(e2e_step, e2e_steps, world) / e2e_steps
+        e2e_val = world * algo_bytes / (e2e_ms * 1e-3) / 1e9
 
     line = {
         "metric": "mxfp8_quantize_bandwidth", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
@@ -464,7 +467,7 @@ def bench_gemm(args, world, rank, local, peaks, with_cpu):
     # the vendor library on the same operands, for context (not part of the roofline): cuBLAS through
     # torch._scaled_mm with the same E8M0 block scales, and with per-tensor scales (plain FP8)
     library = {}
-    if rank == 0 and hasattr(torch, "float8_e8m0fnu"):
+    if rank == 0 and hasattr(torch, "float8_e8m0fnu") and not args.quick:
         aq, asc, bq, bsc, c = sets[0]
         def lib_rate(fn, iters=20):
             for _ in range(3):
@@ -500,12 +503,15 @@ def bench_gemm(args, world, rank, local, peaks, with_cpu):
         mx8.kernel_host(host_in[0], host_in[1], host_in[2], host_in[3], c_h, band_rows=band, workspace=ws, device=dev)
 
     e2e_steps = max(3, min(args.steps, 10))
-    for i in range(2):
-        e2e_step(i)
-    e2e_ms = timed(e2e_step, e2e_steps, world) / e2e_steps
+    if args.quick:
+        e2e_steps, e2e_ms = 0, None
+    else:
+        for i in range(2):
+            e2e_step(i)
+        e2e_ms = timed(e2e_step, e2e_steps, world) / e2e_steps
     # a sustained figure next to the burst above: 200 launches back to back (the power cap lowers the clock)
     sus_sampler = ClockSampler(local) if rank == 0 else None
-    sus_steps = 200
+    sus_steps = 1 if args.quick else 200
     sus_ms = timed(step, sus_steps, world, sus_sampler) / sus_steps
     sustained = {"tflops_per_gpu": flops / (sus_ms * 1e-3) / 1e12, "launches": sus_steps, "ms_per_launch": sus_ms}
     if sus_sampler:
@@ -521,7 +527,7 @@ def bench_gemm(args, world, rank, local, peaks, with_cpu):
         "roofline": tensor_roofline(achieved, local, clocks, traffic=NCU_TRAFFIC_BYTES["gemm_8192"], kernel="gemm_kernel<2>",
                                     algorithmic_flops_per_launch=flops, frac_of_2x_bf16_burst=achieved / (2.0 * peaks["bf16_tflops"])),
         "sustained": sustained,
-        "e2e": {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
+        "e2e": {"value": world * flops / (e2e_ms * 1e-3) / 1e12 if e2e_ms else None, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": e2e_steps, "api": "mx8_gemm_host, bands of %d rows" % band},
         "gpu_launches": args.steps + sus_steps,
         "library": library,
@@ -846,7 +852,12 @@ def main():
     ap.add_argument("--no-layers", action="store_true", help="skip the FFN and MoE objects of the quantize line")
     ap.add_argument("--no-gemm", action="store_true", help="skip the GEMM object of the quantize line")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--quick", action="store_true",
+                    help="timed loop only: no end-to-end leg, no library comparison, no sustained loop, no CPU leg, no extra objects "
+                         "(for profiler captures, which should see few launches)")
     args = ap.parse_args()
+    if args.quick:
+        args.no_cpu = args.no_gemm = args.no_layers = args.no_parity = args.no_bwd = True
     args.warmup = max(args.warmup, 3)
     args.steps = max(args.steps, 1)
 

@@ -25,9 +25,19 @@
 //
 // M/N tails need no special case: out-of-range TMA loads are zero-filled, out-of-range TMA stores
 // are clipped.  Replaces blackwell/047-mxfp8-mma-2cta-MNK128-polished.cu:12-541 of the reference.
+#include <atomic>
+
 #include "mx8_host.cuh"
 #include "mx8_ptx.cuh"
 #include "mx8_qmath.cuh"
+
+// Timing studies switch parts of the kernel off through Params::dbg.  The shipped library is built without
+// MX8_ABLATION: the switches are compile-time false and the setter is not exported.
+#ifdef MX8_ABLATION
+#define MX8_DBG(p, bits) (((p).dbg & (bits)) != 0)
+#else
+#define MX8_DBG(p, bits) false
+#endif
 
 namespace mx8 {
 namespace gemm {
@@ -82,7 +92,8 @@ struct Params {
     int tiles_m, tiles_n, k_steps;      // tile grid (tile = 128*CG x 256) and K / 128
     int group_m;                        // rasterisation: tiles_m rows per supergroup
     int c_mode;                         // 0 bf16, 1 f32, 2 MXFP8 (E4M3 bytes + scale tiles, blocks along N),
-                                        // 3 bf16 rows scattered to the ranks that own the tokens (MoE combine)
+                                        // 3 bf16 rows scattered to the ranks that own the tokens (MoE combine),
+                                        // 4 gate / up as MXFP8 plus hidden = SwiGLU(gate, up) as MXFP8, row-wise and transposed
     const int* sc_peer_rank;            // c_mode 3: destination rank per row (-1: skip) and row in its buffer
     const int* sc_peer_token_idx;
     uint8_t* sc_dst[16];
@@ -95,9 +106,16 @@ struct Params {
     int num_groups;
     int group_b_rows;                   // rows of B per group (N)
     int k_steps2;                       // second operand pair accumulated into the same tile (0 = none)
+    int pair_tiles_n;                   // > 0: two products A B1^T and A B2^T in one launch; column tiles [0, pair_tiles_n) belong
+                                        // to the first (B1 -> C), [pair_tiles_n, 2 pair_tiles_n) to the second (B2 -> C2)
+    uint8_t* c_sc2;                     // scale tiles of C2 for c_mode 2
+    // c_mode 4 (gate and up projections with SwiGLU in the epilogue): a tile is 128 output columns wide, CTA 0 of the
+    // pair holds the gate weights' rows, CTA 1 the up weights' rows, so accumulator columns [0,128) are gate and
+    // [128,256) are up of the same 128 output columns
+    uint8_t *sw_gate, *sw_gate_sc, *sw_up, *sw_up_sc, *sw_h, *sw_h_sc, *sw_ht, *sw_ht_sc;
     int wgrad;                          // 1: one output matrix per group, K runs over the group's rows of A^T / B^T
     int group_c_rows;                   // wgrad: rows of C per group (M)
-    int dbg;                            // ablation switches (MX8_GEMM_DEBUG, timing only, results are wrong):
+    int dbg;                            // ablation switches (only in a build with -DMX8_ABLATION; timing only, results are wrong):
                                         // 1 no MMA, 2 no TMA loads, 4 no C stores, 8 no scale traffic, 16 no scale copies,
                                         // 32 no scale loads, 128 no wait for the epilogue
     int* status;
@@ -124,11 +142,13 @@ struct TileInfo {
     int b_base;        // first row of B for this tile (before the CTA's own offset)
     int c_row;         // first row of C for this tile (before the CTA's own offset)
     int k0, kcount;    // first K step and number of K steps
+    int second;        // 1: this tile belongs to the second product of a pair launch (tn already counts inside it)
 };
 
 template <int CG>
 __device__ __forceinline__ TileInfo tile_info(int t, const Params& p, int tiles_m, const int* seg_end, int tm0 = 0) {
     TileInfo ti;
+    ti.second = 0;
     if (p.wgrad) {
         const int per_group = tiles_m * p.tiles_n;
         const int e = t / per_group;
@@ -142,7 +162,11 @@ __device__ __forceinline__ TileInfo tile_info(int t, const Params& p, int tiles_
     }
     tile_coords(t, p, tiles_m, ti.tm, ti.tn);
     ti.tm += tm0;                                     // row window: tile rows are counted from its first row
-    ti.b_base = ti.tn * BN;
+    if (p.pair_tiles_n > 0 && ti.tn >= p.pair_tiles_n) {
+        ti.second = 1;
+        ti.tn -= p.pair_tiles_n;
+    }
+    ti.b_base = ti.tn * (p.c_mode == 4 ? BN / 2 : BN);
     if (p.num_groups > 0) {
         const int row0 = ti.tm * 128 * CG;
         int lo = 0, hi = p.num_groups - 1;            // first group whose segment ends beyond row0
@@ -158,18 +182,139 @@ __device__ __forceinline__ TileInfo tile_info(int t, const Params& p, int tiles_
     return ti;
 }
 
+// Epilogue of c_mode 4 for one warp (TMEM lane quadrant q, lane = row): accumulator columns [0,128) hold the gate
+// projection and [128,256) the up projection of output columns [ocol0, ocol0 + 128).  Per group of 32 columns:
+// both are rounded to bf16 and quantized as one block each (the bytes and scales the separate launches write),
+// hidden = bf16( silu(dequant(gate)) * dequant(up) ) is computed from the quantized values with the arithmetic of
+// the stand-alone SwiGLU kernel, quantized row-wise, and, after a transposition of the 32 x 32 block through shared
+// memory, quantized along the rows as well.  Replaces expert_grouped_gemm's quantizing epilogue plus swiglu_fwd<false>
+// (blackwell-ultra/022-moe-dispatch-mlp-swiglu-combine-mxfp8-bw.cu:1644-1700, 924-1129).
+// `drain` is called once, after the first two accumulator units (which include the unit the two accumulators share)
+// have been read.
+template <typename DrainFn>
+__device__ __forceinline__ void swiglu_epilogue(const Params& p, uint32_t t_acc, int acc, int row0, int ocol0, int q, int lane,
+                                                uint32_t stg, uint8_t* stg_ptr, DrainFn drain) {
+    using namespace qmath;
+    const int I = p.n_cols;
+    const bool row_ok = row0 + lane < p.rows_cap;
+    const size_t row_off = static_cast<size_t>(row0 + lane) * I + ocol0;
+    uint32_t sc_g = 0, sc_u = 0, sc_h = 0;
+#pragma unroll 1
+    for (int s = 0; s < 4; ++s) {
+        const int j = acc ? s : 3 - s;                        // accumulator 0 shares its last unit, accumulator 1 its first
+        uint32_t rg[32], ru[32];
+        tc_ld_32x32(t_acc + j * 32, rg);
+        tc_ld_32x32(t_acc + (4 + j) * 32, ru);
+        tc_wait_ld(rg);
+        tc_wait_ld(ru);
+        if (s == 0) drain();
+        // ---- gate and up: bf16 rounding, one MXFP8 block each
+        uint32_t hg[16], hu[16], qg[8], qu[8];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            hg[i] = pack_bf16x2(__uint_as_float(rg[2 * i]), __uint_as_float(rg[2 * i + 1]));
+            hu[i] = pack_bf16x2(__uint_as_float(ru[2 * i]), __uint_as_float(ru[2 * i + 1]));
+        }
+        auto block_scale = [&](const uint32_t (&h)[16], uint32_t& byte, uint32_t& inv) {
+            uint32_t m = maxabs_bf16x2(h[0], h[1]);
+#pragma unroll
+            for (int i = 2; i < 16; ++i) m = maxabs_bf16x2(m, h[i]);
+            m &= 0x7FFF7FFFu;
+            byte = scale_bytes2(max(m & 0xFFFFu, m >> 16), RCEIL_ROUND_ADD2, RCEIL_MIN_BYTE8_2) & 0xFFu;
+            inv = inv_scales2(byte | (byte << 16));
+        };
+        uint32_t bg, bu, ig, iu;
+        block_scale(hg, bg, ig);
+        block_scale(hu, bu, iu);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            qg[i] = cvt4(mul_bf16x2(hg[2 * i], ig), mul_bf16x2(hg[2 * i + 1], ig));
+            qu[i] = cvt4(mul_bf16x2(hu[2 * i], iu), mul_bf16x2(hu[2 * i + 1], iu));
+        }
+        if (row_ok) {
+            uint4* dg = reinterpret_cast<uint4*>(p.sw_gate + row_off + j * 32);
+            uint4* du = reinterpret_cast<uint4*>(p.sw_up + row_off + j * 32);
+            dg[0] = make_uint4(qg[0], qg[1], qg[2], qg[3]);
+            dg[1] = make_uint4(qg[4], qg[5], qg[6], qg[7]);
+            du[0] = make_uint4(qu[0], qu[1], qu[2], qu[3]);
+            du[1] = make_uint4(qu[4], qu[5], qu[6], qu[7]);
+        }
+        sc_g |= bg << (8 * j);
+        sc_u |= bu << (8 * j);
+        // ---- hidden from the quantized values, in fp32
+        const float gs = __uint_as_float(bg << 23), us = __uint_as_float(bu << 23);
+        uint32_t hh[16];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            float gf[4], uf[4], h[4];
+            e4m3x4_to_float(qg[i], gf);
+            e4m3x4_to_float(qu[i], uf);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float g = gf[e] * gs;
+                h[e] = __fdividef(g, 1.0f + __expf(-g)) * (uf[e] * us);
+            }
+            hh[2 * i] = pack_bf16x2(h[0], h[1]);
+            hh[2 * i + 1] = pack_bf16x2(h[2], h[3]);
+        }
+        // ---- row-wise block of hidden
+        uint32_t bh, ih;
+        block_scale(hh, bh, ih);
+        if (row_ok) {
+            uint4* dh = reinterpret_cast<uint4*>(p.sw_h + row_off + j * 32);
+            dh[0] = make_uint4(cvt4(mul_bf16x2(hh[0], ih), mul_bf16x2(hh[1], ih)), cvt4(mul_bf16x2(hh[2], ih), mul_bf16x2(hh[3], ih)),
+                               cvt4(mul_bf16x2(hh[4], ih), mul_bf16x2(hh[5], ih)), cvt4(mul_bf16x2(hh[6], ih), mul_bf16x2(hh[7], ih)));
+            dh[1] = make_uint4(cvt4(mul_bf16x2(hh[8], ih), mul_bf16x2(hh[9], ih)), cvt4(mul_bf16x2(hh[10], ih), mul_bf16x2(hh[11], ih)),
+                               cvt4(mul_bf16x2(hh[12], ih), mul_bf16x2(hh[13], ih)), cvt4(mul_bf16x2(hh[14], ih), mul_bf16x2(hh[15], ih)));
+        }
+        sc_h |= bh << (8 * j);
+        // ---- the 32 x 32 block transposed through shared memory (rows of 17 words: stores and loads are conflict-free):
+        // afterwards lane c holds column c of the 32 rows this warp owns, one 32-row block of the transposed matrix
+        __syncwarp();
+#pragma unroll
+        for (int w = 0; w < 16; ++w) asm volatile("st.shared.b32 [%0], %1;" ::"r"(stg + lane * 68 + w * 4), "r"(hh[w]) : "memory");
+        __syncwarp();
+        uint32_t ht[16];
+#pragma unroll
+        for (int r = 0; r < 16; ++r) {
+            const uint32_t lo = *reinterpret_cast<const uint16_t*>(stg_ptr + (2 * r) * 68 + lane * 2);
+            const uint32_t hi = *reinterpret_cast<const uint16_t*>(stg_ptr + (2 * r + 1) * 68 + lane * 2);
+            ht[r] = lo | (hi << 16);
+        }
+        uint32_t bt, it;
+        block_scale(ht, bt, it);
+        const int col = ocol0 + j * 32 + lane;
+        if (row0 < p.rows_cap && col < I) {
+            uint4* dt = reinterpret_cast<uint4*>(p.sw_ht + static_cast<size_t>(col) * p.rows_cap + row0);
+            dt[0] = make_uint4(cvt4(mul_bf16x2(ht[0], it), mul_bf16x2(ht[1], it)), cvt4(mul_bf16x2(ht[2], it), mul_bf16x2(ht[3], it)),
+                               cvt4(mul_bf16x2(ht[4], it), mul_bf16x2(ht[5], it)), cvt4(mul_bf16x2(ht[6], it), mul_bf16x2(ht[7], it)));
+            dt[1] = make_uint4(cvt4(mul_bf16x2(ht[8], it), mul_bf16x2(ht[9], it)), cvt4(mul_bf16x2(ht[10], it), mul_bf16x2(ht[11], it)),
+                               cvt4(mul_bf16x2(ht[12], it), mul_bf16x2(ht[13], it)), cvt4(mul_bf16x2(ht[14], it), mul_bf16x2(ht[15], it)));
+            // scale byte of (column col, rows row0 .. row0 + 31) in the tile layout of the transposed matrix
+            p.sw_ht_sc[(static_cast<size_t>(ocol0 / 128) * (p.rows_cap / 128) + row0 / 128) * 512 + lane * 16 + j * 4 + q] = static_cast<uint8_t>(bt);
+        }
+    }
+    if (row_ok) {
+        const size_t word = (static_cast<size_t>(row0 / 128) * (I / 128) + ocol0 / 128) * 512 + lane * 16 + q * 4;
+        *reinterpret_cast<uint32_t*>(p.sw_gate_sc + word) = sc_g;
+        *reinterpret_cast<uint32_t*>(p.sw_up_sc + word) = sc_u;
+        *reinterpret_cast<uint32_t*>(p.sw_h_sc + word) = sc_h;
+    }
+}
+
 // F16: A and B are bf16 (kind::f16, no scale tiles); the byte images in shared memory, the stage
 // ring and the epilogue are the same, a K step being 128 bytes = 64 bf16 elements of a row.
-template <int CG, bool F16, bool A16 = false>
+template <int CG, bool F16, bool A16 = false, bool SW = false>
 __global__ void __launch_bounds__((Cfg<CG, A16>::threads), 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
             const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb,
             const __grid_constant__ CUtensorMap tm_a2, const __grid_constant__ CUtensorMap tm_b2,
             const __grid_constant__ CUtensorMap tm_sfa2, const __grid_constant__ CUtensorMap tm_sfb2,
-            const __grid_constant__ CUtensorMap tm_c, const Params p) {
+            const __grid_constant__ CUtensorMap tm_c, const __grid_constant__ CUtensorMap tm_c2, const Params p) {
     using C = Cfg<CG, A16>;
     constexpr int S = C::STAGES;
     static_assert(!A16 || (CG == 2 && !F16), "the bf16-activation form exists for the 2-CTA MXFP8 kernel only");
+    static_assert(!SW || (CG == 2 && !F16 && !A16 && EPI_WARPS == 4), "the SwiGLU epilogue exists for the 2-CTA MXFP8 kernel only");
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
@@ -264,7 +409,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 const int a_row = (__shfl_sync(0xFFFFFFFFu, ti.tm, 0) * CG + static_cast<int>(rank)) * 128;
                 const int b_base = __shfl_sync(0xFFFFFFFFu, ti.b_base, 0);
                 const int kcount_t = __shfl_sync(0xFFFFFFFFu, ti.kcount, 0), k0_t = __shfl_sync(0xFFFFFFFFu, ti.k0, 0);
-                const int b_row = b_base + static_cast<int>(rank) * C::B_ROWS;
+                // c_mode 4: both CTAs fetch the same rows, CTA 0 of the gate weights and CTA 1 of the up weights
+                constexpr bool swiglu = SW;
+                const int b_row = swiglu ? b_base : b_base + static_cast<int>(rank) * C::B_ROWS;
+                const bool pair_second = __shfl_sync(0xFFFFFFFFu, ti.second, 0) != 0 || (swiglu && rank == 1);
                 for (int ks = 0; ks < kcount_t; ++ks) {
                     if (!__all_sync(0xFFFFFFFFu, mbar_wait(empty0 + stage * 8, ph ^ 1, ab, DEV_TIMEOUT_EMPTY))) { ok = false; break; }
                     const uint32_t a_dst = base + C::a_off + stage * C::A_BYTES;
@@ -275,9 +423,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     const bool second = ks >= p.k_steps && p.k_steps2 > 0;
                     const int kk = k0_t + (second ? ks - p.k_steps : ks);
                     const CUtensorMap* ma = second ? &tm_a2 : &tm_a;
-                    const CUtensorMap* mb = second ? &tm_b2 : &tm_b;
+                    const CUtensorMap* mb = (second || pair_second) ? &tm_b2 : &tm_b;
                     const CUtensorMap* msa = second ? &tm_sfa2 : &tm_sfa;
-                    const CUtensorMap* msb = second ? &tm_sfb2 : &tm_sfb;
+                    const CUtensorMap* msb = (second || pair_second) ? &tm_sfb2 : &tm_sfb;
                     if (!leader) {
                         // only the elected lane issues
                     } else if constexpr (A16) {
@@ -289,9 +437,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                         tma_load_3d_pair(sfb_dst, msb, 0, kk, b_base / 128, bar);
                     } else if constexpr (CG == 2) {
                         const uint32_t bar = full_leader0 + stage * 8;
-                        if (p.dbg & 2) {
+                        if (MX8_DBG(p, 2)) {
                             if (rank == 0) mbar_arrive(full0 + stage * 8);
-                        } else if (F16 || (p.dbg & (8 | 32))) {
+                        } else if (F16 || MX8_DBG(p, 8 | 32)) {
                             if (rank == 0) mbar_arrive_expect_tx(full0 + stage * 8, 2 * (C::A_BYTES + C::B_BYTES));
                             tma_load_2d_pair(a_dst, ma, kk * BK, a_row, bar);
                             tma_load_2d_pair(b_dst, mb, kk * BK, b_row, bar);
@@ -300,7 +448,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                             tma_load_2d_pair(a_dst, ma, kk * BK, a_row, bar);
                             tma_load_2d_pair(b_dst, mb, kk * BK, b_row, bar);
                             tma_load_3d_pair(sfa_dst, msa, 0, kk, a_row / 128, bar);
-                            tma_load_3d_pair(sfb_dst, msb, 0, kk, b_base / 128, bar);
+                            if (swiglu) {
+                                // one scale tile of each weight matrix (their maps have a box of one tile)
+                                tma_load_3d_pair(sfb_dst, &tm_sfb, 0, kk, b_base / 128, bar);
+                                tma_load_3d_pair(sfb_dst + 512, &tm_sfb2, 0, kk, b_base / 128, bar);
+                            } else {
+                                tma_load_3d_pair(sfb_dst, msb, 0, kk, b_base / 128, bar);
+                            }
                         }
                     } else {
                         const uint32_t bar = full0 + stage * 8;
@@ -333,7 +487,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             uint32_t sf_mma = tmem_base + SF_COL, sf_cp = tmem_base + SF_COL;
             constexpr uint32_t ID0 = idesc_mxf8(128 * CG, BN, 0), ID1 = idesc_mxf8(128 * CG, BN, 1);
             constexpr uint32_t ID2 = idesc_mxf8(128 * CG, BN, 2), ID3 = idesc_mxf8(128 * CG, BN, 3);
-            const bool do_cp = !F16 && !(p.dbg & (8 | 16)), do_mma = !(p.dbg & 1);
+            const bool do_cp = !F16 && !MX8_DBG(p, 8 | 16), do_mma = !MX8_DBG(p, 1);
             const int my_tiles = cluster < num_tiles ? (num_tiles - cluster + num_clusters - 1) / num_clusters : 0;
             long long remaining = 0;                             // K steps whose scales are not copied yet
             for (int t = cluster; t < num_tiles; t += num_clusters) remaining += tile_info<CG>(t, p, tiles_m, seg_end, tm0).kcount;
@@ -366,7 +520,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 if (it > 0) {
                     // the epilogue has emptied the previous-but-one accumulator and the 32 columns
                     // the previous accumulator shares with this one
-                    if (!(p.dbg & 128) && !__all_sync(0xFFFFFFFFu, mbar_wait<true>(drained, (it - 1) & 1, ab, DEV_TIMEOUT_TMEM_FREE))) { ok = false; break; }
+                    if (!MX8_DBG(p, 128) && !__all_sync(0xFFFFFFFFu, mbar_wait<true>(drained, (it - 1) & 1, ab, DEV_TIMEOUT_TMEM_FREE))) { ok = false; break; }
                     tc_fence_after();
                 }
                 const int kcount = __shfl_sync(0xFFFFFFFFu, tile_info<CG>(cluster + it * num_clusters, p, tiles_m, seg_end, tm0).kcount, 0);
@@ -498,8 +652,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + (acc ? ACC1_COL : 0);
             const int row0 = ti.c_row + static_cast<int>(rank) * 128 + q * 32;
             const int col0 = tn * BN;
+            const CUtensorMap* const mc = ti.second ? &tm_c2 : &tm_c;
+            uint8_t* const c_sc = ti.second ? p.c_sc2 : p.c_sc;
             uint32_t scword = 0;                                 // four scale bytes of one row (c_mode 2)
             uint8_t* sc_row = nullptr;                           // c_mode 3: where this lane's row goes
+            if constexpr (SW) {
+                swiglu_epilogue(p, t_acc, acc, row0, tn * (BN / 2), q, lane, stg, base_ptr + C::epi_off + (warp - 2) * C::EPI_BYTES, [&]() {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_remote(drained_leader);
+                });
+                continue;
+            }
 #pragma unroll 1
             for (int s = 0; s < EPI_UNITS; ++s) {
                 // 32-column unit of this warp's half; the unit the two accumulators share (the last of
@@ -526,8 +690,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                         st_shared_v4(rowa + ((j ^ (lane & 7)) << 4), r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
                     fence_proxy_async_smem();
                     __syncwarp();
-                    if (lane == 0 && !(p.dbg & 4)) {
-                        tma_store_2d(&tm_c, col0 + u * 32, row0, stg);
+                    if (lane == 0 && !MX8_DBG(p, 4)) {
+                        tma_store_2d(mc, col0 + u * 32, row0, stg);
                         bulk_commit();
                     }
                 } else if (p.c_mode == 2) {
@@ -561,12 +725,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                         fence_proxy_async_smem();
                         __syncwarp();
                         const int ctile = (col0 + (u & ~3) * 32) / 128;  // scale tile column
-                        if (lane == 0 && !(p.dbg & 4)) {
-                            tma_store_2d(&tm_c, col0 + (u & ~3) * 32, row0, stg);
+                        if (lane == 0 && !MX8_DBG(p, 4)) {
+                            tma_store_2d(mc, col0 + (u & ~3) * 32, row0, stg);
                             bulk_commit();
                         }
                         if (row0 + lane < p.rows_cap && ctile * 128 < p.n_cols)
-                            *reinterpret_cast<uint32_t*>(p.c_sc + (static_cast<size_t>(row0 / 128) * (p.n_cols / 128) + ctile) * 512 +
+                            *reinterpret_cast<uint32_t*>(c_sc + (static_cast<size_t>(row0 / 128) * (p.n_cols / 128) + ctile) * 512 +
                                                          lane * 16 + q * 4) = scword;
                     }
                 } else {
@@ -610,8 +774,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     } else if (s & 1) {
                         fence_proxy_async_smem();
                         __syncwarp();
-                        if (lane == 0 && !(p.dbg & 4)) {
-                            tma_store_2d(&tm_c, col0 + (u & ~1) * 32, row0, stg);
+                        if (lane == 0 && !MX8_DBG(p, 4)) {
+                            tma_store_2d(mc, col0 + (u & ~1) * 32, row0, stg);
                             bulk_commit();
                         }
                     }
@@ -636,11 +800,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     }
 }
 
-// process-wide ablation switches for timing studies (mx8_debug_set_gemm_ablation); 0 in normal use
+#ifdef MX8_ABLATION
+// process-wide ablation switches for timing studies (mx8_debug_set_gemm_ablation, exported by such a build only)
 static int g_ablation_flags = 0;
+#endif
 
 struct Maps {
-    CUtensorMap a, b, sfa, sfb, a2, b2, sfa2, sfb2, c;
+    CUtensorMap a, b, sfa, sfb, a2, b2, sfa2, sfb2, c, c2;
 };
 
 // tensor maps of one operand pair: A [a_rows][K], B [b_rows][K] and their scale tiles
@@ -694,15 +860,15 @@ static int build_c_map(CUtensorMap* mc, void* Cp, int c_rows, int N, int c_dtype
     return make_tmap(mc, dt, 2, Cp, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
-template <int CG, bool F16, bool A16 = false>
+template <int CG, bool F16, bool A16 = false, bool SW = false>
 static int max_grid() {
     // CTAs that can be resident at once (cluster placement included), cached per device
-    static int cached[64] = {};
+    static std::atomic<int> cached[64];
     int dev = 0;
     cudaGetDevice(&dev);
     dev &= 63;
-    if (cached[dev]) return cached[dev];
-    auto kern = gemm_kernel<CG, F16, A16>;
+    if (const int have = cached[dev].load(std::memory_order_acquire)) return have;
+    auto kern = gemm_kernel<CG, F16, A16, SW>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<CG, A16>::dynamic);
     if (e != cudaSuccess) {
         note_cuda_error("cudaFuncSetAttribute(gemm)", cudaGetErrorString(e));
@@ -730,7 +896,7 @@ static int max_grid() {
         }
         n = clusters * 2;
     }
-    cached[dev] = n;
+    cached[dev].store(n, std::memory_order_release);
     return n;
 }
 
@@ -749,9 +915,14 @@ struct Grouping {
     int K2 = 0;
     // weight-gradient form: A is A^T [M][K], B is B^T [N][K] with K = all rows; one C [M][N] per group
     bool wgrad = false;
+    // pair launch: a second product of the same A with B_pair (same shape as B) into C_pair (same type as C)
+    const void *B_pair = nullptr, *B_pair_sc = nullptr;
+    void *C_pair = nullptr, *C_pair_sc = nullptr;
+    // SwiGLU form (B = gate weights, B_pair = up weights): gate, gate_sc, up, up_sc, hidden, hidden_sc, hidden_t, hidden_t_sc
+    void* sw[8] = {};
 };
 
-template <int CG, bool F16 = false, bool A16 = false>
+template <int CG, bool F16 = false, bool A16 = false, bool SW = false>
 static int run(const void* A, const void* A_sc, const void* B, const void* B_sc, void* Cp, int M, int N, int K,
                int c_dtype, int max_ctas, const Grouping& gr, cudaStream_t stream) {
     Maps m;
@@ -772,9 +943,22 @@ static int run(const void* A, const void* A_sc, const void* B, const void* B_sc,
     }
     if (rc != MX8_OK) return rc;
     if (gr.K2 > 0) rc = build_operand_maps<CG>(&m.a2, &m.b2, &m.sfa2, &m.sfb2, gr.A2, gr.A2_sc, gr.B2, gr.B2_sc, M, b_rows, gr.K2);
+    else if (gr.B_pair) rc = build_operand_maps<CG>(&m.a2, &m.b2, &m.sfa2, &m.sfb2, A, A_sc, gr.B_pair, gr.B_pair_sc, M, b_rows, K);
     else { m.a2 = m.a; m.b2 = m.b; m.sfa2 = m.sfa; m.sfb2 = m.sfb; }
     if (rc != MX8_OK) return rc;
     if ((rc = build_c_map(&m.c, Cp, c_rows, N, c_dtype)) != MX8_OK) return rc;
+    if (gr.C_pair) rc = build_c_map(&m.c2, gr.C_pair, c_rows, N, c_dtype);
+    else m.c2 = m.c;
+    if (rc != MX8_OK) return rc;
+    if constexpr (SW) {
+        // a tile takes one scale tile of the gate weights and one of the up weights: maps with a box of one tile
+        const uint64_t kb = static_cast<uint64_t>(K) / 128;
+        const uint64_t dims[3] = {128, kb, static_cast<uint64_t>(b_rows) / 128};
+        const uint64_t strides[2] = {512, 512 * kb};
+        const uint32_t box[3] = {128, 1, 1};
+        if ((rc = make_tmap(&m.sfb, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, B_sc, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE)) != MX8_OK) return rc;
+        if ((rc = make_tmap(&m.sfb2, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, gr.B_pair_sc, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE)) != MX8_OK) return rc;
+    }
     Params p{};
     p.c_sc = static_cast<uint8_t*>(gr.c_sc);
     p.n_cols = N;
@@ -792,13 +976,24 @@ static int run(const void* A, const void* A_sc, const void* B, const void* B_sc,
     for (int i = 0; i < gr.world && i < 16; ++i) p.sc_dst[i] = static_cast<uint8_t*>(gr.dst[i]);
     p.tiles_m = (M + 128 * CG - 1) / (128 * CG);
     p.tiles_n = (N + BN - 1) / BN;
+    if constexpr (SW) {
+        p.tiles_n = N / (BN / 2);                                  // a tile is 128 output columns of gate and of up
+        uint8_t** dst[8] = {&p.sw_gate, &p.sw_gate_sc, &p.sw_up, &p.sw_up_sc, &p.sw_h, &p.sw_h_sc, &p.sw_ht, &p.sw_ht_sc};
+        for (int i = 0; i < 8; ++i) *dst[i] = static_cast<uint8_t*>(gr.sw[i]);
+    } else if (gr.B_pair) {
+        p.pair_tiles_n = p.tiles_n;
+        p.tiles_n *= 2;
+        p.c_sc2 = static_cast<uint8_t*>(gr.C_pair_sc);
+    }
     p.k_steps = gr.wgrad ? 0 : K / BK;
     p.group_m = 16;
-    p.c_mode = gr.dst ? 3 : c_dtype;
-    p.dbg = g_ablation_flags;
+    p.c_mode = SW ? 4 : (gr.dst ? 3 : c_dtype);
+#ifdef MX8_ABLATION
+    p.dbg = gr.wgrad ? (g_ablation_flags & ~128) : g_ablation_flags;   // the weight-gradient form cannot drop the epilogue wait
+#endif
     p.status = device_status_ptr();
     if (!p.status) return MX8_ERR_CUDA;
-    int grid = max_grid<CG, F16, A16>();
+    int grid = max_grid<CG, F16, A16, SW>();
     if (grid <= 0) return MX8_ERR_CUDA;
     if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
     const int tiles = p.tiles_m * p.tiles_n * (gr.wgrad ? groups : 1);
@@ -818,7 +1013,7 @@ static int run(const void* A, const void* A_sc, const void* B, const void* B_sc,
     at[0].val.clusterDim.z = 1;
     cfg.attrs = at;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_kernel<CG, F16, A16>, m.a, m.b, m.sfa, m.sfb, m.a2, m.b2, m.sfa2, m.sfb2, m.c, p);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_kernel<CG, F16, A16, SW>, m.a, m.b, m.sfa, m.sfb, m.a2, m.b2, m.sfa2, m.sfb2, m.c, m.c2, p);
     if (e != cudaSuccess) {
         note_cuda_error("gemm launch", cudaGetErrorString(e));
         return MX8_ERR_CUDA;
@@ -881,6 +1076,82 @@ extern "C" int mx8_gemm_grouped_window(const void* A, const void* A_sc, const vo
         max_ctas = window->max_sms > 0 ? window->max_sms : 0;
     }
     return gemm::run<2>(A, A_sc, B, B_sc, C, M, N, K, c_dtype, max_ctas, gr, static_cast<cudaStream_t>(stream));
+}
+
+// Two grouped products of the same A in one launch (the MoE layer's gate and up projections): column tiles of
+// both share the persistent schedule, so there is one tail and the A panels are fetched once for both.
+extern "C" int mx8_gemm_grouped_pair_window(const void* A, const void* A_sc, const void* B1, const void* B1_sc, const void* B2,
+                                            const void* B2_sc, void* C1, void* C1_sc, void* C2, void* C2_sc, int M, int N, int K,
+                                            int c_dtype, const void* num_rows, const void* group_rows, int num_groups,
+                                            const mx8_window* window, void* stream) {
+    using namespace mx8;
+    if (!A || !A_sc || !B1 || !B1_sc || !B2 || !B2_sc || !C1 || !C2) return MX8_ERR_ARG;
+    if (c_dtype != MX8_C_BF16 && c_dtype != MX8_C_F32 && c_dtype != MX8_C_MXFP8) return MX8_ERR_ARG;
+    if ((c_dtype == MX8_C_MXFP8) != (C1_sc != nullptr) || (C1_sc == nullptr) != (C2_sc == nullptr)) return MX8_ERR_ARG;
+    if (num_groups < 0 || (num_groups > 0 && !group_rows)) return MX8_ERR_ARG;
+    if (num_groups > gemm::MAX_GROUPS) {
+        note_cuda_error("mx8_gemm_grouped_pair", "more than 256 groups in one call");
+        return MX8_ERR_LIMIT;
+    }
+    if (M <= 0 || N <= 0 || K <= 0 || M % 128 || N % 256 || K % 128) return MX8_ERR_SHAPE;     // whole column tiles per product
+    if (num_groups > 0 && M % 256) return MX8_ERR_SHAPE;
+    if (!aligned16(A) || !aligned16(A_sc) || !aligned16(B1) || !aligned16(B1_sc) || !aligned16(B2) || !aligned16(B2_sc) ||
+        !aligned16(C1) || !aligned16(C1_sc) || !aligned16(C2) || !aligned16(C2_sc)) return MX8_ERR_ALIGN;
+    int rc = check_device_sm100();
+    if (rc != MX8_OK) return rc;
+    gemm::Grouping gr;
+    gr.c_sc = C1_sc;
+    gr.rows_dev = static_cast<const int*>(num_rows);
+    gr.group_rows = static_cast<const int*>(group_rows);
+    gr.num_groups = num_groups;
+    gr.B_pair = B2; gr.B_pair_sc = B2_sc; gr.C_pair = C2; gr.C_pair_sc = C2_sc;
+    int max_ctas = 0;
+    if (window) {
+        if (window->row_begin) gr.row_begin_dev = static_cast<const int*>(window->row_begin);
+        if (window->row_end) gr.rows_dev = static_cast<const int*>(window->row_end);
+        max_ctas = window->max_sms > 0 ? window->max_sms : 0;
+    }
+    return gemm::run<2>(A, A_sc, B1, B1_sc, C1, M, N, K, c_dtype, max_ctas, gr, static_cast<cudaStream_t>(stream));
+}
+
+// Gate and up projections with SwiGLU and all four quantizations in the epilogue (see swiglu_epilogue).
+extern "C" int mx8_gemm_grouped_swiglu_window(const void* A, const void* A_sc, const void* B_gate, const void* B_gate_sc,
+                                              const void* B_up, const void* B_up_sc, void* gate_fp8, void* gate_sc, void* up_fp8,
+                                              void* up_sc, void* hidden_fp8, void* hidden_sc, void* hidden_fp8_t, void* hidden_sc_t,
+                                              int M, int N, int K, const void* num_rows, const void* group_rows, int num_groups,
+                                              const mx8_window* window, void* stream) {
+    using namespace mx8;
+    const void* const all[] = {A, A_sc, B_gate, B_gate_sc, B_up, B_up_sc, gate_fp8, gate_sc, up_fp8, up_sc, hidden_fp8, hidden_sc,
+                               hidden_fp8_t, hidden_sc_t};
+    for (const void* q : all) {
+        if (!q) return MX8_ERR_ARG;
+        if (!aligned16(q)) return MX8_ERR_ALIGN;
+    }
+    if (num_groups < 0 || (num_groups > 0 && !group_rows)) return MX8_ERR_ARG;
+    if (num_groups > gemm::MAX_GROUPS) {
+        note_cuda_error("mx8_gemm_grouped_swiglu", "more than 256 groups in one call");
+        return MX8_ERR_LIMIT;
+    }
+    if (M <= 0 || N <= 0 || K <= 0 || M % 256 || N % 128 || K % 128) return MX8_ERR_SHAPE;
+    int rc = check_device_sm100();
+    if (rc != MX8_OK) return rc;
+    gemm::Grouping gr;
+    gr.rows_dev = static_cast<const int*>(num_rows);
+    gr.group_rows = static_cast<const int*>(group_rows);
+    gr.num_groups = num_groups;
+    gr.B_pair = B_up;
+    gr.B_pair_sc = B_up_sc;
+    void* const outs[8] = {gate_fp8, gate_sc, up_fp8, up_sc, hidden_fp8, hidden_sc, hidden_fp8_t, hidden_sc_t};
+    for (int i = 0; i < 8; ++i) gr.sw[i] = outs[i];
+    int max_ctas = 0;
+    if (window) {
+        if (window->row_begin) gr.row_begin_dev = static_cast<const int*>(window->row_begin);
+        if (window->row_end) gr.rows_dev = static_cast<const int*>(window->row_end);
+        max_ctas = window->max_sms > 0 ? window->max_sms : 0;
+    }
+    // the C tensor map is unused by this epilogue; A stands in so that the map encodes
+    return gemm::run<2, false, false, true>(A, A_sc, B_gate, B_gate_sc, const_cast<void*>(A), M, N, K, MX8_C_MXFP8, max_ctas, gr,
+                                            static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int mx8_gemm(const void* A, const void* A_sc, const void* B, const void* B_sc, void* C, int M, int N, int K,
@@ -956,11 +1227,13 @@ extern "C" int mx8_gemm_a_bf16_fused(const void* A_bf16, const void* B, const vo
     return gemm::run<2, false, true>(A_bf16, nullptr, B, B_sc, C, M, N, K, c_dtype, 0, none, static_cast<cudaStream_t>(stream));
 }
 
-extern "C" int mx8_debug_set_gemm_ablation(int flags) {
+#ifdef MX8_ABLATION
+extern "C" MX8_API int mx8_debug_set_gemm_ablation(int flags) {
     const int old = mx8::gemm::g_ablation_flags;
     mx8::gemm::g_ablation_flags = flags;
     return old;
 }
+#endif
 
 extern "C" int mx8_gemm_grouped_dual(const void* A1, const void* A1_sc, const void* B1, const void* B1_sc, const void* A2,
                                      const void* A2_sc, const void* B2, const void* B2_sc, void* C, int M, int N, int K1, int K2,

@@ -179,15 +179,33 @@ extern "C" int mx8_moe_fwd(const mx8_moe_fwd_args* a, void* stream) {
         ck(mx8_gemm_bf16(a->hidden_shared, a->w_shared_down, a->y_shared, T, H, Is, MX8_C_BF16, main));
     };
 
+    // gate and up projections and SwiGLU.  Default: one launch whose epilogue holds gate and up of the same columns,
+    // writes both as MXFP8 and the activation as MXFP8 in both orientations.  split_swiglu: the projections as one
+    // pair launch (or two launches with split_gate_up) followed by the stand-alone SwiGLU kernel.  Same bytes in all forms.
+    auto gate_up = [&](const mx8_window* w) {
+        if (!d.split_swiglu) {
+            ck(mx8_gemm_grouped_swiglu_window(x_fp8, x_sc, a->w_gate, a->w_gate_sc, a->w_up, a->w_up_sc, a->gate_fp8, a->gate_sc, a->up_fp8,
+                                              a->up_sc, h_fp8, h_sc, a->hidden_fp8_t, a->hidden_sc_t, cap, I, H, a->num_tokens,
+                                              a->tokens_per_expert, E, w, main));
+            return;
+        }
+        if (d.split_gate_up) {
+            ck(mx8_gemm_grouped_window(x_fp8, x_sc, a->w_gate, a->w_gate_sc, a->gate_fp8, a->gate_sc, cap, I, H, MX8_C_MXFP8,
+                                       a->num_tokens, a->tokens_per_expert, E, w, main));
+            ck(mx8_gemm_grouped_window(x_fp8, x_sc, a->w_up, a->w_up_sc, a->up_fp8, a->up_sc, cap, I, H, MX8_C_MXFP8, a->num_tokens,
+                                       a->tokens_per_expert, E, w, main));
+        } else {
+            ck(mx8_gemm_grouped_pair_window(x_fp8, x_sc, a->w_gate, a->w_gate_sc, a->w_up, a->w_up_sc, a->gate_fp8, a->gate_sc, a->up_fp8,
+                                            a->up_sc, cap, I, H, MX8_C_MXFP8, a->num_tokens, a->tokens_per_expert, E, w, main));
+        }
+        ck(mx8_swiglu_quantize_window(a->gate_fp8, a->gate_sc, a->up_fp8, a->up_sc, cap, I, a->num_tokens, h_fp8, h_sc, a->hidden_fp8_t,
+                                      a->hidden_sc_t, nullptr, w, main));
+    };
+
     if (nb <= 1) {
         ck(mx8_moe_dispatch_quantize(a->x_ptrs, d.world, H, d.topk, a->peer_rank, a->peer_token_idx, a->num_tokens, cap, x_fp8, x_sc,
                                      a->x_fp8_t, a->x_sc_t, main));
-        ck(mx8_gemm_grouped(x_fp8, x_sc, a->w_gate, a->w_gate_sc, a->gate_fp8, a->gate_sc, cap, I, H, MX8_C_MXFP8, a->num_tokens,
-                            a->tokens_per_expert, E, main));
-        ck(mx8_gemm_grouped(x_fp8, x_sc, a->w_up, a->w_up_sc, a->up_fp8, a->up_sc, cap, I, H, MX8_C_MXFP8, a->num_tokens,
-                            a->tokens_per_expert, E, main));
-        ck(mx8_swiglu_quantize(a->gate_fp8, a->gate_sc, a->up_fp8, a->up_sc, cap, I, a->num_tokens, h_fp8, h_sc, a->hidden_fp8_t,
-                               a->hidden_sc_t, nullptr, main));
+        gate_up(nullptr);
         if (a->fuse_combine) {
             ck(mx8_gemm_grouped_scatter(h_fp8, h_sc, a->w_down, a->w_down_sc, cap, H, I, a->num_tokens, a->tokens_per_expert, E,
                                         a->peer_rank, a->peer_token_idx, a->combine_ptrs, d.world, main));
@@ -227,12 +245,7 @@ extern "C" int mx8_moe_fwd(const mx8_moe_fwd_args* a, void* stream) {
         ck.cuda(cudaStreamWaitEvent(main, disp_done[b], 0), "cudaStreamWaitEvent");
         // the last minibatch's GEMMs run after every dispatch has finished: they take the whole device
         const mx8_window w{bounds + b, bounds + b + 1, b == nb - 1 ? 0 : math_sms};
-        ck(mx8_gemm_grouped_window(x_fp8, x_sc, a->w_gate, a->w_gate_sc, a->gate_fp8, a->gate_sc, cap, I, H, MX8_C_MXFP8, a->num_tokens,
-                                   a->tokens_per_expert, E, &w, main));
-        ck(mx8_gemm_grouped_window(x_fp8, x_sc, a->w_up, a->w_up_sc, a->up_fp8, a->up_sc, cap, I, H, MX8_C_MXFP8, a->num_tokens,
-                                   a->tokens_per_expert, E, &w, main));
-        ck(mx8_swiglu_quantize_window(a->gate_fp8, a->gate_sc, a->up_fp8, a->up_sc, cap, I, a->num_tokens, h_fp8, h_sc, a->hidden_fp8_t,
-                                      a->hidden_sc_t, nullptr, &w, main));
+        gate_up(&w);
         ck(mx8_gemm_grouped_window(h_fp8, h_sc, a->w_down, a->w_down_sc, a->y_routed, nullptr, cap, H, I, MX8_C_BF16, a->num_tokens,
                                    a->tokens_per_expert, E, &w, main));
         ck.cuda(cudaEventRecord(math_done[b], main), "cudaEventRecord");

@@ -19,6 +19,8 @@
 // (the reference executes `trap`), and the counting scratch is supplied by the caller.
 // Two forms: a counting sort over chunks of the table when the scratch has room for the per-chunk
 // counts (mx8_moe_schedule_scratch_bytes), else one scan of the table per (local expert, source rank).
+#include <atomic>
+
 #include "mx8_host.cuh"
 #include "mx8_ptx.cuh"
 
@@ -408,19 +410,21 @@ static __device__ __align__(256) int g_schedule_scratch[STATIC_SCRATCH_INTS];
 // Device address of the array on the current device.  In host code the array's name is only a
 // handle for the runtime, not an address a kernel can use, so it is resolved once per device.
 static int* static_scratch_ptr() {
-    static int* cached[64] = {};
+    static std::atomic<int*> cached[64];
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-    if (!cached[dev]) {
+    int* have = cached[dev].load(std::memory_order_acquire);
+    if (!have) {
         int* p = nullptr;
         cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_schedule_scratch);
         if (e != cudaSuccess) {
             note_cuda_error("cudaGetSymbolAddress(schedule scratch)", cudaGetErrorString(e));
             return nullptr;
         }
-        cached[dev] = p;
+        cached[dev].store(p, std::memory_order_release);
+        have = p;
     }
-    return cached[dev];
+    return have;
 }
 
 }  // namespace moe

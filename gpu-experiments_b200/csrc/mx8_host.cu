@@ -4,7 +4,10 @@
 #include <cstring>
 #include <mutex>
 
+#include <atomic>
+
 #include "mx8_host.cuh"
+#include "mx8_ptx.cuh"
 
 namespace mx8 {
 
@@ -66,8 +69,9 @@ int make_tmap(CUtensorMap* out, CUtensorMapDataType dt, int rank, const void* ba
     return MX8_OK;
 }
 
-static int g_sm_count[64];
-static int g_cc_major[64];
+// filled on first use; two threads racing here write the same values
+static std::atomic<int> g_sm_count[64];
+static std::atomic<int> g_cc_major[64];
 
 static int query_device(int* sm, int* major) {
     int dev = 0;
@@ -77,7 +81,7 @@ static int query_device(int* sm, int* major) {
         return MX8_ERR_CUDA;
     }
     if (dev < 0 || dev >= 64) return MX8_ERR_UNSUPPORTED;
-    if (g_sm_count[dev] == 0) {
+    if (g_sm_count[dev].load(std::memory_order_acquire) == 0) {
         int s = 0, m = 0;
         e = cudaDeviceGetAttribute(&s, cudaDevAttrMultiProcessorCount, dev);
         if (e == cudaSuccess) e = cudaDeviceGetAttribute(&m, cudaDevAttrComputeCapabilityMajor, dev);
@@ -85,11 +89,11 @@ static int query_device(int* sm, int* major) {
             note_cuda_error("cudaDeviceGetAttribute", cudaGetErrorString(e));
             return MX8_ERR_CUDA;
         }
-        g_cc_major[dev] = m;
-        g_sm_count[dev] = s;
+        g_cc_major[dev].store(m, std::memory_order_relaxed);
+        g_sm_count[dev].store(s, std::memory_order_release);
     }
-    *sm = g_sm_count[dev];
-    *major = g_cc_major[dev];
+    *sm = g_sm_count[dev].load(std::memory_order_acquire);
+    *major = g_cc_major[dev].load(std::memory_order_relaxed);
     return MX8_OK;
 }
 
@@ -107,7 +111,43 @@ int check_device_sm100() {
 
 }  // namespace mx8
 
+namespace mx8 {
+// One CTA waits on an mbarrier nobody will ever arrive on, through the same bounded wait every kernel of the
+// library uses, with a short limit: the wait gives up, records DEV_TIMEOUT_SELFTEST in the status word and the
+// kernel returns normally.
+__global__ void selftest_wait_kernel(unsigned long long limit_ns, int* status) {
+    __shared__ alignas(8) unsigned long long bar_storage;
+    __shared__ int abort_flag;
+    const uint32_t bar = smem_u32(&bar_storage);
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(bar, 1);
+        fence_mbar_init();
+    }
+    __syncthreads();
+    const AbortCtl ab{&abort_flag, status};
+    if (threadIdx.x == 0) mbar_wait(bar, 0, ab, DEV_TIMEOUT_SELFTEST, limit_ns);
+    __syncthreads();
+}
+}  // namespace mx8
+
 extern "C" {
+
+int mx8_selftest_bounded_wait(unsigned limit_us, void* stream) {
+    using namespace mx8;
+    if (limit_us == 0 || limit_us > 1000000u) return MX8_ERR_ARG;       // at most a second
+    int rc = check_device_sm100();
+    if (rc != MX8_OK) return rc;
+    int* status = device_status_ptr();
+    if (!status) return MX8_ERR_CUDA;
+    selftest_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<unsigned long long>(limit_us) * 1000ull, status);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        note_cuda_error("selftest launch", cudaGetErrorString(e));
+        return MX8_ERR_CUDA;
+    }
+    return MX8_OK;
+}
 
 int mx8_device_status(int* status_out, void* stream) {
     cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));

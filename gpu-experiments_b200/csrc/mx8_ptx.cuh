@@ -16,6 +16,7 @@ enum : int {
     DEV_TIMEOUT_EMPTY = 2,     // producer waited for a stage to be released
     DEV_TIMEOUT_TMEM_FULL = 3, // epilogue waited for an accumulator
     DEV_TIMEOUT_TMEM_FREE = 4, // MMA issuer waited for the epilogue to drain
+    DEV_TIMEOUT_SELFTEST = 8,  // the wait of mx8_selftest_bounded_wait, which nothing ever satisfies
 };
 
 #ifndef MX8_WAIT_LIMIT_NS
@@ -110,10 +111,11 @@ struct AbortCtl {
     int* global_status;        // device word the host reads after the launch
 };
 
-// Bounded wait.  Returns false after MX8_WAIT_LIMIT_NS (recording `code`) or as soon as
+// Bounded wait.  Returns false after limit_ns (MX8_WAIT_LIMIT_NS unless the caller says otherwise; recording `code`) or as soon as
 // another role of this CTA has given up.  CLUSTER selects the acquire scope (see above).
 template <bool CLUSTER = false>
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const AbortCtl& ab, int code) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const AbortCtl& ab, int code,
+                                          uint64_t limit_ns = MX8_WAIT_LIMIT_NS) {
     auto probe = [&]() { return CLUSTER ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity); };
     if (probe()) return true;
     uint64_t t0 = 0;
@@ -123,7 +125,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const A
             if (*ab.smem_flag) return false;
             const uint64_t now = globaltimer_ns();
             if (t0 == 0) t0 = now;
-            else if (now - t0 > MX8_WAIT_LIMIT_NS) {
+            else if (now - t0 > limit_ns) {
                 *ab.smem_flag = 1;
                 atomicCAS(ab.global_status, 0, code);
                 return false;

@@ -4,6 +4,8 @@
 // memory traffic, no epilogue: what remains is what the tensor pipes sustain for this instruction shape, at
 // whatever clock the power cap allows.  The benchmark divides the GEMM's rate by this figure.
 // The reference has no counterpart; it quotes the data sheet's 4.5 PFLOP/s.
+#include <atomic>
+
 #include "mx8_host.cuh"
 #include "mx8_ptx.cuh"
 
@@ -97,16 +99,16 @@ extern "C" int mx8_probe_mma_peak(int k_steps, double* flops_out, void* stream) 
     if (rc != MX8_OK) return rc;
     int* status = device_status_ptr();
     if (!status) return MX8_ERR_CUDA;
-    static bool configured[64] = {};
+    static std::atomic<bool> configured[64];
     int dev = 0;
     cudaGetDevice(&dev);
-    if (!configured[dev & 63]) {
+    if (!configured[dev & 63].load(std::memory_order_acquire)) {
         cudaError_t e = cudaFuncSetAttribute(probe::mma_peak_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, probe::SMEM);
         if (e != cudaSuccess) {
             note_cuda_error("cudaFuncSetAttribute(mma probe)", cudaGetErrorString(e));
             return MX8_ERR_CUDA;
         }
-        configured[dev & 63] = true;
+        configured[dev & 63].store(true, std::memory_order_release);
     }
     const int sms = sm_count();
     if (sms <= 1) return MX8_ERR_CUDA;

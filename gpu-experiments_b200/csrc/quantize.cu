@@ -19,6 +19,8 @@
 // HBM traffic is the algorithmic minimum: 2 bytes read and (1 + 1/32) bytes written per element
 // and orientation.  Replaces blackwell-ultra/019-mxfp8-quantize.cu:40-179 and the persistent
 // variant blackwell-ultra/020-mxfp8-quantize-persistent.cu:139-219 of the reference.
+#include <atomic>
+
 #include "mx8_host.cuh"
 #include "mx8_ptx.cuh"
 #include "mx8_qmath.cuh"
@@ -439,16 +441,16 @@ static int launch(const CUtensorMap& tm_in, const CUtensorMap& tm_in2, const CUt
                   const CUtensorMap* tm_r2 = nullptr) {
     auto kern = quantize_kernel<W, D, SRC, ROW, COL, RTMA>;
     constexpr int smem = Smem<W, D, slot_bytes(SRC), RTMA>::dynamic;
-    static bool configured[64] = {};
+    static std::atomic<bool> configured[64];
     int dev = 0;
     cudaGetDevice(&dev);
-    if (!configured[dev & 63]) {
+    if (!configured[dev & 63].load(std::memory_order_acquire)) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) {
             note_cuda_error("cudaFuncSetAttribute(quantize)", cudaGetErrorString(e));
             return MX8_ERR_CUDA;
         }
-        configured[dev & 63] = true;
+        configured[dev & 63].store(true, std::memory_order_release);
     }
     kern<<<grid, (producer_warps(SRC) + W) * 32, smem, stream>>>(tm_in, tm_in2, tm_in3, tm_t, tm_t2 ? *tm_t2 : tm_t, tm_r,
                                                                  tm_r2 ? *tm_r2 : tm_r, p);

@@ -24,7 +24,7 @@ _pp = ctypes.POINTER(ctypes.c_void_p)
 class MoeDims(ctypes.Structure):
     """mx8_moe_dims"""
     _fields_ = [(n, ctypes.c_int) for n in ("world", "tokens", "hidden", "intermediate", "shared_intermediate", "num_local_experts",
-                                            "topk", "capacity", "num_comm_sms", "minibatch_size", "minibatches", "ramp", "combine_sms")]
+                                            "topk", "capacity", "num_comm_sms", "minibatch_size", "minibatches", "ramp", "combine_sms", "split_gate_up", "split_swiglu")]
 
 
 FWD_IN = ("w_shared_gate", "w_shared_up", "w_shared_down", "w_gate", "w_gate_sc", "w_up", "w_up_sc", "w_down", "w_down_sc",
@@ -79,6 +79,8 @@ SIGNATURES = {
     "mx8_moe_minibatch_bounds": (_i, [_vp, _i, _i, _vp, _vp]),
     "mx8_moe_dispatch_quantize_window": (_i, [ctypes.POINTER(_vp), _i, _i, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _wp, _vp]),
     "mx8_gemm_grouped_window": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _i, _wp, _vp]),
+    "mx8_gemm_grouped_pair_window": (_i, [_vp] * 10 + [_i, _i, _i, _i, _vp, _vp, _i, _wp, _vp]),
+    "mx8_gemm_grouped_swiglu_window": (_i, [_vp] * 14 + [_i, _i, _i, _vp, _vp, _i, _wp, _vp]),
     "mx8_swiglu_quantize_window": (_i, [_vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _wp, _vp]),
     "mx8_swiglu_bwd_quantize_both_window": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp] + [_vp] * 8 + [_wp, _vp]),
     "mx8_gemm_grouped_dual_window": (_i, [_vp] * 9 + [_i, _i, _i, _i, _vp, _vp, _i, _wp, _vp]),
@@ -95,8 +97,8 @@ SIGNATURES = {
     "mx8_gemm_a_bf16_workspace": (ctypes.c_size_t, [_i, _i]),
     "mx8_gemm_a_bf16_fused": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "mx8_gemm_a_bf16": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, ctypes.c_size_t, _vp]),
-    "mx8_debug_set_gemm_ablation": (_i, [_i]),
     "mx8_probe_mma_peak": (_i, [_i, ctypes.POINTER(ctypes.c_double), _vp]),
+    "mx8_selftest_bounded_wait": (_i, [ctypes.c_uint, _vp]),
     "mx8_device_status": (_i, [ctypes.POINTER(_i), _vp]),
     "mx8_strerror": (ctypes.c_char_p, [_i]),
     "mx8_last_cuda_error": (ctypes.c_char_p, []),

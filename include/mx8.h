@@ -267,6 +267,27 @@ MX8_API int mx8_moe_dispatch_quantize_window(const void* const* x_ptrs, int worl
 MX8_API int mx8_gemm_grouped_window(const void* A, const void* A_sc, const void* B, const void* B_sc, void* C, void* C_sc,
                                     int M, int N, int K, int c_dtype, const void* num_rows, const void* group_rows,
                                     int num_groups, const mx8_window* window, void* stream);
+/* Two grouped products of the same A in one launch: C1 = A . B1_g^T and C2 = A . B2_g^T (B1, B2 of one shape, C1, C2 of
+ * one type; other arguments as mx8_gemm_grouped_window; N a multiple of 256).  The reference's task queue interleaves
+ * the gate and up projections of a minibatch the same way (blackwell-ultra/022-…-mxfp8-bw.cu:1876-1992); one launch has
+ * one partial last round instead of two and reads every A panel once for both. */
+MX8_API int mx8_gemm_grouped_pair_window(const void* A, const void* A_sc, const void* B1, const void* B1_sc, const void* B2,
+                                         const void* B2_sc, void* C1, void* C1_sc, void* C2, void* C2_sc, int M, int N, int K,
+                                         int c_dtype, const void* num_rows, const void* group_rows, int num_groups,
+                                         const mx8_window* window, void* stream);
+/* Gate and up projections of the MoE layer with SwiGLU in the epilogue, one launch: per 256-row x 128-column tile one CTA
+ * of the pair holds the gate weights' rows and the other the up weights' rows, so the epilogue has gate and up of the
+ * same columns side by side.  It writes gate and up as MXFP8 (bytes [M][N] + scale tiles, exactly what two
+ * mx8_gemm_grouped calls with MX8_C_MXFP8 write), and hidden = bf16( silu(dequant(gate)) * dequant(up) ) as MXFP8 in both
+ * orientations (exactly what mx8_swiglu_quantize writes from those): hidden_fp8 [M][N] / hidden_sc and hidden_fp8_t
+ * [N][M] / hidden_sc_t.  A [M][K], B_gate / B_up [num_groups][N][K]; M a multiple of 256, N and K of 128; grouping, num_rows
+ * and window as in mx8_gemm_grouped_window.  Replaces the quantizing epilogue of expert_grouped_gemm plus swiglu_fwd<false>,
+ * blackwell-ultra/022-…-mxfp8-bw.cu:1644-1700 and :924-1129, which the reference runs as separate tasks. */
+MX8_API int mx8_gemm_grouped_swiglu_window(const void* A, const void* A_sc, const void* B_gate, const void* B_gate_sc,
+                                           const void* B_up, const void* B_up_sc, void* gate_fp8, void* gate_sc, void* up_fp8,
+                                           void* up_sc, void* hidden_fp8, void* hidden_sc, void* hidden_fp8_t, void* hidden_sc_t,
+                                           int M, int N, int K, const void* num_rows, const void* group_rows, int num_groups,
+                                           const mx8_window* window, void* stream);
 MX8_API int mx8_swiglu_quantize_window(const void* gate_fp8, const void* gate_sc, const void* up_fp8, const void* up_sc,
                                        int rows, int cols, const void* num_rows, void* hidden_fp8, void* hidden_sc,
                                        void* hidden_fp8_t, void* hidden_sc_t, void* hidden_bf16, const mx8_window* window,
@@ -301,7 +322,9 @@ MX8_API int mx8_moe_minibatch_bounds_split(const void* tokens_per_expert, int nu
  *   ceil(capacity / minibatch_size) minibatches whose transfers overlap the other minibatches' GEMMs on two side
  *   streams the library creates once per device; outputs do not depend on the split.  Otherwise one launch
  *   sequence on `stream`.  Tuning (all may be 0): minibatches overrides the count; ramp = 1 makes the first and
- *   last minibatch half as large; combine_sms caps a combine that runs beside GEMMs (default num_comm_sms / 4).
+ *   last minibatch half as large; combine_sms caps a combine that runs beside GEMMs (default num_comm_sms / 4);
+ *   split_swiglu = 1 runs SwiGLU as its own kernel after the gate / up projections instead of in their epilogue, and
+ *   then split_gate_up = 1 launches the two projections separately instead of as one pair launch.
  *   fuse_combine = 1: the down projection's epilogue writes the owners' buffers directly (one sequence; y_routed
  *   may be NULL).
  * mx8_moe_bwd = dispatch_mlp_swiglu_combine_bwd (same file :2556-2760) in the same style: the eighteen tensors its
@@ -311,7 +334,7 @@ MX8_API int mx8_moe_minibatch_bounds_split(const void* tokens_per_expert, int nu
 typedef struct mx8_moe_dims {
     int world, tokens, hidden, intermediate, shared_intermediate, num_local_experts, topk, capacity;
     int num_comm_sms, minibatch_size;
-    int minibatches, ramp, combine_sms;
+    int minibatches, ramp, combine_sms, split_gate_up, split_swiglu;
 } mx8_moe_dims;
 typedef struct mx8_moe_fwd_args {
     mx8_moe_dims dims;
@@ -376,9 +399,10 @@ MX8_API int mx8_gemm_host(const void* A_host, const void* A_sc_host, const void*
  * bytes: the E4M3 bytes, then the scale tiles), then mx8_gemm runs; two launches on `stream`, same result
  * as calling mx8_quantize and mx8_gemm.  Stands in for a GEMM with a quantizing prologue; the reference
  * quantizes in separate kernels too (blackwell-ultra/022-…-mxfp8-bw.cu:717-828 before :1399-1736).
- * mx8_gemm_a_bf16_fused is the same product with the quantization done inside the GEMM's main loop (four
- * extra warps convert every bf16 A tile to E4M3 + scale bytes in shared memory): no workspace and one launch,
- * bit-identical output, at the price of three pipeline stages instead of six. */
+ * mx8_gemm_a_bf16_fused is the same product with the quantization done inside the GEMM's main loop (eight
+ * converter warps turn every bf16 A tile, fetched into a two-slot staging ring, into E4M3 + scale bytes in shared
+ * memory): no workspace and one launch, bit-identical output, at the price of four pipeline stages instead of
+ * six; measured at about a third of the two-launch form's rate, so nothing in the library calls it. */
 MX8_API int mx8_gemm_a_bf16_fused(const void* A_bf16, const void* B, const void* B_sc, void* C, int M, int N, int K,
                                   int c_dtype, void* stream);
 MX8_API size_t mx8_gemm_a_bf16_workspace(int M, int K);
@@ -392,15 +416,17 @@ MX8_API int mx8_gemm_a_bf16(const void* A_bf16, const void* B, const void* B_sc,
  * benchmark reports the GEMM against (the data sheet's 4.5 PFLOP/s assumes a clock the power cap does not allow). */
 MX8_API int mx8_probe_mma_peak(int k_steps, double* flops_out, void* stream);
 
+/* Exercises the library's failure reporting without a fault: queues a one-block kernel that waits, through the
+ * bounded wait all kernels here use, on a barrier nothing ever signals.  After limit_us microseconds (1 .. 1 000 000)
+ * the wait gives up, the kernel records code 8 in the device status word and returns normally; the next
+ * mx8_device_status call then answers MX8_ERR_DEVICE_TIMEOUT with status 8 and clears the word, and the device
+ * stays usable.  The reference's waits are unbounded (blackwell-ultra/022-…-mxfp8-bw.cu:703-711); no counterpart. */
+MX8_API int mx8_selftest_bounded_wait(unsigned limit_us, void* stream);
+
 /* Synchronizes `stream`, then reads and clears the current device's status word: 0 = healthy,
  * otherwise the code of the first bounded wait that expired (see csrc/mx8_ptx.cuh).
  * Returns MX8_OK, MX8_ERR_DEVICE_TIMEOUT (status != 0) or MX8_ERR_CUDA. */
 MX8_API int mx8_device_status(int* status_out, void* stream);
-
-/* Timing studies only: switches parts of the GEMM kernel off (bit mask, see csrc/gemm.cu `dbg`);
- * results are WRONG while a non-zero mask is set.  Returns the previous mask.  No counterpart in the
- * reference.  Normal use never calls this. */
-MX8_API int mx8_debug_set_gemm_ablation(int flags);
 
 MX8_API const char* mx8_strerror(int code);
 MX8_API const char* mx8_last_cuda_error(void); /* text of the last CUDA failure seen by this thread */

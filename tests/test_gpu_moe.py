@@ -541,3 +541,80 @@ def test_pipelined_backward_equals_single_sequence():
         assert torch.equal(b1[i][:n].view(torch.uint8), b2[i][:n].view(torch.uint8)), i
     for i in (13, 15, 17):                             # weight gradients
         assert torch.equal(b1[i].view(torch.int16), b2[i].view(torch.int16)), i
+
+
+def test_pair_launch_equals_two_grouped_gemms():
+    # gate and up projections as one launch: exactly the bytes of the two separate launches, MXFP8 and bf16 output,
+    # with a device-side row count below the capacity and an empty group
+    E, N, K = 4, 512, 384
+    group_rows = torch.tensor([256, 0, 512, 256], dtype=torch.int32)
+    R = int(group_rows.sum()) + 256
+    a = _quant(O.make_input(R, K, seed=1, std=K ** -0.25))
+    b1 = O.quantize_both(torch.stack([O.make_input(N, K, seed=10 + e, std=K ** -0.25) for e in range(E)]))[:2]
+    b2 = O.quantize_both(torch.stack([O.make_input(N, K, seed=20 + e, std=K ** -0.25) for e in range(E)]))[:2]
+    dev = lambda pair: [t.to(DEV) for t in pair]
+    a, b1, b2 = dev(a), dev(b1), dev(b2)
+    nr = torch.tensor([int(group_rows.sum())], dtype=torch.int32, device=DEV)
+    gr = group_rows.to(DEV)
+    lib = mx8.load()
+    st = torch.cuda.current_stream().cuda_stream
+    n = int(group_rows.sum())
+    for mxfp8 in (True, False):
+        def outs():
+            if mxfp8:
+                return (torch.full((R, N), 0xEE, dtype=torch.uint8, device=DEV), torch.full((R // 128, N // 128, 32, 16), 0xEE, dtype=torch.uint8, device=DEV))
+            return (torch.full((R, N), float("nan"), dtype=torch.bfloat16, device=DEV), None)
+        c1, c2, d1, d2 = outs(), outs(), outs(), outs()
+        mx8.gemm_grouped(a[0], a[1], b1[0], b1[1], c1[0].view(torch.float8_e4m3fn) if mxfp8 else c1[0], c1[1], nr, gr)
+        mx8.gemm_grouped(a[0], a[1], b2[0], b2[1], c2[0].view(torch.float8_e4m3fn) if mxfp8 else c2[0], c2[1], nr, gr)
+        p = lambda t: t.data_ptr() if t is not None else None
+        rc = lib.mx8_gemm_grouped_pair_window(a[0].data_ptr(), a[1].data_ptr(), b1[0].data_ptr(), b1[1].data_ptr(), b2[0].data_ptr(),
+                                              b2[1].data_ptr(), p(d1[0]), p(d1[1]), p(d2[0]), p(d2[1]), R, N, K,
+                                              2 if mxfp8 else 0, nr.data_ptr(), gr.data_ptr(), E, None, st)
+        assert rc == 0 and mx8.device_status() == 0
+        view = torch.uint8 if mxfp8 else torch.int16
+        for sep, pair in ((c1, d1), (c2, d2)):
+            assert torch.equal(sep[0][:n].view(view), pair[0][:n].view(view))
+            if mxfp8:
+                assert torch.equal(sep[1][:n // 128], pair[1][:n // 128])
+        assert not torch.equal(d1[0][:n].view(view), d2[0][:n].view(view))
+
+
+@pytest.mark.parametrize("I,H", [(256, 384), (512, 256)])
+def test_swiglu_in_the_gemm_epilogue_equals_the_separate_kernels(I, H):
+    # gate / up projections with SwiGLU in the epilogue: every output byte equals what the pair launch followed by
+    # the stand-alone SwiGLU kernel writes (gate, up, hidden row-wise and transposed, and all four scale tensors)
+    E = 3
+    group_rows = torch.tensor([256, 512, 256], dtype=torch.int32)
+    n = int(group_rows.sum())
+    R = n + 256                                                   # capacity beyond the rows in use
+    a = [t.to(DEV) for t in _quant(O.make_input(R, H, seed=1))]
+    wg = [t.to(DEV) for t in O.quantize_both(torch.stack([O.make_input(I, H, seed=10 + e, std=H ** -0.5) for e in range(E)]))[:2]]
+    wu = [t.to(DEV) for t in O.quantize_both(torch.stack([O.make_input(I, H, seed=20 + e, std=H ** -0.5) for e in range(E)]))[:2]]
+    nr = torch.tensor([n], dtype=torch.int32, device=DEV)
+    gr = group_rows.to(DEV)
+    lib = mx8.load()
+    st = torch.cuda.current_stream().cuda_stream
+    u8 = lambda *shape: torch.full(shape, 0xEE, dtype=torch.uint8, device=DEV)
+    sep = dict(g=u8(R, I), gs=u8(R // 128, I // 128, 32, 16), u=u8(R, I), us=u8(R // 128, I // 128, 32, 16))
+    rc = lib.mx8_gemm_grouped_pair_window(a[0].data_ptr(), a[1].data_ptr(), wg[0].data_ptr(), wg[1].data_ptr(), wu[0].data_ptr(),
+                                          wu[1].data_ptr(), sep["g"].data_ptr(), sep["gs"].data_ptr(), sep["u"].data_ptr(),
+                                          sep["us"].data_ptr(), R, I, H, 2, nr.data_ptr(), gr.data_ptr(), E, None, st)
+    assert rc == 0
+    h, hs, ht, hts = mx8.swiglu_quantize(sep["g"].view(torch.float8_e4m3fn), sep["gs"], sep["u"].view(torch.float8_e4m3fn), sep["us"], nr)
+    fused = [u8(R, I), u8(R // 128, I // 128, 32, 16), u8(R, I), u8(R // 128, I // 128, 32, 16), u8(R, I), u8(R // 128, I // 128, 32, 16),
+             u8(I, R), u8(I // 128, R // 128, 32, 16)]
+    rc = lib.mx8_gemm_grouped_swiglu_window(a[0].data_ptr(), a[1].data_ptr(), wg[0].data_ptr(), wg[1].data_ptr(), wu[0].data_ptr(),
+                                            wu[1].data_ptr(), *[t.data_ptr() for t in fused], R, I, H, nr.data_ptr(), gr.data_ptr(), E,
+                                            None, st)
+    assert rc == 0 and mx8.device_status() == 0
+    want = [sep["g"], sep["gs"], sep["u"], sep["us"], h.view(torch.uint8), hs, ht.view(torch.uint8), hts]
+    names = ["gate", "gate_sc", "up", "up_sc", "hidden", "hidden_sc", "hidden_t", "hidden_t_sc"]
+    for name, got, ref in zip(names, fused, want):
+        if name in ("hidden_t", "hidden_t_sc"):
+            got, ref = got[:, :n // (128 if name.endswith("sc") else 1)], ref[:, :n // (128 if name.endswith("sc") else 1)]
+        else:
+            got, ref = got[:n // (128 if name.endswith("sc") else 1)], ref[:n // (128 if name.endswith("sc") else 1)]
+        assert torch.equal(got, ref), name
+    # rows beyond the count are untouched
+    assert bool((fused[0][n:] == 0xEE).all()) and bool((fused[4][n:] == 0xEE).all())
