@@ -450,10 +450,19 @@ def bench_gemm(args, world, rank, local, peaks, with_cpu):
         sets.append((aq, asc, bq, bsc, torch.empty(M, N, dtype=torch.bfloat16, device=dev)))
         del a, b
     flops = 2.0 * M * N * K
+    # --gemm-form: the activation arrives as bf16 and is quantized by a separate launch (a-bf16) or inside the GEMM's
+    # main loop (a-bf16-fused, the optional prologue); default: operands already MXFP8
+    a16 = a16_ws = None
+    if args.gemm_form != "mxfp8" or (rank == 0 and not args.quick):
+        a16 = O.make_input(M, K, seed=100 + rank, std=K ** -0.5).to(dev)
+        a16_ws = torch.empty(mx8.load().mx8_gemm_a_bf16_workspace(M, K), dtype=torch.uint8, device=dev)
 
     def step(i):
         aq, asc, bq, bsc, c = sets[i % 3]
-        mx8.kernel(aq, asc, bq, bsc, c)
+        if args.gemm_form == "mxfp8":
+            mx8.kernel(aq, asc, bq, bsc, c)
+        else:
+            mx8.kernel_a_bf16(a16, bq, bsc, c, a16_ws, fused=args.gemm_form == "a-bf16-fused")
 
     for i in range(args.warmup):
         step(i)
@@ -488,6 +497,26 @@ def bench_gemm(args, world, rank, local, peaks, with_cpu):
             library["mx8_same_loop_tflops"] = lib_rate(lambda: mx8.kernel(aq, asc, bq, bsc, c))
         except Exception as ex:
             library["error"] = f"{type(ex).__name__}: {ex}"[:200]
+    # the three forms of the product for a bf16 activation, same loop (the evidence behind "the prologue is not used")
+    forms = {}
+    if rank == 0 and not args.quick and a16 is not None:
+        aq, asc, bq, bsc, c = sets[0]
+        def form_rate(fn, iters=10):
+            for _ in range(2):
+                fn()
+            torch.cuda.synchronize()
+            time.sleep(0.3)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(iters):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            return flops / (e0.elapsed_time(e1) / iters * 1e-3) / 1e12
+        forms = {"operands_already_mxfp8_tflops": form_rate(lambda: mx8.kernel(aq, asc, bq, bsc, c)),
+                 "a_bf16_quantize_then_gemm_tflops": form_rate(lambda: mx8.kernel_a_bf16(a16, bq, bsc, c, a16_ws)),
+                 "a_bf16_quantized_in_main_loop_tflops": form_rate(lambda: mx8.kernel_a_bf16(a16, bq, bsc, c, a16_ws, fused=True))}
+        mx8.device_status()
     aq, asc, bq, bsc, c = sets[0]
     host_in = [t.cpu().pin_memory() for t in (aq, asc, bq, bsc)]
     c_h = torch.empty(c.shape, dtype=c.dtype).pin_memory()
@@ -531,6 +560,7 @@ def bench_gemm(args, world, rank, local, peaks, with_cpu):
                 "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": e2e_steps, "api": "mx8_gemm_host, bands of %d rows" % band},
         "gpu_launches": args.steps + sus_steps,
         "library": library,
+        "bf16_activation_forms": forms,
     }
     if clocks:
         line["clocks"] = clocks
@@ -588,8 +618,9 @@ def bench_moe(args, world, rank, local, peaks, with_cpu=False):
     the ranks, top-8 routing, routed experts only.  A step is the reference harness's run_fwd_once."""
     import mx8
     dev = torch.device("cuda", local)
-    E_total, H, I, k = 256, 7168, 2048, 8
-    T, E = 32768 // world, E_total // world
+    E_total, H, I, k = args.moe_experts, 7168, 2048, 8
+    tokens_total = args.moe_tokens
+    T, E = tokens_total // world, E_total // world
     cap = ((T * k * max(2, world // 4)) // 256) * 256
     g = torch.Generator(device=dev).manual_seed(1234 + rank)
     logits = torch.randn(T, E_total, device=dev, generator=g)
@@ -711,8 +742,8 @@ def bench_moe(args, world, rank, local, peaks, with_cpu=False):
                   "ok": flags[0].item() == 0.0 and flags[1].item() == 0.0 and flags[2].item() < 1e-2 and flags[3].item() == 0.0}
         del single, piped, cb_single, out_single
 
-    steps = LAYER_STEPS
-    for i in range(3):
+    steps = 2 if args.quick else LAYER_STEPS
+    for i in range(1 if args.quick else 3):
         step(i)
     ms_single = timed(step, steps, world) / steps
     mx8.device_status()
@@ -786,14 +817,14 @@ def bench_moe(args, world, rank, local, peaks, with_cpu=False):
         bms = bms_pipe if use_pipe else bms_single
         pipeline["backward_ms_per_step"] = bms_pipe
         pipeline["backward_single_sequence_ms_per_step"] = bms_single
-        bwd = {"ms_per_step": bms, "value": 12.0 * (32768 * k) * H * I / (bms * 1e-3) / 1e12, "unit": "TFLOP/s",
+        bwd = {"ms_per_step": bms, "value": 12.0 * (tokens_total * k) * H * I / (bms * 1e-3) / 1e12, "unit": "TFLOP/s",
                "flops": "12 * routed rows * hidden * intermediate"}
-    flops_total = 6.0 * (32768 * k) * H * I
+    flops_total = 6.0 * (tokens_total * k) * H * I
     value = flops_total / (ms * 1e-3) / 1e12
     per_gpu = value / world
     return {"metric": "mxfp8_moe_forward_throughput", "value": value, "unit": "TFLOP/s", "ms_per_step": ms, "steps": steps,
             "scaling": "strong",
-            "config": {"workload": f"MoE forward, {E_total} experts / {world} GPUs, hidden {H}, intermediate {I}, 32768 tokens, top-{k}, routed experts only",
+            "config": {"workload": f"MoE forward, {E_total} experts / {world} GPUs, hidden {H}, intermediate {I}, {tokens_total} tokens, top-{k}, routed experts only",
                        "flops": "6 * routed rows * hidden * intermediate (padding rows not counted)",
                        "sharding": "experts and tokens split across GPUs; dispatch pulls and combine pushes over peer-mapped memory"},
             "roofline": tensor_roofline(per_gpu, local, sampler.summary() if sampler else None, traffic=None),
@@ -840,6 +871,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="mx8", choices=["mx8", "reference"])
     ap.add_argument("--workload", default="quantize", choices=["quantize", "gemm", "ffn", "moe"])
+    ap.add_argument("--gemm-form", default="mxfp8", choices=["mxfp8", "a-bf16", "a-bf16-fused"],
+                    help="GEMM: what the timed step launches (bf16 activation quantized by its own launch, or inside the main loop)")
     ap.add_argument("--moe-comm-sms", type=int, default=28, help="MoE: multiprocessors left to the dispatch of the next minibatch")
     ap.add_argument("--moe-minibatch", type=int, default=0,
                     help="MoE: schedule rows per minibatch of the pipelined layer (0 = a quarter of the schedule capacity; "
@@ -847,6 +880,8 @@ def main():
     ap.add_argument("--moe-minibatches", type=int, default=4, help="MoE: minibatches when --moe-minibatch is 0")
     ap.add_argument("--moe-ramp", type=int, default=0, help="MoE: 1 = first and last minibatch half as large")
     ap.add_argument("--moe-combine-sms", type=int, default=0, help="MoE: multiprocessors' worth of blocks for a combine beside GEMMs (0 = comm SMs / 4)")
+    ap.add_argument("--moe-tokens", type=int, default=32768, help="MoE: tokens in total (smaller for profiler captures)")
+    ap.add_argument("--moe-experts", type=int, default=256, help="MoE: experts in total (smaller for profiler captures)")
     ap.add_argument("--no-parity", action="store_true", help="MoE: skip the parity checks that precede the timing")
     ap.add_argument("--no-bwd", action="store_true", help="MoE: skip the backward")
     ap.add_argument("--no-layers", action="store_true", help="skip the FFN and MoE objects of the quantize line")
@@ -874,7 +909,7 @@ def main():
         if not args.no_gemm:
             g = bench_gemm(args, world, rank, local, peaks, with_cpu)
             line["gemm"] = {k: g[k] for k in ("metric", "value", "unit", "ms_per_step", "scaling", "config", "roofline", "e2e",
-                                              "gpu_launches", "clocks", "cpu_baseline", "library", "sustained") if k in g}
+                                              "gpu_launches", "clocks", "cpu_baseline", "library", "sustained", "bf16_activation_forms") if k in g}
             line["gpu_launches"] += g["gpu_launches"]
         if not args.no_layers:
             for name, fn in (("ffn", bench_ffn), ("moe", bench_moe)):

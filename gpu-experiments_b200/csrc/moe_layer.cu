@@ -10,8 +10,8 @@
 // combine of minibatch b-1 on a third stream, the GEMMs and SwiGLU of minibatch b on the caller's stream on the
 // remaining multiprocessors.  Events order the three legs of a minibatch; no kernel waits on another kernel.
 // Every kernel is the row-window form of the one the unsplit layer launches, so the outputs do not depend on
-// the split.  Nothing is allocated: intermediates live in the caller's workspace, the two side streams and a
-// pool of events are created once per device and kept.
+// the split.  No device memory is allocated: intermediates live in the caller's workspace; the two side streams are
+// created once per device and kept, the events of a call live as long as the call.
 #include <mutex>
 
 #include "mx8_host.cuh"
@@ -23,11 +23,25 @@ constexpr int MAX_MINIBATCHES = 64;
 
 struct DeviceCtx {
     cudaStream_t disp = nullptr, comb = nullptr;
-    cudaEvent_t ev[2 * MAX_MINIBATCHES + 4] = {};
     bool ready = false;
 };
 
-// side streams and events of the current device (created on first use, kept until the process exits)
+// Events of one call: created at its start, destroyed when it returns (the runtime keeps an event alive until the
+// work that references it has finished), so concurrent calls never share one.
+struct CallEvents {
+    cudaEvent_t ev[2 * MAX_MINIBATCHES + 2] = {};
+    int n = 0;
+    cudaError_t err = cudaSuccess;
+    explicit CallEvents(int count) {
+        for (; n < count && err == cudaSuccess; ++n) err = cudaEventCreateWithFlags(&ev[n], cudaEventDisableTiming);
+        if (err != cudaSuccess) --n;
+    }
+    ~CallEvents() {
+        for (int i = 0; i < n; ++i) cudaEventDestroy(ev[i]);
+    }
+};
+
+// side streams of the current device (created on first use, kept until the process exits)
 static int device_ctx(DeviceCtx** out) {
     static DeviceCtx per_device[64];
     static std::mutex mu;
@@ -42,10 +56,8 @@ static int device_ctx(DeviceCtx** out) {
     if (!c.ready) {
         e = cudaStreamCreateWithFlags(&c.disp, cudaStreamNonBlocking);
         if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&c.comb, cudaStreamNonBlocking);
-        for (cudaEvent_t& ev : c.ev)
-            if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
         if (e != cudaSuccess) {
-            note_cuda_error("moe layer: stream / event creation", cudaGetErrorString(e));
+            note_cuda_error("moe layer: stream creation", cudaGetErrorString(e));
             return MX8_ERR_CUDA;
         }
         c.ready = true;
@@ -227,9 +239,12 @@ extern "C" int mx8_moe_fwd(const mx8_moe_fwd_args* a, void* stream) {
     if (math_sms < 2) return MX8_ERR_ARG;
     const int combine_sms = d.combine_sms > 0 ? d.combine_sms : (d.num_comm_sms / 4 > 0 ? d.num_comm_sms / 4 : 1);
     ck(mx8_moe_minibatch_bounds_split(a->tokens_per_expert, E, nb, first_expert, bounds, main));
-    cudaEvent_t start = cx->ev[0], done = cx->ev[1];
-    cudaEvent_t* disp_done = cx->ev + 2;
-    cudaEvent_t* math_done = cx->ev + 2 + MAX_MINIBATCHES;
+    CallEvents evs(2 * nb + 2);
+    ck.cuda(evs.err, "cudaEventCreateWithFlags");
+    if (!ck.ok()) return ck.rc;
+    cudaEvent_t start = evs.ev[0], done = evs.ev[1];
+    cudaEvent_t* disp_done = evs.ev + 2;
+    cudaEvent_t* math_done = evs.ev + 2 + nb;
     ck.cuda(cudaEventRecord(start, main), "cudaEventRecord");
     ck.cuda(cudaStreamWaitEvent(cx->disp, start, 0), "cudaStreamWaitEvent");
     ck.cuda(cudaStreamWaitEvent(cx->comb, start, 0), "cudaStreamWaitEvent");
@@ -324,6 +339,9 @@ extern "C" int mx8_moe_bwd(const mx8_moe_bwd_args* a, void* stream) {
     int math_sms = 0, combine_sms = 0;
     cudaEvent_t* disp_done = nullptr;
     cudaEvent_t* math_done = nullptr;
+    CallEvents evs(pipe ? 2 * nb + 2 : 0);
+    ck.cuda(evs.err, "cudaEventCreateWithFlags");
+    if (!ck.ok()) return ck.rc;
     if (pipe) {
         if ((rc = device_ctx(&cx)) != MX8_OK) return rc;
         const int sms = sm_count();
@@ -333,12 +351,12 @@ extern "C" int mx8_moe_bwd(const mx8_moe_bwd_args* a, void* stream) {
         combine_sms = d.combine_sms > 0 ? d.combine_sms : (d.num_comm_sms / 4 > 0 ? d.num_comm_sms / 4 : 1);
         s_disp = cx->disp;
         s_comb = cx->comb;
-        disp_done = cx->ev + 2;
-        math_done = cx->ev + 2 + MAX_MINIBATCHES;
+        disp_done = evs.ev + 2;
+        math_done = evs.ev + 2 + nb;
         ck(mx8_moe_minibatch_bounds_split(a->tokens_per_expert, E, nb, first_expert, bounds, main));
-        ck.cuda(cudaEventRecord(cx->ev[0], main), "cudaEventRecord");
-        ck.cuda(cudaStreamWaitEvent(s_disp, cx->ev[0], 0), "cudaStreamWaitEvent");
-        ck.cuda(cudaStreamWaitEvent(s_comb, cx->ev[0], 0), "cudaStreamWaitEvent");
+        ck.cuda(cudaEventRecord(evs.ev[0], main), "cudaEventRecord");
+        ck.cuda(cudaStreamWaitEvent(s_disp, evs.ev[0], 0), "cudaStreamWaitEvent");
+        ck.cuda(cudaStreamWaitEvent(s_comb, evs.ev[0], 0), "cudaStreamWaitEvent");
     }
     for (int b = 0; b < nb && ck.ok(); ++b) {
         const mx8_window w{pipe ? bounds + b : nullptr, pipe ? bounds + b + 1 : nullptr, (pipe && b > 0) ? d.num_comm_sms : 0};
@@ -373,8 +391,8 @@ extern "C" int mx8_moe_bwd(const mx8_moe_bwd_args* a, void* stream) {
     ck(mx8_gemm_wgrad(d_y_fp8_t, d_y_sc_t, a->hidden_fp8_t, a->hidden_sc_t, a->d_w_down, H, I, cap, a->tokens_per_expert, E, main));
     if (pipe) {
         // the last gradient combine ran beside the weight gradients
-        ck.cuda(cudaEventRecord(cx->ev[1], s_comb), "cudaEventRecord");
-        ck.cuda(cudaStreamWaitEvent(main, cx->ev[1], 0), "cudaStreamWaitEvent");
+        ck.cuda(cudaEventRecord(evs.ev[1], s_comb), "cudaEventRecord");
+        ck.cuda(cudaStreamWaitEvent(main, evs.ev[1], 0), "cudaStreamWaitEvent");
     }
     if (shared && ck.ok()) {
         const int T = d.tokens, Is = d.shared_intermediate;
