@@ -2,8 +2,10 @@
  * block-scaled GEMM that consumes it.
  *
  * Conventions
- *   - every pointer is a DEVICE pointer owned by the caller; the library allocates nothing and
- *     keeps no reference after the call returns;
+ *   - every pointer is a DEVICE pointer owned by the caller (HOST arrays of device pointers and the *_host forms are
+ *     marked as such); the library allocates no device memory and keeps no reference after the call returns.  Two
+ *     families create CUDA streams once per device and keep them: the *_host forms (copy streams) and mx8_moe_fwd /
+ *     mx8_moe_bwd in minibatch mode (two side streams);
  *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream); launches are
  *     asynchronous, exactly like the reference's entry points;
  *   - the return value is a status code (MX8_OK == 0); nothing calls exit() and nothing traps.

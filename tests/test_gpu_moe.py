@@ -618,3 +618,34 @@ def test_swiglu_in_the_gemm_epilogue_equals_the_separate_kernels(I, H):
         assert torch.equal(got, ref), name
     # rows beyond the count are untouched
     assert bool((fused[0][n:] == 0xEE).all()) and bool((fused[4][n:] == 0xEE).all())
+
+
+def test_layer_after_an_overflowed_schedule_reports_and_does_not_fault():
+    # capacity too small for the routed pairs: the schedule raises the status word; the layer that was queued behind it
+    # clamps every kernel to the capacity (dispatch, GEMMs, the SwiGLU epilogue, combine), so nothing is read or written
+    # out of bounds and the device stays healthy
+    W, T, H, I, k, E_local = 1, 1024, 256, 256, 2, 2
+    topk_all, _ = make_topk(W, T, W * E_local, k, seed=13)
+    cap = 512                                                      # 2048 pairs + padding would need 2304 rows
+    pr, pt, nt, tpe = mx8.schedule(topk_all.to(DEV), E_local, cap, 0)
+    x = O.make_input(T, H, seed=14).to(DEV)
+    guard = 8
+    cb = torch.full((T * k + guard, H), -5.0, dtype=torch.bfloat16, device=DEV)
+    q2 = lambda r, c, sd: [t.to(DEV) for t in O.quantize_both(torch.stack([O.make_input(r, c, seed=sd + e, std=c ** -0.5) for e in range(E_local)]))[:2]]
+    wg, wu, wd = q2(I, H, 100), q2(I, H, 200), q2(H, I, 300)
+    for kw in ({}, dict(num_comm_sms=28, minibatch_size=256)):
+        f = mx8.dispatch_mlp_swiglu_combine_fwd(x, [x.data_ptr()], cb[:T * k], [cb.data_ptr()], None, *wg, None, *wu, None, *wd,
+                                                pr, pt, nt, tpe, k, **kw)
+        with pytest.raises(mx8.Mx8Error):
+            mx8.device_status()                                    # the overflow, reported once
+        assert int(nt) > cap and f[12].shape[0] == cap
+        assert bool((cb[T * k:] == -5.0).all())
+        pr, pt, nt, tpe = mx8.schedule(topk_all.to(DEV), E_local, cap, 0)
+    with pytest.raises(mx8.Mx8Error):
+        mx8.device_status()
+    # and the same layer with room for everything works right after
+    cap = ((T * k) // 256 + E_local) * 256
+    pr, pt, nt, tpe = mx8.schedule(topk_all.to(DEV), E_local, cap, 0)
+    f = mx8.dispatch_mlp_swiglu_combine_fwd(x, [x.data_ptr()], cb[:T * k], [cb.data_ptr()], None, *wg, None, *wu, None, *wd, pr, pt, nt, tpe, k)
+    assert mx8.device_status() == 0
+    assert bool((cb[T * k:] == -5.0).all())
