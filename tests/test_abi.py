@@ -90,3 +90,51 @@ def test_torch_module_mirrors_reference_bindings(lib):
     x = torch.zeros(128, 128, dtype=torch.bfloat16)
     with pytest.raises(RuntimeError):
         _C.mxfp8_quantize(x, True, False)          # CPU tensor: rejected, never computed on the host
+
+
+def test_moe_layer_structs_match_the_header_layout(lib):
+    # the argument structs of mx8_moe_fwd / mx8_moe_bwd as ctypes declares them against what the library reads:
+    # every pointer field set to a (never dereferenced) address and an undersized workspace in the LAST field must get
+    # past the null checks and stop at the size check; clearing any one pointer must stop at the null check
+    fake = 4096
+    dims = _lib.MoeDims(world=2, tokens=256, hidden=512, intermediate=256, shared_intermediate=0, num_local_experts=4, topk=2,
+                        capacity=1024, num_comm_sms=0, minibatch_size=0)
+    need = lib.mx8_moe_fwd_workspace_bytes(ctypes.byref(dims))
+    assert need >= 1024 * 512 + 1024 * 256
+    bad = _lib.MoeDims(world=2, tokens=256, hidden=500, intermediate=256, num_local_experts=4, topk=2, capacity=1024)
+    assert lib.mx8_moe_fwd_workspace_bytes(ctypes.byref(bad)) == 0
+    ptrs = (ctypes.c_void_p * 2)(fake, fake)
+    shared_only = {"w_shared_gate", "w_shared_up", "w_shared_down", "gate_shared", "up_shared", "hidden_shared", "y_shared"}
+
+    def fwd_args():
+        a = _lib.MoeFwdArgs()
+        a.dims = dims
+        a.x, a.x_ptrs, a.combine_ptrs = fake, ptrs, ptrs
+        for name in _lib.FWD_IN + _lib.FWD_OUT:
+            setattr(a, name, None if name in shared_only else fake)
+        a.workspace, a.workspace_bytes = fake, 1
+        return a
+
+    assert lib.mx8_moe_fwd(ctypes.byref(fwd_args()), None) == _lib.ERR_LIMIT
+    for name in ("w_gate", "tokens_per_expert", "x_fp8_t", "hidden_sc_t", "y_routed", "workspace"):
+        a = fwd_args()
+        setattr(a, name, None)
+        assert lib.mx8_moe_fwd(ctypes.byref(a), None) == _lib.ERR_ARG, name
+
+    def bwd_args():
+        a = _lib.MoeBwdArgs()
+        a.dims = dims
+        a.d_combine_ptrs, a.d_x_routed_ptrs = ptrs, ptrs
+        shared = {"w_shared_gate_T", "w_shared_up_T", "w_shared_down_T", "gate_shared", "up_shared", "hidden_shared", "x", "d_x_shared",
+                  "d_gate_shared", "d_up_shared", "d_hidden_shared", "d_w_shared_gate", "d_w_shared_up", "d_w_shared_down"}
+        for name in _lib.BWD_IN + _lib.BWD_OUT:
+            setattr(a, name, None if name in shared else fake)
+        a.workspace, a.workspace_bytes = fake, 1
+        return a
+
+    assert lib.mx8_moe_bwd_workspace_bytes(ctypes.byref(dims)) > 0
+    assert lib.mx8_moe_bwd(ctypes.byref(bwd_args()), None) == _lib.ERR_LIMIT
+    for name in ("w_down_T_sc", "hidden_sc_t", "d_w_down", "d_y_sc"):
+        a = bwd_args()
+        setattr(a, name, None)
+        assert lib.mx8_moe_bwd(ctypes.byref(a), None) == _lib.ERR_ARG, name
