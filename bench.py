@@ -884,6 +884,7 @@ def main():
     ap.add_argument("--moe-experts", type=int, default=256, help="MoE: experts in total (smaller for profiler captures)")
     ap.add_argument("--no-parity", action="store_true", help="MoE: skip the parity checks that precede the timing")
     ap.add_argument("--no-bwd", action="store_true", help="MoE: skip the backward")
+    ap.add_argument("--with-bwd", action="store_true", help="MoE: keep the backward under --quick")
     ap.add_argument("--no-layers", action="store_true", help="skip the FFN and MoE objects of the quantize line")
     ap.add_argument("--no-gemm", action="store_true", help="skip the GEMM object of the quantize line")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
@@ -892,7 +893,8 @@ def main():
                          "(for profiler captures, which should see few launches)")
     args = ap.parse_args()
     if args.quick:
-        args.no_cpu = args.no_gemm = args.no_layers = args.no_parity = args.no_bwd = True
+        args.no_cpu = args.no_gemm = args.no_layers = args.no_parity = True
+        args.no_bwd = not args.with_bwd
     args.warmup = max(args.warmup, 3)
     args.steps = max(args.steps, 1)
 

@@ -20,6 +20,7 @@
 // and orientation.  Replaces blackwell-ultra/019-mxfp8-quantize.cu:40-179 and the persistent
 // variant blackwell-ultra/020-mxfp8-quantize-persistent.cu:139-219 of the reference.
 #include <atomic>
+#include <type_traits>
 
 #include "mx8_host.cuh"
 #include "mx8_ptx.cuh"
@@ -58,6 +59,13 @@
 #endif
 #ifndef MX8_Q_MOE_RTMA
 #define MX8_Q_MOE_RTMA 1
+#endif
+// SwiGLU backward (both gradients): consumer warps and row-store form
+#ifndef MX8_Q_SWB_W
+#define MX8_Q_SWB_W 8
+#endif
+#ifndef MX8_Q_SWB_RTMA
+#define MX8_Q_SWB_RTMA MX8_Q_MOE_RTMA
 #endif
 
 namespace mx8 {
@@ -283,37 +291,71 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
             const uint32_t gw = *reinterpret_cast<const uint32_t*>(p.gate_sc + sc_tile);   // lane i: scale bytes of row i
             const uint32_t uw = *reinterpret_cast<const uint32_t*>(p.up_sc + sc_tile);
             const int sh = (l >> 3) * 8;                                                 // this lane's 32-column block
+            // The loop body is compiled once per mode.  MODE 0: forward, or d_gate alone.  MODE 1: d_up alone, which
+            // needs neither the up projection nor the derivative of silu.  MODE 2 (both gradients from one visit of
+            // the slot): d_gate, and d_up = bf16(silu(g) * d_hidden) of the same elements written over the lane's own
+            // d_hidden words in the slot, so that the second pass only loads them.
+            auto rows = [&](auto mode) {
+                constexpr int MODE = decltype(mode)::value;
+                constexpr bool D_UP = MODE == 1;
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                uint32_t g4, u4;
-                asm volatile("ld.shared.b32 %0, [%1];" : "=r"(g4) : "r"(slot_addr + i * 128 + l * 4));
-                asm volatile("ld.shared.b32 %0, [%1];" : "=r"(u4) : "r"(slot_addr + SLOT_BYTES / 2 + i * 128 + l * 4));
-                const float gs = __uint_as_float(((__shfl_sync(0xFFFFFFFFu, gw, i) >> sh) & 0xFFu) << 23);
-                const float us = __uint_as_float(((__shfl_sync(0xFFFFFFFFu, uw, i) >> sh) & 0xFFu) << 23);
-                float gf[4], uf[4], h[4];
-                e4m3x4_to_float(g4, gf);
-                e4m3x4_to_float(u4, uf);
-#pragma unroll
-                float dh[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                if constexpr (SRC == SRC_SWIGLU_BWD) {
-                    uint32_t d0, d1;
-                    ld_shared_v2(slot_addr + SLOT_BYTES + i * 256 + l * 8, d0, d1);
-                    dh[0] = bf16_lo(d0); dh[1] = bf16_hi(d0); dh[2] = bf16_lo(d1); dh[3] = bf16_hi(d1);
-                }
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float g = gf[e] * gs;
+                for (int i = 0; i < 32; ++i) {
+                    uint32_t g4, u4 = 0;
+                    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(g4) : "r"(slot_addr + i * 128 + l * 4));
+                    if constexpr (!D_UP) asm volatile("ld.shared.b32 %0, [%1];" : "=r"(u4) : "r"(slot_addr + SLOT_BYTES / 2 + i * 128 + l * 4));
+                    const float gs = __uint_as_float(((__shfl_sync(0xFFFFFFFFu, gw, i) >> sh) & 0xFFu) << 23);
+                    float us = 0.0f;
+                    if constexpr (!D_UP) us = __uint_as_float(((__shfl_sync(0xFFFFFFFFu, uw, i) >> sh) & 0xFFu) << 23);
+                    float gf[4], uf[4] = {0.0f, 0.0f, 0.0f, 0.0f}, h[4];
+                    [[maybe_unused]] float h_up[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                    e4m3x4_to_float(g4, gf);
+                    if constexpr (!D_UP) e4m3x4_to_float(u4, uf);
+                    [[maybe_unused]] float dh[4] = {0.0f, 0.0f, 0.0f, 0.0f};
                     if constexpr (SRC == SRC_SWIGLU_BWD) {
-                        const float sig = __fdividef(1.0f, 1.0f + __expf(-g));
-                        const float silu = g * sig;
-                        const float dsilu = (1.0f - silu) * sig + silu;
-                        h[e] = pass ? silu * dh[e] : (dsilu * (uf[e] * us)) * dh[e];
-                    } else {
-                        h[e] = __fdividef(g, 1.0f + __expf(-g)) * (uf[e] * us);
+                        uint32_t d0, d1;
+                        ld_shared_v2(slot_addr + SLOT_BYTES + i * 256 + l * 8, d0, d1);
+                        dh[0] = bf16_lo(d0); dh[1] = bf16_hi(d0); dh[2] = bf16_lo(d1); dh[3] = bf16_hi(d1);
                     }
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float g = gf[e] * gs;
+                        if constexpr (SRC == SRC_SWIGLU_BWD) {
+                            const float sig = __fdividef(1.0f, 1.0f + __expf(-g));
+                            const float silu = g * sig;
+                            if constexpr (D_UP) {
+                                h[e] = silu * dh[e];
+                            } else {
+                                const float dsilu = (1.0f - silu) * sig + silu;
+                                h[e] = (dsilu * (uf[e] * us)) * dh[e];
+                                if constexpr (MODE == 2) h_up[e] = silu * dh[e];
+                            }
+                        } else {
+                            h[e] = __fdividef(g, 1.0f + __expf(-g)) * (uf[e] * us);
+                        }
+                    }
+                    c[i][0] = pack_bf16x2(h[0], h[1]);
+                    c[i][1] = pack_bf16x2(h[2], h[3]);
+                    if constexpr (MODE == 2)
+                        st_shared_v2(slot_addr + SLOT_BYTES + i * 256 + l * 8, pack_bf16x2(h_up[0], h_up[1]), pack_bf16x2(h_up[2], h_up[3]));
                 }
-                c[i][0] = pack_bf16x2(h[0], h[1]);
-                c[i][1] = pack_bf16x2(h[2], h[3]);
+            };
+            if constexpr (SRC == SRC_SWIGLU_BWD) {
+                if (p.bwd_which == 2) {
+                    if (pass == 0) {
+                        rows(std::integral_constant<int, 2>{});
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) ld_shared_v2(slot_addr + SLOT_BYTES + i * 256 + l * 8, c[i][0], c[i][1]);
+                        // the slot was written through the generic proxy and is refilled through the async proxy next
+                        fence_proxy_async_smem();
+                    }
+                } else if (pass) {
+                    rows(std::integral_constant<int, 1>{});
+                } else {
+                    rows(std::integral_constant<int, 0>{});
+                }
+            } else {
+                rows(std::integral_constant<int, 0>{});
             }
             if (o_bf16) {
                 uint8_t* hb = o_bf16 + ((static_cast<size_t>(tr) * TILE + wq * SLAB_ROWS) * p.N + tc * TILE + l * 4) * 2;
@@ -759,5 +801,5 @@ extern "C" int mx8_swiglu_bwd_quantize_both_window(const void* gate_fp8, const v
     const int tiles = p.tiles_r * p.tiles_c;
     if (grid > tiles) grid = tiles;
     apply_window(p, grid, window);
-    return launch<8, 1, SRC_SWIGLU_BWD, true, true, (MX8_Q_MOE_RTMA != 0)>(tm_g, tm_u, tm_d, tm_t, tm_r, p, grid, static_cast<cudaStream_t>(stream), &tm_t2, &tm_r2);
+    return launch<MX8_Q_SWB_W, 1, SRC_SWIGLU_BWD, true, true, (MX8_Q_SWB_RTMA != 0)>(tm_g, tm_u, tm_d, tm_t, tm_r, p, grid, static_cast<cudaStream_t>(stream), &tm_t2, &tm_r2);
 }
