@@ -878,7 +878,7 @@ def main():
                     help="MoE: schedule rows per minibatch of the pipelined layer (0 = a quarter of the schedule capacity; "
                          "the reference harness uses 16384, which is the same at 8 GPUs)")
     ap.add_argument("--moe-minibatches", type=int, default=4, help="MoE: minibatches when --moe-minibatch is 0")
-    ap.add_argument("--moe-ramp", type=int, default=0, help="MoE: 1 = first and last minibatch half as large")
+    ap.add_argument("--moe-ramp", type=int, default=0, help="MoE: 1 = first and last minibatch half as large; > 100 = growth in percent from both ends toward the middle")
     ap.add_argument("--moe-combine-sms", type=int, default=0, help="MoE: multiprocessors' worth of blocks for a combine beside GEMMs (0 = comm SMs / 4)")
     ap.add_argument("--moe-tokens", type=int, default=32768, help="MoE: tokens in total (smaller for profiler captures)")
     ap.add_argument("--moe-experts", type=int, default=256, help="MoE: experts in total (smaller for profiler captures)")

@@ -93,7 +93,7 @@ struct Carver {
 };
 
 // Minibatches: ceil(capacity / minibatch_size) groups of consecutive local experts (the reference's argument),
-// at most one per expert.  With `ramp` the first and the last group hold half as many experts as the others:
+// at most one per expert.  `ramp` makes the first and the last groups smaller than the middle ones:
 // the first dispatch and the last combine are the two transfers nothing can hide.
 static int plan_minibatches(const mx8_moe_dims& d, int first_expert[MAX_MINIBATCHES + 1]) {
     int nb = 1;
@@ -102,12 +102,23 @@ static int plan_minibatches(const mx8_moe_dims& d, int first_expert[MAX_MINIBATC
     if (nb > d.num_local_experts) nb = d.num_local_experts;
     if (nb > MAX_MINIBATCHES) nb = MAX_MINIBATCHES;
     if (nb < 1) nb = 1;
-    const bool ramp = d.ramp && nb >= 3;
-    const double total = ramp ? nb - 1.0 : nb;
+    // weight of group b: 1 (equal groups); ramp = 1: the two end groups half; ramp > 100: groups grow by ramp percent
+    // from either end toward the middle (a transfer hides behind the GEMMs of the group before it as long as the
+    // growth stays below the ratio of GEMM time to transfer time)
+    double w[MAX_MINIBATCHES], total = 0.0;
+    for (int b = 0; b < nb; ++b) {
+        w[b] = 1.0;
+        if (d.ramp == 1 && nb >= 3 && (b == 0 || b == nb - 1)) w[b] = 0.5;
+        if (d.ramp > 100 && nb >= 3) {
+            const int steps = b < nb - 1 - b ? b : nb - 1 - b;
+            for (int i = 0; i < steps; ++i) w[b] *= d.ramp / 100.0;
+        }
+        total += w[b];
+    }
     double acc = 0.0;
     first_expert[0] = 0;
     for (int b = 0; b < nb; ++b) {
-        acc += (ramp && (b == 0 || b == nb - 1)) ? 0.5 : 1.0;
+        acc += w[b];
         int e = static_cast<int>(d.num_local_experts * acc / total + 0.5);
         if (e <= first_expert[b]) e = first_expert[b] + 1;            // every group has an expert
         if (e > d.num_local_experts - (nb - 1 - b)) e = d.num_local_experts - (nb - 1 - b);

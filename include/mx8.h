@@ -324,7 +324,7 @@ MX8_API int mx8_moe_minibatch_bounds_split(const void* tokens_per_expert, int nu
  *   ceil(capacity / minibatch_size) minibatches whose transfers overlap the other minibatches' GEMMs on two side
  *   streams the library creates once per device; outputs do not depend on the split.  Otherwise one launch
  *   sequence on `stream`.  Tuning (all may be 0): minibatches overrides the count; ramp = 1 makes the first and
- *   last minibatch half as large; combine_sms caps a combine that runs beside GEMMs (default num_comm_sms / 4);
+ *   last minibatch half as large, ramp > 100 lets the minibatches grow by ramp percent from both ends toward the middle; combine_sms caps a combine that runs beside GEMMs (default num_comm_sms / 4);
  *   split_swiglu = 1 runs SwiGLU as its own kernel after the gate / up projections instead of in their epilogue, and
  *   then split_gate_up = 1 launches the two projections separately instead of as one pair launch.
  *   fuse_combine = 1: the down projection's epilogue writes the owners' buffers directly (one sequence; y_routed

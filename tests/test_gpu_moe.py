@@ -471,10 +471,11 @@ def test_schedule_both_forms_agree_with_oracle(W, T, E_local, k, rank):
                                 tpe.data_ptr(), small.data_ptr(), 16, None) == 7
 
 
-@pytest.mark.parametrize("E_local,minibatch", [(5, 512), (4, 256), (3, 100000)])
-def test_pipelined_forward_equals_single_sequence(E_local, minibatch):
+@pytest.mark.parametrize("E_local,minibatch,tuning", [(5, 512, None), (4, 256, None), (3, 100000, None),
+                                                        (7, 256, {"minibatches": 5, "ramp": 150}), (6, 256, {"minibatches": 4, "ramp": 1})])
+def test_pipelined_forward_equals_single_sequence(E_local, minibatch, tuning):
     # minibatches of experts on three streams must leave exactly the bytes of the one-stream layer:
-    # every routed output and both ranks' combine buffers
+    # every routed output and both ranks' combine buffers; also with minibatches of unequal size
     W, T, H, I, k, rank = 2, 384, 512, 256, 4, 1
     topk_all, _ = make_topk(W, T, W * E_local, k, seed=191)
     cap = ((W * T * k) // 256 + E_local) * 256
@@ -489,7 +490,7 @@ def test_pipelined_forward_equals_single_sequence(E_local, minibatch):
         bufs = [torch.full((T * k, H), -1.0, dtype=torch.bfloat16, device=DEV) for _ in range(W)]
         outs = mx8.dispatch_mlp_swiglu_combine_fwd(xs[rank], [t.data_ptr() for t in xs], bufs[rank], [b.data_ptr() for b in bufs],
                                                    None, ws[0][0], ws[0][1], None, ws[1][0], ws[1][1], None, ws[2][0], ws[2][1],
-                                                   pr, pt, nt, tpe, k, comm_sms, 0, mb)
+                                                   pr, pt, nt, tpe, k, comm_sms, 0, mb, tuning=tuning if comm_sms else None)
         assert mx8.device_status() == 0
         results.append((outs, [b.cpu() for b in bufs]))
     n = int(nt)
