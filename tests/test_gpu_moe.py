@@ -35,6 +35,47 @@ def test_schedule_matches_oracle(W, T, E_local, k, rank):
     assert int(tpe.sum()) == int(nt) and bool((tpe % 256 == 0).all())
 
 
+def test_schedule_matches_oracle_on_random_shapes():
+    # property test: odd token counts, 1-8 source ranks, 1-40 local experts, top-1 to top-8, skewed routing with a hot
+    # expert (lists many rounds long), a capacity that is exactly enough; the C ABI with full scratch (counting-sort
+    # form), with minimal scratch (scan-per-expert form) and the entry point with built-in scratch
+    from hypothesis import given, settings, strategies as st
+    from mx8 import _lib
+    lib = _lib.load()
+
+    @settings(max_examples=40, deadline=None, derandomize=True)
+    @given(W=st.integers(1, 8), T=st.integers(1, 3000), k=st.integers(1, 8), E_local=st.integers(1, 40),
+           hot=st.sampled_from([0, 20, 80]), seed=st.integers(0, 10 ** 6), data=st.data())
+    def check(W, T, k, E_local, hot, seed, data):
+        rank = data.draw(st.integers(0, W - 1))
+        g = torch.Generator().manual_seed(seed)
+        topk_all = torch.randint(0, W * E_local, (W, T, k), generator=g, dtype=torch.int32)
+        topk_all[torch.rand(W, T, k, generator=g) * 100 < hot] = rank * E_local
+        roomy = (W * T * k + 256 * E_local + 255) // 256 * 256
+        cap = max(256, int(MO.schedule_ref(topk_all, E_local, roomy, rank)[2]))     # exactly what the schedule needs
+        rpr, rpt, rnt, rtpe, written = MO.schedule_ref(topk_all, E_local, cap, rank)
+        ids = topk_all.to(DEV)
+        stream = torch.cuda.current_stream().cuda_stream
+        full = lib.mx8_moe_schedule_scratch_bytes(W, T, k, E_local)
+        for form, nbytes in (("full scratch", full), ("minimal scratch", E_local * (W + 1) * 4), ("built-in scratch", 0)):
+            pr = torch.full((cap,), -7, dtype=torch.int32, device=DEV)
+            pt, nt, tpe = torch.full_like(pr, -7), torch.full((1,), -7, dtype=torch.int32, device=DEV), torch.full((E_local,), -7, dtype=torch.int32, device=DEV)
+            if nbytes:
+                scratch = torch.empty(nbytes, dtype=torch.uint8, device=DEV)
+                rc = lib.mx8_moe_schedule(ids.data_ptr(), W, T, k, E_local, cap, rank, pr.data_ptr(), pt.data_ptr(), nt.data_ptr(),
+                                          tpe.data_ptr(), scratch.data_ptr(), nbytes, stream)
+            else:
+                rc = lib.mx8_moe_schedule_static(ids.data_ptr(), W, T, k, E_local, cap, rank, pr.data_ptr(), pt.data_ptr(),
+                                                 nt.data_ptr(), tpe.data_ptr(), stream)
+            assert rc == _lib.OK, form
+            assert mx8.device_status() == 0, form
+            assert torch.equal(nt.cpu(), rnt) and torch.equal(tpe.cpu(), rtpe), form
+            assert torch.equal(pr.cpu(), rpr), form
+            assert torch.equal(pt.cpu()[written], rpt[written]), form
+
+    check()
+
+
 def test_schedule_is_a_permutation_of_the_routed_pairs():
     W, T, E_local, k, rank = 4, 512, 8, 8, 1
     topk_all, _ = make_topk(W, T, W * E_local, k, seed=5)

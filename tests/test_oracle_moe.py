@@ -146,3 +146,41 @@ def test_shared_expert_oracle_reproduces_the_reference_functions(golden_dir):
     for have, name in zip(bwd, ("d_x_shared", "d_gate_shared", "d_up_shared", "d_hidden_shared", "d_w_shared_gate",
                                 "d_w_shared_up", "d_w_shared_down")):
         assert O.rel_frobenius(have, bf(name)) < 1e-4, name
+
+
+def _skewed_topk(W, T, E, k, seed, hot):
+    """routing with one hot expert: `hot` percent of the pairs go to expert 0, the rest uniformly anywhere"""
+    g = torch.Generator().manual_seed(seed)
+    ids = torch.randint(0, E, (W, T, k), generator=g, dtype=torch.int32)
+    ids[torch.rand(W, T, k, generator=g) * 100 < hot] = 0
+    return ids
+
+
+def test_schedule_transcription_equals_threads_on_random_shapes():
+    # property test over odd shapes: token counts that are no multiple of anything, one to eight source ranks,
+    # skewed routing (a hot expert whose list is many rounds long), tables below and above the 1024-entry stride
+    from hypothesis import given, settings, strategies as st
+
+    @settings(max_examples=30, deadline=None, derandomize=True)
+    @given(W=st.integers(1, 4), T=st.integers(1, 900), k=st.integers(1, 4), E_local=st.integers(1, 5),
+           hot=st.sampled_from([0, 30, 90]), seed=st.integers(0, 10 ** 6), data=st.data())
+    def check(W, T, k, E_local, hot, seed, data):
+        rank = data.draw(st.integers(0, W - 1))
+        topk_all = _skewed_topk(W, T, W * E_local, k, seed, hot)
+        cap = (W * T * k + 256 * E_local + 255) // 256 * 256
+        a = MO.schedule_ref(topk_all, E_local, cap, rank)
+        b = MO.schedule_ref_threads(topk_all, E_local, cap, rank)
+        n = int(a[2])
+        assert int(b[2]) == n and torch.equal(a[3], b[3]) and torch.equal(a[0], b[0])
+        assert torch.equal(a[1][a[4]], b[1][a[4]])
+        # every pair routed to a local expert appears exactly once, in its expert's segment
+        local = (topk_all >= rank * E_local) & (topk_all < (rank + 1) * E_local)
+        assert int(a[4].sum()) == int(local.sum())
+        seg = torch.repeat_interleave(torch.arange(E_local), a[3].long())
+        pr, pt = a[0][:n].long(), a[1][:n].long()
+        valid = pr >= 0
+        assert torch.equal(topk_all.view(W, -1)[pr[valid], pt[valid]].long() - rank * E_local, seg[valid])
+        pairs = pr[valid] * (T * k) + pt[valid]
+        assert pairs.unique().numel() == pairs.numel()
+
+    check()
