@@ -193,3 +193,22 @@ def test_gemm_with_quantizing_prologue_equals_quantize_then_gemm(shape):
         assert mx8.device_status() == 0
         assert torch.equal(got.view(torch.int32 if dt == torch.float32 else torch.int16),
                            want.view(torch.int32 if dt == torch.float32 else torch.int16))
+
+
+def test_parity_on_random_shapes():
+    # property test: every dimension an arbitrary multiple of 128 (tiles that hang over the edge of C, one to
+    # twelve K steps), both CTA-group forms, bf16 and fp32 output, and grids smaller than the tile count so that the
+    # persistent loop takes several rounds with a partial last one
+    from hypothesis import given, settings, strategies as st
+
+    @settings(max_examples=30, deadline=None, derandomize=True)
+    @given(m=st.integers(1, 9), n=st.integers(1, 10), k=st.integers(1, 12), cg=st.sampled_from([0, 1, 2]),
+           f32=st.booleans(), ctas=st.sampled_from([0, 2, 6, 20]), seed=st.integers(0, 10 ** 6))
+    def check(m, n, k, cg, f32, ctas, seed):
+        M, N, K = 128 * m, 128 * n, 128 * k
+        ops = make_operands(M, N, K, seed=seed)
+        ref = O.gemm_ref(*ops) if not f32 else O.gemm_ref(*ops, out_dtype=torch.float32)
+        got = run_gemm(*ops, dtype=torch.float32 if f32 else torch.bfloat16, cta_group=cg, max_ctas=ctas)
+        compare(got, ref, f"({M}, {N}, {K}) cg{cg} f32={f32} ctas={ctas}")
+
+    check()

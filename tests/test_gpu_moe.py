@@ -125,6 +125,53 @@ def test_gemm_quantizing_epilogue_dense():
     assert torch.equal(c_sc.cpu(), want_sc)
 
 
+def test_gemm_grouped_on_random_group_sizes():
+    # property test: one to seven experts with 0 to 3 row tiles each (empty experts first, last and in between),
+    # capacity beyond the rows in use, N and K arbitrary multiples of 256 / 128, bf16 and quantizing epilogue
+    from hypothesis import given, settings, strategies as st
+
+    @settings(max_examples=20, deadline=None, derandomize=True)
+    @given(tiles=st.lists(st.integers(0, 3), min_size=1, max_size=7), n=st.integers(1, 3), k=st.integers(1, 6),
+           spare=st.integers(0, 2), mxfp8=st.booleans(), seed=st.integers(0, 10 ** 6))
+    def check(tiles, n, k, spare, mxfp8, seed):
+        E, N, K = len(tiles), 256 * n, 128 * k
+        group_rows = torch.tensor(tiles, dtype=torch.int32) * 256
+        used = int(group_rows.sum())
+        cap = used + 256 * spare
+        if cap == 0:
+            return
+        a = O.make_input(cap, K, seed=seed, std=K ** -0.25)
+        w = torch.stack([O.make_input(N, K, seed=seed + 1 + e, std=K ** -0.25) for e in range(E)])
+        aq, asc = _quant(a)
+        wq, wsc, _, _ = O.quantize_both(w)
+        d = [t.to(DEV) for t in (aq, asc, wq, wsc)]
+        nr, gr = torch.tensor([used], dtype=torch.int32, device=DEV), group_rows.to(DEV)
+        if mxfp8:
+            c = torch.full((cap, N), 0xFF, dtype=torch.uint8, device=DEV)
+            csc = torch.full((cap // 128, N // 128, 32, 16), 0xFF, dtype=torch.uint8, device=DEV)
+            mx8.gemm_grouped(*d, c, csc, nr, gr)
+        else:
+            c = torch.full((cap, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+            mx8.gemm_grouped(*d, c, None, nr, gr)
+        assert mx8.device_status() == 0
+        off = 0
+        for e, rows in enumerate(group_rows.tolist()):
+            if rows:
+                ref = O.gemm_ref(aq[off:off + rows], asc[off // 128:(off + rows) // 128], wq[e], wsc[e * N // 128:(e + 1) * N // 128])
+                if mxfp8:
+                    # the bytes are the oracle's quantization of a bf16 product that may differ from the oracle's in the last bit
+                    deq = O.dequantize(c[off:off + rows].cpu(), O.scale_unswizzle(csc[off // 128:(off + rows) // 128].cpu()))
+                    assert O.rel_frobenius(deq, ref) < 5e-2, (tiles, e)
+                else:
+                    got = c[off:off + rows].cpu()
+                    assert not torch.isnan(got.float()).any() and O.rel_frobenius(got, ref) < 2e-3, (tiles, e)
+            off += rows
+        if not mxfp8 and cap > used:
+            assert torch.isnan(c[used:].float()).all()              # rows beyond num_rows are not touched
+
+    check()
+
+
 @pytest.mark.parametrize("mode", ["bf16", "mxfp8"])
 def test_gemm_grouped_by_expert(mode):
     E, N, K = 5, 512, 384
