@@ -745,7 +745,8 @@ def bench_moe(args, world, rank, local, peaks, with_cpu=False):
     steps = 2 if args.quick else LAYER_STEPS
     for i in range(1 if args.quick else 3):
         step(i)
-    ms_single = timed(step, steps, world) / steps
+    sampler_single = ClockSampler(local) if rank == 0 else None
+    ms_single = timed(step, steps, world, sampler_single) / steps
     mx8.device_status()
     # the same layer with the routed experts cut into minibatches whose transfers overlap the GEMMs
     pipe[:] = [comm_sms, minibatch]
@@ -759,6 +760,8 @@ def bench_moe(args, world, rank, local, peaks, with_cpu=False):
     # there is nothing to overlap and the default arguments (one sequence) are the form to report
     use_pipe = world > 1
     ms = ms_pipe if use_pipe else ms_single
+    if not use_pipe:
+        sampler = sampler_single              # the clocks reported are those of the timed region that is reported
     pipeline = {"reported": "minibatches" if use_pipe else "single sequence", "comm_sms": comm_sms, "minibatch_rows": minibatch,
                 "minibatches": min(E, -(-cap // minibatch)), "ramp": args.moe_ramp, "combine_sms": args.moe_combine_sms,
                 "ms_per_step": ms_pipe, "single_sequence_ms_per_step": ms_single}
