@@ -607,6 +607,7 @@ def bench_ffn(args, world, rank, local, peaks, with_cpu=False):
     return {"metric": "mxfp8_ffn_throughput", "value": world * achieved, "unit": "TFLOP/s", "ms_per_step": ms, "steps": steps,
             "scaling": "strong",
             "config": {"workload": f"FFN X[{T}x{H}] bf16 -> quantize -> [{F}x{H}] GEMM with MXFP8-quantizing epilogue -> [{H}x{F}] GEMM -> bf16, per GPU",
+                       "l2": "per step about 1 GB of activations and 0.47 GB of weights per GPU at one GPU: larger than L2",
                        "sharding": "tokens split across GPUs, weights replicated, no collective"},
             "roofline": tensor_roofline(achieved, local, sampler.summary() if sampler else None, traffic=None),
             **({"clocks": sampler.summary()} if sampler else {}),
@@ -829,6 +830,7 @@ def bench_moe(args, world, rank, local, peaks, with_cpu=False):
             "scaling": "strong",
             "config": {"workload": f"MoE forward, {E_total} experts / {world} GPUs, hidden {H}, intermediate {I}, {tokens_total} tokens, top-{k}, routed experts only",
                        "flops": "6 * routed rows * hidden * intermediate (padding rows not counted)",
+                       "l2": "per step 11 GB of expert weights over all GPUs plus the routed activations: larger than L2",
                        "sharding": "experts and tokens split across GPUs; dispatch pulls and combine pushes over peer-mapped memory"},
             "roofline": tensor_roofline(per_gpu, local, sampler.summary() if sampler else None, traffic=None),
             **({"clocks": sampler.summary()} if sampler else {}),
