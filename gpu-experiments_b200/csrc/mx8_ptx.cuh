@@ -195,22 +195,6 @@ __device__ __forceinline__ void tma_store_4d(const CUtensorMap* m, int x, int y,
                  ::"l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y), "r"(z), "r"(w), "r"(src)
                  : "memory");
 }
-// the same stores with an L2 eviction policy for the lines they write
-__device__ __forceinline__ uint64_t l2_policy_evict_first() {
-    uint64_t p;
-    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
-    return p;
-}
-__device__ __forceinline__ void tma_store_2d_hint(const CUtensorMap* m, int x, int y, uint32_t src, uint64_t policy) {
-    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%1, %2}], [%3], %4;"
-                 ::"l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y), "r"(src), "l"(policy)
-                 : "memory");
-}
-__device__ __forceinline__ void tma_store_4d_hint(const CUtensorMap* m, int x, int y, int z, int w, uint32_t src, uint64_t policy) {
-    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%1, %2, %3, %4}], [%5], %6;"
-                 ::"l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y), "r"(z), "r"(w), "r"(src), "l"(policy)
-                 : "memory");
-}
 // contiguous bytes, shared -> global; both addresses 16-byte aligned, size a multiple of 16
 __device__ __forceinline__ void bulk_store_1d(void* gdst, uint32_t src, uint32_t bytes) {
     asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"

@@ -57,9 +57,6 @@
 #ifndef MX8_Q_COL_D
 #define MX8_Q_COL_D 2
 #endif
-#ifndef MX8_Q_STORE_HINT
-#define MX8_Q_STORE_HINT 0
-#endif
 #ifndef MX8_Q_MOE_RTMA
 #define MX8_Q_MOE_RTMA 1
 #endif
@@ -256,9 +253,6 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
     const uint32_t rstage = base + L::rstage + w * RSTAGE_BYTES;
     uint8_t* scstage_ptr = base_ptr + L::scstage + w * SCSTAGE_BYTES;
     const int hswap = (l >> 2) & 1;     // staging stores: which 16-byte half goes first (bank spreading)
-#if MX8_Q_STORE_HINT
-    const uint64_t store_policy = l2_policy_evict_first();
-#endif
 
     for (int n = w; n < my_slabs; n += W) {
         // slab n lives in slot n % S; S is a multiple of W, so a slot is only ever read by one warp
@@ -418,11 +412,7 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
             if constexpr (RTMA) fence_proxy_async_smem();
             __syncwarp();
             if (RTMA && l == 0) {
-#if MX8_Q_STORE_HINT
-                tma_store_2d_hint(o_tm_r, tc * TILE, tr * TILE + wq * SLAB_ROWS, rstage, store_policy);
-#else
                 tma_store_2d(o_tm_r, tc * TILE, tr * TILE + wq * SLAB_ROWS, rstage);
-#endif
                 if (!COL) bulk_commit();
             }
             // row r of the tile keeps its four scale bytes at (r % 32) * 16 + (r / 32) * 4
@@ -478,11 +468,7 @@ quantize_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant
             if (l == 0) {
 #pragma unroll
                 for (int k = 0; k < 4; ++k)
-#if MX8_Q_STORE_HINT
-                    tma_store_4d_hint(o_tm_t, trm * TILE + wq * SLAB_ROWS, k, tc * 32, e, tstage + k * 1024, store_policy);
-#else
                     tma_store_4d(o_tm_t, trm * TILE + wq * SLAB_ROWS, k, tc * 32, e, tstage + k * 1024);
-#endif
                 bulk_commit();
             }
         }
