@@ -195,24 +195,17 @@ __global__ void __launch_bounds__(1024) sched_scan_kernel(SchedParams p) {
     const int c_begin = min(cpr, warp * per_warp), c_end = min(cpr, c_begin + per_warp);
     const int pairs = p.experts * p.world;
     if (cpr <= 64) {
-        // few chunks: one warp per (expert, rank) pair, a lane holds chunks `lane` and `lane + 32`; the loads of a
-        // pair are independent, so the prefix costs one memory round trip per pair instead of one per chunk
-        for (int idx = warp; idx < pairs; idx += 32) {
+        // few chunks: one thread walks the chunks of its pair, no exchange between warps
+        for (int idx = threadIdx.x; idx < pairs; idx += blockDim.x) {
             const int r = idx / p.experts, e = idx - r * p.experts;
-            int* q = cc + static_cast<size_t>(r) * cpr * p.experts + e;
-            const bool has0 = lane < cpr, has1 = lane + 32 < cpr;
-            const int v0 = has0 ? q[static_cast<size_t>(lane) * p.experts] : 0;
-            const int v1 = has1 ? q[static_cast<size_t>(lane + 32) * p.experts] : 0;
-            int i0 = v0, i1 = v1;
-#pragma unroll
-            for (int d = 1; d < 32; d <<= 1) {
-                const int a = __shfl_up_sync(0xFFFFFFFFu, i0, d), b = __shfl_up_sync(0xFFFFFFFFu, i1, d);
-                if (lane >= d) { i0 += a; i1 += b; }
+            int running = 0;
+            for (int c = 0; c < cpr; ++c) {
+                int* cell = cc + (static_cast<size_t>(r) * cpr + c) * p.experts + e;
+                const int v = *cell;
+                *cell = running;
+                running += v;
             }
-            const int total0 = __shfl_sync(0xFFFFFFFFu, i0, 31);
-            if (has0) q[static_cast<size_t>(lane) * p.experts] = i0 - v0;
-            if (has1) q[static_cast<size_t>(lane + 32) * p.experts] = total0 + i1 - v1;
-            if (lane == 31) p.counts[e * p.world + r] = total0 + i1;
+            p.counts[e * p.world + r] = running;
         }
     } else
     for (int g0 = 0; g0 < pairs; g0 += 32) {
