@@ -660,7 +660,7 @@ def bench_moe(args, world, rank, local, peaks, with_cpu=False):
     comm_sms = args.moe_comm_sms
     nb_default = args.moe_minibatches
     minibatch = args.moe_minibatch if args.moe_minibatch > 0 else -(-cap // (nb_default * 256)) * 256
-    tuning = {"ramp": args.moe_ramp, "combine_sms": args.moe_combine_sms}
+    tuning = {"ramp": args.moe_ramp, "combine_sms": args.moe_combine_sms, "combine_own_sms": args.moe_combine_own_sms}
     pipe = [0, 0]
 
     def layer(pr, pt, nt, tpe):
@@ -764,7 +764,7 @@ def bench_moe(args, world, rank, local, peaks, with_cpu=False):
     if not use_pipe:
         sampler = sampler_single              # the clocks reported are those of the timed region that is reported
     pipeline = {"reported": "minibatches" if use_pipe else "single sequence", "comm_sms": comm_sms, "minibatch_rows": minibatch,
-                "minibatches": min(E, -(-cap // minibatch)), "ramp": args.moe_ramp, "combine_sms": args.moe_combine_sms,
+                "minibatches": min(E, -(-cap // minibatch)), "ramp": args.moe_ramp, "combine_sms": args.moe_combine_sms, "combine_own_sms": args.moe_combine_own_sms,
                 "ms_per_step": ms_pipe, "single_sequence_ms_per_step": ms_single}
 
     # ---- backward of the same layer (routed experts): prologue, barrier, fused backward, barrier, epilogue
@@ -883,6 +883,8 @@ def main():
                     help="MoE: schedule rows per minibatch of the pipelined layer (0 = a quarter of the schedule capacity; "
                          "the reference harness uses 16384, which is the same at 8 GPUs)")
     ap.add_argument("--moe-minibatches", type=int, default=4, help="MoE: minibatches when --moe-minibatch is 0")
+    ap.add_argument("--moe-combine-own-sms", type=int, default=0,
+                    help="MoE: > 0 gives a combine that runs beside GEMMs that many multiprocessors of its own")
     ap.add_argument("--moe-ramp", type=int, default=0, help="MoE: 1 = first and last minibatch half as large; > 100 = growth in percent from both ends toward the middle")
     ap.add_argument("--moe-combine-sms", type=int, default=0, help="MoE: multiprocessors' worth of blocks for a combine beside GEMMs (0 = comm SMs / 4)")
     ap.add_argument("--moe-tokens", type=int, default=32768, help="MoE: tokens in total (smaller for profiler captures)")

@@ -12,6 +12,8 @@
 // epilogue: out[t] = bf16( y_shared[t] + sum_j w[t][j] * combine[t*topk + j] ), fp32, products and
 // sums rounded separately, j ascending, so the result does not depend on the launch shape.
 // Replaces fwd_epilogue_kernel, blackwell-ultra/022-…-mxfp8-bw.cu:2789-2856.
+#include <atomic>
+
 #include "mx8_host.cuh"
 #include "mx8_ptx.cuh"
 
@@ -29,6 +31,8 @@ struct CombineParams {
     int world;
     long long dst_rows;          // rows of every destination buffer
     uint8_t* dst[16];            // every rank's combine buffer [tokens*topk][hidden] bf16
+    int* status;                 // device status word (bounded waits of the bulk-copy forms)
+    int piece_bytes;             // bulk-copy forms: bytes per copy (a row goes in ceil(row / piece) pieces), multiple of 16
 };
 
 __global__ void __launch_bounds__(256) combine_kernel(CombineParams p) {
@@ -46,19 +50,74 @@ __global__ void __launch_bounds__(256) combine_kernel(CombineParams p) {
         const uint4* src = reinterpret_cast<const uint4*>(p.y + r * row_bytes);
         uint4* dst = reinterpret_cast<uint4*>(p.dst[pr] + static_cast<size_t>(pt) * row_bytes);
         const int n16 = p.hidden / 8;
-        for (int i = lane; i < n16; i += 128) {
-            // four independent 16-byte copies in flight per lane
-            uint4 v0 = src[i], v1, v2, v3;
-            const bool b1 = i + 32 < n16, b2 = i + 64 < n16, b3 = i + 96 < n16;
-            if (b1) v1 = src[i + 32];
-            if (b2) v2 = src[i + 64];
-            if (b3) v3 = src[i + 96];
-            dst[i] = v0;
-            if (b1) dst[i + 32] = v1;
-            if (b2) dst[i + 64] = v2;
-            if (b3) dst[i + 96] = v3;
+        constexpr int U = 4;                             // independent 16-byte copies in flight per lane
+        for (int i = lane; i < n16; i += 32 * U) {
+            uint4 v[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+                if (i + 32 * u < n16) v[u] = src[i + 32 * u];
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+                if (i + 32 * u < n16) dst[i + 32 * u] = v[u];
         }
     }
+}
+
+// The form with multiprocessors of its own (mx8_window.own_sms): every warp moves rows with bulk copies through two
+// buffers in shared memory (global -> shared, then shared -> the owner's buffer, local or a peer's over NVLink; no
+// multicast anywhere), a row in pieces of at most 7.5 KB.  One lane issues; while the store of one piece drains from its
+// buffer the load of the next is in flight in the other.  The blocks ask for more shared memory than a multiprocessor
+// has left beside a GEMM or a dispatch block, so they never share one.
+constexpr int BULK_WARPS = 6;
+__global__ void __launch_bounds__(32 * BULK_WARPS) combine_bulk_kernel(CombineParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 127u) & ~127u;
+    uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t row_bytes = static_cast<uint32_t>(p.hidden) * 2u;
+    const uint32_t piece = static_cast<uint32_t>(p.piece_bytes);
+    const uint32_t buf_bytes = (piece + 127u) & ~127u;
+    const int warp_in_block = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // per warp: two buffers, then (after all buffers) two barriers; the abort flag follows the barriers
+    const uint32_t buf0 = base + (warp_in_block * 2) * buf_bytes;
+    const uint32_t bar0 = base + BULK_WARPS * 2 * buf_bytes + warp_in_block * 16;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + BULK_WARPS * 2 * buf_bytes + BULK_WARPS * 16);
+    if (threadIdx.x == 0) *abort_flag = 0;
+    if (lane == 0) {
+        mbar_init(bar0, 1);
+        mbar_init(bar0 + 8, 1);
+        fence_mbar_init();
+    }
+    __syncthreads();
+    if (lane != 0) return;
+    const AbortCtl ab{abort_flag, p.status};
+    const int rows = min(*p.num_tokens, p.capacity);
+    const int row0 = p.row_begin ? *p.row_begin : 0;
+    const int warp = blockIdx.x * BULK_WARPS + warp_in_block;
+    const int warps = gridDim.x * BULK_WARPS;
+    uint32_t phase[2] = {0, 0};
+    int n = 0;                                           // copies this warp has issued
+    bool ok = true;
+    for (int r = row0 + warp; r < rows && ok; r += warps) {
+        const int pr = p.peer_rank[r];
+        if (pr < 0 || pr >= p.world) continue;
+        const int pt = p.peer_token_idx[r];
+        if (pt < 0 || pt >= p.dst_rows) continue;
+        const uint8_t* src = p.y + static_cast<size_t>(r) * row_bytes;
+        uint8_t* dst = p.dst[pr] + static_cast<size_t>(pt) * row_bytes;
+        for (uint32_t off = 0; off < row_bytes; off += piece, ++n) {
+            const uint32_t len = min(piece, row_bytes - off);
+            const int s = n & 1;
+            // the store issued from this buffer two copies ago must have finished reading it
+            bulk_wait_read<1>();
+            mbar_arrive_expect_tx(bar0 + s * 8, len);
+            bulk_load_1d(buf0 + s * buf_bytes, src + off, len, bar0 + s * 8);
+            if (!mbar_wait(bar0 + s * 8, phase[s], ab, DEV_TIMEOUT_FULL)) { ok = false; break; }
+            phase[s] ^= 1;
+            bulk_store_1d(dst + off, buf0 + s * buf_bytes, len);
+            bulk_commit();
+        }
+    }
+    bulk_wait_all<0>();
 }
 
 struct EpilogueParams {
@@ -168,8 +227,49 @@ extern "C" int mx8_moe_combine_window(const void* y_routed, const void* peer_ran
         if (window->row_end) p.num_tokens = static_cast<const int*>(window->row_end);
         if (window->max_sms > 0 && window->max_sms < sms) sms = window->max_sms;
     }
-    moe::combine_kernel<<<sms * 4, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e;
+    if (window && window->own_sms && window->max_sms > 0 && window->max_sms < sm_count()) {
+        // Multiprocessors of its own, as clusters of two so that the blocks fill whole pairs of multiprocessors (the
+        // GEMMs' clusters need both halves of a pair).  Why one would: copy warps on a GEMM's multiprocessor take issue
+        // slots from its two single-thread issuers, and with tiles assigned in fixed strides the whole GEMM then waits
+        // for the blocks that were slowed down.  Why not always: a multiprocessor moves only about 15 GB/s over NVLink
+        // whatever it does, so a transfer that is mostly remote wants many of them.
+        const size_t row_bytes = static_cast<size_t>(hidden) * 2;
+        const size_t pieces = (row_bytes + 7679) / 7680;
+        p.piece_bytes = static_cast<int>(((row_bytes + pieces - 1) / pieces + 15) & ~static_cast<size_t>(15));
+        const size_t buf_bytes = (static_cast<size_t>(p.piece_bytes) + 127) & ~static_cast<size_t>(127);
+        size_t smem = moe::BULK_WARPS * 2 * buf_bytes + moe::BULK_WARPS * 16 + 16 + 128;
+        if (smem < 64 * 1024) smem = 64 * 1024;          // more than a GEMM or dispatch block leaves free
+        static std::atomic<size_t> configured[64];
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (configured[dev & 63].load(std::memory_order_acquire) < smem) {
+            e = cudaFuncSetAttribute(moe::combine_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+            if (e != cudaSuccess) {
+                note_cuda_error("cudaFuncSetAttribute(combine)", cudaGetErrorString(e));
+                return MX8_ERR_CUDA;
+            }
+            configured[dev & 63].store(smem, std::memory_order_release);
+        }
+        p.status = device_status_ptr();
+        if (!p.status) return MX8_ERR_CUDA;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(static_cast<unsigned>((sms + 1) & ~1));
+        cfg.blockDim = dim3(32 * moe::BULK_WARPS);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = static_cast<cudaStream_t>(stream);
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension;
+        at[0].val.clusterDim.x = 2;
+        at[0].val.clusterDim.y = 1;
+        at[0].val.clusterDim.z = 1;
+        cfg.attrs = at;
+        cfg.numAttrs = 1;
+        e = cudaLaunchKernelEx(&cfg, moe::combine_bulk_kernel, p);
+    } else {
+        moe::combine_kernel<<<sms * 4, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+        e = cudaGetLastError();
+    }
     if (e != cudaSuccess) {
         note_cuda_error("moe combine launch", cudaGetErrorString(e));
         return MX8_ERR_CUDA;

@@ -12,6 +12,7 @@
 // Every kernel is the row-window form of the one the unsplit layer launches, so the outputs do not depend on
 // the split.  No device memory is allocated: intermediates live in the caller's workspace; the two side streams are
 // created once per device and kept, the events of a call live as long as the call.
+#include <cstdio>
 #include <mutex>
 
 #include "mx8_host.cuh"
@@ -77,6 +78,30 @@ struct Check {
     }
     bool ok() const { return rc == MX8_OK; }
 };
+
+#ifdef MX8_TRACE
+// Timing study only (a build with -DMX8_TRACE): timed events around every launch of the minibatch forward, read back
+// by mx8_debug_moe_trace_dump after the caller has synchronized.  Not part of the shipped library.
+struct TraceRec { const char* name; int b; int stream; cudaEvent_t a, e; };
+static TraceRec g_trace[8 * MAX_MINIBATCHES + 8];
+static int g_trace_n = 0;
+static cudaEvent_t g_trace_t0 = nullptr;
+struct TraceScope {
+    TraceRec* r = nullptr;
+    cudaStream_t st;
+    TraceScope(const char* name, int b, int stream_id, cudaStream_t s) : st(s) {
+        if (g_trace_n >= static_cast<int>(sizeof(g_trace) / sizeof(g_trace[0]))) return;
+        r = &g_trace[g_trace_n++];
+        r->name = name; r->b = b; r->stream = stream_id;
+        cudaEventCreate(&r->a); cudaEventCreate(&r->e);
+        cudaEventRecord(r->a, st);
+    }
+    ~TraceScope() { if (r) cudaEventRecord(r->e, st); }
+};
+#define MX8_TRACE_SCOPE(name, b, id, s) TraceScope trace_scope_(name, b, id, s)
+#else
+#define MX8_TRACE_SCOPE(name, b, id, s) do {} while (0)
+#endif
 
 inline size_t up256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
 
@@ -248,7 +273,11 @@ extern "C" int mx8_moe_fwd(const mx8_moe_fwd_args* a, void* stream) {
     if (sms <= 0) return MX8_ERR_CUDA;
     const int math_sms = (sms - d.num_comm_sms) & ~1;
     if (math_sms < 2) return MX8_ERR_ARG;
-    const int combine_sms = d.combine_sms > 0 ? d.combine_sms : (d.num_comm_sms / 4 > 0 ? d.num_comm_sms / 4 : 1);
+    // A combine that runs beside GEMMs either shares their multiprocessors, held to combine_sms multiprocessors' worth of
+    // copy blocks, or (combine_own_sms > 0) gets multiprocessors of its own, which the GEMMs beside it then leave free.
+    const int own_sms = d.combine_own_sms > 0 ? ((d.combine_own_sms + 1) & ~1) : 0;
+    const int combine_sms = own_sms ? own_sms : (d.combine_sms > 0 ? d.combine_sms : (d.num_comm_sms / 4 > 0 ? d.num_comm_sms / 4 : 1));
+    if (math_sms - own_sms < 2) return MX8_ERR_ARG;
     ck(mx8_moe_minibatch_bounds_split(a->tokens_per_expert, E, nb, first_expert, bounds, main));
     CallEvents evs(2 * nb + 2);
     ck.cuda(evs.err, "cudaEventCreateWithFlags");
@@ -257,30 +286,50 @@ extern "C" int mx8_moe_fwd(const mx8_moe_fwd_args* a, void* stream) {
     cudaEvent_t* disp_done = evs.ev + 2;
     cudaEvent_t* math_done = evs.ev + 2 + nb;
     ck.cuda(cudaEventRecord(start, main), "cudaEventRecord");
+#ifdef MX8_TRACE
+    for (int i = 0; i < g_trace_n; ++i) { cudaEventDestroy(g_trace[i].a); cudaEventDestroy(g_trace[i].e); }
+    g_trace_n = 0;
+    if (!g_trace_t0) cudaEventCreate(&g_trace_t0);
+    cudaEventRecord(g_trace_t0, main);
+#endif
     ck.cuda(cudaStreamWaitEvent(cx->disp, start, 0), "cudaStreamWaitEvent");
     ck.cuda(cudaStreamWaitEvent(cx->comb, start, 0), "cudaStreamWaitEvent");
     for (int b = 0; b < nb && ck.ok(); ++b) {
         // the first minibatch has the device to itself; later ones run beside the GEMMs
         const mx8_window w{bounds + b, bounds + b + 1, b == 0 ? 0 : d.num_comm_sms};
-        ck(mx8_moe_dispatch_quantize_window(a->x_ptrs, d.world, H, d.topk, a->peer_rank, a->peer_token_idx, a->num_tokens, cap, x_fp8,
-                                            x_sc, a->x_fp8_t, a->x_sc_t, &w, cx->disp));
+        {
+            MX8_TRACE_SCOPE("dispatch", b, 1, cx->disp);
+            ck(mx8_moe_dispatch_quantize_window(a->x_ptrs, d.world, H, d.topk, a->peer_rank, a->peer_token_idx, a->num_tokens, cap,
+                                                x_fp8, x_sc, a->x_fp8_t, a->x_sc_t, &w, cx->disp));
+        }
         ck.cuda(cudaEventRecord(disp_done[b], cx->disp), "cudaEventRecord");
     }
     shared_expert();
     for (int b = 0; b < nb && ck.ok(); ++b) {
         ck.cuda(cudaStreamWaitEvent(main, disp_done[b], 0), "cudaStreamWaitEvent");
         // the last minibatch's GEMMs run after every dispatch has finished: they take the whole device
-        const mx8_window w{bounds + b, bounds + b + 1, b == nb - 1 ? 0 : math_sms};
-        gate_up(&w);
-        ck(mx8_gemm_grouped_window(h_fp8, h_sc, a->w_down, a->w_down_sc, a->y_routed, nullptr, cap, H, I, MX8_C_BF16, a->num_tokens,
-                                   a->tokens_per_expert, E, &w, main));
+        // and, with combine_own_sms, every minibatch but the first leaves the combine of the one before it its multiprocessors
+        const int gemm_sms = (b == nb - 1 ? (sms & ~1) : math_sms) - (b > 0 ? own_sms : 0);
+        const mx8_window w{bounds + b, bounds + b + 1, gemm_sms >= (sms & ~1) ? 0 : gemm_sms, 0};
+        {
+            MX8_TRACE_SCOPE("gate_up", b, 0, main);
+            gate_up(&w);
+        }
+        {
+            MX8_TRACE_SCOPE("down", b, 0, main);
+            ck(mx8_gemm_grouped_window(h_fp8, h_sc, a->w_down, a->w_down_sc, a->y_routed, nullptr, cap, H, I, MX8_C_BF16,
+                                       a->num_tokens, a->tokens_per_expert, E, &w, main));
+        }
         ck.cuda(cudaEventRecord(math_done[b], main), "cudaEventRecord");
         ck.cuda(cudaStreamWaitEvent(cx->comb, math_done[b], 0), "cudaStreamWaitEvent");
         // beside GEMMs the combine is held to a few thread blocks: with more, its stores queue up in front of the
         // NVLink ports and hold up the GEMMs' operand traffic by as much as the overlap gains
-        const mx8_window wc{bounds + b, bounds + b + 1, b < nb - 1 ? combine_sms : 0};
-        ck(mx8_moe_combine_window(a->y_routed, a->peer_rank, a->peer_token_idx, a->num_tokens, cap, H, a->combine_ptrs, d.world,
-                                  static_cast<long long>(d.tokens) * d.topk, &wc, cx->comb));
+        const mx8_window wc{bounds + b, bounds + b + 1, b < nb - 1 ? combine_sms : 0, (own_sms && b < nb - 1) ? 1 : 0};
+        {
+            MX8_TRACE_SCOPE("combine", b, 2, cx->comb);
+            ck(mx8_moe_combine_window(a->y_routed, a->peer_rank, a->peer_token_idx, a->num_tokens, cap, H, a->combine_ptrs, d.world,
+                                      static_cast<long long>(d.tokens) * d.topk, &wc, cx->comb));
+        }
     }
     ck.cuda(cudaEventRecord(done, cx->comb), "cudaEventRecord");
     ck.cuda(cudaStreamWaitEvent(main, done, 0), "cudaStreamWaitEvent");
@@ -347,7 +396,7 @@ extern "C" int mx8_moe_bwd(const mx8_moe_bwd_args* a, void* stream) {
     Check ck;
     DeviceCtx* cx = nullptr;
     cudaStream_t s_disp = main, s_comb = main;
-    int math_sms = 0, combine_sms = 0;
+    int math_sms = 0, combine_sms = 0, own_sms = 0, all_sms = 0;
     cudaEvent_t* disp_done = nullptr;
     cudaEvent_t* math_done = nullptr;
     CallEvents evs(pipe ? 2 * nb + 2 : 0);
@@ -359,7 +408,10 @@ extern "C" int mx8_moe_bwd(const mx8_moe_bwd_args* a, void* stream) {
         if (sms <= 0) return MX8_ERR_CUDA;
         math_sms = (sms - d.num_comm_sms) & ~1;
         if (math_sms < 2) return MX8_ERR_ARG;
-        combine_sms = d.combine_sms > 0 ? d.combine_sms : (d.num_comm_sms / 4 > 0 ? d.num_comm_sms / 4 : 1);
+        own_sms = d.combine_own_sms > 0 ? ((d.combine_own_sms + 1) & ~1) : 0;          // as in the forward
+        combine_sms = own_sms ? own_sms : (d.combine_sms > 0 ? d.combine_sms : (d.num_comm_sms / 4 > 0 ? d.num_comm_sms / 4 : 1));
+        if (math_sms - own_sms < 2) return MX8_ERR_ARG;
+        all_sms = sms & ~1;
         s_disp = cx->disp;
         s_comb = cx->comb;
         disp_done = evs.ev + 2;
@@ -380,7 +432,9 @@ extern "C" int mx8_moe_bwd(const mx8_moe_bwd_args* a, void* stream) {
     for (int b = 0; b < nb && ck.ok(); ++b) {
         if (pipe) ck.cuda(cudaStreamWaitEvent(main, disp_done[b], 0), "cudaStreamWaitEvent");
         // the weight-gradient GEMMs follow the last minibatch, so no minibatch has the whole device for its data gradients
-        const mx8_window w{pipe ? bounds + b : nullptr, pipe ? bounds + b + 1 : nullptr, (pipe && b < nb - 1) ? math_sms : 0};
+        // and, with combine_own_sms, every minibatch but the first leaves the gradient combine of the one before it its multiprocessors
+        const int gemm_sms = !pipe ? 0 : (b < nb - 1 ? math_sms : all_sms) - (b > 0 ? own_sms : 0);
+        const mx8_window w{pipe ? bounds + b : nullptr, pipe ? bounds + b + 1 : nullptr, gemm_sms >= all_sms ? 0 : gemm_sms, 0};
         ck(mx8_gemm_grouped_window(a->d_y_fp8, a->d_y_sc, a->w_down_T, a->w_down_T_sc, a->d_hidden_routed, nullptr, cap, I, H, MX8_C_BF16,
                                    a->num_tokens, a->tokens_per_expert, E, &w, main));
         ck(mx8_swiglu_bwd_quantize_both_window(a->gate_fp8, a->gate_sc, a->up_fp8, a->up_sc, a->d_hidden_routed, cap, I, a->num_tokens,
@@ -392,7 +446,8 @@ extern "C" int mx8_moe_bwd(const mx8_moe_bwd_args* a, void* stream) {
             ck.cuda(cudaEventRecord(math_done[b], main), "cudaEventRecord");
             ck.cuda(cudaStreamWaitEvent(s_comb, math_done[b], 0), "cudaStreamWaitEvent");
         }
-        const mx8_window wc{pipe ? bounds + b : nullptr, pipe ? bounds + b + 1 : nullptr, (pipe && b < nb - 1) ? combine_sms : 0};
+        const mx8_window wc{pipe ? bounds + b : nullptr, pipe ? bounds + b + 1 : nullptr, (pipe && b < nb - 1) ? combine_sms : 0,
+                            (pipe && own_sms && b < nb - 1) ? 1 : 0};
         ck(mx8_moe_combine_window(a->d_x_routed, a->peer_rank, a->peer_token_idx, a->num_tokens, cap, H, a->d_x_routed_ptrs, d.world,
                                   static_cast<long long>(d.tokens) * d.topk, &wc, s_comb));
     }
@@ -430,3 +485,19 @@ extern "C" int mx8_moe_bwd(const mx8_moe_bwd_args* a, void* stream) {
     }
     return ck.rc;
 }
+
+#ifdef MX8_TRACE
+// prints the timeline of the last minibatch forward of this process (call after synchronizing the device)
+extern "C" MX8_API int mx8_debug_moe_trace_dump(void) {
+    using namespace mx8::layer;
+    for (int i = 0; i < g_trace_n; ++i) {
+        float t_a = 0.f, t_e = 0.f;
+        cudaEventElapsedTime(&t_a, g_trace_t0, g_trace[i].a);
+        cudaEventElapsedTime(&t_e, g_trace_t0, g_trace[i].e);
+        printf("  stream %d  %-8s mb %d  start %7.3f  end %7.3f  dur %6.3f ms\n", g_trace[i].stream, g_trace[i].name, g_trace[i].b,
+               t_a, t_e, t_e - t_a);
+    }
+    fflush(stdout);
+    return g_trace_n;
+}
+#endif

@@ -14,7 +14,7 @@ C_BF16, C_F32, C_MXFP8 = 0, 1, 2
 _vp, _i = ctypes.c_void_p, ctypes.c_int
 class Window(ctypes.Structure):
     """mx8_window: rows [*row_begin, *row_end) (device ints) on at most max_sms multiprocessors."""
-    _fields_ = [("row_begin", ctypes.c_void_p), ("row_end", ctypes.c_void_p), ("max_sms", ctypes.c_int)]
+    _fields_ = [("row_begin", ctypes.c_void_p), ("row_end", ctypes.c_void_p), ("max_sms", ctypes.c_int), ("own_sms", ctypes.c_int)]
 
 
 _wp = ctypes.POINTER(Window)
@@ -24,7 +24,7 @@ _pp = ctypes.POINTER(ctypes.c_void_p)
 class MoeDims(ctypes.Structure):
     """mx8_moe_dims"""
     _fields_ = [(n, ctypes.c_int) for n in ("world", "tokens", "hidden", "intermediate", "shared_intermediate", "num_local_experts",
-                                            "topk", "capacity", "num_comm_sms", "minibatch_size", "minibatches", "ramp", "combine_sms", "split_gate_up", "split_swiglu")]
+                                            "topk", "capacity", "num_comm_sms", "minibatch_size", "minibatches", "ramp", "combine_sms", "split_gate_up", "split_swiglu", "combine_own_sms")]
 
 
 FWD_IN = ("w_shared_gate", "w_shared_up", "w_shared_down", "w_gate", "w_gate_sc", "w_up", "w_up_sc", "w_down", "w_down_sc",

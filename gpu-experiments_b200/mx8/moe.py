@@ -136,7 +136,7 @@ def dispatch_mlp_swiglu_combine_fwd(x, x_ptrs, combine_buffer, combine_buffer_pt
     macrobatch_size (the backward's replay granularity in the reference) has no effect.  The shared expert
     (bf16) runs when its weights are given, else those outputs are None.
     fuse_combine=True (an addition) lets the down projection's epilogue do the combine; y_routed is then None.
-    tuning (an addition): dict of mx8_moe_dims fields minibatches / ramp / combine_sms."""
+    tuning (an addition): dict of mx8_moe_dims fields minibatches / ramp / combine_sms / combine_own_sms."""
     lib = _lib.load()
     E, I, H = w_routed_gate.shape
     cap = schedule_peer_rank.numel()

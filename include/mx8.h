@@ -253,13 +253,18 @@ MX8_API int mx8_transpose_bf16(const void* in, void* out, int rows, int cols, vo
  * kernel of the layer has a form that works on rows [*row_begin, *row_end) only, on at most max_sms
  * multiprocessors, and the host orders the pieces with streams and events.
  *   row_begin, row_end: device ints (multiples of 256), NULL = 0 / the entry point's own row count;
- *   max_sms: 0 = the whole device.
+ *   max_sms: 0 = the whole device;
+ *   own_sms: 0, or 1 in mx8_moe_combine_window to give the combine max_sms multiprocessors of its own: bulk-copy blocks
+ *   whose shared memory keeps GEMM and dispatch blocks off them (the caller launches its GEMMs on max_sms fewer
+ *   multiprocessors).  Without it a throttled combine shares multiprocessors with the GEMMs.  Other entry points ignore
+ *   the field.
  * mx8_moe_minibatch_bounds fills bounds[0..minibatches] with the row at which each group of
  * num_local_experts / minibatches consecutive experts starts (from tokens_per_expert). */
 typedef struct mx8_window {
     const void* row_begin;
     const void* row_end;
     int max_sms;
+    int own_sms;
 } mx8_window;
 MX8_API int mx8_moe_minibatch_bounds(const void* tokens_per_expert, int num_local_experts, int minibatches, void* bounds,
                                      void* stream);
@@ -325,6 +330,7 @@ MX8_API int mx8_moe_minibatch_bounds_split(const void* tokens_per_expert, int nu
  *   streams the library creates once per device; outputs do not depend on the split.  Otherwise one launch
  *   sequence on `stream`.  Tuning (all may be 0): minibatches overrides the count; ramp = 1 makes the first and
  *   last minibatch half as large, ramp > 100 lets the minibatches grow by ramp percent from both ends toward the middle; combine_sms caps a combine that runs beside GEMMs (default num_comm_sms / 4);
+ *   combine_own_sms > 0 instead gives such a combine that many multiprocessors of its own and the GEMMs beside it as many fewer;
  *   split_swiglu = 1 runs SwiGLU as its own kernel after the gate / up projections instead of in their epilogue, and
  *   then split_gate_up = 1 launches the two projections separately instead of as one pair launch.
  *   fuse_combine = 1: the down projection's epilogue writes the owners' buffers directly (one sequence; y_routed
@@ -336,7 +342,7 @@ MX8_API int mx8_moe_minibatch_bounds_split(const void* tokens_per_expert, int nu
 typedef struct mx8_moe_dims {
     int world, tokens, hidden, intermediate, shared_intermediate, num_local_experts, topk, capacity;
     int num_comm_sms, minibatch_size;
-    int minibatches, ramp, combine_sms, split_gate_up, split_swiglu;
+    int minibatches, ramp, combine_sms, split_gate_up, split_swiglu, combine_own_sms;
 } mx8_moe_dims;
 typedef struct mx8_moe_fwd_args {
     mx8_moe_dims dims;

@@ -599,10 +599,12 @@ def test_schedule_both_forms_agree_with_oracle(W, T, E_local, k, rank):
 
 
 @pytest.mark.parametrize("E_local,minibatch,tuning", [(5, 512, None), (4, 256, None), (3, 100000, None),
-                                                        (7, 256, {"minibatches": 5, "ramp": 150}), (6, 256, {"minibatches": 4, "ramp": 1})])
+                                                        (7, 256, {"minibatches": 5, "ramp": 150}), (6, 256, {"minibatches": 4, "ramp": 1}),
+                                                        (6, 256, {"minibatches": 3, "combine_own_sms": 4})])
 def test_pipelined_forward_equals_single_sequence(E_local, minibatch, tuning):
     # minibatches of experts on three streams must leave exactly the bytes of the one-stream layer:
-    # every routed output and both ranks' combine buffers; also with minibatches of unequal size
+    # every routed output and both ranks' combine buffers; also with minibatches of unequal size, and with the combine
+    # that moves rows by bulk copies on multiprocessors of its own
     W, T, H, I, k, rank = 2, 384, 512, 256, 4, 1
     topk_all, _ = make_topk(W, T, W * E_local, k, seed=191)
     cap = ((W * T * k) // 256 + E_local) * 256
@@ -635,7 +637,8 @@ def test_pipelined_forward_equals_single_sequence(E_local, minibatch, tuning):
     assert torch.equal(o1[12][:n].view(torch.int16), o2[12][:n].view(torch.int16))
 
 
-def test_pipelined_backward_equals_single_sequence():
+@pytest.mark.parametrize("tuning", [None, {"combine_own_sms": 6}])
+def test_pipelined_backward_equals_single_sequence(tuning):
     W, T, H, I, k, E = 1, 384, 512, 256, 4, 6
     topk_all, weights = make_topk(W, T, E, k, seed=271)
     x = O.make_input(T, H, seed=272).to(DEV)
@@ -656,7 +659,7 @@ def test_pipelined_backward_equals_single_sequence():
         d_xb = torch.full((T * k, H), -5.0, dtype=torch.bfloat16, device=DEV)
         b = mx8.dispatch_mlp_swiglu_combine_bwd(None, d_cb, [d_cb.data_ptr()], d_xb, [d_xb.data_ptr()], None, *bw[0], None, *bw[1], None, *bw[2],
                                                 f[0], f[1], None, f[3], f[4], None, f[6], f[7], None, f[9], f[10], x, [x.data_ptr()],
-                                                *fw[0], *fw[1], pr, pt, nt, tpe, k, *knobs)
+                                                *fw[0], *fw[1], pr, pt, nt, tpe, k, *knobs, tuning=tuning if knobs[0] else None)
         torch.cuda.synchronize()
         assert mx8.device_status() == 0
         res.append((b, d_xb))
