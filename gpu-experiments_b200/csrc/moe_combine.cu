@@ -266,6 +266,12 @@ extern "C" int mx8_moe_combine_window(const void* y_routed, const void* peer_ran
         cfg.attrs = at;
         cfg.numAttrs = 1;
         e = cudaLaunchKernelEx(&cfg, moe::combine_bulk_kernel, p);
+    } else if (window && window->max_sms > 0 && window->max_sms < sm_count()) {
+        // held to max_sms multiprocessors' worth of copy warps, in blocks of two warps: spread thinly over the GEMMs'
+        // multiprocessors they slow every GEMM block a little instead of a few blocks a lot (tiles are assigned to GEMM
+        // blocks in fixed strides, so the slowest block sets the GEMM's time)
+        moe::combine_kernel<<<sms * 16, 64, 0, static_cast<cudaStream_t>(stream)>>>(p);
+        e = cudaGetLastError();
     } else {
         moe::combine_kernel<<<sms * 4, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
         e = cudaGetLastError();
