@@ -418,6 +418,12 @@ extern "C" int mx8_moe_bwd(const mx8_moe_bwd_args* a, void* stream) {
         math_done = evs.ev + 2 + nb;
         ck(mx8_moe_minibatch_bounds_split(a->tokens_per_expert, E, nb, first_expert, bounds, main));
         ck.cuda(cudaEventRecord(evs.ev[0], main), "cudaEventRecord");
+#ifdef MX8_TRACE
+        for (int i = 0; i < g_trace_n; ++i) { cudaEventDestroy(g_trace[i].a); cudaEventDestroy(g_trace[i].e); }
+        g_trace_n = 0;
+        if (!g_trace_t0) cudaEventCreate(&g_trace_t0);
+        cudaEventRecord(g_trace_t0, main);
+#endif
         ck.cuda(cudaStreamWaitEvent(s_disp, evs.ev[0], 0), "cudaStreamWaitEvent");
         ck.cuda(cudaStreamWaitEvent(s_comb, evs.ev[0], 0), "cudaStreamWaitEvent");
     }
@@ -425,8 +431,11 @@ extern "C" int mx8_moe_bwd(const mx8_moe_bwd_args* a, void* stream) {
         const mx8_window w{pipe ? bounds + b : nullptr, pipe ? bounds + b + 1 : nullptr, (pipe && b > 0) ? d.num_comm_sms : 0};
         // gradient rows of the routed outputs, pulled from the owners' buffers: one row per (token, k) pair,
         // hence topk = 1 for the index
-        ck(mx8_moe_dispatch_quantize_window(a->d_combine_ptrs, d.world, H, 1, a->peer_rank, a->peer_token_idx, a->num_tokens, cap,
-                                            a->d_y_fp8, a->d_y_sc, d_y_fp8_t, d_y_sc_t, &w, s_disp));
+        {
+            MX8_TRACE_SCOPE("dispatch", b, 1, s_disp);
+            ck(mx8_moe_dispatch_quantize_window(a->d_combine_ptrs, d.world, H, 1, a->peer_rank, a->peer_token_idx, a->num_tokens, cap,
+                                                a->d_y_fp8, a->d_y_sc, d_y_fp8_t, d_y_sc_t, &w, s_disp));
+        }
         if (pipe) ck.cuda(cudaEventRecord(disp_done[b], s_disp), "cudaEventRecord");
     }
     for (int b = 0; b < nb && ck.ok(); ++b) {
@@ -435,26 +444,42 @@ extern "C" int mx8_moe_bwd(const mx8_moe_bwd_args* a, void* stream) {
         // and, with combine_own_sms, every minibatch but the first leaves the gradient combine of the one before it its multiprocessors
         const int gemm_sms = !pipe ? 0 : (b < nb - 1 ? math_sms : all_sms) - (b > 0 ? own_sms : 0);
         const mx8_window w{pipe ? bounds + b : nullptr, pipe ? bounds + b + 1 : nullptr, gemm_sms >= all_sms ? 0 : gemm_sms, 0};
-        ck(mx8_gemm_grouped_window(a->d_y_fp8, a->d_y_sc, a->w_down_T, a->w_down_T_sc, a->d_hidden_routed, nullptr, cap, I, H, MX8_C_BF16,
-                                   a->num_tokens, a->tokens_per_expert, E, &w, main));
-        ck(mx8_swiglu_bwd_quantize_both_window(a->gate_fp8, a->gate_sc, a->up_fp8, a->up_sc, a->d_hidden_routed, cap, I, a->num_tokens,
-                                               a->d_gate_fp8, a->d_gate_sc, d_gate_fp8_t, d_gate_sc_t, a->d_up_fp8, a->d_up_sc,
-                                               d_up_fp8_t, d_up_sc_t, &w, main));
-        ck(mx8_gemm_grouped_dual_window(a->d_gate_fp8, a->d_gate_sc, a->w_gate_T, a->w_gate_T_sc, a->d_up_fp8, a->d_up_sc, a->w_up_T,
-                                        a->w_up_T_sc, a->d_x_routed, cap, H, I, I, a->num_tokens, a->tokens_per_expert, E, &w, main));
+        {
+            MX8_TRACE_SCOPE("d_hidden", b, 0, main);
+            ck(mx8_gemm_grouped_window(a->d_y_fp8, a->d_y_sc, a->w_down_T, a->w_down_T_sc, a->d_hidden_routed, nullptr, cap, I, H,
+                                       MX8_C_BF16, a->num_tokens, a->tokens_per_expert, E, &w, main));
+        }
+        {
+            MX8_TRACE_SCOPE("swiglu", b, 0, main);
+            ck(mx8_swiglu_bwd_quantize_both_window(a->gate_fp8, a->gate_sc, a->up_fp8, a->up_sc, a->d_hidden_routed, cap, I,
+                                                   a->num_tokens, a->d_gate_fp8, a->d_gate_sc, d_gate_fp8_t, d_gate_sc_t, a->d_up_fp8,
+                                                   a->d_up_sc, d_up_fp8_t, d_up_sc_t, &w, main));
+        }
+        {
+            MX8_TRACE_SCOPE("d_x", b, 0, main);
+            ck(mx8_gemm_grouped_dual_window(a->d_gate_fp8, a->d_gate_sc, a->w_gate_T, a->w_gate_T_sc, a->d_up_fp8, a->d_up_sc,
+                                            a->w_up_T, a->w_up_T_sc, a->d_x_routed, cap, H, I, I, a->num_tokens, a->tokens_per_expert,
+                                            E, &w, main));
+        }
         if (pipe) {
             ck.cuda(cudaEventRecord(math_done[b], main), "cudaEventRecord");
             ck.cuda(cudaStreamWaitEvent(s_comb, math_done[b], 0), "cudaStreamWaitEvent");
         }
         const mx8_window wc{pipe ? bounds + b : nullptr, pipe ? bounds + b + 1 : nullptr, (pipe && b < nb - 1) ? combine_sms : 0,
                             (pipe && own_sms && b < nb - 1) ? 1 : 0};
-        ck(mx8_moe_combine_window(a->d_x_routed, a->peer_rank, a->peer_token_idx, a->num_tokens, cap, H, a->d_x_routed_ptrs, d.world,
-                                  static_cast<long long>(d.tokens) * d.topk, &wc, s_comb));
+        {
+            MX8_TRACE_SCOPE("combine", b, 2, s_comb);
+            ck(mx8_moe_combine_window(a->d_x_routed, a->peer_rank, a->peer_token_idx, a->num_tokens, cap, H, a->d_x_routed_ptrs,
+                                      d.world, static_cast<long long>(d.tokens) * d.topk, &wc, s_comb));
+        }
     }
     // weight gradients on the transposed activations the forward produced and the transposed gradients
-    ck(mx8_gemm_wgrad(d_gate_fp8_t, d_gate_sc_t, a->x_fp8_t, a->x_sc_t, a->d_w_gate, I, H, cap, a->tokens_per_expert, E, main));
-    ck(mx8_gemm_wgrad(d_up_fp8_t, d_up_sc_t, a->x_fp8_t, a->x_sc_t, a->d_w_up, I, H, cap, a->tokens_per_expert, E, main));
-    ck(mx8_gemm_wgrad(d_y_fp8_t, d_y_sc_t, a->hidden_fp8_t, a->hidden_sc_t, a->d_w_down, H, I, cap, a->tokens_per_expert, E, main));
+    {
+        MX8_TRACE_SCOPE("wgrad x3", 0, 0, main);
+        ck(mx8_gemm_wgrad(d_gate_fp8_t, d_gate_sc_t, a->x_fp8_t, a->x_sc_t, a->d_w_gate, I, H, cap, a->tokens_per_expert, E, main));
+        ck(mx8_gemm_wgrad(d_up_fp8_t, d_up_sc_t, a->x_fp8_t, a->x_sc_t, a->d_w_up, I, H, cap, a->tokens_per_expert, E, main));
+        ck(mx8_gemm_wgrad(d_y_fp8_t, d_y_sc_t, a->hidden_fp8_t, a->hidden_sc_t, a->d_w_down, H, I, cap, a->tokens_per_expert, E, main));
+    }
     if (pipe) {
         // the last gradient combine ran beside the weight gradients
         ck.cuda(cudaEventRecord(evs.ev[1], s_comb), "cudaEventRecord");
