@@ -64,8 +64,8 @@ __global__ void __launch_bounds__(256) combine_kernel(CombineParams p) {
 }
 
 // The form with multiprocessors of its own (mx8_window.own_sms): every warp moves rows with bulk copies through two
-// buffers in shared memory (global -> shared, then shared -> the owner's buffer, local or a peer's over NVLink; no
-// multicast anywhere), a row in pieces of at most 7.5 KB.  One lane issues; while the store of one piece drains from its
+// buffers in shared memory (global -> shared, then shared -> the owner's buffer, local or a peer's over NVLink; every
+// copy has one source and one destination), a row in pieces of at most 7.5 KB.  One lane issues; while the store of one piece drains from its
 // buffer the load of the next is in flight in the other.  The blocks ask for more shared memory than a multiprocessor
 // has left beside a GEMM or a dispatch block, so they never share one.
 constexpr int BULK_WARPS = 6;
