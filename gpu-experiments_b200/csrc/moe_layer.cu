@@ -322,8 +322,9 @@ extern "C" int mx8_moe_fwd(const mx8_moe_fwd_args* a, void* stream) {
         }
         ck.cuda(cudaEventRecord(math_done[b], main), "cudaEventRecord");
         ck.cuda(cudaStreamWaitEvent(cx->comb, math_done[b], 0), "cudaStreamWaitEvent");
-        // beside GEMMs the combine is held to a few thread blocks: with more, its stores queue up in front of the
-        // NVLink ports and hold up the GEMMs' operand traffic by as much as the overlap gains
+        // beside GEMMs the combine is held to combine_sms multiprocessors' worth of copy warps, spread thinly over the
+        // GEMMs' multiprocessors: more of them slow the GEMM blocks they share a multiprocessor with by more than the
+        // overlap gains
         const mx8_window wc{bounds + b, bounds + b + 1, b < nb - 1 ? combine_sms : 0, (own_sms && b < nb - 1) ? 1 : 0};
         {
             MX8_TRACE_SCOPE("combine", b, 2, cx->comb);
